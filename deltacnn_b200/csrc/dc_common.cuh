@@ -1,0 +1,103 @@
+// Shared device helpers for the delta-update kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "deltacnn_b200.h"
+
+#define DC_WARP 32
+#define DC_FULL 0xffffffffu
+
+namespace dc {
+
+__host__ __device__ constexpr inline int64_t divup64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+__host__ __device__ constexpr inline int divup(int a, int b) { return (a + b - 1) / b; }
+
+// Number of SMs of the current device (cached per thread), for grid sizing.
+int sm_count();
+// Record a launch failure for dc_last_cuda_error(); returns DC_OK or DC_ERR_LAUNCH.
+int check_launch();
+
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f<__half>(__half x) { return __half2float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+// Value of x after a round trip through the storage type.
+template <typename T> __device__ __forceinline__ float rnd(float x) { return to_f<T>(from_f<T>(x)); }
+
+// Elements of T in one 16-byte vector.
+template <typename T> struct VecTraits { static constexpr int kVec = 16 / (int)sizeof(T); };
+
+// W consecutive elements of T held in storage precision: W == VecTraits<T>::kVec is
+// one 16-byte access, W == 1 is the scalar fallback for channel counts whose pixel
+// stride is not a multiple of 16 bytes.
+template <typename T, int W> struct Pack {
+    alignas(W * sizeof(T) == 16 ? 16 : alignof(T)) T s[W];
+    __device__ __forceinline__ void load(const T* p) {
+        if constexpr (W * sizeof(T) == 16) {
+            *reinterpret_cast<uint4*>(s) = *reinterpret_cast<const uint4*>(p);
+        } else {
+#pragma unroll
+            for (int i = 0; i < W; ++i) s[i] = p[i];
+        }
+    }
+    __device__ __forceinline__ void store(T* p) const {
+        if constexpr (W * sizeof(T) == 16) {
+            *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(s);
+        } else {
+#pragma unroll
+            for (int i = 0; i < W; ++i) p[i] = s[i];
+        }
+    }
+    __device__ __forceinline__ float get(int i) const { return to_f<T>(s[i]); }
+    __device__ __forceinline__ void set(int i, float x) { s[i] = from_f<T>(x); }
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int i = 0; i < W; ++i) s[i] = from_f<T>(0.f);
+    }
+};
+
+__device__ __forceinline__ float act_apply(float x, int code) {
+    switch (code) {
+        case DC_ACT_RELU: return fmaxf(x, 0.f);
+        case DC_ACT_RELU6: return fminf(fmaxf(x, 0.f), 6.f);
+        case DC_ACT_LEAKY: return x < 0.f ? 0.1f * x : x;
+        case DC_ACT_SIGMOID: return 1.f / (1.f + __expf(-x));
+        case DC_ACT_SWISH: return x / (1.f + __expf(-x));
+        default: return x;
+    }
+}
+
+// Threshold as the storage type sees it (the half kernels compare against the
+// threshold rounded to half).
+template <typename T> inline float host_round_threshold(float t);
+template <> inline float host_round_threshold<float>(float t) { return t; }
+template <> inline float host_round_threshold<__half>(float t) { return __half2float(__float2half_rn(t)); }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Lanes cooperating on one pixel: smallest power of two >= nvec, capped at 32.
+inline int lanes_per_pixel(int nvec) {
+    int g = 1;
+    while (g < nvec && g < 32) g <<= 1;
+    return g;
+}
+
+// OR-reduce a predicate over an aligned group of `g` lanes (g power of two <= 32).
+__device__ __forceinline__ bool group_any(bool p, int g, int lane) {
+    unsigned b = __ballot_sync(DC_FULL, p);
+    if (g == 32) return b != 0;
+    unsigned base = (unsigned)(lane & ~(g - 1));
+    unsigned gm = ((1u << g) - 1u) << base;
+    return (b & gm) != 0;
+}
+
+// Sum-reduce over an aligned group of g lanes.
+__device__ __forceinline__ float group_sum(float x, int g) {
+    for (int o = g >> 1; o > 0; o >>= 1) x += __shfl_xor_sync(DC_FULL, x, o);
+    return x;
+}
+
+}  // namespace dc

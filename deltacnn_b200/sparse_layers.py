@@ -1,0 +1,751 @@
+"""Stateful module API of the delta-update path (drop-in for the reference's
+src/deltacnn/sparse_layers.py): the same class names, constructor signatures, tuple
+convention ``(delta, mask)`` between layers, first-frame behaviour, threshold registry and
+``process_filters()`` / ``reset_layers()`` protocol, driving the sm_100a kernels of this
+package through ``cuda_kernels``.
+
+Not carried over (no multi-backend dispatch): the ``delta_cudnn`` soft-threshold training
+emulation (reference :37-82, :467-533) and the TensorBoard logging forward (:535-601);
+selecting them raises. ``DCBackend.cudnn`` keeps working by delegating to torch, as in the
+reference (:449-465).
+
+Per-layer output buffers are allocated once and reused every frame (the reference calls
+``torch.empty`` per layer per frame, cuda_kernels.py:34-37), which also makes a whole frame
+step capturable in a CUDA graph.
+"""
+from collections import OrderedDict
+from enum import Enum
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from . import cuda_kernels as K
+from .filter_conversion import convert_filter_out_channels_last, convert_half_filter
+
+
+def convert_activation_string(name, **kwargs):
+    """Activation name -> (torch callable, kernel code). Codes as reference :20-34; the kernels'
+    leaky slope is 0.1 (src/cuda/other_nn_layers.cu:33) and the torch module uses the same."""
+    if name is None or name == "" or name.lower() == "linear":
+        return None, -1
+    key = name.lower()
+    if key == "relu":
+        return torch.nn.ReLU(), 1
+    if key == "relu6":
+        return torch.nn.ReLU6(), 2
+    if key == "leaky":
+        return torch.nn.LeakyReLU(kwargs.get("leaky_relu_negative_slope", 0.1)), 3
+    if key == "sigmoid":
+        return torch.nn.Sigmoid(), 4
+    if key == "swish":
+        return (lambda x: torch.sigmoid(x).mul_(x)), 5
+    raise Exception(f"Activation {name} not implemented")
+
+
+class DCBackend(Enum):
+    cudnn = 0
+    deltacnn = 1
+    delta_cudnn = 2
+
+    @classmethod
+    def parse_string(cls, x):
+        try:
+            return cls[x.lower()]
+        except KeyError:
+            raise Exception(f"invalid backend {x}") from None
+
+
+class DCTruncation(Enum):
+    none = -1
+    max = 0
+    norm = 1
+    rms = 2
+
+    @classmethod
+    def parse_string(cls, x):
+        try:
+            return cls[x.lower()]
+        except KeyError:
+            raise Exception(f"invalid truncation mode {x}") from None
+
+
+class DCThreshold:
+    """Registry of per-layer thresholds keyed by module, in frame-0 forward order
+    (reference :122-208). JSON files map the stringified position to the value."""
+    t_default = 0.0
+    t = OrderedDict()
+    path = None
+    initialized = False
+    scale = 1.0
+
+    @classmethod
+    def get(cls, key, default=0.0):
+        return cls.t.get(key, default)
+
+    @classmethod
+    def set(cls, key, val):
+        if key not in cls.t:
+            cls.t[key] = val
+
+    @classmethod
+    def load_thresholds(cls):
+        if cls.initialized:
+            return
+        cls.initialized = True
+        if cls.path is None:
+            return
+        import json
+        with open(cls.path) as f:
+            thresholds = json.load(f)
+        if len(thresholds) != len(cls.t):
+            print(f"WARNING: thresholds file contains different number of thresholds. file: {len(thresholds)} expected {len(cls.t)}")
+        # a shorter file addresses the LAST len(file) layers
+        skip = len(cls.t) - len(thresholds)
+        for i, key in enumerate(list(cls.t.keys())):
+            if i >= skip:
+                cls.t[key] = thresholds[str(i - skip)] * cls.scale
+
+    @classmethod
+    def save_thresholds(cls, name):
+        import json
+        with open(f"thresholds_{name}.json", "w+") as f:
+            json.dump({i: v for i, v in enumerate(cls.t.values())}, f)
+
+    @classmethod
+    def reset(cls):
+        cls.t.clear()
+        cls.initialized = False
+        cls.path = None
+
+    @classmethod
+    def create_trainable_parameters(cls, device):
+        raise NotImplementedError("trainable thresholds belong to the delta_cudnn training emulation, which this package does not provide")
+
+
+class DCModule(nn.Module):
+    temp_buffers = []
+
+    def __init__(self):
+        super().__init__()
+
+    @classmethod
+    def get_temp_buffer_numel(cls):
+        return sum(x.numel() for x in cls.temp_buffers)
+
+    def reset(self):
+        DCModule.temp_buffers = []
+
+    def process_filters(self):
+        """Re-layout the filters of every delta convolution below this module (once, after
+        ``.to(device, memory_format=channels_last)`` and the optional ``.half()``)."""
+        for mod in self.modules():
+            if type(mod) in (DCConv2d, DCConvTranspose2d):
+                mod.process_filters()
+
+    def reset_layers(self):
+        """Drop every cache below this module; the next forward is a first frame again."""
+        for mod in self.modules():
+            if mod is not self and isinstance(mod, DCModule):
+                mod.reset()
+        DCModule.temp_buffers.clear()
+
+
+def to_tuple(*args):
+    result = []
+    for x in args:
+        if type(x) == int:
+            result.append((x, x))
+        elif len(x) == 1:
+            result.append((x[0], x[0]))
+        else:
+            result.append(tuple(x))
+    return result[0] if len(result) == 1 else result
+
+
+def _unsupported_backend(backend):
+    raise NotImplementedError(
+        f"backend {backend} is not provided: deltacnn_b200 implements DCBackend.deltacnn (sm_100a kernels) and "
+        "delegates DCBackend.cudnn to torch; the delta_cudnn soft-threshold emulation is training-side code")
+
+
+class _DeltaConvMixin:
+    """State and forward logic shared by DCConv2d and DCConvTranspose2d."""
+    _transposed = False
+
+    def _init_delta_state(self, delta_threshold, name, activation, dense_out, backend, use_logging, kwargs):
+        self.prev_in = None
+        self.prev_out = None
+        self.delta_threshold = delta_threshold if delta_threshold is not None else DCThreshold.t_default
+        self.name = name
+        self.backend = backend if backend is not None else DCConv2d.backend
+        self.activation, self.activation_int = convert_activation_string(activation, **kwargs)
+        self.dense_out = dense_out
+        self.use_logging = use_logging
+        if self.logging_enabled():
+            raise NotImplementedError("the TensorBoard logging forward of the reference is not provided")
+        self.densify_layer = None
+        self.activation_layer = None
+        if self.dense_out:
+            self.densify_layer = DCDensify(activation=activation, name=self.name)
+        elif self.activation is not None:
+            self.activation_layer = DCActivation(self.name, delta_threshold=delta_threshold, activation=activation)
+        self.conv_idx = -1
+        self.dense_in = False
+        self.mask = None
+        self.frame_idx = -1
+        self.out_truncated = None
+        self.out_mask = None
+        self.out_shape = []
+        self.kwargs = kwargs
+        self.in_shape = None
+        self.orig_weights = None
+        self.weight_umma = None
+        self._out = None
+        self._desc = None
+        self._epilogue = None
+        self.fuse_activation = True
+        assert kwargs.get("leaky_relu_negative_slope", 0.1) == 0.1, "Leaky ReLU implementation uses hard coded negative slope of 0.1"
+
+    def logging_enabled(self):
+        return self.use_logging if self.use_logging is not None else DCConv2d.use_logging
+
+    def init_first_iter(self, input):
+        self.conv_idx = DCConv2d.conv_idx
+        self.dense_in = type(input) == Tensor
+        self.in_shape = input.shape if self.dense_in else input[0].shape
+        registers = self.activation is not None or self.dense_in or (self._transposed and self.dense_out)
+        if registers and self.backend != DCBackend.cudnn:
+            DCThreshold.set(self, self.delta_threshold)
+        if self.dense_in:
+            DCConv2d.n_dense_inputs += 1
+        else:
+            DCConv2d.n_sparse_inputs += 1
+        if self.dense_out:
+            DCConv2d.n_dense_output += 1
+        else:
+            DCConv2d.n_sparse_output += 1
+
+    def __repr__(self):
+        return f"MyConv2d{self.conv_idx} cin={self.in_channels} cout={self.out_channels}"
+
+    def _delta_forward_common(self, input):
+        DCConv2d.conv_idx += 1
+        self.frame_idx += 1
+        first_iter = self.conv_idx == -1
+        if first_iter:
+            self.init_first_iter(input)
+        if self.backend == DCBackend.cudnn:
+            assert len(self.padding) == 2
+            return self._forward_cudnn(input, first_iter)
+        if self.backend != DCBackend.deltacnn:
+            _unsupported_backend(self.backend)
+        return self._forward_delta_conv(input, first_iter)
+
+    def _forward_cudnn(self, input, first_iter):
+        out = super(_DeltaConvMixin, self).forward(input)
+        if self.activation is not None:
+            out = self.activation(out)
+        if DCConv2d.measure_flops:
+            n_updated = (input if self._transposed else out)[:, :1].numel()
+            DCConv2d.flops_sum += n_updated * self.weight.numel()
+        return out
+
+    def _forward_delta_conv(self, input, first_iter):
+        if type(input) == Tensor:
+            raise RuntimeError("delta convolutions take a (delta, mask) tuple; put a DCSparsify in front of the first layer")
+        if self.orig_weights is None:
+            raise RuntimeError("process_filters() must be called on the model before the first forward")
+        x, mask = input
+        if x.shape[-1] != self.in_shape[-1] or x.shape[-2] != self.in_shape[-2] or x.shape[0] != self.in_shape[0]:
+            # resolution or batch change: forget the cached geometry and buffers
+            self.in_shape = x.shape
+            self.out_shape = []
+            self._out = self.out_mask = self._desc = None
+
+        epilogue = None
+        act = self.activation_layer
+        fuse = act is not None and self.fuse_activation and not act.first_iter and act.inplace and \
+            act.truncation_mode == DCTruncation.max and self.frame_idx > 0
+        if fuse:
+            epilogue = K.make_epilogue(act.prev_out, act.out_truncated, DCThreshold.get(act), act.activation_int,
+                                       act.truncation_mode.value)
+        if self._desc is None:
+            size_fn = K.deconv_out_hw if self._transposed else K.conv_out_hw
+            hw = size_fn(x.shape[2], x.shape[3], self.kernel_size, self.stride, self.padding, self.dilation)
+            self.out_shape = list(hw)
+            self._desc = K.make_conv_desc(tuple(x.shape), self.out_channels, hw, tuple(self.kernel_size), self.stride,
+                                          self.padding, self.dilation, self.groups, K._dtype(x))
+        op = K.sparse_deconv if self._transposed else K.sparse_conv
+        extra = {} if self._transposed else {"filter_umma": self.weight_umma}
+        out, out_mask = op(
+            x=x, filter=self.weight, mask=mask, bias=self.bias if self.frame_idx <= 0 else None, stride=self.stride,
+            padding=self.padding, dilation=self.dilation, groups=self.groups, c_out=self.out_channels, create_out_mask=True,
+            out_mask=self.out_mask, out_shape=self.out_shape, out=self._out, epilogue=epilogue, desc=self._desc, **extra)
+        if DCModule_reuse_buffers():
+            self._out, self.out_mask = out, out_mask
+
+        if self.dense_out:
+            return self.densify_layer((out, out_mask))
+        if act is not None:
+            if fuse:
+                return out, out_mask
+            return act((out, out_mask))
+        return out, out_mask
+
+    def reset(self):
+        DCModule.reset(self)
+        self.frame_idx = -1
+        self.conv_idx = -1
+        self.prev_out = None
+        self.prev_in = None
+        self.out_truncated = None
+        self.out_mask = None
+        self.out_shape = []
+        self._out = None
+        self._desc = None
+        DCConv2d.conv_idx = -1
+        DCConv2d.n_dense_output, DCConv2d.n_sparse_output = 0, 0
+        DCConv2d.n_dense_inputs, DCConv2d.n_sparse_inputs = 0, 0
+
+    def process_filters(self):
+        """Keep the torch-layout weights in ``orig_weights`` and replace ``weight.data`` by the
+        kernel layout (reference :655-675)."""
+        if self.orig_weights is not None:
+            return
+        self.orig_weights = self.weight.data.clone()
+        if self.backend != DCBackend.deltacnn:
+            return
+        if self.weight.data.dtype == torch.float16:
+            self.weight.data = convert_half_filter(self.weight.data, transposed=self._transposed)
+        else:
+            self.weight.data = convert_filter_out_channels_last(self.weight.data, transposed=self._transposed)
+        self._pack_umma()
+
+    def _pack_umma(self):
+        """Build the tensor-core image of the filter when the shape has a tcgen05 kernel."""
+        self.weight_umma = None
+        if self._transposed or self.weight.dtype != torch.float16 or not self.weight.is_cuda:
+            return
+        from ._lib import lib, check
+        kh, kw = self.kernel_size
+        desc = K.make_conv_desc((1, self.in_channels, 8, 8), self.out_channels, (8, 8), (kh, kw), self.stride,
+                                self.padding, self.dilation, self.groups, 1)
+        nbytes = lib.dc_filter_umma_bytes(desc, 0)
+        if nbytes == 0:
+            return
+        packed = torch.empty(nbytes, dtype=torch.uint8, device=self.weight.device)
+        check(lib.dc_pack_filter_umma(desc, 0, self.weight.data_ptr(), packed.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream), "pack_filter_umma")
+        self.weight_umma = packed
+
+
+def DCModule_reuse_buffers():
+    return DCConv2d.reuse_buffers
+
+
+class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
+    """Delta convolution module (reference :261-675)."""
+    backend = DCBackend.deltacnn
+    conv_idx = -1
+    out_masks = []
+    use_logging = False
+    n_sparse_inputs = 0
+    n_dense_inputs = 0
+    n_sparse_output = 0
+    n_dense_output = 0
+    store_out_masks = False
+    flops_sum = 0
+    measure_flops = False
+    reuse_buffers = True      # keep per-layer output buffers across frames
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1, groups: int = 1,
+                 bias: bool = True, padding_mode: str = "zeros", delta_threshold: float = None, name: str = None,
+                 activation: str = None, dense_out=False, backend=None, use_logging=None, **kwargs):
+        kernel_size, stride, padding, dilation = to_tuple(kernel_size, stride, padding, dilation)
+        nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias, padding_mode)
+        self._init_delta_state(delta_threshold, name, activation, dense_out, backend, use_logging, kwargs)
+
+    def forward(self, input):
+        return self._delta_forward_common(input)
+
+
+class DCConvTranspose2d(_DeltaConvMixin, nn.ConvTranspose2d, DCModule):
+    """Delta transposed convolution module (reference :678-1083). output_padding is ignored by the
+    delta path, as in the reference (cuda_kernels.py:55-57)."""
+    _transposed = True
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, output_padding=0,
+                 groups: int = 1, bias: bool = True, dilation=1, padding_mode: str = "zeros", delta_threshold: float = None,
+                 name: str = None, activation: str = None, store_prev_in=False, dense_out=False, backend=None,
+                 use_logging=None, **kwargs):
+        kernel_size, stride, padding, dilation = to_tuple(kernel_size, stride, padding, dilation)
+        nn.ConvTranspose2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, output_padding, groups,
+                                    bias, dilation, padding_mode)
+        self.stores_prev_in = store_prev_in
+        self._init_delta_state(delta_threshold, name, activation, dense_out, backend, use_logging, kwargs)
+
+    def forward(self, input):
+        assert self.backend == DCBackend.cudnn or self.backend == DCBackend.deltacnn
+        return self._delta_forward_common(input)
+
+
+class DCAdd(DCModule):
+    """Residual add of two delta tensors (reference :1086-1182)."""
+    idx = -1
+
+    def __init__(self, activation: str = None, dense_out=False, weight_a=None, weight_b=None, name=""):
+        super().__init__()
+        self.name = name
+        self.dense_out = dense_out
+        self.activation, self.activation_int = convert_activation_string(activation)
+        self.idx = -1
+        self.prev_out = None
+        self.mask_out = None
+        self.weight_a = 1.0 if weight_a is None else weight_a
+        self.weight_b = 1.0 if weight_b is None else weight_b
+        self.first_iter = True
+        self._out = None
+
+    def forward(self, a, b, weight_a=None, weight_b=None):
+        w_a = self.weight_a if weight_a is None else weight_a
+        w_b = self.weight_b if weight_b is None else weight_b
+        if type(a) == torch.Tensor:
+            if DCConv2d.backend == DCBackend.delta_cudnn:
+                _unsupported_backend(DCConv2d.backend)
+            c = w_a * a + w_b * b
+            return self.activation(c) if self.activation is not None else c
+
+        val_a, mask_a = a
+        val_b, mask_b = b
+        if self.first_iter:
+            self.first_iter = False
+            DCAdd.idx += 1
+            self.idx = DCAdd.idx
+            if self.dense_out or self.activation is not None:
+                self.prev_out = torch.zeros_like(val_a)
+                DCModule.temp_buffers.append(self.prev_out)
+        if self.mask_out is None or self.mask_out.shape != mask_a.shape:
+            self.mask_out = torch.empty_like(mask_a)
+        if self._out is None or self._out.shape != val_a.shape or not DCConv2d.reuse_buffers or self.dense_out:
+            self._out = torch.empty_like(val_a)
+        out, mask_out = self._out, self.mask_out
+        K.sparse_add_tensors(val_a, val_b, self.prev_out, out, mask_a, mask_b, mask_out, w_a, w_b, self.activation_int,
+                             self.dense_out)
+        if self.dense_out:
+            return out
+        return out, mask_out
+
+    def reset(self):
+        super().reset()
+        self.idx = -1
+        self.mask_out = None
+        self.prev_out = None
+        self._out = None
+        self.first_iter = True
+        DCAdd.idx = -1
+
+
+class DCConcatenate(DCModule):
+    """Channel concatenation (reference :1185-1194)."""
+
+    def __init__(self, name=""):
+        super().__init__()
+        self.name = name
+
+    def forward(self, a, b):
+        if type(a) == torch.Tensor:
+            return torch.cat((a, b), dim=1)
+        return K.sparse_concatenate(a, b)
+
+
+class DCSparsify(DCModule):
+    """Dense frame -> (delta, mask) against the cached previous frame (reference :1197-1273)."""
+    idx = -1
+
+    def __init__(self, name="", delta_threshold=None, dilation=-1):
+        super().__init__()
+        self.name = name
+        self.prev_in = None
+        self.idx = -1
+        self.delta_threshold = delta_threshold if delta_threshold is not None else DCThreshold.t_default
+        self.dilation = dilation
+        self.frame_idx = -1
+        self.mask = None
+        self._delta = None
+
+    def forward(self, input):
+        if DCConv2d.backend == DCBackend.cudnn:
+            return input
+        if DCConv2d.backend != DCBackend.deltacnn:
+            _unsupported_backend(DCConv2d.backend)
+        first_iter = self.idx == -1
+        self.frame_idx += 1
+        if first_iter:
+            if self not in DCThreshold.t:
+                DCThreshold.set(self, self.delta_threshold)
+            DCSparsify.idx += 1
+            self.idx = DCSparsify.idx
+            self.prev_in = input.clone()
+            DCModule.temp_buffers.append(self.prev_in)
+            mask = torch.ones_like(input[:, :1], dtype=torch.int)
+            return input, mask
+
+        threshold = DCThreshold.get(self)
+        if self.dilation > 1:
+            # noise-robust variant: the mask is the max-pooled |delta| (reference :1233-1244), torch ops
+            x = input - self.prev_in
+            mask = torch.max(torch.abs(x), dim=1, keepdim=True)[0]
+            k = self.dilation
+            mask = torch.max_pool2d(mask, (k, k), stride=(1, 1), padding=((k - 1) // 2, (k - 1) // 2)) > threshold
+            tiled = mask.expand_as(x)
+            self.prev_in[tiled] = input[tiled]
+            return x, mask.int()
+
+        if self.mask is None or self.mask.shape[0] != input.shape[0] or self.mask.shape[2:] != input.shape[2:]:
+            self.mask = torch.empty_like(input[:, :1], dtype=torch.int)
+        if self._delta is None or self._delta.shape != input.shape or not DCConv2d.reuse_buffers:
+            self._delta = torch.empty_like(input)
+        K.sparsify(input, self.prev_in, self._delta, self.mask, threshold)
+        return self._delta, self.mask
+
+    def reset(self):
+        super().reset()
+        self.idx = -1
+        self.frame_idx = -1
+        self.prev_in = None
+        self.prev_out = None
+        self.mask = None
+        self._delta = None
+        DCSparsify.idx = -1
+
+
+class DCDensify(DCModule):
+    """(delta, mask) -> dense accumulated tensor (reference :1276-1333), one kernel."""
+    idx = -1
+
+    def __init__(self, activation: str = None, name="", clone_out=True):
+        super().__init__()
+        self.name = name
+        self.activation, self.activation_int = convert_activation_string(activation)
+        self.prev_out = None
+        self.idx = -1
+        self.clone_out = clone_out
+
+    def forward(self, input):
+        if type(input) == torch.Tensor:
+            if DCConv2d.backend == DCBackend.delta_cudnn:
+                _unsupported_backend(DCConv2d.backend)
+            return input
+        input, mask = input
+        if self.prev_out is None:
+            DCDensify.idx += 1
+            self.idx = DCDensify.idx
+            self.prev_out = torch.zeros_like(input)
+            DCModule.temp_buffers.append(self.prev_out)
+        if not self.clone_out and self.activation is None:
+            K.sparse_activation(input, self.prev_out, None, mask, -1, -1, DCTruncation.none.value)
+            return self.prev_out
+        return K.sparse_densify(input, mask, self.prev_out, None, self.activation_int)
+
+    def reset(self):
+        super().reset()
+        self.prev_out = None
+
+
+class DCUpsamplingNearest2d(DCModule):
+    """Nearest-neighbour upsampling of a (delta, mask) pair (reference :1336-1359)."""
+    idx = -1
+
+    def __init__(self, scale_factor=2, name=""):
+        super().__init__()
+        self.name = name
+        self.scale_factor = int(scale_factor)
+        self.idx = -1
+        self.out = None
+        self.torch_upsample = nn.UpsamplingNearest2d(scale_factor=scale_factor)
+
+    def forward(self, input):
+        if type(input) == torch.Tensor:
+            return self.torch_upsample(input)
+        val, mask = input
+        if self.out is not None and (self.out[0].shape[0] != val.shape[0] or self.out[0].shape[2] != val.shape[2] * self.scale_factor
+                                     or self.out[0].shape[3] != val.shape[3] * self.scale_factor):
+            self.out = None
+        self.out = K.sparse_upsample(val, mask, self.scale_factor, self.out)
+        return self.out
+
+    def reset(self):
+        super().reset()
+        self.out = None
+
+
+class DCActivation(DCModule):
+    """Accumulate + activation delta + truncation (reference :1362-1425)."""
+    idx = -1
+    truncation_default = DCTruncation.max
+
+    def __init__(self, name="", inplace=True, delta_threshold=None, activation="relu", truncation_mode: DCTruncation = None):
+        super().__init__()
+        self.name = name
+        self.idx = -1
+        self.prev_out = None
+        self.inplace = inplace
+        self.out_truncated = None
+        self.activation, self.activation_int = convert_activation_string(activation)
+        self.delta_threshold = delta_threshold if delta_threshold is not None else DCThreshold.t_default
+        self.first_iter = True
+        self.truncation_mode = truncation_mode if truncation_mode is not None else DCActivation.truncation_default
+
+    def forward(self, input):
+        if type(input) == torch.Tensor:
+            if DCConv2d.backend == DCBackend.delta_cudnn:
+                _unsupported_backend(DCConv2d.backend)
+            return self.activation(input) if self.activation is not None else input
+        val, mask = input
+        if self.first_iter:
+            self.first_iter = False
+            if self not in DCThreshold.t:
+                DCThreshold.set(self, self.delta_threshold)
+            if self.idx < 0:
+                DCActivation.idx += 1
+                self.idx = DCActivation.idx
+            self.prev_out = val.clone()
+            self.out_truncated = torch.zeros_like(val)
+            DCModule.temp_buffers.append(self.prev_out)
+            DCModule.temp_buffers.append(self.out_truncated)
+            if self.activation is not None:
+                val = self.activation(val)
+            return val, mask
+
+        threshold = DCThreshold.get(self)
+        if not self.inplace:
+            val = val.clone()
+            mask = mask.clone()
+        K.sparse_activation(val, self.prev_out, self.out_truncated, mask, threshold, self.activation_int, self.truncation_mode.value)
+        return val, mask
+
+    def reset(self):
+        super().reset()
+        self.idx = -1
+        self.prev_out = None
+        self.out_truncated = None
+        self.first_iter = True
+        DCActivation.idx = -1
+
+
+class DCMaxPooling(nn.MaxPool2d, DCModule):
+    """Delta max pooling with an accumulated-input cache (reference :1428-1474); the cache
+    update is part of the same library call."""
+
+    def __init__(self, kernel_size, stride=(1, 1), padding=(0, 0), dilation=(1, 1)):
+        kernel_size, stride, padding, dilation = to_tuple(kernel_size, stride, padding, dilation)
+        super().__init__(kernel_size, stride=stride, padding=padding, dilation=dilation)
+        self.first_iter = True
+        self.out_shape = []
+        self.prev_in = None
+        self._out = None
+
+    def forward(self, input):
+        if type(input) == Tensor:
+            if DCConv2d.backend == DCBackend.delta_cudnn:
+                _unsupported_backend(DCConv2d.backend)
+            if len(self.padding) == 4:
+                pt, pb, pl, pr = self.padding
+                input = torch.nn.functional.pad(input, (pl, pr, pt, pb))
+                return torch.nn.functional.max_pool2d(input, self.kernel_size, self.stride, 0, self.dilation)
+            return super().forward(input)
+        x, mask = input
+        if self.first_iter:
+            self.first_iter = False
+            self.prev_in = torch.zeros_like(x)
+            DCModule.temp_buffers.append(self.prev_in)
+        if self._out is not None and self._out[0].shape[0] != x.shape[0]:
+            self._out = None
+        buf, mbuf = self._out if self._out is not None else (None, None)
+        out = K.sparse_pooling(x, self.prev_in, self.kernel_size, mask, self.stride, self.padding, self.dilation,
+                               create_out_mask=True, pooling_mode_int=0, out_shape=self.out_shape, out=buf, out_mask=mbuf,
+                               update_prev=True)
+        if DCConv2d.reuse_buffers:
+            self._out = out
+        return out
+
+    def reset(self):
+        DCModule.reset(self)
+        self.first_iter = True
+        self.prev_in = None
+        self.out_shape = []
+        self._out = None
+
+
+class DCAdaptiveAveragePooling(nn.AdaptiveAvgPool2d, DCModule):
+    """Delta global average pooling, output 1x1 only (reference :1477-1513)."""
+
+    def __init__(self, output_size=None):
+        output_size = to_tuple(output_size)
+        super().__init__(output_size=output_size)
+        self.first_iter = True
+        self.out_shape = output_size
+        self.prev_in = None
+
+    def get_target_size(self, input):
+        assert self.output_size[0] == 1 and self.output_size[1] == 1
+        return tuple(input.shape[2:]), (1, 1), (0, 0), (1, 1)
+
+    def forward(self, input):
+        if type(input) == Tensor:
+            return super().forward(input)
+        x, mask = input
+        self.first_iter = False
+        kernel_size, stride, padding, dilation = self.get_target_size(x)
+        return K.sparse_pooling(x, None, kernel_size, mask, stride, padding, dilation, create_out_mask=True,
+                                pooling_mode_int=1, out_shape=list(self.out_shape))
+
+    def reset(self):
+        DCModule.reset(self)
+        self.first_iter = True
+        self.prev_in = None
+
+
+class DCBatchNorm2d(nn.BatchNorm2d, DCModule):
+    """Inference BatchNorm on delta tensors: scale every frame, offset on the first only
+    (reference :1516-1585). Folding it into the preceding convolution is cheaper."""
+
+    def __init__(self, num_features, eps=1e-5, momentum=0.1, affine=True, track_running_stats=True, inplace=True):
+        super().__init__(num_features, eps, momentum, affine, track_running_stats)
+        self.first_iter = True
+        self.scale = None
+        self.offset = None
+        self.inplace = inplace
+
+    def convert_to_scale_offset(self, input):
+        bn_scale = self.weight * torch.rsqrt(self.running_var + self.eps)
+        self.scale = bn_scale[None, :, None, None]
+        self.offset = (-self.running_mean * bn_scale + self.bias)[None, :, None, None]
+
+    def forward(self, input):
+        mask = None
+        dense = type(input) != tuple
+        if not dense:
+            input, mask = input
+        use_offset = dense
+        if self.first_iter:
+            self.first_iter = False
+            use_offset = True
+            self.convert_to_scale_offset(input)
+        if dense:
+            out = input.mul_(self.scale) if self.inplace else input * self.scale
+            out.add_(self.offset)
+            return out
+        bias = self.offset if use_offset else None
+        if self.inplace:
+            K.sparse_mul_add(input, mask, input, mask, self.scale, bias)
+            return input, mask
+        out = torch.empty_like(input)
+        out_mask = torch.empty_like(mask)
+        K.sparse_mul_add(input, mask, out, out_mask, self.scale, bias)
+        return out, out_mask
+
+    def reset(self):
+        DCModule.reset(self)
+        self.first_iter = True

@@ -1,0 +1,190 @@
+/*
+ * deltacnn_b200 -- C-ABI of the delta-update inference kernels (sm_100a).
+ *
+ * Every entry point takes raw DEVICE pointers, plain sizes, and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t; NULL is the legacy default stream), and
+ * returns a dc_status. Nothing here allocates, frees or synchronises: all tensors,
+ * caches and masks are owned by the caller, as in the reference extension, whose
+ * wrappers receive preallocated torch tensors (src/deltacnn/cuda_kernels.py:34-45).
+ *
+ * Layout: feature/delta tensors are N,H,W,C contiguous ("channels last"), dtype
+ * float32 or float16; masks are int32, one word per pixel, values 0/1, N,H,W
+ * contiguous. "npix" is N*H*W. Pixels whose mask is 0 are never read; output
+ * pixels whose out-mask is 0 are left untouched (undefined, as in the reference).
+ *
+ * Each declaration cites the reference interface it replaces (path:line within the
+ * reference project).
+ */
+#ifndef DELTACNN_B200_H
+#define DELTACNN_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum dc_status {
+    DC_OK = 0,
+    DC_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+    DC_ERR_UNSUPPORTED = 2,    /* kernel size / stride / groups / mode not supported */
+    DC_ERR_ALIGNMENT = 3,      /* a pointer is not aligned for the vector width in use */
+    DC_ERR_SHAPE = 4,          /* inconsistent or non-positive sizes */
+    DC_ERR_DTYPE = 5,          /* dtype is neither DC_F32 nor DC_F16 */
+    DC_ERR_LAUNCH = 6,         /* the CUDA runtime refused the launch (see dc_last_cuda_error) */
+    DC_ERR_WORKSPACE = 7       /* caller-provided workspace too small */
+} dc_status;
+
+typedef enum dc_dtype { DC_F32 = 0, DC_F16 = 1 } dc_dtype;
+
+/* Activation codes, as src/deltacnn/sparse_layers.py:20-34 (<=0: identity). */
+typedef enum dc_activation {
+    DC_ACT_NONE = 0, DC_ACT_RELU = 1, DC_ACT_RELU6 = 2, DC_ACT_LEAKY = 3 /* slope 0.1 */,
+    DC_ACT_SIGMOID = 4, DC_ACT_SWISH = 5
+} dc_activation;
+
+/* Truncation modes, as DCTruncation in src/deltacnn/sparse_layers.py:102-106. */
+typedef enum dc_truncation { DC_TRUNC_NONE = -1, DC_TRUNC_MAX = 0, DC_TRUNC_NORM = 1, DC_TRUNC_RMS = 2 } dc_truncation;
+
+/* Shape and geometry of a convolution, transposed convolution or pooling call.
+ * Replaces Dimensions + ConvConfig (src/cuda/common.cuh:14-35), with 32-bit fields. */
+typedef struct dc_conv_desc {
+    int32_t n, h_in, w_in, c_in;
+    int32_t h_out, w_out, c_out;
+    int32_t kh, kw;
+    int32_t stride_h, stride_w;
+    int32_t pad_top, pad_left, pad_bottom, pad_right;
+    int32_t dil_h, dil_w;
+    int32_t groups;          /* 1, or c_in == c_out == groups (depthwise) */
+    int32_t dtype;           /* dc_dtype */
+} dc_conv_desc;
+
+/* Optional fused epilogue of dc_conv2d / dc_deconv2d: the accumulate + activation
+ * delta + truncation step of dc_activate_truncate applied to the convolution result
+ * before it is stored. prev_out / truncated have the shape of the output. */
+typedef struct dc_epilogue {
+    void* prev_out;
+    void* truncated;
+    float threshold;
+    int32_t activation;      /* dc_activation */
+    int32_t truncation;      /* dc_truncation; DC_TRUNC_MAX only when fused */
+} dc_epilogue;
+
+/* Filter layouts understood by dc_conv2d / dc_deconv2d. */
+typedef enum dc_filter_layout {
+    DC_FILTER_HWIO = 0,      /* [kh][kw][c_in/groups][c_out], same dtype as the features */
+    DC_FILTER_UMMA = 1       /* private pre-tiled fp16 layout written by dc_pack_filter_umma */
+} dc_filter_layout;
+
+int dc_version(void);
+const char* dc_status_string(int status);
+/* cudaError_t of the most recent failed launch on this thread (0 if none). */
+int dc_last_cuda_error(void);
+
+/* Input delta + update mask. Replaces deltacnn_prepare_diff_mask_wrapper
+ * (src/cuda/conv_torch_wrapper.cpp:347-384; kernels src/cuda/other_nn_layers.cu:821,1261).
+ * d = x - prev_in; mask = any_c(|d| > threshold); active pixels: delta = d, prev_in = x. */
+int dc_sparsify(const void* x, void* prev_in, void* delta, int32_t* mask,
+                int64_t npix, int32_t channels, int32_t dtype, float threshold, void* stream);
+
+/* Same as dc_sparsify on an 8-bit frame: x_u8 holds N,H,W,C bytes and the pixel
+ * value compared and cached is x_u8 * scale[c] + offset[c] (float32 per-channel
+ * tables on the device). No reference counterpart; it fuses the preprocessing of
+ * example/mobilenetv2_webcam_example.py:79-111 into the first kernel. */
+int dc_sparsify_u8(const uint8_t* x_u8, const float* scale, const float* offset, void* prev_in, void* delta,
+                   int32_t* mask, int64_t npix, int32_t channels, int32_t dtype, float threshold, void* stream);
+
+/* Delta convolution. Replaces sparse_conv_bias_wrapper_masked
+ * (src/cuda/conv_torch_wrapper.cpp:62-134 -> deltacnn / deltacnn_hp, src/cuda/conv_kernel.cu:3443,3947).
+ * mask_out[q] = OR of mask_in over the in-bounds taps of q; out[q] = sum_taps W^T (in * mask_in) (+ bias).
+ * mask_in NULL: every input pixel is active. mask_out NULL: out is written at every
+ * pixel (zeros (+bias) where no tap is active), the reference's set_sparse_zero mode.
+ * epilogue may be NULL. */
+int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in,
+              const void* filter, int32_t filter_layout, const void* bias,
+              void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream);
+
+/* Delta transposed convolution (4x4 stride 2, 6x6 stride 4 and any k = m*stride, groups 1).
+ * Replaces sparse_deconv_bias_wrapper_masked (src/cuda/conv_torch_wrapper.cpp:136-210 ->
+ * delta_deconv / delta_deconv_hp, src/cuda/deconv_kernel.cu:854-932). Filter HWIO:
+ * [kh][kw][c_in][c_out] (taps un-flipped, as torch ConvTranspose2d weight[ci][co][ky][kx]). */
+int dc_deconv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in,
+                const void* filter, int32_t filter_layout, const void* bias,
+                void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream);
+
+/* Bytes of the DC_FILTER_UMMA image of a filter (0 if the shape has no tensor-core kernel). */
+size_t dc_filter_umma_bytes(const dc_conv_desc* desc, int32_t transposed);
+/* Repack an fp16 HWIO filter on the device into the DC_FILTER_UMMA layout. */
+int dc_pack_filter_umma(const dc_conv_desc* desc, int32_t transposed, const void* filter_hwio,
+                        void* filter_umma, void* stream);
+
+/* Accumulate + activation delta + truncation, in place on delta, mask and both caches.
+ * Replaces deltacnn_activate_truncate (src/cuda/conv_torch_wrapper.cpp:295-344;
+ * kernels src/cuda/other_nn_layers.cu:755,1198). truncated may be NULL when
+ * truncation == DC_TRUNC_NONE. */
+int dc_activate_truncate(void* delta, void* prev_out, void* truncated, int32_t* mask,
+                         int64_t npix, int32_t channels, int32_t dtype,
+                         float threshold, int32_t activation, int32_t truncation, void* stream);
+
+/* Weighted add of two delta tensors. Replaces sparse_add_tensors_wrapper
+ * (src/cuda/conv_torch_wrapper.cpp:387-444; kernels other_nn_layers.cu:1380,1563).
+ * prev_out is required when activation > 0 or dense_out != 0. With dense_out the
+ * output is f(prev_out) at every pixel and mask_out is not written (may be NULL). */
+int dc_add(const void* a, const void* b, void* prev_out, void* out,
+           const int32_t* mask_a, const int32_t* mask_b, int32_t* mask_out,
+           float weight_a, float weight_b, int64_t npix, int32_t channels, int32_t dtype,
+           int32_t activation, int32_t dense_out, void* stream);
+
+/* b += a on the masked pixels of a. Replaces sparse_add_to_dense_tensor_wrapper
+ * (src/cuda/conv_torch_wrapper.cpp:446-482; kernels other_nn_layers.cu:1732,1851). */
+int dc_add_to_dense(const void* a, void* b, const int32_t* mask_a,
+                    int64_t npix, int32_t channels, int32_t dtype, void* stream);
+
+/* out = in * scale[c] (+ bias[c]) on masked pixels; mask copied to mask_out when they
+ * differ. Replaces sparse_mul_add_wrapper (src/cuda/conv_torch_wrapper.cpp:569-630;
+ * kernels other_nn_layers.cu:3774,3821). scale/bias have the feature dtype. */
+int dc_scale_bias(const void* in, const int32_t* mask_in, void* out, int32_t* mask_out,
+                  const void* scale, const void* bias,
+                  int64_t npix, int32_t channels, int32_t dtype, void* stream);
+
+/* Delta pooling. Replaces sparse_pooling_wrapper_masked (src/cuda/conv_torch_wrapper.cpp:213-293 ->
+ * sparse_pool / sparse_pool_hp, other_nn_layers.cu:4509-4661).
+ * pooling_mode 0 (max): out = max_win(prev_in + in*mask) - max_win(prev_in); when
+ *   update_prev != 0 prev_in += in*mask is applied by the same call (the reference
+ *   issues sparse_add_to_dense_tensor afterwards, src/deltacnn/sparse_layers.py:1468).
+ * pooling_mode 1 (average): out = sum_win(in*mask) / (kh*kw); with h_out == w_out == 1
+ *   and the window covering the image this is the global average pool, reduced in
+ *   fp32 in a fixed order and stored in the feature dtype. */
+int dc_pool(const dc_conv_desc* desc, const void* in, void* prev_in, const int32_t* mask_in,
+            void* out, int32_t* mask_out, int32_t pooling_mode, int32_t update_prev, void* stream);
+
+/* Nearest-neighbour upsampling of values and mask by an integer factor. Replaces
+ * sparse_upsample_wrapper (src/cuda/conv_torch_wrapper.cpp:484-521; other_nn_layers.cu:3451,3527). */
+int dc_upsample(const void* in, const int32_t* mask_in, void* out, int32_t* mask_out,
+                int32_t n, int32_t h, int32_t w, int32_t channels, int32_t scale, int32_t dtype, void* stream);
+
+/* Channel concatenation with mask union; the inactive side is zero-filled. Replaces
+ * sparse_concatenate_wrapper (src/cuda/conv_torch_wrapper.cpp:523-567; other_nn_layers.cu:3602,3676). */
+int dc_concat(const void* a, const void* b, void* out,
+              const int32_t* mask_a, const int32_t* mask_b, int32_t* mask_out,
+              int64_t npix, int32_t channels_a, int32_t channels_b, int32_t dtype, void* stream);
+
+/* prev_out += delta on masked pixels and dense_out = f(prev_out) at every pixel, one
+ * pass. Replaces the three launches of DCDensify.forward (src/deltacnn/sparse_layers.py:1322-1329:
+ * deltacnn_activate_truncate without truncation, clone, torch activation).
+ * dense_out may alias nothing; it may be NULL to only accumulate. */
+int dc_densify(const void* delta, const int32_t* mask, void* prev_out, void* dense_out,
+               int64_t npix, int32_t channels, int32_t dtype, int32_t activation, void* stream);
+
+/* Number of active pixels of a mask and their compacted indices (ascending), built
+ * with warp ballots and a block prefix scan; count is one int32 on the device,
+ * indices holds up to npix int32. Used to size work by the active set. No reference
+ * counterpart (the reference re-derives activity inside every kernel,
+ * src/cuda/conv_kernel.cu:46-108). */
+int dc_compact_mask(const int32_t* mask, int64_t npix, int32_t* indices, int32_t* count, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DELTACNN_B200_H */

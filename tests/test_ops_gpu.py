@@ -1,0 +1,309 @@
+"""Parity of every C-ABI operator (through the Python operator API) with the CPU oracle on
+seeded inputs. Integer results (masks) must be bit-exact; floating point within the stated
+tolerance of the oracle at the pixels the operator defines (out-mask == 1)."""
+import pytest
+import torch
+
+from oracle import delta_ops as O
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.float16]
+TOL = {torch.float32: 1e-4, torch.float16: 1e-2}   # relative to max |reference|
+
+
+def K():
+    import deltacnn_b200.cuda_kernels as k
+    return k
+
+
+def cl(t):
+    return t.contiguous(memory_format=torch.channels_last)
+
+
+def rand_feat(g, n, c, h, w, dtype, scale=1.0):
+    return cl((torch.randn(n, c, h, w, generator=g) * scale).to(dtype))
+
+
+def rand_mask(g, n, h, w, density):
+    if density >= 1.0:
+        return torch.ones(n, 1, h, w, dtype=torch.int32)
+    if density <= 0.0:
+        return torch.zeros(n, 1, h, w, dtype=torch.int32)
+    return (torch.rand(n, 1, h, w, generator=g) < density).to(torch.int32)
+
+
+def assert_close_masked(got, ref, mask, dtype, what=""):
+    sel = (mask != 0).expand_as(ref)
+    if sel.sum() == 0:
+        return
+    r = ref.float()[sel]
+    g_ = got.float().cpu()[sel]
+    scale = max(r.abs().max().item(), 1e-6)
+    err = (g_ - r).abs().max().item() / scale
+    assert err <= TOL[dtype], f"{what}: relative error {err:.3e} > {TOL[dtype]}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("c", [3, 8, 17, 64])
+@pytest.mark.parametrize("thr", [0.0, 0.05])
+def test_sparsify(dtype, c, thr):
+    g = torch.Generator().manual_seed(1)
+    n, h, w = 2, 13, 19
+    prev = rand_feat(g, n, c, h, w, dtype)
+    x = prev.clone()
+    upd = torch.rand(n, 1, h, w, generator=g) < 0.3
+    x = cl(torch.where(upd.expand_as(x), rand_feat(g, n, c, h, w, dtype), x + (0.01 * torch.randn(n, c, h, w, generator=g)).to(dtype)))
+    d_ref, m_ref, p_ref = torch.zeros_like(x), torch.zeros(n, 1, h, w, dtype=torch.int32), prev.clone()
+    O.sparsify(x, p_ref, d_ref, m_ref, thr)
+    xd, pd = x.cuda(), prev.cuda()
+    dd = torch.full_like(xd, float("nan"))
+    md = torch.full((n, 1, h, w), -7, dtype=torch.int32, device="cuda")
+    K().sparsify(xd, pd, dd, md, thr)
+    assert torch.equal(md.cpu(), m_ref)
+    assert torch.equal(pd.cpu(), p_ref)
+    sel = (m_ref != 0).expand_as(x)
+    assert torch.equal(dd.cpu()[sel], d_ref[sel])
+    assert torch.isnan(dd.cpu()[~sel]).all(), "inactive pixels of delta must not be written"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("c", [3, 32, 96, 200, 1280])
+@pytest.mark.parametrize("act,mode", [(1, 0), (2, 0), (0, 0), (3, 0), (2, 1), (2, 2), (1, -1), (0, -1)])
+def test_activate_truncate(dtype, c, act, mode):
+    if c == 1280 and dtype == torch.float32 and mode > 0:
+        pytest.skip("covered by the other widths")
+    g = torch.Generator().manual_seed(2)
+    n, h, w = 2, 9, 11
+    delta = rand_feat(g, n, c, h, w, dtype, 0.05)
+    prev = rand_feat(g, n, c, h, w, dtype, 2.0)
+    trunc = rand_feat(g, n, c, h, w, dtype, 0.01)
+    mask = rand_mask(g, n, h, w, 0.5)
+    thr = 0.12 if mode == 0 else (0.5 if mode == 1 else 0.04)
+    d_ref, p_ref, t_ref, m_ref = delta.clone(), prev.clone(), trunc.clone(), mask.clone()
+    O.activate_truncate(d_ref, p_ref, t_ref, m_ref, thr, act, mode)
+    dd, pd, td, md = delta.cuda(), prev.cuda(), trunc.cuda(), mask.cuda()
+    K().sparse_activation(dd, pd, td if mode >= 0 else None, md, thr, act, mode)
+    if mode <= 0:
+        assert torch.equal(md.cpu(), m_ref)
+        assert torch.equal(pd.cpu(), p_ref)
+        if mode == 0:
+            assert torch.equal(td.cpu(), t_ref)
+        sel = (m_ref != 0).expand_as(delta)
+        assert torch.equal(dd.cpu()[sel], d_ref[sel])
+    else:
+        # the norm is a floating-point reduction: allow decisions to differ only where it ties the threshold
+        agree = (md.cpu() == m_ref).float().mean().item()
+        assert agree > 0.99
+    # pixels outside the incoming mask are untouched
+    off = (mask == 0).expand_as(delta)
+    assert torch.equal(dd.cpu()[off], delta[off]) and torch.equal(pd.cpu()[off], prev[off])
+
+
+CONV_CASES = [
+    # cin, cout, k, stride, pad, dil, groups, h, w
+    (3, 32, 3, 2, 1, 1, 1, 18, 22),
+    (16, 24, 1, 1, 0, 1, 1, 9, 13),
+    (24, 144, 1, 1, 0, 1, 1, 8, 8),
+    (32, 64, 1, 2, 0, 1, 1, 10, 12),
+    (20, 36, 3, 1, 1, 1, 1, 11, 9),
+    (64, 64, 3, 2, 1, 1, 1, 12, 12),
+    (8, 8, 3, 1, 2, 2, 1, 12, 12),
+    (3, 16, 7, 2, 3, 1, 1, 20, 20),
+    (6, 10, 5, 1, 2, 1, 1, 9, 9),
+    (32, 32, 3, 1, 1, 1, 32, 9, 10),
+    (96, 96, 3, 2, 1, 1, 96, 12, 12),
+    (12, 12, 5, 1, 2, 1, 12, 8, 8),
+    (7, 7, 3, 1, 1, 1, 7, 8, 8),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CONV_CASES)
+@pytest.mark.parametrize("density", [0.0, 0.1, 1.0])
+def test_conv(dtype, case, density):
+    cin, cout, k, s, p, d, groups, h, w = case
+    g = torch.Generator().manual_seed(3)
+    n = 2
+    x = rand_feat(g, n, cin, h, w, dtype)
+    mask = rand_mask(g, n, h, w, density)
+    wt = (torch.randn(cout, cin // groups, k, k, generator=g) * (1.0 / (k * (cin // groups) ** 0.5))).to(dtype)
+    bias = torch.randn(cout, generator=g).to(dtype)
+    ref, m_ref = O.conv(x, mask, wt, bias, (s, s), (p, p), (d, d), groups)
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    f = convert_filter_out_channels_last(wt).cuda()
+    xd = x.cuda()
+    xd[(mask == 0).expand_as(x)] = float("nan")       # inactive inputs must never be read
+    out, om = K().sparse_conv(xd, f, mask.cuda(), bias.cuda(), (s, s), (p, p), (d, d), groups, create_out_mask=True)
+    assert torch.equal(om.cpu(), m_ref)
+    assert_close_masked(out, ref, m_ref, dtype, "conv")
+    # dense-output mode (no out-mask): every pixel defined, zeros + bias where nothing is active
+    out2 = K().sparse_conv(xd, f, mask.cuda(), bias.cuda(), (s, s), (p, p), (d, d), groups, create_out_mask=False)
+    assert_close_masked(out2, ref, torch.ones_like(m_ref), dtype, "conv dense-out")
+
+
+def test_conv_asymmetric_padding():
+    g = torch.Generator().manual_seed(4)
+    x = rand_feat(g, 1, 8, 9, 9, torch.float32)
+    mask = rand_mask(g, 1, 9, 9, 0.4)
+    wt = torch.randn(8, 8, 3, 3, generator=g) * 0.1
+    ref, m_ref = O.conv(x, mask, wt, None, (2, 2), (0, 1, 0, 1), (1, 1), 1)
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    out, om = K().sparse_conv(x.cuda(), convert_filter_out_channels_last(wt).cuda(), mask.cuda(), None, (2, 2), (0, 1, 0, 1),
+                              (1, 1), 1, create_out_mask=True)
+    assert torch.equal(om.cpu(), m_ref)
+    assert_close_masked(out, ref, m_ref, torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("k,s,p", [(4, 2, 1), (6, 4, 1), (2, 2, 0)])
+@pytest.mark.parametrize("density", [0.0, 0.15, 1.0])
+def test_deconv(dtype, k, s, p, density):
+    g = torch.Generator().manual_seed(5)
+    n, cin, cout, h, w = 2, 24, 20, 7, 9
+    x = rand_feat(g, n, cin, h, w, dtype)
+    mask = rand_mask(g, n, h, w, density)
+    wt = (torch.randn(cin, cout, k, k, generator=g) * 0.1).to(dtype)
+    bias = torch.randn(cout, generator=g).to(dtype)
+    ref, m_ref = O.deconv(x, mask, wt, bias, (s, s), (p, p))
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    f = convert_filter_out_channels_last(wt, transposed=True).cuda()
+    out, om = K().sparse_deconv(x.cuda(), f, mask.cuda(), bias.cuda(), (s, s), (p, p), (1, 1), 1, create_out_mask=True)
+    assert out.shape == ref.shape
+    assert torch.equal(om.cpu(), m_ref)
+    assert_close_masked(out, ref, m_ref, dtype, "deconv")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("c", [5, 64])
+@pytest.mark.parametrize("act,dense_out", [(0, False), (1, False), (1, True), (0, True)])
+def test_add(dtype, c, act, dense_out):
+    g = torch.Generator().manual_seed(6)
+    n, h, w = 2, 7, 9
+    a, b = rand_feat(g, n, c, h, w, dtype), rand_feat(g, n, c, h, w, dtype)
+    ma, mb = rand_mask(g, n, h, w, 0.3), rand_mask(g, n, h, w, 0.3)
+    prev = rand_feat(g, n, c, h, w, dtype)
+    p_ref = prev.clone()
+    ref, m_ref = O.add(a, ma, b, mb, p_ref, 0.5, 2.0, act, dense_out)
+    pd = prev.cuda()
+    out = torch.full_like(a, float("nan")).cuda()
+    mo = torch.full((n, 1, h, w), -3, dtype=torch.int32, device="cuda")
+    K().sparse_add_tensors(a.cuda(), b.cuda(), pd if (act > 0 or dense_out) else None, out, ma.cuda(), mb.cuda(), mo, 0.5, 2.0, act, dense_out)
+    if dense_out:
+        assert_close_masked(out, ref, torch.ones(n, 1, h, w, dtype=torch.int32), dtype, "add dense")
+    else:
+        assert torch.equal(mo.cpu(), m_ref)
+        assert_close_masked(out, ref, m_ref, dtype, "add")
+    if act > 0 or dense_out:
+        assert_close_masked(pd, p_ref, torch.ones(n, 1, h, w, dtype=torch.int32), dtype, "add prev")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_to_dense_and_densify(dtype):
+    g = torch.Generator().manual_seed(7)
+    n, c, h, w = 2, 24, 6, 5
+    a, b = rand_feat(g, n, c, h, w, dtype), rand_feat(g, n, c, h, w, dtype)
+    m = rand_mask(g, n, h, w, 0.4)
+    b_ref = b.clone()
+    O.add_to_dense(a, b_ref, m)
+    bd = b.cuda()
+    K().sparse_add_to_dense_tensor(a.cuda(), bd, m.cuda())
+    assert torch.equal(bd.cpu(), b_ref)
+    p_ref = b.clone()
+    ref = O.densify(a, m, p_ref, 2)
+    pd = b.cuda()
+    out = K().sparse_densify(a.cuda(), m.cuda(), pd, None, 2)
+    assert torch.equal(pd.cpu(), p_ref)
+    assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("k,s,p,c", [(3, 2, 1, 64), (2, 2, 0, 12), (3, 1, 1, 5)])
+def test_max_pool(dtype, k, s, p, c):
+    g = torch.Generator().manual_seed(8)
+    n, h, w = 2, 12, 14
+    x = rand_feat(g, n, c, h, w, dtype)
+    prev = rand_feat(g, n, c, h, w, dtype)
+    m = rand_mask(g, n, h, w, 0.2)
+    ref, m_ref = O.max_pool(x, m, prev, (k, k), (s, s), (p, p))
+    p_ref = prev.clone()
+    O.add_to_dense(x, p_ref, m)
+    pd = prev.cuda()
+    out, om = K().sparse_pooling(x.cuda(), pd, (k, k), m.cuda(), (s, s), (p, p), (1, 1), update_prev=True)
+    assert torch.equal(om.cpu(), m_ref)
+    assert_close_masked(out, ref, m_ref, dtype, "maxpool")
+    assert torch.equal(pd.cpu(), p_ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("c,h,w", [(1280, 7, 7), (40, 16, 16), (6, 40, 40)])
+@pytest.mark.parametrize("density", [0.0, 0.3, 1.0])
+def test_global_avg_pool(dtype, c, h, w, density):
+    g = torch.Generator().manual_seed(9)
+    n = 3
+    x = rand_feat(g, n, c, h, w, dtype)
+    m = rand_mask(g, n, h, w, density)
+    m[1] = 0
+    ref, m_ref = O.global_avg_pool(x, m)
+    out, om = K().sparse_pooling(x.cuda(), None, (h, w), m.cuda(), (1, 1), (0, 0), (1, 1), pooling_mode_int=1)
+    assert torch.equal(om.cpu(), m_ref)
+    assert_close_masked(out, ref, torch.ones_like(m_ref), dtype, "avgpool")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("scale,c", [(2, 32), (4, 5), (8, 64)])
+def test_upsample(dtype, scale, c):
+    g = torch.Generator().manual_seed(10)
+    x = rand_feat(g, 2, c, 5, 6, dtype)
+    m = rand_mask(g, 2, 5, 6, 0.4)
+    ref, m_ref = O.upsample(x, m, scale)
+    out, om = K().sparse_upsample(x.cuda(), m.cuda(), scale)
+    assert torch.equal(om.cpu().view_as(m_ref), m_ref)
+    sel = (m_ref != 0).expand_as(ref)
+    assert torch.equal(out.cpu()[sel], ref[sel])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("ca,cb", [(8, 16), (3, 5)])
+def test_concat_and_scale_bias(dtype, ca, cb):
+    g = torch.Generator().manual_seed(11)
+    n, h, w = 2, 6, 7
+    a, b = rand_feat(g, n, ca, h, w, dtype), rand_feat(g, n, cb, h, w, dtype)
+    ma, mb = rand_mask(g, n, h, w, 0.4), rand_mask(g, n, h, w, 0.4)
+    ref, m_ref = O.concatenate(a, ma, b, mb)
+    out, om = K().sparse_concatenate((a.cuda(), ma.cuda()), (b.cuda(), mb.cuda()))
+    assert torch.equal(om.cpu().view_as(m_ref), m_ref)
+    sel = (m_ref != 0).expand_as(ref)
+    assert torch.equal(out.cpu()[sel], ref[sel])
+    scale, bias = torch.randn(ca, generator=g).to(dtype), torch.randn(ca, generator=g).to(dtype)
+    ref2, _ = O.scale_bias(a, ma, scale, bias)
+    ad = a.cuda()
+    K().sparse_mul_add(ad, ma.cuda(), ad, ma.cuda(), scale.cuda(), bias.cuda())
+    assert_close_masked(ad, ref2, ma, dtype, "scale_bias")
+
+
+def test_compact_mask():
+    g = torch.Generator().manual_seed(12)
+    m = rand_mask(g, 3, 37, 41, 0.13)
+    idx, cnt = K().compact_mask(m.cuda())
+    k = int(cnt.item())
+    want = torch.nonzero(m.flatten()).flatten()
+    assert k == want.numel()
+    assert torch.equal(torch.sort(idx[:k].cpu().long())[0], want)
+
+
+def test_empty_batch_and_errors():
+    k = K()
+    x = torch.zeros(0, 8, 4, 4, device="cuda").contiguous(memory_format=torch.channels_last)
+    k.sparsify(x, x.clone(), x.clone(), torch.zeros(0, 1, 4, 4, dtype=torch.int32, device="cuda"), 0.1)
+    with pytest.raises(RuntimeError):
+        k.sparsify(torch.zeros(1, 8, 4, 4), torch.zeros(1, 8, 4, 4), torch.zeros(1, 8, 4, 4), torch.zeros(1, 1, 4, 4, dtype=torch.int32), 0.1)
+    with pytest.raises(RuntimeError):      # NCHW-contiguous input is rejected, not silently misread
+        k.sparse_activation(torch.zeros(1, 8, 4, 4, device="cuda"), torch.zeros(1, 8, 4, 4, device="cuda"), None,
+                            torch.zeros(1, 1, 4, 4, dtype=torch.int32, device="cuda"), 0.0, 1, -1)
+    with pytest.raises(RuntimeError):      # grouped convolution that is neither dense nor depthwise
+        xx = torch.zeros(1, 8, 4, 4, device="cuda").contiguous(memory_format=torch.channels_last)
+        k.sparse_conv(xx, torch.zeros(3, 3, 4, 8, device="cuda"), torch.ones(1, 1, 4, 4, dtype=torch.int32, device="cuda"), None,
+                      (1, 1), (1, 1), (1, 1), 2, create_out_mask=True)
+    with pytest.raises(RuntimeError):
+        k.sparsify(x.double(), x.double(), x.double(), torch.zeros(0, 1, 4, 4, dtype=torch.int32, device="cuda"), 0.1)
