@@ -490,9 +490,9 @@ extern "C" {
 
 int dc_sparsify(const void* x, void* prev_in, void* delta, int32_t* mask, int64_t npix, int32_t channels, int32_t dtype,
                 float threshold, void* stream) {
-    DC_REQUIRE(x); DC_REQUIRE(prev_in); DC_REQUIRE(delta); DC_REQUIRE(mask);
     if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
     if (npix == 0) return DC_OK;
+    DC_REQUIRE(x); DC_REQUIRE(prev_in); DC_REQUIRE(delta); DC_REQUIRE(mask);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == DC_F32) return sparsify_t<float>((const float*)x, (float*)prev_in, (float*)delta, mask, npix, channels, threshold, st);
     if (dtype == DC_F16) return sparsify_t<__half>((const __half*)x, (__half*)prev_in, (__half*)delta, mask, npix, channels, threshold, st);
@@ -501,9 +501,9 @@ int dc_sparsify(const void* x, void* prev_in, void* delta, int32_t* mask, int64_
 
 int dc_sparsify_u8(const uint8_t* x_u8, const float* scale, const float* offset, void* prev_in, void* delta, int32_t* mask,
                    int64_t npix, int32_t channels, int32_t dtype, float threshold, void* stream) {
-    DC_REQUIRE(x_u8); DC_REQUIRE(scale); DC_REQUIRE(offset); DC_REQUIRE(prev_in); DC_REQUIRE(delta); DC_REQUIRE(mask);
     if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
     if (npix == 0) return DC_OK;
+    DC_REQUIRE(x_u8); DC_REQUIRE(scale); DC_REQUIRE(offset); DC_REQUIRE(prev_in); DC_REQUIRE(delta); DC_REQUIRE(mask);
     cudaStream_t st = (cudaStream_t)stream;
     const int g = lanes_per_pixel(channels);
     if (dtype == DC_F32)
@@ -516,12 +516,12 @@ int dc_sparsify_u8(const uint8_t* x_u8, const float* scale, const float* offset,
 
 int dc_activate_truncate(void* delta, void* prev_out, void* truncated, int32_t* mask, int64_t npix, int32_t channels,
                          int32_t dtype, float threshold, int32_t activation, int32_t truncation, void* stream) {
+    if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
+    if (npix == 0) return DC_OK;
     DC_REQUIRE(delta); DC_REQUIRE(prev_out); DC_REQUIRE(mask);
     if (truncation >= 0) DC_REQUIRE(truncated);
     if (truncation > DC_TRUNC_RMS) return DC_ERR_UNSUPPORTED;
     if (activation > DC_ACT_SWISH) return DC_ERR_UNSUPPORTED;
-    if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
-    if (npix == 0) return DC_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == DC_F32) return act_trunc_t<float>((float*)delta, (float*)prev_out, (float*)truncated, mask, npix, channels, threshold, activation, truncation, st);
     if (dtype == DC_F16) return act_trunc_t<__half>((__half*)delta, (__half*)prev_out, (__half*)truncated, mask, npix, channels, threshold, activation, truncation, st);
@@ -531,11 +531,11 @@ int dc_activate_truncate(void* delta, void* prev_out, void* truncated, int32_t* 
 int dc_add(const void* a, const void* b, void* prev_out, void* out, const int32_t* mask_a, const int32_t* mask_b,
            int32_t* mask_out, float weight_a, float weight_b, int64_t npix, int32_t channels, int32_t dtype,
            int32_t activation, int32_t dense_out, void* stream) {
+    if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
+    if (npix == 0) return DC_OK;
     DC_REQUIRE(a); DC_REQUIRE(b); DC_REQUIRE(out); DC_REQUIRE(mask_a); DC_REQUIRE(mask_b);
     if (!dense_out) DC_REQUIRE(mask_out);
     if (dense_out || activation > 0) DC_REQUIRE(prev_out);
-    if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
-    if (npix == 0) return DC_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == DC_F32)
         DC_DISPATCH_W(float, channels, DC_PTRS(a, b, prev_out, out), k_add, npix, (const float*)a, (const float*)b,
@@ -551,9 +551,9 @@ int dc_add(const void* a, const void* b, void* prev_out, void* out, const int32_
 
 int dc_add_to_dense(const void* a, void* b, const int32_t* mask_a, int64_t npix, int32_t channels, int32_t dtype,
                     void* stream) {
-    DC_REQUIRE(a); DC_REQUIRE(b); DC_REQUIRE(mask_a);
     if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
     if (npix == 0) return DC_OK;
+    DC_REQUIRE(a); DC_REQUIRE(b); DC_REQUIRE(mask_a);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == DC_F32)
         DC_DISPATCH_W(float, channels, DC_PTRS(a, b), k_add_to_dense, npix, (const float*)a, (float*)b, mask_a, npix, channels);
@@ -565,9 +565,9 @@ int dc_add_to_dense(const void* a, void* b, const int32_t* mask_a, int64_t npix,
 
 int dc_scale_bias(const void* in, const int32_t* mask_in, void* out, int32_t* mask_out, const void* scale,
                   const void* bias, int64_t npix, int32_t channels, int32_t dtype, void* stream) {
-    DC_REQUIRE(in); DC_REQUIRE(out); DC_REQUIRE(scale);
     if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
     if (npix == 0) return DC_OK;
+    DC_REQUIRE(in); DC_REQUIRE(out); DC_REQUIRE(scale);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == DC_F32)
         DC_DISPATCH_W(float, channels, DC_PTRS(in, out, scale, bias), k_scale_bias, npix, (const float*)in, mask_in,
@@ -581,9 +581,9 @@ int dc_scale_bias(const void* in, const int32_t* mask_in, void* out, int32_t* ma
 
 int dc_concat(const void* a, const void* b, void* out, const int32_t* mask_a, const int32_t* mask_b, int32_t* mask_out,
               int64_t npix, int32_t channels_a, int32_t channels_b, int32_t dtype, void* stream) {
-    DC_REQUIRE(a); DC_REQUIRE(b); DC_REQUIRE(out); DC_REQUIRE(mask_a); DC_REQUIRE(mask_b); DC_REQUIRE(mask_out);
     if (npix < 0 || channels_a <= 0 || channels_b <= 0) return DC_ERR_SHAPE;
     if (npix == 0) return DC_OK;
+    DC_REQUIRE(a); DC_REQUIRE(b); DC_REQUIRE(out); DC_REQUIRE(mask_a); DC_REQUIRE(mask_b); DC_REQUIRE(mask_out);
     cudaStream_t st = (cudaStream_t)stream;
     const int ctot = channels_a + channels_b;
     // the vector path needs both halves to be whole packs
@@ -601,9 +601,9 @@ int dc_concat(const void* a, const void* b, void* out, const int32_t* mask_a, co
 
 int dc_densify(const void* delta, const int32_t* mask, void* prev_out, void* dense_out, int64_t npix, int32_t channels,
                int32_t dtype, int32_t activation, void* stream) {
-    DC_REQUIRE(delta); DC_REQUIRE(mask); DC_REQUIRE(prev_out);
     if (npix < 0 || channels <= 0) return DC_ERR_SHAPE;
     if (npix == 0) return DC_OK;
+    DC_REQUIRE(delta); DC_REQUIRE(mask); DC_REQUIRE(prev_out);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == DC_F32)
         DC_DISPATCH_W(float, channels, DC_PTRS(delta, prev_out, dense_out), k_densify, npix, (const float*)delta, mask,
@@ -617,9 +617,9 @@ int dc_densify(const void* delta, const int32_t* mask, void* prev_out, void* den
 
 int dc_upsample(const void* in, const int32_t* mask_in, void* out, int32_t* mask_out, int32_t n, int32_t h, int32_t w,
                 int32_t channels, int32_t scale, int32_t dtype, void* stream) {
-    DC_REQUIRE(in); DC_REQUIRE(mask_in); DC_REQUIRE(out); DC_REQUIRE(mask_out);
     if (n < 0 || h <= 0 || w <= 0 || channels <= 0 || scale <= 0) return DC_ERR_SHAPE;
     if (n == 0) return DC_OK;
+    DC_REQUIRE(in); DC_REQUIRE(mask_in); DC_REQUIRE(out); DC_REQUIRE(mask_out);
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t npix = (int64_t)n * h * scale * w * scale;
     if (dtype == DC_F32)

@@ -1,0 +1,121 @@
+"""Network-level gates: with every threshold at 0 the delta network must reproduce the dense
+PyTorch network on every frame (1e-4 relative for fp32, 1e-2 for fp16, relative = max abs
+difference / max abs reference per frame); caches reset cleanly; CUDA-graph replay equals eager."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.float16: 1e-2}
+
+
+def _frames(config, seed, n, size=None):
+    from examples.synthetic_video import make_video
+    f = make_video(config, seed).frames(n)
+    if size is not None:
+        f = f[:, :, :size[0], :size[1]].contiguous()
+    return f
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / max(b.float().abs().max().item(), 1e-12)
+
+
+def _outs(y):
+    return list(y) if isinstance(y, (tuple, list)) else [y]
+
+
+def _run_equivalence(name, frames, dtype, n_streams=1, **kw):
+    from examples.nets import build_pair
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    dense32, _ = build_pair(name, frames[:4], device="cpu", **kw)
+    dense32 = dense32.cuda()
+    _, delta = build_pair(name, frames[:4], device="cuda", dtype=dtype, **kw)
+    worst = 0.0
+    with torch.no_grad():
+        for t in range(frames.shape[0]):
+            x = frames[t:t + 1].cuda().repeat(n_streams, 1, 1, 1).contiguous(memory_format=torch.channels_last)
+            ref = _outs(dense32(x))
+            got = _outs(delta(x.to(dtype)))
+            for r, g in zip(ref, got):
+                assert g.shape == r.shape
+                e = _rel(g, r)
+                worst = max(worst, e)
+                assert e <= TOL[dtype], f"{name} frame {t}: relative error {e:.3e}"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_mobilenet_threshold0_matches_dense(dtype):
+    frames = _frames("mobilenet", 0, 12)
+    _run_equivalence("mobilenet", frames, dtype, n_streams=2)
+
+
+def test_mobilenet_fp32_matches_cpu_dense_anchor():
+    from examples.nets import build_pair
+    frames = _frames("mobilenet", 0, 6)
+    dense_cpu, _ = build_pair("mobilenet", frames[:4], device="cpu")
+    _, delta = build_pair("mobilenet", frames[:4], device="cuda")
+    with torch.no_grad():
+        for t in range(frames.shape[0]):
+            ref = dense_cpu(frames[t:t + 1])
+            got = delta(frames[t:t + 1].cuda().contiguous(memory_format=torch.channels_last))
+            assert _rel(got.cpu(), ref) <= 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_resnet50_threshold0_matches_dense(dtype):
+    frames = _frames("resnet50", 0, 3)
+    _run_equivalence("resnet50", frames, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_centernet_threshold0_matches_dense(dtype):
+    frames = _frames("centernet", 0, 3, size=(272, 480))
+    _run_equivalence("centernet", frames, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_hrnet_threshold0_matches_dense(dtype):
+    frames = _frames("hrnet", 0, 3)
+    _run_equivalence("hrnet", frames, dtype)
+
+
+def test_reset_layers_restarts_the_stream():
+    from examples.nets import build_pair
+    frames = _frames("mobilenet", 3, 5)
+    _, delta = build_pair("mobilenet", frames[:4], device="cuda")
+    xs = [frames[t:t + 1].cuda().contiguous(memory_format=torch.channels_last) for t in range(5)]
+    with torch.no_grad():
+        first = [delta(x).clone() for x in xs]
+        delta.reset_layers()
+        again = [delta(x).clone() for x in xs]
+    for a, b in zip(first, again):
+        assert torch.equal(a, b)
+
+
+def test_nonzero_thresholds_bounded_error_and_graph_replay():
+    from deltacnn_b200 import DCThreshold
+    from examples.nets import build_pair
+    from examples.runner import GraphedStep, set_depth_thresholds
+    frames = _frames("mobilenet", 1, 10)
+    dense, delta = build_pair("mobilenet", frames[:4], device="cuda", dtype=torch.float16)
+    xs = [frames[t:t + 1].cuda().half().contiguous(memory_format=torch.channels_last) for t in range(10)]
+    with torch.no_grad():
+        delta(xs[0])
+        table = set_depth_thresholds(0.05, 0.01, 0.05)
+        assert len(table) == len(DCThreshold.t) and table[0] == 0.05
+        eager = [delta(x).clone() for x in xs[1:4]]
+        # replay the same frames through a captured step on a second, identical model
+        _, delta2 = build_pair("mobilenet", frames[:4], device="cuda", dtype=torch.float16)
+        DCThreshold.reset()
+        delta2(xs[0])
+        set_depth_thresholds(0.05, 0.01, 0.05)
+        step = GraphedStep(delta2, xs[1], warmup_frames=[xs[1]])
+        # the warm-up consumed frame 1 eagerly; replay 2 and 3 and compare with the eager model
+        for t in (2, 3):
+            out = step(xs[t]).clone()
+            assert _rel(out, eager[t - 1]) < 1e-3
+        ref = dense(xs[3])
+        assert _rel(eager[2], ref) < 0.5, "thresholded output drifted far from the dense network"
