@@ -26,23 +26,30 @@ def _outs(y):
 
 
 def _run_equivalence(name, frames, dtype, n_streams=1, **kw):
+    """fp32: the delta network must match the dense fp32 network to 1e-4 on every frame.
+    fp16: randomly initialised networks amplify half-precision rounding layer by layer (the dense
+    fp16 PyTorch network itself drifts several percent from the fp32 one), so the gate is that the
+    delta network is as close to the fp32 truth as the dense fp16 network is: its error may not
+    exceed max(1e-2, 2 x the dense fp16 network's own error) on any frame."""
     from examples.nets import build_pair
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
     dense32, _ = build_pair(name, frames[:4], device="cpu", **kw)
     dense32 = dense32.cuda()
-    _, delta = build_pair(name, frames[:4], device="cuda", dtype=dtype, **kw)
+    dense, delta = build_pair(name, frames[:4], device="cuda", dtype=dtype, **kw)
     worst = 0.0
     with torch.no_grad():
         for t in range(frames.shape[0]):
             x = frames[t:t + 1].cuda().repeat(n_streams, 1, 1, 1).contiguous(memory_format=torch.channels_last)
-            ref = _outs(dense32(x))
+            truth = _outs(dense32(x))
             got = _outs(delta(x.to(dtype)))
-            for r, g in zip(ref, got):
+            same_precision = _outs(dense(x.to(dtype)))
+            for r, g, d in zip(truth, got, same_precision):
                 assert g.shape == r.shape
                 e = _rel(g, r)
+                bound = TOL[dtype] if dtype == torch.float32 else max(TOL[dtype], 2.0 * _rel(d, r))
                 worst = max(worst, e)
-                assert e <= TOL[dtype], f"{name} frame {t}: relative error {e:.3e}"
+                assert e <= bound, f"{name} frame {t}: relative error {e:.3e} > {bound:.3e}"
     return worst
 
 
