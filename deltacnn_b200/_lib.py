@@ -30,7 +30,7 @@ class Epilogue(ctypes.Structure):
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} not found: the CUDA extension is not built. Run `python -m deltacnn_b200.build` "
+        f"{LIB_PATH} not found: the CUDA extension is not built. Run `python deltacnn_b200/build.py` "
         "(needs nvcc with sm_100a support). deltacnn_b200 has no CPU or PyTorch fallback.")
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -40,6 +40,7 @@ _SIGNATURES = {
     "dc_version": (c_int, []),
     "dc_status_string": (ctypes.c_char_p, [c_int]),
     "dc_last_cuda_error": (c_int, []),
+    "dc_umma_error": (c_int, []),
     "dc_sparsify": (c_int, [_P, _P, _P, _P, c_i64, c_int, c_int, c_float, _P]),
     "dc_sparsify_u8": (c_int, [_P, _P, _P, _P, _P, _P, c_i64, c_int, c_int, c_float, _P]),
     "dc_conv2d": (c_int, [ctypes.POINTER(ConvDesc), _P, _P, _P, c_int, _P, _P, _P, ctypes.POINTER(Epilogue), _P]),

@@ -4,7 +4,7 @@ Each translation unit under csrc/ is compiled to an object file in parallel and
 relinked only when a source or header is newer than its object. The shared library
 lands next to this file so that it travels with the package.
 
-Usage: python -m deltacnn_b200.build [--force] [--verbose]
+Usage: python deltacnn_b200/build.py [--force] [--verbose]
 """
 import os
 import subprocess

@@ -35,6 +35,7 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
                 int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 size_t filter_umma_bytes(const dc_conv_desc* d, int transposed);
 int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, void* packed, cudaStream_t st);
+int umma_error_code();
 
 static int run_epilogue(const dc_conv_desc* d, void* out, int32_t* mo, const dc_epilogue* ep, void* stream) {
     if (ep == nullptr) return DC_OK;
@@ -66,6 +67,8 @@ const char* dc_status_string(int status) {
 }
 
 int dc_last_cuda_error(void) { return t_last_cuda_error; }
+
+int dc_umma_error(void) { return umma_error_code(); }
 
 int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
               const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream) {

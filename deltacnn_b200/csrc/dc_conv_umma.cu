@@ -1,16 +1,468 @@
-// Tensor-core (tcgen05 / TMEM) delta convolutions. Placeholder translation unit: the
-// entry points report "no tensor-core kernel for this shape" until the kernels land.
+// Tensor-core delta convolution for sm_100a: pointwise (1x1) layers as a gather-GEMM on
+// tcgen05.mma with the accumulator in tensor memory.
+//
+//   rows (M = 128 per tile)   the ACTIVE output pixels of a span of consecutive pixels, compacted
+//                             inside the CTA with warp ballots and a prefix over the warps
+//   K                         input channels, streamed in blocks of 64 through a shared-memory ring;
+//                             the gathered rows are written in the 128-byte-swizzled K-major layout
+//                             the tensor core reads (inactive pixels are never loaded)
+//   N                         output channels (<= 256 per CTA); the filter is pre-tiled on the device
+//                             into the same swizzled layout, so a K block of it is one contiguous bulk
+//                             copy (cp.async.bulk, completion on an mbarrier)
+//   epilogue                  tcgen05.ld -> registers (+bias) -> fp16 staging tile in shared memory ->
+//                             coalesced rows; optionally the activation/truncation step of
+//                             dc_activate_truncate is applied here, so the convolution result never
+//                             makes a round trip through HBM
+//
+// Every wait on an mbarrier is bounded; a wait that gives up sets a sticky device-side error code
+// (dc_umma_error) and the CTA frees its tensor memory and returns.
 #include "dc_common.cuh"
 
 namespace dc {
 
-size_t filter_umma_bytes(const dc_conv_desc*, int) { return 0; }
+__device__ int g_umma_error = 0;
 
-int pack_filter_umma(const dc_conv_desc*, int, const void*, void*, cudaStream_t) { return DC_ERR_UNSUPPORTED; }
+constexpr int kRows = 128;            // M of one MMA tile
+constexpr int kKBlock = 64;           // fp16 elements per K block (one 128-byte swizzle row)
+constexpr int kABytes = kRows * 128;  // one A stage
+constexpr int kStages = 3;
+constexpr int kMaxResidentKB = 16;
+constexpr int kPwThreads = 128;
+constexpr uint32_t kWaitLimit = 1u << 22;
 
-int conv2d_umma(const dc_conv_desc*, const void*, const int32_t*, const void*, const void*, void*, int32_t*,
-                const dc_epilogue*, cudaStream_t) {
-    return DC_ERR_UNSUPPORTED;
+struct PwParams {
+    const __half* in; const int32_t* mi; const uint8_t* wimg; const __half* bias;
+    __half* out; int32_t* mo; __half* prev; __half* trunc;
+    float thr; int act; int fused;
+    int64_t npix_out;
+    int hi, wi, ho, wo, sh, sw;
+    int cin, cout;
+    int nkb, bn, span, b_resident, tmem_cols;
+    uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the phase did not complete within the iteration limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t holder, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                               // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
+    return d;
+}
+// kind::f16, A and B fp16 K-major, D fp32, M = 128, N = n
+__host__ __device__ inline uint32_t make_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+}
+
+// ---- kernel -----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + p.off_b;
+    uint8_t* sStage = smem + p.off_stage;
+    int* s_out = reinterpret_cast<int*>(smem + p.off_list);        // [span] output pixel of every active row
+    int* s_in = s_out + p.span;                                    // [span] input pixel of every active row
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_misc);
+    // bars[0..kStages)            slot_free   (tcgen05.commit of the MMAs that read stage s)
+    // bars[kStages..+16)          b_full      (bulk copy of a filter block landed)
+    // bars[kStages+16]            accum_full  (all MMAs of a tile done)
+    uint32_t* s_u32 = reinterpret_cast<uint32_t*>(bars + kStages + kMaxResidentKB + 1);
+    // s_u32[0] tmem base, [1] ok flag, [2] running count, [3..6] warp counts
+    float* s_bias = reinterpret_cast<float*>(s_u32 + 8);           // [bn]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar_slot = [&](int s) { return bar0 + 8u * s; };
+    auto bar_bfull = [&](int s) { return bar0 + 8u * (kStages + s); };
+    const uint32_t bar_accum = bar0 + 8u * (kStages + kMaxResidentKB);
+
+    const int n0 = blockIdx.y * p.bn;                              // first output channel of this CTA
+    const int ncols = min(p.bn, p.cout - n0);                      // real output channels here
+    const uint8_t* wimg = p.wimg + (size_t)blockIdx.y * p.nkb * p.bn * 128;
+
+    // ---- compaction of the span's active pixels (order preserved) ----
+    if (tid == 0) s_u32[2] = 0;
+    __syncthreads();
+    const int64_t q0 = (int64_t)blockIdx.x * p.span;
+    const int64_t hw_out = (int64_t)p.ho * p.wo;
+    for (int base = 0; base < p.span; base += kPwThreads) {
+        const int64_t q = q0 + base + tid;
+        bool on = false;
+        int pin = 0;
+        if (base + tid < p.span && q < p.npix_out) {
+            if (p.sh == 1 && p.sw == 1) {
+                pin = (int)q;
+            } else {
+                const int64_t b = q / hw_out;
+                const int r = (int)(q - b * hw_out);
+                pin = (int)((b * p.hi + (int64_t)(r / p.wo) * p.sh) * p.wi + (int64_t)(r % p.wo) * p.sw);
+            }
+            on = p.mi[pin] != 0;
+            if (blockIdx.y == 0 && (!p.fused || !on)) p.mo[q] = on ? 1 : 0;
+        }
+        const unsigned bal = __ballot_sync(DC_FULL, on);
+        if (lane == 0) s_u32[3 + warp] = __popc(bal);
+        __syncthreads();
+        int pre = s_u32[2];
+        for (int w = 0; w < warp; ++w) pre += s_u32[3 + w];
+        if (on) {
+            const int slot = pre + __popc(bal & ((1u << lane) - 1u));
+            s_out[slot] = (int)(q - q0);
+            s_in[slot] = pin;
+        }
+        __syncthreads();
+        if (tid == 0) s_u32[2] += s_u32[3] + s_u32[4] + s_u32[5] + s_u32[6];
+        __syncthreads();
+    }
+    const int cnt = (int)s_u32[2];
+    if (cnt == 0) return;                 // nothing active in this span: no barriers, no tensor memory
+
+    if (tid == 0) {
+        for (int i = 0; i < kStages + kMaxResidentKB + 1; ++i) mbar_init(bar0 + 8u * i, 1);
+        fence_barrier_init();
+        s_u32[1] = 1;
+    }
+    for (int i = tid; i < p.bn; i += kPwThreads) s_bias[i] = (p.bias != nullptr && i < ncols) ? __half2float(p.bias[n0 + i]) : 0.f;
+    if (warp == 0) tmem_alloc(smem_u32(&s_u32[0]), (uint32_t)p.tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_u32[0];
+
+
+    const uint32_t idesc = make_idesc(p.bn);
+    const uint32_t b_block_bytes = (uint32_t)p.bn * 128u;
+    const int row_in_pass = tid >> 3, chunk = tid & 7;
+    const uint32_t a_thread_off = (uint32_t)((row_in_pass >> 3) * 1024 + (row_in_pass & 7) * 128 + ((chunk ^ (row_in_pass & 7)) << 4));
+    int it = 0;                       // global K-block iteration counter (ring position)
+    bool ok = true;
+
+    for (int t0 = 0; t0 < cnt && ok; t0 += kRows) {
+        const int cnt_t = min(kRows, cnt - t0);
+        const int tile = t0 / kRows;
+        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+            const int slot = it % kStages;
+            const int use = it / kStages;
+            if (use > 0) {            // the stage is being read by MMAs issued kStages iterations ago
+                if (tid == 0 && !mbar_wait(bar_slot(slot), (uint32_t)((use - 1) & 1))) { s_u32[1] = 0; atomicExch(&g_umma_error, 1); }
+                __syncthreads();
+                if (s_u32[1] == 0) { ok = false; break; }
+            }
+            const bool load_b = p.b_resident ? (tile == 0) : true;
+            const int bslot = p.b_resident ? kb : slot;
+            if (tid == 0 && load_b) {
+                mbar_expect_tx(bar_bfull(bslot), b_block_bytes);
+                bulk_g2s(smem_u32(sB + (size_t)bslot * b_block_bytes), wimg + (size_t)kb * b_block_bytes, b_block_bytes, bar_bfull(bslot));
+            }
+            // gather: 8 lanes per row, one 16-byte chunk each, 16 rows per pass
+            const int kk = kb * kKBlock + chunk * 8;
+            const int kleft = p.cin - kb * kKBlock;
+            const int ksteps = (min(kleft, kKBlock) + 15) >> 4;
+            uint8_t* a_stage = sA + (size_t)slot * kABytes;
+            if (chunk < ksteps * 2) {
+                uint4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int r = row_in_pass + 16 * j;
+                    v[j] = make_uint4(0, 0, 0, 0);
+                    if (r < cnt_t && kk < p.cin)
+                        v[j] = __ldg(reinterpret_cast<const uint4*>(p.in + (int64_t)s_in[t0 + r] * p.cin + kk));
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int r = row_in_pass + 16 * j;
+                    if (r < cnt_t) *reinterpret_cast<uint4*>(a_stage + a_thread_off + j * 2048) = v[j];
+                }
+            }
+            fence_proxy_async();
+            __syncthreads();
+            if (tid == 0) {
+                bool bok = true;
+                if (load_b) bok = mbar_wait(bar_bfull(bslot), p.b_resident ? 0u : (uint32_t)(use & 1));
+                if (!bok) { s_u32[1] = 0; atomicExch(&g_umma_error, 2); }
+                else {
+                    tc_fence_after();
+                    const uint64_t ad = make_smem_desc(smem_u32(a_stage));
+                    const uint64_t bd = make_smem_desc(smem_u32(sB + (size_t)bslot * b_block_bytes));
+                    for (int ks = 0; ks < ksteps; ++ks)
+                        umma_f16(tmem_base, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(bar_slot(slot));
+                }
+            }
+        }
+        if (!ok) break;
+        if (tid == 0) {
+            umma_commit(bar_accum);
+            if (!mbar_wait(bar_accum, (uint32_t)(tile & 1))) { s_u32[1] = 0; atomicExch(&g_umma_error, 3); }
+        }
+        __syncthreads();
+        if (s_u32[1] == 0) { ok = false; break; }
+        tc_fence_after();
+
+        // ---- epilogue 1: tensor memory -> fp16 staging tile (row = TMEM lane) ----
+        {
+            const int r = warp * 32 + lane;
+            uint8_t* srow = sStage + (size_t)r * p.stage_pitch;
+            for (int c0 = 0; c0 < p.bn; c0 += 16) {
+                uint32_t acc[16];
+                tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, acc);
+                tmem_ld_wait();
+                uint4 o[2];
+                __half2* h = reinterpret_cast<__half2*>(o);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    h[j] = __floats2half2_rn(__uint_as_float(acc[2 * j]) + s_bias[c0 + 2 * j],
+                                             __uint_as_float(acc[2 * j + 1]) + s_bias[c0 + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(srow + c0 * 2) = o[0];
+                *reinterpret_cast<uint4*>(srow + c0 * 2 + 16) = o[1];
+            }
+        }
+        tc_fence_before();
+        __syncthreads();
+
+        // ---- epilogue 2: coalesced rows; optional accumulate + activation delta + truncation ----
+        {
+            const int nch = ncols >> 3;                           // 16-byte packs per row
+            int g = 1;
+            while (g < nch && g < 32) g <<= 1;
+            const int lig = lane & (g - 1);
+            const int ppw = 32 / g;
+            for (int rb = warp * ppw; rb < kRows; rb += 4 * ppw) {
+                const int r = rb + lane / g;
+                const bool valid = r < cnt_t;
+                const bool mine = valid && lig < nch;
+                const int64_t q = valid ? q0 + s_out[t0 + r] : 0;
+                Pack<__half, 8> d;
+                if (mine) d.load(reinterpret_cast<const __half*>(sStage + (size_t)r * p.stage_pitch) + lig * 8);
+                if (!p.fused) {
+                    if (mine) d.store(p.out + q * p.cout + n0 + lig * 8);
+                    continue;
+                }
+                Pack<__half, 8> y, tr, e;
+                bool hit = false;
+                if (mine) {
+                    const int64_t off = q * p.cout + n0 + lig * 8;
+                    y.load(p.prev + off);
+                    tr.load(p.trunc + off);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const float yo = y.get(k);
+                        const float rr = rnd<__half>(tr.get(k) + d.get(k));
+                        const float u = rnd<__half>(yo + rr);
+                        const float ee = rnd<__half>(act_apply(u, p.act) - act_apply(yo, p.act));
+                        tr.set(k, rr); y.set(k, u); e.set(k, ee);
+                        hit |= fabsf(ee) > p.thr;
+                    }
+                }
+                const bool active = group_any(hit, g, lane);
+                if (mine) {
+                    const int64_t off = q * p.cout + n0 + lig * 8;
+                    if (active) {
+                        Pack<__half, 8> z; z.zero();
+                        y.store(p.prev + off);
+                        e.store(p.out + off);
+                        z.store(p.trunc + off);
+                    } else {
+                        tr.store(p.trunc + off);
+                    }
+                }
+                if (valid && lig == 0) p.mo[q] = active ? 1 : 0;
+            }
+        }
+        __syncthreads();
+        tc_fence_after();
+    }
+
+    // drain: every MMA that was issued has to finish before tensor memory is released
+    if (!ok && tid == 0) {
+        for (int s = 0; s < kStages; ++s) { (void)mbar_try_wait(bar_slot(s), 0); }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+}
+
+// ---- filter packing ---------------------------------------------------------------------------
+// HWIO (1,1,cin,cout) fp16 -> per N tile, per K block: bn rows x 64 K values, K-major, 128-byte swizzled.
+__global__ void k_pack_pw(const __half* __restrict__ w, __half* __restrict__ img, int cin, int cout, int bn, int nkb, int ntiles) {
+    const int64_t total = (int64_t)ntiles * nkb * bn * 64;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int e = (int)(i & 7);
+        const int cpos = (int)((i >> 3) & 7);       // swizzled chunk position inside the 128-byte row
+        const int64_t rowi = i >> 6;
+        const int n = (int)(rowi % bn);
+        const int kb = (int)((rowi / bn) % nkb);
+        const int tile = (int)(rowi / ((int64_t)bn * nkb));
+        const int c = cpos ^ (n & 7);               // logical chunk stored at this position
+        const int k = kb * 64 + c * 8 + e;
+        const int co = tile * bn + n;
+        img[i] = (k < cin && n < bn && co < cout && co < (tile + 1) * bn) ? w[(int64_t)k * cout + co] : __float2half(0.f);
+    }
+}
+
+struct PwPlan {
+    bool ok;
+    int bn, ntiles, nkb, tmem_cols, b_resident, span;
+    uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
+    size_t smem, img_bytes;
+};
+
+static PwPlan plan_pw(const dc_conv_desc* d) {
+    PwPlan pl{};
+    pl.ok = d->dtype == DC_F16 && d->kh == 1 && d->kw == 1 && d->groups == 1 && d->pad_top == 0 && d->pad_left == 0 &&
+            d->pad_bottom == 0 && d->pad_right == 0 && d->c_in % 8 == 0 && d->c_out % 8 == 0 && d->c_in >= 16 && d->c_out >= 16;
+    if (!pl.ok) return pl;
+    pl.ntiles = divup(d->c_out, 256);
+    pl.bn = divup(divup(d->c_out, pl.ntiles), 16) * 16;
+    pl.nkb = divup(d->c_in, kKBlock);
+    pl.tmem_cols = 32;
+    while (pl.tmem_cols < pl.bn) pl.tmem_cols <<= 1;
+    const size_t b_block = (size_t)pl.bn * 128;
+    pl.b_resident = (pl.nkb <= kMaxResidentKB && pl.nkb * b_block <= 64 * 1024) ? 1 : 0;
+    const size_t b_bytes = (pl.b_resident ? pl.nkb : kStages) * b_block;
+    pl.span = 1024;
+    pl.stage_pitch = (uint32_t)pl.bn * 2 + 16;
+    pl.off_b = kStages * kABytes;
+    pl.off_stage = pl.off_b + (uint32_t)b_bytes;
+    pl.off_list = pl.off_stage + kRows * pl.stage_pitch;
+    pl.off_list = (pl.off_list + 15) & ~15u;
+    pl.img_bytes = (size_t)pl.ntiles * pl.nkb * b_block;
+    return pl;
+}
+
+static void finish_plan(PwPlan& pl, int64_t npix_out) {
+    // spans small enough to give every SM a few CTAs, large enough to fill an MMA tile when sparse
+    int span = 1024;
+    const int64_t want = (int64_t)sm_count() * 4;
+    while (span > 128 && divup64(npix_out, span) * pl.ntiles < want) span >>= 1;
+    pl.span = span;
+    pl.off_misc = (pl.off_list + 2u * (uint32_t)span * 4u + 15) & ~15u;
+    pl.smem = pl.off_misc + 8 * (kStages + kMaxResidentKB + 1) + 32 + 4 * (size_t)pl.bn + 1024 /* alignment slack */;
+}
+
+size_t filter_umma_bytes(const dc_conv_desc* d, int transposed) {
+    if (transposed) return 0;
+    PwPlan pl = plan_pw(d);
+    return pl.ok ? pl.img_bytes : 0;
+}
+
+int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, void* packed, cudaStream_t st) {
+    if (transposed) return DC_ERR_UNSUPPORTED;
+    PwPlan pl = plan_pw(d);
+    if (!pl.ok) return DC_ERR_UNSUPPORTED;
+    if (!aligned16(packed)) return DC_ERR_ALIGNMENT;
+    const int64_t total = (int64_t)pl.img_bytes / 2;
+    int64_t blocks = divup64(total, 256);
+    if (blocks > 4096) blocks = 4096;
+    k_pack_pw<<<(unsigned)blocks, 256, 0, st>>>((const __half*)hwio, (__half*)packed, d->c_in, d->c_out, pl.bn, pl.nkb, pl.ntiles);
+    return check_launch();
+}
+
+int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+                int32_t* mo, const dc_epilogue* ep, cudaStream_t st) {
+    PwPlan pl = plan_pw(d);
+    if (!pl.ok || mi == nullptr || mo == nullptr) return DC_ERR_UNSUPPORTED;
+    if (!aligned16(in) || !aligned16(out) || !aligned16(filt)) return DC_ERR_ALIGNMENT;
+    const int64_t npix_out = (int64_t)d->n * d->h_out * d->w_out;
+    if (npix_out == 0) return DC_OK;
+    if ((int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
+    finish_plan(pl, npix_out);
+    const bool fused = ep != nullptr && pl.ntiles == 1 && ep->truncation == DC_TRUNC_MAX;
+    PwParams p{};
+    p.in = (const __half*)in; p.mi = mi; p.wimg = (const uint8_t*)filt; p.bias = (const __half*)bias;
+    p.out = (__half*)out; p.mo = mo;
+    p.prev = fused ? (__half*)ep->prev_out : nullptr;
+    p.trunc = fused ? (__half*)ep->truncated : nullptr;
+    p.thr = fused ? host_round_threshold<__half>(ep->threshold) : 0.f;
+    p.act = fused ? ep->activation : 0;
+    p.fused = fused ? 1 : 0;
+    p.npix_out = npix_out;
+    p.hi = d->h_in; p.wi = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.sh = d->stride_h; p.sw = d->stride_w;
+    p.cin = d->c_in; p.cout = d->c_out;
+    p.nkb = pl.nkb; p.bn = pl.bn; p.span = pl.span; p.b_resident = pl.b_resident; p.tmem_cols = pl.tmem_cols;
+    p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_list = pl.off_list; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(k_pw_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return check_launch();
+        attr_set = true;
+    }
+    if (pl.smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)divup64(npix_out, pl.span), (unsigned)pl.ntiles);
+    k_pw_umma<<<grid, kPwThreads, pl.smem, st>>>(p);
+    int rc = check_launch();
+    if (rc != DC_OK) return rc;
+    if (ep != nullptr && !fused)
+        return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,
+                                    ep->activation, ep->truncation, (void*)st);
+    return DC_OK;
+}
+
+int umma_error_code() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_umma_error, sizeof(int)) != cudaSuccess) return -1;
+    return v;
 }
 
 }  // namespace dc

@@ -111,7 +111,7 @@ def sparse_conv(x, filter, mask=None, bias=None, stride=(1, 1), padding=(0, 0), 
         out_mask = torch.empty((x.shape[0], 1, out_h, out_w), dtype=torch.int32, device=x.device)
     if desc is None:
         desc = make_conv_desc(tuple(x.shape), out_c, (out_h, out_w), kernel, stride, padding, dilation, groups, _dtype(x))
-    if filter_umma is not None:
+    if filter_umma is not None and mask is not None and out_mask is not None:
         filt, layout = filter_umma, _lib.DC_FILTER_UMMA
     else:
         filt, layout = filter, _lib.DC_FILTER_HWIO

@@ -119,6 +119,11 @@ size_t dc_filter_umma_bytes(const dc_conv_desc* desc, int32_t transposed);
 int dc_pack_filter_umma(const dc_conv_desc* desc, int32_t transposed, const void* filter_hwio,
                         void* filter_umma, void* stream);
 
+/* Sticky device-side error code of the tensor-core kernels on the current device: 0 = none,
+ * otherwise the bounded wait that gave up (1 stage ring, 2 filter copy, 3 accumulator). The
+ * call synchronises with the device. No reference counterpart. */
+int dc_umma_error(void);
+
 /* Accumulate + activation delta + truncation, in place on delta, mask and both caches.
  * Replaces deltacnn_activate_truncate (src/cuda/conv_torch_wrapper.cpp:295-344;
  * kernels src/cuda/other_nn_layers.cu:755,1198). truncated may be NULL when
@@ -177,9 +182,9 @@ int dc_concat(const void* a, const void* b, void* out,
 int dc_densify(const void* delta, const int32_t* mask, void* prev_out, void* dense_out,
                int64_t npix, int32_t channels, int32_t dtype, int32_t activation, void* stream);
 
-/* Number of active pixels of a mask and their compacted indices (ascending), built
+/* Number of active pixels of a mask and their compacted indices, built
  * with warp ballots and a block prefix scan; count is one int32 on the device,
- * indices holds up to npix int32. Used to size work by the active set. No reference
+ * indices holds up to npix int32 (ascending inside a block of 256 pixels, blocks in any order). Used to size work by the active set. No reference
  * counterpart (the reference re-derives activity inside every kernel,
  * src/cuda/conv_kernel.cu:46-108). */
 int dc_compact_mask(const int32_t* mask, int64_t npix, int32_t* indices, int32_t* count, void* stream);

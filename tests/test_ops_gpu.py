@@ -307,3 +307,89 @@ def test_empty_batch_and_errors():
                       (1, 1), (1, 1), (1, 1), 2, create_out_mask=True)
     with pytest.raises(RuntimeError):
         k.sparsify(x.double(), x.double(), x.double(), torch.zeros(0, 1, 4, 4, dtype=torch.int32, device="cuda"), 0.1)
+
+
+# ---------------------------------------------------------------------------------------------
+# tensor-core pointwise convolution (tcgen05 gather-GEMM), fp16
+# ---------------------------------------------------------------------------------------------
+PW_CASES = [
+    # cin, cout, stride, n, h, w
+    (32, 16, 1, 2, 20, 24), (16, 96, 1, 2, 24, 20), (96, 24, 1, 2, 16, 16), (24, 144, 1, 2, 16, 12), (144, 32, 1, 3, 9, 9),
+    (192, 64, 1, 2, 14, 14), (64, 384, 1, 2, 14, 14), (576, 160, 1, 2, 7, 7), (960, 320, 1, 2, 7, 7), (320, 1280, 1, 3, 7, 7),
+    (256, 512, 2, 2, 16, 16), (64, 256, 1, 1, 40, 40), (1024, 2048, 2, 1, 8, 8),
+]
+
+
+def _pack_umma(wt_hwio, cin, cout, stride):
+    from deltacnn_b200 import _lib
+    import deltacnn_b200.cuda_kernels as k
+    desc = k.make_conv_desc((1, cin, 8, 8), cout, (8, 8), (1, 1), (stride, stride), (0, 0), (1, 1), 1, 1)
+    nbytes = _lib.lib.dc_filter_umma_bytes(desc, 0)
+    assert nbytes > 0
+    packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    _lib.check(_lib.lib.dc_pack_filter_umma(desc, 0, wt_hwio.data_ptr(), packed.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+    return packed
+
+
+@pytest.mark.parametrize("case", PW_CASES)
+@pytest.mark.parametrize("density", [0.0, 0.08, 0.6, 1.0])
+def test_pointwise_umma_matches_oracle(case, density):
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    cin, cout, s, n, h, w = case
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(21)
+    x = rand_feat(g, n, cin, h, w, dtype)
+    mask = rand_mask(g, n, h, w, density)
+    wt = (torch.randn(cout, cin, 1, 1, generator=g) / cin ** 0.5).to(dtype)
+    bias = torch.randn(cout, generator=g).to(dtype)
+    ref, m_ref = O.conv(x, mask, wt, bias, (s, s), (0, 0), (1, 1), 1)
+    f = convert_filter_out_channels_last(wt).cuda()
+    packed = _pack_umma(f, cin, cout, s)
+    xd = x.cuda()
+    xd[(mask == 0).expand_as(x)] = float("nan")
+    out = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last)
+    out, om = K().sparse_conv(xd, f, mask.cuda(), bias.cuda(), (s, s), (0, 0), (1, 1), 1, create_out_mask=True, out=out, filter_umma=packed)
+    assert _lib.lib.dc_umma_error() == 0
+    assert torch.equal(om.cpu(), m_ref)
+    assert_close_masked(out, ref, m_ref, dtype, "pointwise umma")
+    off = (m_ref == 0).expand_as(ref)
+    assert torch.isnan(out.cpu()[off]).all(), "pixels outside the out-mask must not be written"
+    # the CUDA-core kernel computes the same thing
+    out2, om2 = K().sparse_conv(xd, f, mask.cuda(), bias.cuda(), (s, s), (0, 0), (1, 1), 1, create_out_mask=True)
+    assert torch.equal(om2, om)
+    assert_close_masked(out2, out.cpu(), m_ref, dtype, "umma vs simt")
+
+
+@pytest.mark.parametrize("case", [c for c in PW_CASES if c[1] <= 256] + [(64, 384, 1, 2, 14, 14)])
+@pytest.mark.parametrize("act", [2, 0])
+def test_pointwise_umma_fused_epilogue_equals_two_kernels(case, act):
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    import deltacnn_b200.cuda_kernels as k
+    cin, cout, s, n, h, w = case
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(22)
+    x = rand_feat(g, n, cin, h, w, dtype, 0.2).cuda()
+    mask = rand_mask(g, n, h, w, 0.3).cuda()
+    wt = (torch.randn(cout, cin, 1, 1, generator=g) / cin ** 0.5).to(dtype)
+    f = convert_filter_out_channels_last(wt).cuda()
+    packed = _pack_umma(f, cin, cout, s)
+    ho, wo = k.conv_out_hw(h, w, (1, 1), (s, s), (0, 0), (1, 1))
+    prev = rand_feat(g, n, cout, ho, wo, dtype, 1.0).cuda()
+    trunc = rand_feat(g, n, cout, ho, wo, dtype, 0.02).cuda()
+    thr = 0.6 if cout <= 64 else 0.9       # drops some pixels and keeps others
+    # two kernels: convolution, then activation/truncation
+    o1, m1 = k.sparse_conv(x, f, mask, None, (s, s), (0, 0), (1, 1), 1, create_out_mask=True, filter_umma=packed)
+    p1, t1 = prev.clone(), trunc.clone()
+    k.sparse_activation(o1, p1, t1, m1, thr, act, 0)
+    # fused
+    p2, t2 = prev.clone(), trunc.clone()
+    ep = k.make_epilogue(p2, t2, thr, act, 0)
+    o2, m2 = k.sparse_conv(x, f, mask, None, (s, s), (0, 0), (1, 1), 1, create_out_mask=True, filter_umma=packed, epilogue=ep)
+    assert _lib.lib.dc_umma_error() == 0
+    assert torch.equal(m1, m2)
+    assert int(m2.sum()) <= int(m1.numel())
+    assert torch.equal(p1, p2) and torch.equal(t1, t2)
+    sel = (m1 != 0).expand_as(o1)
+    assert torch.equal(o1[sel], o2[sel])
