@@ -1,0 +1,87 @@
+"""The CPU oracle against fixtures recorded from the reference's own CUDA kernels
+(tests/golden/ref_ops.npz, written by tests/golden/make_golden.py on a B200). Masks and every
+state tensor of the element-wise operators must be bit-exact; convolution values are compared at
+out-mask pixels within a tolerance (the reference accumulates fp16 convolutions in fp16)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from golden.make_golden import cases  # noqa: E402
+from oracle import delta_ops as O  # noqa: E402
+
+GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_ops.npz"))
+CASES = cases()
+
+
+def gold(name, key, like=None):
+    a = torch.from_numpy(GOLD[f"{name}/{key}"].astype(np.float32) if GOLD[f"{name}/{key}"].dtype != np.int32 else GOLD[f"{name}/{key}"])
+    return a
+
+
+def close_at(got, ref, mask, tol):
+    sel = (mask != 0).expand_as(ref)
+    if sel.sum() == 0:
+        return
+    r, g = ref.float()[sel], got.float()[sel]
+    err = (g - r).abs().max().item() / max(r.abs().max().item(), 1e-6)
+    assert err <= tol, f"relative error {err:.3e} > {tol}"
+
+
+def test_every_recorded_case_is_checked():
+    recorded = {k.split("/")[0] for k in GOLD.files}
+    assert recorded == set(CASES), "fixture file and case list are out of step: re-run tests/golden/make_golden.py"
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if CASES[n]["op"] == "sparsify"])
+def test_sparsify_bit_exact(name):
+    c = CASES[name]
+    prev, delta, mask = c["prev"].clone(), torch.zeros_like(c["x"]), torch.zeros(c["x"].shape[0], 1, *c["x"].shape[2:], dtype=torch.int32)
+    O.sparsify(c["x"], prev, delta, mask, c["thr"])
+    m_ref = gold(name, "mask")
+    assert torch.equal(mask, m_ref)
+    assert torch.equal(prev.float(), gold(name, "prev"))
+    sel = (m_ref != 0).expand_as(delta)
+    assert torch.equal(delta.float()[sel], gold(name, "delta")[sel])
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if CASES[n]["op"] == "act"])
+def test_activation_truncation_bit_exact(name):
+    c = CASES[name]
+    d, p, t, m = c["delta"].clone(), c["prev"].clone(), c["trunc"].clone(), c["mask"].clone()
+    O.activate_truncate(d, p, t, m, c["thr"], c["act"], c["mode"])
+    m_ref = gold(name, "mask")
+    assert torch.equal(m, m_ref)
+    assert torch.equal(p.float(), gold(name, "prev"))
+    assert torch.equal(t.float(), gold(name, "trunc"))
+    sel = (m_ref != 0).expand_as(d)
+    assert torch.equal(d.float()[sel], gold(name, "delta")[sel])
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if CASES[n]["op"] in ("conv", "deconv")])
+def test_convolutions(name):
+    c = CASES[name]
+    if c["op"] == "conv":
+        out, om = O.conv(c["x"], c["mask"], c["w"], c["b"], c["s"], c["p"], (1, 1), c["groups"])
+    else:
+        out, om = O.deconv(c["x"], c["mask"], c["w"], c["b"], c["s"], c["p"])
+    m_ref = gold(name, "mask")
+    assert torch.equal(om, m_ref), "out-mask differs from the reference kernels"
+    close_at(out, gold(name, "out"), m_ref, 1e-4 if name.endswith("f32") else 3e-2)
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if CASES[n]["op"] in ("add", "maxpool", "upsample")])
+def test_other_ops(name):
+    c = CASES[name]
+    if c["op"] == "add":
+        out, om = O.add(c["a"], c["ma"], c["b"], c["mb"], None, c["wa"], c["wb"], c["act"], False)
+    elif c["op"] == "maxpool":
+        out, om = O.max_pool(c["x"], c["mask"], c["prev"], c["k"], c["s"], c["p"])
+    else:
+        out, om = O.upsample(c["x"], c["mask"], c["scale"])
+    m_ref = gold(name, "mask")
+    assert torch.equal(om.view_as(m_ref), m_ref)
+    close_at(out, gold(name, "out"), m_ref, 1e-6 if name.endswith("f32") else 2e-3)
