@@ -393,3 +393,38 @@ def test_pointwise_umma_fused_epilogue_equals_two_kernels(case, act):
     assert torch.equal(p1, p2) and torch.equal(t1, t2)
     sel = (m1 != 0).expand_as(o1)
     assert torch.equal(o1[sel], o2[sel])
+
+
+@pytest.mark.parametrize("c,h,w,s", [(32, 40, 36, 1), (96, 30, 30, 2), (144, 17, 19, 1), (576, 14, 14, 1), (960, 7, 7, 1), (192, 28, 28, 2)])
+@pytest.mark.parametrize("density", [0.05, 0.7])
+def test_depthwise_fused_epilogue_equals_two_kernels(c, h, w, s, density):
+    """fp16 depthwise 3x3 tile kernel with the fused activation/truncation epilogue against the same
+    convolution followed by the stand-alone activation kernel (bit-exact), and against the oracle."""
+    import deltacnn_b200.cuda_kernels as k
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(31)
+    n = 2
+    x = rand_feat(g, n, c, h, w, dtype, 0.3)
+    mask = rand_mask(g, n, h, w, density)
+    mask[:, :, : h // 3, : w // 2] = 0            # some tiles without any active input
+    wt = (torch.randn(c, 1, 3, 3, generator=g) * 0.4).to(dtype)
+    f = convert_filter_out_channels_last(wt).cuda()
+    ho, wo = k.conv_out_hw(h, w, (3, 3), (s, s), (1, 1), (1, 1))
+    prev = rand_feat(g, n, c, ho, wo, dtype, 1.0)
+    trunc = rand_feat(g, n, c, ho, wo, dtype, 0.02)
+    thr = 0.8
+    xd, md = x.cuda(), mask.cuda()
+    xd[(mask == 0).expand_as(x)] = float("nan")
+    o1, m1 = k.sparse_conv(xd, f, md, None, (s, s), (1, 1), (1, 1), c, create_out_mask=True)
+    ref, m_ref = O.conv(x, mask, wt, None, (s, s), (1, 1), (1, 1), c)
+    assert torch.equal(m1.cpu(), m_ref)
+    assert_close_masked(o1, ref, m_ref, dtype, "depthwise tile")
+    p1, t1 = prev.cuda(), trunc.cuda()
+    k.sparse_activation(o1, p1, t1, m1, thr, 2, 0)
+    p2, t2 = prev.cuda(), trunc.cuda()
+    o2, m2 = k.sparse_conv(xd, f, md, None, (s, s), (1, 1), (1, 1), c, create_out_mask=True,
+                           epilogue=k.make_epilogue(p2, t2, thr, 2, 0))
+    assert torch.equal(m1, m2) and torch.equal(p1, p2) and torch.equal(t1, t2)
+    sel = (m1 != 0).expand_as(o1)
+    assert torch.equal(o1[sel], o2[sel])
