@@ -36,6 +36,8 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
 size_t filter_umma_bytes(const dc_conv_desc* d, int transposed);
 int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, void* packed, cudaStream_t st);
 int umma_error_code();
+int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+              int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 int dwconv3x3_tile(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
                    int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 
@@ -81,6 +83,8 @@ int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, 
     if (filter_layout == DC_FILTER_UMMA) return conv2d_umma(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
     if (filter_layout != DC_FILTER_HWIO) return DC_ERR_UNSUPPORTED;
     int rc = dwconv3x3_tile(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
+    if (rc != DC_ERR_UNSUPPORTED) return rc;
+    rc = conv_stem(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;
     rc = conv2d_simt(desc, in, mask_in, filter, bias, out, mask_out, st);
     if (rc != DC_OK) return rc;

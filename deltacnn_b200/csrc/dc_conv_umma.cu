@@ -37,7 +37,7 @@ struct PwParams {
     int64_t npix_out;
     int hi, wi, ho, wo, sh, sw;
     int cin, cout;
-    int nkb, bn, span, b_resident, tmem_cols;
+    int nkb, bn, span, b_resident, tmem_cols, nslots;
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
 
@@ -116,20 +116,22 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 }
 
 // ---- kernel -----------------------------------------------------------------------------------
+// Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
+//                [ row lists ][ mbarriers, scalars, bias ]
 __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
+    uint8_t* sStage = smem;                                        // aliases the A ring (dead once a tile's MMAs are done)
     uint8_t* sB = smem + p.off_b;
-    uint8_t* sStage = smem + p.off_stage;
-    int* s_out = reinterpret_cast<int*>(smem + p.off_list);        // [span] output pixel of every active row
+    int* s_out = reinterpret_cast<int*>(smem + p.off_list);        // [span] output pixel (relative) of every active row
     int* s_in = s_out + p.span;                                    // [span] input pixel of every active row
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_misc);
     // bars[0..kStages)            slot_free   (tcgen05.commit of the MMAs that read stage s)
     // bars[kStages..+16)          b_full      (bulk copy of a filter block landed)
     // bars[kStages+16]            accum_full  (all MMAs of a tile done)
     uint32_t* s_u32 = reinterpret_cast<uint32_t*>(bars + kStages + kMaxResidentKB + 1);
-    // s_u32[0] tmem base, [1] ok flag, [2] running count, [3..6] warp counts
+    // s_u32[0] tmem base, [1] ok flag, [3..7] warp offsets / total
     float* s_bias = reinterpret_cast<float*>(s_u32 + 8);           // [bn]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -142,47 +144,72 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
     const int ncols = min(p.bn, p.cout - n0);                      // real output channels here
     const uint8_t* wimg = p.wimg + (size_t)blockIdx.y * p.nkb * p.bn * 128;
 
-    // ---- compaction of the span's active pixels (order preserved) ----
-    if (tid == 0) s_u32[2] = 0;
-    __syncthreads();
+    // ---- compaction of the span's active pixels, one pass (order preserved) ----
     const int64_t q0 = (int64_t)blockIdx.x * p.span;
+    const int spt = p.span / kPwThreads;                           // consecutive pixels per thread (1..8)
     const int64_t hw_out = (int64_t)p.ho * p.wo;
-    for (int base = 0; base < p.span; base += kPwThreads) {
-        const int64_t q = q0 + base + tid;
-        bool on = false;
-        int pin = 0;
-        if (base + tid < p.span && q < p.npix_out) {
-            if (p.sh == 1 && p.sw == 1) {
-                pin = (int)q;
-            } else {
-                const int64_t b = q / hw_out;
-                const int r = (int)(q - b * hw_out);
-                pin = (int)((b * p.hi + (int64_t)(r / p.wo) * p.sh) * p.wi + (int64_t)(r % p.wo) * p.sw);
+    int pin[8];
+    unsigned bits = 0;
+    {
+        int m[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            m[j] = 0;
+            pin[j] = 0;
+            const int64_t q = q0 + (int64_t)tid * spt + j;
+            if (j < spt && q < p.npix_out) {
+                if (p.sh == 1 && p.sw == 1) {
+                    pin[j] = (int)q;
+                } else {
+                    const int64_t b = q / hw_out;
+                    const int r = (int)(q - b * hw_out);
+                    pin[j] = (int)((b * p.hi + (int64_t)(r / p.wo) * p.sh) * p.wi + (int64_t)(r % p.wo) * p.sw);
+                }
+                m[j] = p.mi[pin[j]];
             }
-            on = p.mi[pin] != 0;
-            if (blockIdx.y == 0 && (!p.fused || !on)) p.mo[q] = on ? 1 : 0;
         }
-        const unsigned bal = __ballot_sync(DC_FULL, on);
-        if (lane == 0) s_u32[3 + warp] = __popc(bal);
-        __syncthreads();
-        int pre = s_u32[2];
-        for (int w = 0; w < warp; ++w) pre += s_u32[3 + w];
-        if (on) {
-            const int slot = pre + __popc(bal & ((1u << lane) - 1u));
-            s_out[slot] = (int)(q - q0);
-            s_in[slot] = pin;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int64_t q = q0 + (int64_t)tid * spt + j;
+            if (j < spt && q < p.npix_out) {
+                if (m[j] != 0) bits |= 1u << j;
+                if (blockIdx.y == 0 && (!p.fused || m[j] == 0)) p.mo[q] = m[j] != 0 ? 1 : 0;
+            }
         }
-        __syncthreads();
-        if (tid == 0) s_u32[2] += s_u32[3] + s_u32[4] + s_u32[5] + s_u32[6];
-        __syncthreads();
     }
-    const int cnt = (int)s_u32[2];
+    const int mine_cnt = __popc(bits);
+    int incl = mine_cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(DC_FULL, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_u32[3 + warp] = incl;
+    __syncthreads();
+    int slot0 = incl - mine_cnt;
+    for (int w = 0; w < warp; ++w) slot0 += s_u32[3 + w];
+    const int cnt = (int)(s_u32[3] + s_u32[4] + s_u32[5] + s_u32[6]);
     if (cnt == 0) return;                 // nothing active in this span: no barriers, no tensor memory
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (bits & (1u << j)) {
+            s_out[slot0] = tid * spt + j;
+            s_in[slot0] = pin[j];
+            ++slot0;
+        }
+    }
 
+    const uint32_t b_block_bytes = (uint32_t)p.bn * 128u;
     if (tid == 0) {
         for (int i = 0; i < kStages + kMaxResidentKB + 1; ++i) mbar_init(bar0 + 8u * i, 1);
         fence_barrier_init();
         s_u32[1] = 1;
+        if (p.b_resident) {               // the whole filter slab of this CTA, one bulk copy per K block
+            for (int kb = 0; kb < p.nkb; ++kb) {
+                mbar_expect_tx(bar_bfull(kb), b_block_bytes);
+                bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + (size_t)kb * b_block_bytes, b_block_bytes, bar_bfull(kb));
+            }
+        }
     }
     for (int i = tid; i < p.bn; i += kPwThreads) s_bias[i] = (p.bias != nullptr && i < ncols) ? __half2float(p.bias[n0 + i]) : 0.f;
     if (warp == 0) tmem_alloc(smem_u32(&s_u32[0]), (uint32_t)p.tmem_cols);
@@ -191,56 +218,64 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
     tc_fence_after();
     const uint32_t tmem_base = s_u32[0];
 
-
     const uint32_t idesc = make_idesc(p.bn);
-    const uint32_t b_block_bytes = (uint32_t)p.bn * 128u;
     const int row_in_pass = tid >> 3, chunk = tid & 7;
     const uint32_t a_thread_off = (uint32_t)((row_in_pass >> 3) * 1024 + (row_in_pass & 7) * 128 + ((chunk ^ (row_in_pass & 7)) << 4));
     int it = 0;                       // global K-block iteration counter (ring position)
     bool ok = true;
 
+    // gather of one K block of one tile into registers: 8 lanes per row, one 16-byte chunk each, 16 rows per pass
+    uint4 v[8];
+    auto gather_load = [&](int t0_, int kb_) {
+        const int cnt_t_ = min(kRows, cnt - t0_);
+        const int kk = kb_ * kKBlock + chunk * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int r = row_in_pass + 16 * j;
+            v[j] = make_uint4(0, 0, 0, 0);
+            if (r < cnt_t_ && kk < p.cin)
+                v[j] = __ldg(reinterpret_cast<const uint4*>(p.in + (int64_t)s_in[t0_ + r] * p.cin + kk));
+        }
+    };
+    __syncthreads();                  // row lists complete
+    gather_load(0, 0);
+
     for (int t0 = 0; t0 < cnt && ok; t0 += kRows) {
         const int cnt_t = min(kRows, cnt - t0);
         const int tile = t0 / kRows;
         for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-            const int slot = it % kStages;
-            const int use = it / kStages;
-            if (use > 0) {            // the stage is being read by MMAs issued kStages iterations ago
+            const int slot = it % p.nslots;
+            const int use = it / p.nslots;
+            if (use > 0) {            // the stage is being read by MMAs issued nslots iterations ago
                 if (tid == 0 && !mbar_wait(bar_slot(slot), (uint32_t)((use - 1) & 1))) { s_u32[1] = 0; atomicExch(&g_umma_error, 1); }
                 __syncthreads();
                 if (s_u32[1] == 0) { ok = false; break; }
             }
-            const bool load_b = p.b_resident ? (tile == 0) : true;
+            const bool load_b = !p.b_resident;
             const int bslot = p.b_resident ? kb : slot;
             if (tid == 0 && load_b) {
                 mbar_expect_tx(bar_bfull(bslot), b_block_bytes);
                 bulk_g2s(smem_u32(sB + (size_t)bslot * b_block_bytes), wimg + (size_t)kb * b_block_bytes, b_block_bytes, bar_bfull(bslot));
             }
-            // gather: 8 lanes per row, one 16-byte chunk each, 16 rows per pass
-            const int kk = kb * kKBlock + chunk * 8;
             const int kleft = p.cin - kb * kKBlock;
             const int ksteps = (min(kleft, kKBlock) + 15) >> 4;
             uint8_t* a_stage = sA + (size_t)slot * kABytes;
             if (chunk < ksteps * 2) {
-                uint4 v[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int r = row_in_pass + 16 * j;
-                    v[j] = make_uint4(0, 0, 0, 0);
-                    if (r < cnt_t && kk < p.cin)
-                        v[j] = __ldg(reinterpret_cast<const uint4*>(p.in + (int64_t)s_in[t0 + r] * p.cin + kk));
-                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int r = row_in_pass + 16 * j;
                     if (r < cnt_t) *reinterpret_cast<uint4*>(a_stage + a_thread_off + j * 2048) = v[j];
                 }
             }
+            // prefetch the next K block (of this tile or of the next one) while this one is multiplied
+            if (kb + 1 < p.nkb) gather_load(t0, kb + 1);
+            else if (t0 + kRows < cnt) gather_load(t0 + kRows, 0);
             fence_proxy_async();
             __syncthreads();
             if (tid == 0) {
                 bool bok = true;
-                if (load_b) bok = mbar_wait(bar_bfull(bslot), p.b_resident ? 0u : (uint32_t)(use & 1));
+                if (load_b) bok = mbar_wait(bar_bfull(bslot), (uint32_t)(use & 1));
+                else if (tile == 0) bok = mbar_wait(bar_bfull(bslot), 0u);
                 if (!bok) { s_u32[1] = 0; atomicExch(&g_umma_error, 2); }
                 else {
                     tc_fence_after();
@@ -282,53 +317,66 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
         tc_fence_before();
         __syncthreads();
 
-        // ---- epilogue 2: coalesced rows; optional accumulate + activation delta + truncation ----
+        // ---- epilogue 2: coalesced rows, kU row groups in flight per warp; optional accumulate +
+        //      activation delta + any-channel truncation against the two caches ----
         {
+            constexpr int kU = 4;
             const int nch = ncols >> 3;                           // 16-byte packs per row
             int g = 1;
             while (g < nch && g < 32) g <<= 1;
             const int lig = lane & (g - 1);
             const int ppw = 32 / g;
-            for (int rb = warp * ppw; rb < kRows; rb += 4 * ppw) {
-                const int r = rb + lane / g;
-                const bool valid = r < cnt_t;
-                const bool mine = valid && lig < nch;
-                const int64_t q = valid ? q0 + s_out[t0 + r] : 0;
-                Pack<__half, 8> d;
-                if (mine) d.load(reinterpret_cast<const __half*>(sStage + (size_t)r * p.stage_pitch) + lig * 8);
-                if (!p.fused) {
-                    if (mine) d.store(p.out + q * p.cout + n0 + lig * 8);
-                    continue;
-                }
-                Pack<__half, 8> y, tr, e;
-                bool hit = false;
-                if (mine) {
-                    const int64_t off = q * p.cout + n0 + lig * 8;
-                    y.load(p.prev + off);
-                    tr.load(p.trunc + off);
+            for (int rb = warp * ppw * kU; rb < cnt_t; rb += 4 * ppw * kU) {
+                Pack<__half, 8> d[kU], y[kU], tr[kU];
+                int64_t off[kU];
+                bool mine[kU];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const float yo = y.get(k);
-                        const float rr = rnd<__half>(tr.get(k) + d.get(k));
-                        const float u = rnd<__half>(yo + rr);
-                        const float ee = rnd<__half>(act_apply(u, p.act) - act_apply(yo, p.act));
-                        tr.set(k, rr); y.set(k, u); e.set(k, ee);
-                        hit |= fabsf(ee) > p.thr;
+                for (int u = 0; u < kU; ++u) {
+                    const int r = rb + u * ppw + lane / g;
+                    mine[u] = r < cnt_t && lig < nch;
+                    off[u] = 0;
+                    if (mine[u]) {
+                        off[u] = (q0 + s_out[t0 + r]) * p.cout + n0 + lig * 8;
+                        d[u].load(reinterpret_cast<const __half*>(sStage + (size_t)r * p.stage_pitch) + lig * 8);
+                        if (p.fused) {
+                            y[u].load(p.prev + off[u]);
+                            tr[u].load(p.trunc + off[u]);
+                        }
                     }
                 }
-                const bool active = group_any(hit, g, lane);
-                if (mine) {
-                    const int64_t off = q * p.cout + n0 + lig * 8;
-                    if (active) {
-                        Pack<__half, 8> z; z.zero();
-                        y.store(p.prev + off);
-                        e.store(p.out + off);
-                        z.store(p.trunc + off);
-                    } else {
-                        tr.store(p.trunc + off);
+#pragma unroll
+                for (int u = 0; u < kU; ++u) {
+                    if (!p.fused) {
+                        if (mine[u]) d[u].store(p.out + off[u]);
+                        continue;
                     }
+                    Pack<__half, 8> e;
+                    bool hit = false;
+                    if (mine[u]) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            const float yo = y[u].get(k);
+                            const float rr = rnd<__half>(tr[u].get(k) + d[u].get(k));
+                            const float uu = rnd<__half>(yo + rr);
+                            const float ee = rnd<__half>(act_apply(uu, p.act) - act_apply(yo, p.act));
+                            tr[u].set(k, rr); y[u].set(k, uu); e.set(k, ee);
+                            hit |= fabsf(ee) > p.thr;
+                        }
+                    }
+                    const bool active = group_any(hit, g, lane);
+                    if (mine[u]) {
+                        if (active) {
+                            Pack<__half, 8> z; z.zero();
+                            y[u].store(p.prev + off[u]);
+                            e.store(p.out + off[u]);
+                            z.store(p.trunc + off[u]);
+                        } else {
+                            tr[u].store(p.trunc + off[u]);
+                        }
+                    }
+                    const int r = rb + u * ppw + lane / g;
+                    if (r < cnt_t && lig == 0) p.mo[q0 + s_out[t0 + r]] = active ? 1 : 0;
                 }
-                if (valid && lig == 0) p.mo[q] = active ? 1 : 0;
             }
         }
         __syncthreads();
@@ -384,10 +432,11 @@ static PwPlan plan_pw(const dc_conv_desc* d) {
     const size_t b_bytes = (pl.b_resident ? pl.nkb : kStages) * b_block;
     pl.span = 1024;
     pl.stage_pitch = (uint32_t)pl.bn * 2 + 16;
-    pl.off_b = kStages * kABytes;
-    pl.off_stage = pl.off_b + (uint32_t)b_bytes;
-    pl.off_list = pl.off_stage + kRows * pl.stage_pitch;
-    pl.off_list = (pl.off_list + 15) & ~15u;
+    const uint32_t ring = (uint32_t)(pl.nkb < kStages ? pl.nkb : kStages) * kABytes;
+    const uint32_t staging = kRows * pl.stage_pitch;
+    pl.off_stage = 0;
+    pl.off_b = ((ring > staging ? ring : staging) + 1023) & ~1023u;
+    pl.off_list = (pl.off_b + (uint32_t)b_bytes + 15) & ~15u;
     pl.img_bytes = (size_t)pl.ntiles * pl.nkb * b_block;
     return pl;
 }
@@ -442,6 +491,7 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     p.hi = d->h_in; p.wi = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.sh = d->stride_h; p.sw = d->stride_w;
     p.cin = d->c_in; p.cout = d->c_out;
     p.nkb = pl.nkb; p.bn = pl.bn; p.span = pl.span; p.b_resident = pl.b_resident; p.tmem_cols = pl.tmem_cols;
+    p.nslots = pl.nkb < kStages ? pl.nkb : kStages;
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_list = pl.off_list; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
     static thread_local bool attr_set = false;
     if (!attr_set) {

@@ -66,6 +66,43 @@ __global__ void __launch_bounds__(256) k_sparsify(const T* __restrict__ x, T* __
     }
 }
 
+// RGB frames (3 channels): a thread owns the run of pixels that fills three 16-byte vectors (8 fp16
+// pixels or 4 fp32 pixels), so the two full reads of the frame are 16-byte accesses; the mask words
+// go out as vectors too and only the (few) active pixels are written back element-wise.
+template <typename T>
+__global__ void __launch_bounds__(256) k_sparsify_c3(const T* __restrict__ x, T* __restrict__ prev, T* __restrict__ delta,
+                                                     int32_t* __restrict__ mask, int64_t npix, float thr) {
+    constexpr int PPT = sizeof(T) == 2 ? 8 : 4;                         // pixels per thread
+    constexpr int NE = PPT * 3;                                         // elements per thread (3 x 16 bytes)
+    const int64_t ngroups = npix / PPT;
+    for (int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gi < ngroups; gi += (int64_t)gridDim.x * blockDim.x) {
+        alignas(16) T xa[NE];
+        alignas(16) T pa[NE];
+        const uint4* xs = reinterpret_cast<const uint4*>(x + gi * NE);
+        const uint4* ps = reinterpret_cast<const uint4*>(prev + gi * NE);
+#pragma unroll
+        for (int i = 0; i < 3; ++i) { reinterpret_cast<uint4*>(xa)[i] = xs[i]; reinterpret_cast<uint4*>(pa)[i] = ps[i]; }
+        alignas(16) int32_t m[PPT];
+#pragma unroll
+        for (int px = 0; px < PPT; ++px) {
+            bool hit = false;
+#pragma unroll
+            for (int c = 0; c < 3; ++c) hit |= fabsf(rnd<T>(to_f<T>(xa[px * 3 + c]) - to_f<T>(pa[px * 3 + c]))) > thr;
+            m[px] = hit ? 1 : 0;
+            if (hit) {
+                const int64_t o = (gi * PPT + px) * 3;
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    delta[o + c] = from_f<T>(to_f<T>(xa[px * 3 + c]) - to_f<T>(pa[px * 3 + c]));
+                    prev[o + c] = xa[px * 3 + c];
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PPT / 4; ++i) reinterpret_cast<int4*>(mask + gi * PPT)[i] = reinterpret_cast<const int4*>(m)[i];
+    }
+}
+
 // 8-bit frame: value = u8 * scale[c] + offset[c], rounded to T before the compare.
 template <typename T>
 __global__ void __launch_bounds__(256) k_sparsify_u8(const uint8_t* __restrict__ x, const float* __restrict__ scale,
@@ -431,6 +468,22 @@ static int sparsify_t(const T* x, T* prev, T* delta, int32_t* mask, int64_t npix
     constexpr int V = VecTraits<T>::kVec;
     const int W = pick_w<T>(C, {x, prev, delta});
     const float t = host_round_threshold<T>(thr);
+    if (C == 3 && aligned16(x) && aligned16(prev) && aligned16(mask)) {
+        constexpr int PPT = sizeof(T) == 2 ? 8 : 4;
+        const int64_t ngroups = npix / PPT;
+        if (ngroups > 0) {
+            int64_t blocks = divup64(ngroups, 256);
+            const int64_t cap = (int64_t)sm_count() * 16;
+            if (blocks > cap) blocks = cap;
+            k_sparsify_c3<T><<<(unsigned)blocks, 256, 0, st>>>(x, prev, delta, mask, npix, t);
+        }
+        const int64_t done = ngroups * PPT;
+        if (done < npix) {      // ragged tail: the generic kernel on the last few pixels
+            const int g = lanes_per_pixel(C);
+            k_sparsify<T, 1><<<1, 256, 0, st>>>(x + done * 3, prev + done * 3, delta + done * 3, mask + done, npix - done, C, g, t);
+        }
+        return check_launch();
+    }
     if (W == V) {
         const int g = lanes_per_pixel(C / V);
         k_sparsify<T, V><<<pixel_grid(npix, g), 256, 0, st>>>(x, prev, delta, mask, npix, C, g, t);

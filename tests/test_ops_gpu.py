@@ -428,3 +428,28 @@ def test_depthwise_fused_epilogue_equals_two_kernels(c, h, w, s, density):
     assert torch.equal(m1, m2) and torch.equal(p1, p2) and torch.equal(t1, t2)
     sel = (m1 != 0).expand_as(o1)
     assert torch.equal(o1[sel], o2[sel])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cout,k,s,p", [(32, 3, 2, 1), (64, 7, 2, 3), (24, 3, 1, 1)])
+def test_stem_conv_fused_epilogue_equals_two_kernels(dtype, cout, k, s, p):
+    import deltacnn_b200.cuda_kernels as kk
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    g = torch.Generator().manual_seed(41)
+    n, h, w = 2, 37, 41
+    x = rand_feat(g, n, 3, h, w, dtype, 0.5).cuda()
+    mask = rand_mask(g, n, h, w, 0.15).cuda()
+    wt = (torch.randn(cout, 3, k, k, generator=g) * 0.3).to(dtype)
+    f = convert_filter_out_channels_last(wt).cuda()
+    ho, wo = kk.conv_out_hw(h, w, (k, k), (s, s), (p, p), (1, 1))
+    prev = rand_feat(g, n, cout, ho, wo, dtype, 1.0)
+    trunc = rand_feat(g, n, cout, ho, wo, dtype, 0.02)
+    o1, m1 = kk.sparse_conv(x, f, mask, None, (s, s), (p, p), (1, 1), 1, create_out_mask=True)
+    p1, t1 = prev.cuda(), trunc.cuda()
+    kk.sparse_activation(o1, p1, t1, m1, 0.9, 2, 0)
+    p2, t2 = prev.cuda(), trunc.cuda()
+    o2, m2 = kk.sparse_conv(x, f, mask, None, (s, s), (p, p), (1, 1), 1, create_out_mask=True, epilogue=kk.make_epilogue(p2, t2, 0.9, 2, 0))
+    assert torch.equal(m1, m2) and torch.equal(p1, p2) and torch.equal(t1, t2)
+    assert 0 < int(m2.sum())
+    sel = (m1 != 0).expand_as(o1)
+    assert torch.equal(o1[sel], o2[sel])
