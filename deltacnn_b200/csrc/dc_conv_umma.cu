@@ -25,9 +25,11 @@ __device__ int g_umma_error = 0;
 constexpr int kRows = 128;            // M of one MMA tile
 constexpr int kKBlock = 64;           // fp16 elements per K block (one 128-byte swizzle row)
 constexpr int kABytes = kRows * 128;  // one A stage
-constexpr int kStages = 3;
+constexpr int kStages = 4;           // shared-memory ring depth
+constexpr int kPrefetch = 3;         // K blocks in flight ahead of the tensor core
 constexpr int kMaxResidentKB = 16;
-constexpr int kPwThreads = 128;
+constexpr int kPwThreads = 256;
+constexpr int kPwWarps = kPwThreads / 32;
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 struct PwParams {
@@ -38,6 +40,7 @@ struct PwParams {
     int hi, wi, ho, wo, sh, sw;
     int cin, cout;
     int nkb, bn, span, b_resident, tmem_cols, nslots;
+    uint32_t b_kb_stride;           // bytes between consecutive K blocks of the packed filter
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
 
@@ -68,6 +71,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// 16-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_pending(int n) {      // at most n groups still in flight
+    if (n <= 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    else if (n == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else asm volatile("cp.async.wait_group 2;" ::: "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -118,7 +131,7 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 // ---- kernel -----------------------------------------------------------------------------------
 // Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
 //                [ row lists ][ mbarriers, scalars, bias ]
-__global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
+__global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
@@ -131,8 +144,8 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
     // bars[kStages..+16)          b_full      (bulk copy of a filter block landed)
     // bars[kStages+16]            accum_full  (all MMAs of a tile done)
     uint32_t* s_u32 = reinterpret_cast<uint32_t*>(bars + kStages + kMaxResidentKB + 1);
-    // s_u32[0] tmem base, [1] ok flag, [3..7] warp offsets / total
-    float* s_bias = reinterpret_cast<float*>(s_u32 + 8);           // [bn]
+    // s_u32[0] tmem base, [1] ok flag, [3..3+warps) warp totals
+    float* s_bias = reinterpret_cast<float*>(s_u32 + 12);          // [bn]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar0 = smem_u32(bars);
@@ -142,11 +155,11 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
 
     const int n0 = blockIdx.y * p.bn;                              // first output channel of this CTA
     const int ncols = min(p.bn, p.cout - n0);                      // real output channels here
-    const uint8_t* wimg = p.wimg + (size_t)blockIdx.y * p.nkb * p.bn * 128;
+    const uint8_t* wimg = p.wimg + (size_t)blockIdx.y * p.bn * 128;   // this CTA's rows inside every K block
 
     // ---- compaction of the span's active pixels, one pass (order preserved) ----
     const int64_t q0 = (int64_t)blockIdx.x * p.span;
-    const int spt = p.span / kPwThreads;                           // consecutive pixels per thread (1..8)
+    const int spt = max(1, p.span / kPwThreads);                   // consecutive pixels per thread (1..8)
     const int64_t hw_out = (int64_t)p.ho * p.wo;
     int pin[8];
     unsigned bits = 0;
@@ -157,7 +170,7 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
             m[j] = 0;
             pin[j] = 0;
             const int64_t q = q0 + (int64_t)tid * spt + j;
-            if (j < spt && q < p.npix_out) {
+            if (j < spt && tid * spt + j < p.span && q < p.npix_out) {
                 if (p.sh == 1 && p.sw == 1) {
                     pin[j] = (int)q;
                 } else {
@@ -171,7 +184,7 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int64_t q = q0 + (int64_t)tid * spt + j;
-            if (j < spt && q < p.npix_out) {
+            if (j < spt && tid * spt + j < p.span && q < p.npix_out) {
                 if (m[j] != 0) bits |= 1u << j;
                 if (blockIdx.y == 0 && (!p.fused || m[j] == 0)) p.mo[q] = m[j] != 0 ? 1 : 0;
             }
@@ -188,7 +201,8 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
     __syncthreads();
     int slot0 = incl - mine_cnt;
     for (int w = 0; w < warp; ++w) slot0 += s_u32[3 + w];
-    const int cnt = (int)(s_u32[3] + s_u32[4] + s_u32[5] + s_u32[6]);
+    int cnt = 0;
+    for (int w = 0; w < kPwWarps; ++w) cnt += (int)s_u32[3 + w];
     if (cnt == 0) return;                 // nothing active in this span: no barriers, no tensor memory
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -207,7 +221,7 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
         if (p.b_resident) {               // the whole filter slab of this CTA, one bulk copy per K block
             for (int kb = 0; kb < p.nkb; ++kb) {
                 mbar_expect_tx(bar_bfull(kb), b_block_bytes);
-                bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + (size_t)kb * b_block_bytes, b_block_bytes, bar_bfull(kb));
+                bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + (size_t)kb * p.b_kb_stride, b_block_bytes, bar_bfull(kb));
             }
         }
     }
@@ -221,70 +235,74 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
     const uint32_t idesc = make_idesc(p.bn);
     const int row_in_pass = tid >> 3, chunk = tid & 7;
     const uint32_t a_thread_off = (uint32_t)((row_in_pass >> 3) * 1024 + (row_in_pass & 7) * 128 + ((chunk ^ (row_in_pass & 7)) << 4));
+    constexpr int kPasses = kRows / (kPwThreads / 8);            // row passes per K block
+    constexpr int kRowsPerPass = kPwThreads / 8;
     int it = 0;                       // global K-block iteration counter (ring position)
     bool ok = true;
 
-    // gather of one K block of one tile into registers: 8 lanes per row, one 16-byte chunk each, 16 rows per pass
-    uint4 v[8];
-    auto gather_load = [&](int t0_, int kb_) {
+    // one K block of one tile: every thread copies its 16-byte chunks of the gathered rows straight into the
+    // swizzled stage (cp.async, zero fill beyond the last input channel); thread 0 adds the filter block when
+    // the filter is streamed. I = global block index (ring position and mbarrier phase derive from it).
+    const int nse = p.nslots;
+    auto issue_block = [&](int t0_, int kb_, int I) {
+        const int slot_ = I % nse;
         const int cnt_t_ = min(kRows, cnt - t0_);
         const int kk = kb_ * kKBlock + chunk * 8;
+        const int ksteps_ = (min(p.cin - kb_ * kKBlock, kKBlock) + 15) >> 4;
+        if (chunk < ksteps_ * 2) {
+            const uint32_t dst0 = smem_u32(sA + (size_t)slot_ * kABytes) + a_thread_off;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int r = row_in_pass + 16 * j;
-            v[j] = make_uint4(0, 0, 0, 0);
-            if (r < cnt_t_ && kk < p.cin)
-                v[j] = __ldg(reinterpret_cast<const uint4*>(p.in + (int64_t)s_in[t0_ + r] * p.cin + kk));
+            for (int j = 0; j < kPasses; ++j) {
+                const int r = row_in_pass + kRowsPerPass * j;
+                if (r < cnt_t_) {
+                    const bool real = kk < p.cin;
+                    const __half* src = real ? p.in + (int64_t)s_in[t0_ + r] * p.cin + kk : p.in;
+                    cp_async16(dst0 + j * (kRowsPerPass / 8) * 1024, src, real ? 16u : 0u);
+                }
+            }
+        }
+        cp_async_commit();
+        if (tid == 0 && !p.b_resident) {
+            mbar_expect_tx(bar_bfull(slot_), b_block_bytes);
+            bulk_g2s(smem_u32(sB + (size_t)slot_ * b_block_bytes), wimg + (size_t)kb_ * p.b_kb_stride, b_block_bytes, bar_bfull(slot_));
         }
     };
     __syncthreads();                  // row lists complete
-    gather_load(0, 0);
 
     for (int t0 = 0; t0 < cnt && ok; t0 += kRows) {
         const int cnt_t = min(kRows, cnt - t0);
         const int tile = t0 / kRows;
-        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-            const int slot = it % p.nslots;
-            const int use = it / p.nslots;
-            if (use > 0) {            // the stage is being read by MMAs issued nslots iterations ago
-                if (tid == 0 && !mbar_wait(bar_slot(slot), (uint32_t)((use - 1) & 1))) { s_u32[1] = 0; atomicExch(&g_umma_error, 1); }
-                __syncthreads();
-                if (s_u32[1] == 0) { ok = false; break; }
-            }
-            const bool load_b = !p.b_resident;
-            const int bslot = p.b_resident ? kb : slot;
-            if (tid == 0 && load_b) {
-                mbar_expect_tx(bar_bfull(bslot), b_block_bytes);
-                bulk_g2s(smem_u32(sB + (size_t)bslot * b_block_bytes), wimg + (size_t)kb * b_block_bytes, b_block_bytes, bar_bfull(bslot));
-            }
-            const int kleft = p.cin - kb * kKBlock;
-            const int ksteps = (min(kleft, kKBlock) + 15) >> 4;
-            uint8_t* a_stage = sA + (size_t)slot * kABytes;
-            if (chunk < ksteps * 2) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int r = row_in_pass + 16 * j;
-                    if (r < cnt_t) *reinterpret_cast<uint4*>(a_stage + a_thread_off + j * 2048) = v[j];
-                }
-            }
-            // prefetch the next K block (of this tile or of the next one) while this one is multiplied
-            if (kb + 1 < p.nkb) gather_load(t0, kb + 1);
-            else if (t0 + kRows < cnt) gather_load(t0 + kRows, 0);
+        const int it0 = tile * p.nkb;
+        // every MMA of the previous tile has completed (accumulator barrier), so the first stages are free
+        for (int d = 0; d < kPrefetch && d < p.nkb; ++d) issue_block(t0, d, it0 + d);
+        for (int kb = 0; kb < p.nkb; ++kb) {
+            const int I = it0 + kb;
+            const int slot = I % nse;
+            cp_async_wait_pending(min(kPrefetch - 1, p.nkb - 1 - kb));
             fence_proxy_async();
             __syncthreads();
+            if (s_u32[1] == 0) { ok = false; break; }
+            const int ksteps = (min(p.cin - kb * kKBlock, kKBlock) + 15) >> 4;
             if (tid == 0) {
                 bool bok = true;
-                if (load_b) bok = mbar_wait(bar_bfull(bslot), (uint32_t)(use & 1));
-                else if (tile == 0) bok = mbar_wait(bar_bfull(bslot), 0u);
+                if (!p.b_resident) bok = mbar_wait(bar_bfull(slot), (uint32_t)((I / nse) & 1));
+                else if (tile == 0) bok = mbar_wait(bar_bfull(kb), 0u);
                 if (!bok) { s_u32[1] = 0; atomicExch(&g_umma_error, 2); }
                 else {
                     tc_fence_after();
-                    const uint64_t ad = make_smem_desc(smem_u32(a_stage));
-                    const uint64_t bd = make_smem_desc(smem_u32(sB + (size_t)bslot * b_block_bytes));
+                    const uint64_t ad = make_smem_desc(smem_u32(sA + (size_t)slot * kABytes));
+                    const uint64_t bd = make_smem_desc(smem_u32(sB + (size_t)(p.b_resident ? kb : slot) * b_block_bytes));
                     for (int ks = 0; ks < ksteps; ++ks)
                         umma_f16(tmem_base, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(bar_slot(slot));
                 }
+            }
+            const int nxt = kb + kPrefetch;
+            if (nxt < p.nkb) {
+                // the stage block `nxt` goes into was last read by the MMAs of block nxt - nse
+                const int Ip = it0 + nxt - nse;
+                if (Ip >= 0 && !mbar_wait(bar_slot((it0 + nxt) % nse), (uint32_t)((Ip / nse) & 1))) { s_u32[1] = 0; atomicExch(&g_umma_error, 1); }
+                issue_block(t0, nxt, it0 + nxt);
             }
         }
         if (!ok) break;
@@ -298,11 +316,12 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
 
         // ---- epilogue 1: tensor memory -> fp16 staging tile (row = TMEM lane) ----
         {
-            const int r = warp * 32 + lane;
+            const int quarter = warp & 3;                          // TMEM lanes a warp may read: 32 * (warp % 4) ...
+            const int r = quarter * 32 + lane;
             uint8_t* srow = sStage + (size_t)r * p.stage_pitch;
-            for (int c0 = 0; c0 < p.bn; c0 += 16) {
+            for (int c0 = (warp >> 2) * 16; c0 < p.bn; c0 += 16 * (kPwWarps / 4)) {
                 uint32_t acc[16];
-                tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, acc);
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, acc);
                 tmem_ld_wait();
                 uint4 o[2];
                 __half2* h = reinterpret_cast<__half2*>(o);
@@ -320,13 +339,13 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
         // ---- epilogue 2: coalesced rows, kU row groups in flight per warp; optional accumulate +
         //      activation delta + any-channel truncation against the two caches ----
         {
-            constexpr int kU = 4;
+            constexpr int kU = 2;
             const int nch = ncols >> 3;                           // 16-byte packs per row
             int g = 1;
             while (g < nch && g < 32) g <<= 1;
             const int lig = lane & (g - 1);
             const int ppw = 32 / g;
-            for (int rb = warp * ppw * kU; rb < cnt_t; rb += 4 * ppw * kU) {
+            for (int rb = warp * ppw * kU; rb < cnt_t; rb += kPwWarps * ppw * kU) {
                 Pack<__half, 8> d[kU], y[kU], tr[kU];
                 int64_t off[kU];
                 bool mine[kU];
@@ -393,26 +412,26 @@ __global__ void __launch_bounds__(kPwThreads) k_pw_umma(PwParams p) {
 }
 
 // ---- filter packing ---------------------------------------------------------------------------
-// HWIO (1,1,cin,cout) fp16 -> per N tile, per K block: bn rows x 64 K values, K-major, 128-byte swizzled.
-__global__ void k_pack_pw(const __half* __restrict__ w, __half* __restrict__ img, int cin, int cout, int bn, int nkb, int ntiles) {
-    const int64_t total = (int64_t)ntiles * nkb * bn * 64;
+// HWIO (1,1,cin,cout) fp16 -> [K block][row = output channel, padded][64 K values], K-major, 128-byte
+// swizzled per 8-row group. An N tile of any width (multiple of 16) is a contiguous run of rows inside
+// every K block, so the launch can choose its N tiling without repacking.
+__global__ void k_pack_pw(const __half* __restrict__ w, __half* __restrict__ img, int cin, int cout, int rows, int nkb) {
+    const int64_t total = (int64_t)nkb * rows * 64;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int e = (int)(i & 7);
         const int cpos = (int)((i >> 3) & 7);       // swizzled chunk position inside the 128-byte row
         const int64_t rowi = i >> 6;
-        const int n = (int)(rowi % bn);
-        const int kb = (int)((rowi / bn) % nkb);
-        const int tile = (int)(rowi / ((int64_t)bn * nkb));
+        const int n = (int)(rowi % rows);
+        const int kb = (int)(rowi / rows);
         const int c = cpos ^ (n & 7);               // logical chunk stored at this position
         const int k = kb * 64 + c * 8 + e;
-        const int co = tile * bn + n;
-        img[i] = (k < cin && n < bn && co < cout && co < (tile + 1) * bn) ? w[(int64_t)k * cout + co] : __float2half(0.f);
+        img[i] = (k < cin && n < cout) ? w[(int64_t)k * cout + n] : __float2half(0.f);
     }
 }
 
 struct PwPlan {
     bool ok;
-    int bn, ntiles, nkb, tmem_cols, b_resident, span;
+    int bn, ntiles, nkb, rows, tmem_cols, b_resident, span, nslots;
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
     size_t smem, img_bytes;
 };
@@ -422,33 +441,46 @@ static PwPlan plan_pw(const dc_conv_desc* d) {
     pl.ok = d->dtype == DC_F16 && d->kh == 1 && d->kw == 1 && d->groups == 1 && d->pad_top == 0 && d->pad_left == 0 &&
             d->pad_bottom == 0 && d->pad_right == 0 && d->c_in % 8 == 0 && d->c_out % 8 == 0 && d->c_in >= 16 && d->c_out >= 16;
     if (!pl.ok) return pl;
+    pl.nkb = divup(d->c_in, kKBlock);
+    pl.rows = divup(d->c_out, 256) * 256 + 256;     // room for a ragged last N tile of any width
+    pl.img_bytes = (size_t)pl.nkb * pl.rows * 128;
+    return pl;
+}
+
+// Launch-time choices: N tiling, span of pixels per CTA, shared-memory layout.
+static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, bool want_fused) {
+    const int sms = sm_count();
     pl.ntiles = divup(d->c_out, 256);
     pl.bn = divup(divup(d->c_out, pl.ntiles), 16) * 16;
-    pl.nkb = divup(d->c_in, kKBlock);
+    // few pixels (deep layers): split the output channels over more CTAs, unless the fused epilogue
+    // needs a pixel's whole channel vector in one CTA
+    if (!(want_fused && pl.ntiles == 1)) {
+        const int64_t pix_ctas = divup64(npix_out, 128);
+        while (pix_ctas * pl.ntiles < 2 * sms && pl.bn > 32) {
+            ++pl.ntiles;
+            pl.bn = divup(divup(d->c_out, pl.ntiles), 16) * 16;
+        }
+        pl.ntiles = divup(d->c_out, pl.bn);
+    }
     pl.tmem_cols = 32;
     while (pl.tmem_cols < pl.bn) pl.tmem_cols <<= 1;
     const size_t b_block = (size_t)pl.bn * 128;
     pl.b_resident = (pl.nkb <= kMaxResidentKB && pl.nkb * b_block <= 64 * 1024) ? 1 : 0;
-    const size_t b_bytes = (pl.b_resident ? pl.nkb : kStages) * b_block;
-    pl.span = 1024;
+    pl.nslots = pl.nkb < kStages ? pl.nkb : kStages;
+    const size_t b_bytes = (pl.b_resident ? pl.nkb : pl.nslots) * b_block;
+    // spans small enough to give every SM several CTAs, large enough to fill an MMA tile when sparse
+    int span = 1024;
+    const int64_t want = (int64_t)sms * 6;
+    while (span > 128 && divup64(npix_out, span) * pl.ntiles < want) span >>= 1;
+    pl.span = span;
     pl.stage_pitch = (uint32_t)pl.bn * 2 + 16;
-    const uint32_t ring = (uint32_t)(pl.nkb < kStages ? pl.nkb : kStages) * kABytes;
+    const uint32_t ring = (uint32_t)pl.nslots * kABytes;
     const uint32_t staging = kRows * pl.stage_pitch;
     pl.off_stage = 0;
     pl.off_b = ((ring > staging ? ring : staging) + 1023) & ~1023u;
     pl.off_list = (pl.off_b + (uint32_t)b_bytes + 15) & ~15u;
-    pl.img_bytes = (size_t)pl.ntiles * pl.nkb * b_block;
-    return pl;
-}
-
-static void finish_plan(PwPlan& pl, int64_t npix_out) {
-    // spans small enough to give every SM a few CTAs, large enough to fill an MMA tile when sparse
-    int span = 1024;
-    const int64_t want = (int64_t)sm_count() * 4;
-    while (span > 128 && divup64(npix_out, span) * pl.ntiles < want) span >>= 1;
-    pl.span = span;
     pl.off_misc = (pl.off_list + 2u * (uint32_t)span * 4u + 15) & ~15u;
-    pl.smem = pl.off_misc + 8 * (kStages + kMaxResidentKB + 1) + 32 + 4 * (size_t)pl.bn + 1024 /* alignment slack */;
+    pl.smem = pl.off_misc + 8 * (kStages + kMaxResidentKB + 1) + 48 + 4 * (size_t)pl.bn + 1024 /* alignment slack */;
 }
 
 size_t filter_umma_bytes(const dc_conv_desc* d, int transposed) {
@@ -465,7 +497,7 @@ int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, vo
     const int64_t total = (int64_t)pl.img_bytes / 2;
     int64_t blocks = divup64(total, 256);
     if (blocks > 4096) blocks = 4096;
-    k_pack_pw<<<(unsigned)blocks, 256, 0, st>>>((const __half*)hwio, (__half*)packed, d->c_in, d->c_out, pl.bn, pl.nkb, pl.ntiles);
+    k_pack_pw<<<(unsigned)blocks, 256, 0, st>>>((const __half*)hwio, (__half*)packed, d->c_in, d->c_out, pl.rows, pl.nkb);
     return check_launch();
 }
 
@@ -477,8 +509,9 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     const int64_t npix_out = (int64_t)d->n * d->h_out * d->w_out;
     if (npix_out == 0) return DC_OK;
     if ((int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
-    finish_plan(pl, npix_out);
-    const bool fused = ep != nullptr && pl.ntiles == 1 && ep->truncation == DC_TRUNC_MAX;
+    const bool want_fused = ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
+    finish_plan(pl, d, npix_out, want_fused);
+    const bool fused = want_fused && pl.ntiles == 1;
     PwParams p{};
     p.in = (const __half*)in; p.mi = mi; p.wimg = (const uint8_t*)filt; p.bias = (const __half*)bias;
     p.out = (__half*)out; p.mo = mo;
@@ -491,7 +524,8 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     p.hi = d->h_in; p.wi = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.sh = d->stride_h; p.sw = d->stride_w;
     p.cin = d->c_in; p.cout = d->c_out;
     p.nkb = pl.nkb; p.bn = pl.bn; p.span = pl.span; p.b_resident = pl.b_resident; p.tmem_cols = pl.tmem_cols;
-    p.nslots = pl.nkb < kStages ? pl.nkb : kStages;
+    p.nslots = pl.nslots;
+    p.b_kb_stride = (uint32_t)pl.rows * 128u;
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_list = pl.off_list; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
     static thread_local bool attr_set = false;
     if (!attr_set) {
