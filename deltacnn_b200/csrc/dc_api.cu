@@ -38,7 +38,7 @@ int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, vo
 int umma_error_code();
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
-int dwconv3x3_tile(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
                    int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 
 static int run_epilogue(const dc_conv_desc* d, void* out, int32_t* mo, const dc_epilogue* ep, void* stream) {
@@ -82,7 +82,7 @@ int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, 
     cudaStream_t st = (cudaStream_t)stream;
     if (filter_layout == DC_FILTER_UMMA) return conv2d_umma(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
     if (filter_layout != DC_FILTER_HWIO) return DC_ERR_UNSUPPORTED;
-    int rc = dwconv3x3_tile(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
+    int rc = dwconv3x3_strip(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;
     rc = conv_stem(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;

@@ -1,0 +1,213 @@
+// Depthwise 3x3 delta convolution fused with the activation/truncation step (fp16), "warp strip" form.
+//
+// A warp owns a strip of 32 consecutive output pixels. Phase 1: lane i ORs the in-mask over the nine
+// taps of pixel i (each mask word is read once per tap by one lane, coalesced) and the warp ballots the
+// active set; strips without an active pixel cost one round of mask loads. Phase 2: the active pixels are
+// handed to aligned lane groups (8 channels per lane and step); a lane reads its 16-byte channel packs of
+// the active taps straight from global memory (neighbouring output pixels share them through L1/L2),
+// multiplies with the filter held in shared memory, accumulates in fp32 and applies the epilogue in
+// registers: plain store, or accumulate + activation delta + any-channel truncation against the two
+// caches. No staging buffers, so occupancy is bounded by registers only.
+#include "dc_common.cuh"
+
+namespace dc {
+
+struct DwStripParams {
+    const __half* in; const int32_t* mi; const __half* w; const __half* bias;
+    __half* out; int32_t* mo; __half* prev; __half* trunc;
+    float thr; int act; int fused;
+    int n, hi, wi, c, ho, wo, s, pt, pl;
+    int strip;          // output pixels per warp and iteration: a multiple of the pixels a warp processes at once, <= 32
+};
+
+template <int NV>   // channel packs per lane: ceil(C / 8 / lanes-per-pixel)
+__global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __half* s_w = reinterpret_cast<__half*>(smem);                    // [9][C]
+    __half* s_b = s_w + 9 * p.c;                                      // [C]
+    const int npk = p.c >> 3;
+    for (int i = threadIdx.x; i < 9 * npk; i += 256)
+        reinterpret_cast<uint4*>(s_w)[i] = __ldg(reinterpret_cast<const uint4*>(p.w) + i);
+    for (int i = threadIdx.x; i < npk; i += 256)
+        reinterpret_cast<uint4*>(s_b)[i] = p.bias ? __ldg(reinterpret_cast<const uint4*>(p.bias) + i) : make_uint4(0, 0, 0, 0);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    int g = 1;
+    while (g < npk && g < 32) g <<= 1;
+    const int lig = lane & (g - 1);
+    const int gi = lane / g;                                          // lane group inside the warp
+    const int ppw = 32 / g;
+    const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
+    const uint32_t warp0 = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const uint32_t nwarps = gridDim.x * 8;
+    for (uint32_t base = warp0 * p.strip; base < npix; base += nwarps * p.strip) {
+        // ---- phase 1: lane = output pixel ----
+        const uint32_t q = base + lane;
+        unsigned taps = 0;                                            // bit t: tap t in bounds and active
+        int oy = 0, ox = 0, b = 0;
+        if (lane < p.strip && q < npix) {
+            ox = (int)(q % (uint32_t)p.wo);
+            const uint32_t t = q / (uint32_t)p.wo;
+            oy = (int)(t % (uint32_t)p.ho);
+            b = (int)(t / (uint32_t)p.ho);
+            const int y0 = oy * p.s - p.pt, x0 = ox * p.s - p.pl;
+            const int32_t* mrow = p.mi + (int64_t)b * p.hi * p.wi;
+#pragma unroll
+            for (int t9 = 0; t9 < 9; ++t9) {
+                const int iy = y0 + t9 / 3, ix = x0 + t9 % 3;
+                if (iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi && mrow[iy * p.wi + ix] != 0) taps |= 1u << t9;
+            }
+            if (!p.fused || taps == 0) p.mo[q] = taps != 0 ? 1 : 0;
+        }
+        unsigned todo = __ballot_sync(DC_FULL, taps != 0);
+        // ---- phase 2: ppw active pixels per round ----
+        while (todo) {
+            unsigned rem = todo;
+            int src = -1;
+            for (int k = 0; k <= gi && rem; ++k) {
+                const int bpos = __ffs(rem) - 1;
+                rem &= rem - 1;
+                if (k == gi) src = bpos;
+            }
+            for (int k = 0; k < ppw && todo; ++k) todo &= todo - 1;
+            const int srcl = src < 0 ? 0 : src;
+            const unsigned tb = __shfl_sync(DC_FULL, taps, srcl);
+            const int soy = __shfl_sync(DC_FULL, oy, srcl), sox = __shfl_sync(DC_FULL, ox, srcl), sb = __shfl_sync(DC_FULL, b, srcl);
+            const bool on = src >= 0;
+            const int y0 = soy * p.s - p.pt, x0 = sox * p.s - p.pl;
+            const __half* img = p.in + (int64_t)sb * p.hi * p.wi * p.c;
+            float acc[NV][8];
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int i = lig + j * g;
+                Pack<__half, 8> bb;
+                bb.zero();
+                if (on && i < npk) bb.load(s_b + i * 8);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[j][k] = bb.get(k);
+            }
+            if (on) {
+#pragma unroll
+                for (int t9 = 0; t9 < 9; ++t9) {
+                    if (!(tb & (1u << t9))) continue;
+                    const __half* px = img + ((int64_t)(y0 + t9 / 3) * p.wi + (x0 + t9 % 3)) * p.c;
+#pragma unroll
+                    for (int j = 0; j < NV; ++j) {
+                        const int i = lig + j * g;
+                        if (i >= npk) continue;
+                        Pack<__half, 8> v, w;
+                        *reinterpret_cast<uint4*>(v.s) = __ldg(reinterpret_cast<const uint4*>(px) + i);
+                        w.load(s_w + t9 * p.c + i * 8);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) acc[j][k] = fmaf(v.get(k), w.get(k), acc[j][k]);
+                    }
+                }
+            }
+            const int64_t qq = (int64_t)base + srcl;
+            const int64_t off = qq * p.c;
+            if (!p.fused) {
+                if (on) {
+#pragma unroll
+                    for (int j = 0; j < NV; ++j) {
+                        const int i = lig + j * g;
+                        if (i >= npk) continue;
+                        Pack<__half, 8> o;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) o.set(k, acc[j][k]);
+                        o.store(p.out + off + i * 8);
+                    }
+                }
+                continue;
+            }
+            Pack<__half, 8> pe[NV], pu[NV], pr[NV];
+            bool hit = false;
+            if (on) {
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const int i = lig + j * g;
+                    if (i >= npk) continue;
+                    pu[j].load(p.prev + off + i * 8);
+                    pr[j].load(p.trunc + off + i * 8);
+                }
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const int i = lig + j * g;
+                    if (i >= npk) continue;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const float yo = pu[j].get(k);
+                        const float rr = rnd<__half>(pr[j].get(k) + rnd<__half>(acc[j][k]));
+                        const float u = rnd<__half>(yo + rr);
+                        const float ee = rnd<__half>(act_apply(u, p.act) - act_apply(yo, p.act));
+                        pr[j].set(k, rr); pu[j].set(k, u); pe[j].set(k, ee);
+                        hit |= fabsf(ee) > p.thr;
+                    }
+                }
+            }
+            const bool active = group_any(hit, g, lane);
+            if (!on) continue;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int i = lig + j * g;
+                if (i >= npk) continue;
+                if (active) {
+                    Pack<__half, 8> z; z.zero();
+                    pu[j].store(p.prev + off + i * 8);
+                    pe[j].store(p.out + off + i * 8);
+                    z.store(p.trunc + off + i * 8);
+                } else {
+                    pr[j].store(p.trunc + off + i * 8);
+                }
+            }
+            if (lig == 0) p.mo[qq] = active ? 1 : 0;
+        }
+    }
+}
+
+// Depthwise 3x3 (stride 1 or 2, dilation 1) in fp16 with in- and out-mask; DC_ERR_UNSUPPORTED tells the
+// caller to use the generic kernels.
+int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+                    int32_t* mo, const dc_epilogue* ep, cudaStream_t st) {
+    const bool ok = d->dtype == DC_F16 && d->kh == 3 && d->kw == 3 && d->dil_h == 1 && d->dil_w == 1 &&
+                    d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) && d->groups == d->c_in &&
+                    d->c_in == d->c_out && d->c_in % 8 == 0 && d->c_in <= 1024 && mi != nullptr && mo != nullptr &&
+                    aligned16(in) && aligned16(out) && aligned16(filt) && (bias == nullptr || aligned16(bias)) &&
+                    (ep == nullptr || (ep->truncation == DC_TRUNC_MAX && aligned16(ep->prev_out) && aligned16(ep->truncated)));
+    if (!ok) return DC_ERR_UNSUPPORTED;
+    const int64_t npix = (int64_t)d->n * d->h_out * d->w_out;
+    if (npix == 0) return DC_OK;
+    if (npix > 0x7fffffffLL || (int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
+    DwStripParams p{};
+    p.in = (const __half*)in; p.mi = mi; p.w = (const __half*)filt; p.bias = (const __half*)bias;
+    p.out = (__half*)out; p.mo = mo;
+    p.fused = ep != nullptr;
+    p.prev = p.fused ? (__half*)ep->prev_out : nullptr;
+    p.trunc = p.fused ? (__half*)ep->truncated : nullptr;
+    p.thr = p.fused ? host_round_threshold<__half>(ep->threshold) : 0.f;
+    p.act = p.fused ? ep->activation : 0;
+    p.n = d->n; p.hi = d->h_in; p.wi = d->w_in; p.c = d->c_in; p.ho = d->h_out; p.wo = d->w_out; p.s = d->stride_h;
+    p.pt = d->pad_top; p.pl = d->pad_left;
+    const int npk = p.c / 8;
+    const int nv = divup(npk, 32);
+    const size_t smem = (size_t)10 * p.c * 2;
+    // wide pixels keep a whole warp busy, so give every warp few of them; narrow pixels share a warp
+    int g = 1;
+    while (g < npk && g < 32) g <<= 1;
+    const int ppw = 32 / g;
+    int strip = 32;
+    while (strip > ppw && divup64(npix, strip) < (int64_t)sm_count() * 64) strip >>= 1;
+    p.strip = strip;
+    int64_t blocks = divup64(divup64(npix, strip), 8);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    switch (nv) {
+        case 1: k_dw3x3_strip<1><<<(unsigned)blocks, 256, smem, st>>>(p); break;
+        case 2: k_dw3x3_strip<2><<<(unsigned)blocks, 256, smem, st>>>(p); break;
+        case 3: k_dw3x3_strip<3><<<(unsigned)blocks, 256, smem, st>>>(p); break;
+        default: k_dw3x3_strip<4><<<(unsigned)blocks, 256, smem, st>>>(p); break;
+    }
+    return check_launch();
+}
+
+}  // namespace dc
