@@ -32,14 +32,15 @@ int deconv2d_simt(const dc_conv_desc* d, const void* in, const int32_t* mi, cons
                   int32_t* mo, cudaStream_t st);
 // tensor-core kernels (dc_conv_umma.cu); return DC_ERR_UNSUPPORTED when the shape has none
 int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
-                int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
+                int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t filter_umma_bytes(const dc_conv_desc* d, int transposed);
 int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, void* packed, cudaStream_t st);
 int umma_error_code();
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
-                   int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
+                    int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st);
+size_t conv_workspace_bytes(const dc_conv_desc* d);
 
 static int run_epilogue(const dc_conv_desc* d, void* out, int32_t* mo, const dc_epilogue* ep, void* stream) {
     if (ep == nullptr) return DC_OK;
@@ -74,15 +75,18 @@ int dc_last_cuda_error(void) { return t_last_cuda_error; }
 
 int dc_umma_error(void) { return umma_error_code(); }
 
-int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
-              const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream) {
+int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
+                 const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* workspace,
+                 size_t workspace_bytes, void* stream) {
     if (desc == nullptr || in == nullptr || filter == nullptr || out == nullptr) return DC_ERR_NULL_POINTER;
     if (epilogue != nullptr && (epilogue->prev_out == nullptr || (epilogue->truncation >= 0 && epilogue->truncated == nullptr)))
         return DC_ERR_NULL_POINTER;
+    if (workspace != nullptr && workspace_bytes < conv_workspace_bytes(desc)) return DC_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
-    if (filter_layout == DC_FILTER_UMMA) return conv2d_umma(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
+    if (filter_layout == DC_FILTER_UMMA)
+        return conv2d_umma(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
     if (filter_layout != DC_FILTER_HWIO) return DC_ERR_UNSUPPORTED;
-    int rc = dwconv3x3_strip(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
+    int rc = dwconv3x3_strip(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;
     rc = conv_stem(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;
@@ -90,6 +94,13 @@ int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, 
     if (rc != DC_OK) return rc;
     return run_epilogue(desc, out, mask_out, epilogue, stream);
 }
+
+int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
+              const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream) {
+    return dc_conv2d_ws(desc, in, mask_in, filter, filter_layout, bias, out, mask_out, epilogue, nullptr, 0, stream);
+}
+
+size_t dc_conv_workspace_bytes(const dc_conv_desc* desc) { return desc == nullptr ? 0 : conv_workspace_bytes(desc); }
 
 int dc_deconv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
                 const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream) {

@@ -41,6 +41,8 @@ struct PwParams {
     int cin, cout;
     int nkb, bn, span, b_resident, tmem_cols, nslots;
     uint32_t b_kb_stride;           // bytes between consecutive K blocks of the packed filter
+    const int32_t* wl_count;        // work-list mode (else nullptr): number of active output pixels
+    const uint32_t* wl_list;        //   and their indices, written by k_scan_conv_mask
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
 
@@ -158,9 +160,15 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     const uint8_t* wimg = p.wimg + (size_t)blockIdx.y * p.bn * 128;   // this CTA's rows inside every K block
 
     // ---- compaction of the span's active pixels, one pass (order preserved) ----
-    const int64_t q0 = (int64_t)blockIdx.x * p.span;
-    const int spt = max(1, p.span / kPwThreads);                   // consecutive pixels per thread (1..8)
+    const bool list_mode = p.wl_list != nullptr;
     const int64_t hw_out = (int64_t)p.ho * p.wo;
+    const int64_t q0 = list_mode ? 0 : (int64_t)blockIdx.x * p.span;
+    int cnt = 0;
+    if (list_mode) {
+        cnt = *p.wl_count;
+        if ((int64_t)blockIdx.x * kRows >= cnt) return;            // persistent CTAs beyond the work
+    } else {
+    const int spt = max(1, p.span / kPwThreads);                   // consecutive pixels per thread (1..8)
     int pin[8];
     unsigned bits = 0;
     {
@@ -201,7 +209,6 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     __syncthreads();
     int slot0 = incl - mine_cnt;
     for (int w = 0; w < warp; ++w) slot0 += s_u32[3 + w];
-    int cnt = 0;
     for (int w = 0; w < kPwWarps; ++w) cnt += (int)s_u32[3 + w];
     if (cnt == 0) return;                 // nothing active in this span: no barriers, no tensor memory
 #pragma unroll
@@ -212,6 +219,7 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
             ++slot0;
         }
     }
+    }   // span mode
 
     const uint32_t b_block_bytes = (uint32_t)p.bn * 128u;
     if (tid == 0) {
@@ -244,9 +252,8 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     // swizzled stage (cp.async, zero fill beyond the last input channel); thread 0 adds the filter block when
     // the filter is streamed. I = global block index (ring position and mbarrier phase derive from it).
     const int nse = p.nslots;
-    auto issue_block = [&](int t0_, int kb_, int I) {
+    auto issue_block = [&](int t0_, int cnt_t_, int kb_, int I) {
         const int slot_ = I % nse;
-        const int cnt_t_ = min(kRows, cnt - t0_);
         const int kk = kb_ * kKBlock + chunk * 8;
         const int ksteps_ = (min(p.cin - kb_ * kKBlock, kKBlock) + 15) >> 4;
         if (chunk < ksteps_ * 2) {
@@ -269,12 +276,32 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     };
     __syncthreads();                  // row lists complete
 
-    for (int t0 = 0; t0 < cnt && ok; t0 += kRows) {
-        const int cnt_t = min(kRows, cnt - t0);
-        const int tile = t0 / kRows;
+    // span mode: the tiles of this CTA's own list; list mode: every gridDim.x-th tile of the global list
+    const int tile_first = list_mode ? (int)blockIdx.x : 0;
+    const int tile_step = list_mode ? (int)gridDim.x : 1;
+    const int tiles_total = (cnt + kRows - 1) / kRows;
+    int tile = 0;                     // tiles processed by this CTA (mbarrier phases count these)
+    for (int tg = tile_first; tg < tiles_total && ok; tg += tile_step, ++tile) {
+        const int cnt_t = min(kRows, cnt - tg * kRows);
+        const int t0 = list_mode ? 0 : tg * kRows;                  // offset of the tile's rows in the shared lists
+        if (list_mode) {
+            __syncthreads();                                        // previous tile's epilogue has read the lists
+            for (int r = tid; r < cnt_t; r += kPwThreads) {
+                const uint32_t q = p.wl_list[(size_t)tg * kRows + r];
+                s_out[r] = (int)q;
+                int pin_ = (int)q;
+                if (p.sh != 1 || p.sw != 1) {
+                    const uint32_t b = q / (uint32_t)hw_out;
+                    const uint32_t rr = q - b * (uint32_t)hw_out;
+                    pin_ = (int)((b * p.hi + (rr / p.wo) * p.sh) * p.wi + (rr % p.wo) * p.sw);
+                }
+                s_in[r] = pin_;
+            }
+            __syncthreads();
+        }
         const int it0 = tile * p.nkb;
         // every MMA of the previous tile has completed (accumulator barrier), so the first stages are free
-        for (int d = 0; d < kPrefetch && d < p.nkb; ++d) issue_block(t0, d, it0 + d);
+        for (int d = 0; d < kPrefetch && d < p.nkb; ++d) issue_block(t0, cnt_t, d, it0 + d);
         for (int kb = 0; kb < p.nkb; ++kb) {
             const int I = it0 + kb;
             const int slot = I % nse;
@@ -302,7 +329,7 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
                 // the stage block `nxt` goes into was last read by the MMAs of block nxt - nse
                 const int Ip = it0 + nxt - nse;
                 if (Ip >= 0 && !mbar_wait(bar_slot((it0 + nxt) % nse), (uint32_t)((Ip / nse) & 1))) { s_u32[1] = 0; atomicExch(&g_umma_error, 1); }
-                issue_block(t0, nxt, it0 + nxt);
+                issue_block(t0, cnt_t, nxt, it0 + nxt);
             }
         }
         if (!ok) break;
@@ -448,7 +475,7 @@ static PwPlan plan_pw(const dc_conv_desc* d) {
 }
 
 // Launch-time choices: N tiling, span of pixels per CTA, shared-memory layout.
-static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, bool want_fused) {
+static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, bool want_fused, bool list_mode) {
     const int sms = sm_count();
     pl.ntiles = divup(d->c_out, 256);
     pl.bn = divup(divup(d->c_out, pl.ntiles), 16) * 16;
@@ -472,6 +499,7 @@ static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, boo
     int span = 1024;
     const int64_t want = (int64_t)sms * 6;
     while (span > 128 && divup64(npix_out, span) * pl.ntiles < want) span >>= 1;
+    if (list_mode) span = kRows;      // the shared row lists hold one tile
     pl.span = span;
     pl.stage_pitch = (uint32_t)pl.bn * 2 + 16;
     const uint32_t ring = (uint32_t)pl.nslots * kABytes;
@@ -501,8 +529,10 @@ int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, vo
     return check_launch();
 }
 
+int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
+
 int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
-                int32_t* mo, const dc_epilogue* ep, cudaStream_t st) {
+                int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
     PwPlan pl = plan_pw(d);
     if (!pl.ok || mi == nullptr || mo == nullptr) return DC_ERR_UNSUPPORTED;
     if (!aligned16(in) || !aligned16(out) || !aligned16(filt)) return DC_ERR_ALIGNMENT;
@@ -510,7 +540,7 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     if (npix_out == 0) return DC_OK;
     if ((int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
     const bool want_fused = ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
-    finish_plan(pl, d, npix_out, want_fused);
+    finish_plan(pl, d, npix_out, want_fused, ws != nullptr);
     const bool fused = want_fused && pl.ntiles == 1;
     PwParams p{};
     p.in = (const __half*)in; p.mi = mi; p.wimg = (const uint8_t*)filt; p.bias = (const __half*)bias;
@@ -534,6 +564,15 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     }
     if (pl.smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
     dim3 grid((unsigned)divup64(npix_out, pl.span), (unsigned)pl.ntiles);
+    if (ws != nullptr) {              // work-list mode: scan pass, then persistent CTAs over the active rows
+        int rc = scan_conv_mask(d, mi, mo, ws, ws_bytes, fused ? 1 : 0, st);
+        if (rc != DC_OK) return rc;
+        p.wl_count = reinterpret_cast<const int32_t*>(ws);
+        p.wl_list = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(ws) + 16);
+        int64_t persistent = (int64_t)sm_count() * 4 / pl.ntiles;
+        if (persistent < 1) persistent = 1;
+        if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
+    }
     k_pw_umma<<<grid, kPwThreads, pl.smem, st>>>(p);
     int rc = check_launch();
     if (rc != DC_OK) return rc;

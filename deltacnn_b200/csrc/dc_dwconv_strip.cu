@@ -20,6 +20,135 @@ struct DwStripParams {
     int strip;          // output pixels per warp and iteration: a multiple of the pixels a warp processes at once, <= 32
 };
 
+// One output pixel per aligned lane group: depthwise taps -> fp32 accumulators -> epilogue in registers.
+// Must be called by all 32 lanes of a warp (the any-channel decision ballots across the warp).
+template <int NV>
+__device__ __forceinline__ void dw_pixel(const DwStripParams& p, const __half* s_w, const __half* s_b, bool on, unsigned tb,
+                                         int64_t qq, int sb, int soy, int sox, int lig, int g, int npk, int lane) {
+    const int y0 = soy * p.s - p.pt, x0 = sox * p.s - p.pl;
+    const __half* img = p.in + (int64_t)sb * p.hi * p.wi * p.c;
+    float acc[NV][8];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = lig + j * g;
+        Pack<__half, 8> bb;
+        bb.zero();
+        if (on && i < npk) bb.load(s_b + i * 8);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[j][k] = bb.get(k);
+    }
+    if (on) {
+#pragma unroll
+        for (int t9 = 0; t9 < 9; ++t9) {
+            if (!(tb & (1u << t9))) continue;
+            const __half* px = img + ((int64_t)(y0 + t9 / 3) * p.wi + (x0 + t9 % 3)) * p.c;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int i = lig + j * g;
+                if (i >= npk) continue;
+                Pack<__half, 8> v, w;
+                *reinterpret_cast<uint4*>(v.s) = __ldg(reinterpret_cast<const uint4*>(px) + i);
+                w.load(s_w + t9 * p.c + i * 8);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[j][k] = fmaf(v.get(k), w.get(k), acc[j][k]);
+            }
+        }
+    }
+    const int64_t off = qq * p.c;
+    if (!p.fused) {
+        if (on) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int i = lig + j * g;
+                if (i >= npk) continue;
+                Pack<__half, 8> o;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o.set(k, acc[j][k]);
+                o.store(p.out + off + i * 8);
+            }
+        }
+        return;
+    }
+    Pack<__half, 8> pe[NV], pu[NV], pr[NV];
+    bool hit = false;
+    if (on) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = lig + j * g;
+            if (i >= npk) continue;
+            pu[j].load(p.prev + off + i * 8);
+            pr[j].load(p.trunc + off + i * 8);
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = lig + j * g;
+            if (i >= npk) continue;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float yo = pu[j].get(k);
+                const float rr = rnd<__half>(pr[j].get(k) + rnd<__half>(acc[j][k]));
+                const float u = rnd<__half>(yo + rr);
+                const float ee = rnd<__half>(act_apply(u, p.act) - act_apply(yo, p.act));
+                pr[j].set(k, rr); pu[j].set(k, u); pe[j].set(k, ee);
+                hit |= fabsf(ee) > p.thr;
+            }
+        }
+    }
+    const bool active = group_any(hit, g, lane);
+    if (!on) return;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = lig + j * g;
+        if (i >= npk) continue;
+        if (active) {
+            Pack<__half, 8> z; z.zero();
+            pu[j].store(p.prev + off + i * 8);
+            pe[j].store(p.out + off + i * 8);
+            z.store(p.trunc + off + i * 8);
+        } else {
+            pr[j].store(p.trunc + off + i * 8);
+        }
+    }
+    if (lig == 0) p.mo[qq] = active ? 1 : 0;
+}
+
+// List-driven form: persistent warps pull active output pixels from the work list written by
+// k_scan_conv_mask, so the active set is spread evenly over the SMs however it clusters in the image.
+template <int NV>
+__global__ void __launch_bounds__(256) k_dw3x3_list(DwStripParams p, const int32_t* __restrict__ count,
+                                                    const uint32_t* __restrict__ list, const uint32_t* __restrict__ taps) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __half* s_w = reinterpret_cast<__half*>(smem);                    // [9][C]
+    __half* s_b = s_w + 9 * p.c;                                      // [C]
+    const int cnt = *count;
+    if (cnt == 0) return;
+    const int npk = p.c >> 3;
+    for (int i = threadIdx.x; i < 9 * npk; i += 256)
+        reinterpret_cast<uint4*>(s_w)[i] = __ldg(reinterpret_cast<const uint4*>(p.w) + i);
+    for (int i = threadIdx.x; i < npk; i += 256)
+        reinterpret_cast<uint4*>(s_b)[i] = p.bias ? __ldg(reinterpret_cast<const uint4*>(p.bias) + i) : make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    int g = 1;
+    while (g < npk && g < 32) g <<= 1;
+    const int lig = lane & (g - 1);
+    const int gi = lane / g;
+    const int ppw = 32 / g;
+    const int warp0 = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int nwarps = gridDim.x * 8;
+    for (int r = warp0 * ppw; r < cnt; r += nwarps * ppw) {
+        const int idx = r + gi;
+        const bool on = idx < cnt;
+        const uint32_t q = on ? list[idx] : 0u;
+        const unsigned tb = on ? taps[idx] : 0u;
+        const int ox = (int)(q % (uint32_t)p.wo);
+        const uint32_t t = q / (uint32_t)p.wo;
+        const int oy = (int)(t % (uint32_t)p.ho);
+        const int b = (int)(t / (uint32_t)p.ho);
+        dw_pixel<NV>(p, s_w, s_b, on, tb, (int64_t)q, b, oy, ox, lig, g, npk, lane);
+    }
+}
+
 template <int NV>   // channel packs per lane: ceil(C / 8 / lanes-per-pixel)
 __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -74,101 +203,17 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
             const int srcl = src < 0 ? 0 : src;
             const unsigned tb = __shfl_sync(DC_FULL, taps, srcl);
             const int soy = __shfl_sync(DC_FULL, oy, srcl), sox = __shfl_sync(DC_FULL, ox, srcl), sb = __shfl_sync(DC_FULL, b, srcl);
-            const bool on = src >= 0;
-            const int y0 = soy * p.s - p.pt, x0 = sox * p.s - p.pl;
-            const __half* img = p.in + (int64_t)sb * p.hi * p.wi * p.c;
-            float acc[NV][8];
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int i = lig + j * g;
-                Pack<__half, 8> bb;
-                bb.zero();
-                if (on && i < npk) bb.load(s_b + i * 8);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) acc[j][k] = bb.get(k);
-            }
-            if (on) {
-#pragma unroll
-                for (int t9 = 0; t9 < 9; ++t9) {
-                    if (!(tb & (1u << t9))) continue;
-                    const __half* px = img + ((int64_t)(y0 + t9 / 3) * p.wi + (x0 + t9 % 3)) * p.c;
-#pragma unroll
-                    for (int j = 0; j < NV; ++j) {
-                        const int i = lig + j * g;
-                        if (i >= npk) continue;
-                        Pack<__half, 8> v, w;
-                        *reinterpret_cast<uint4*>(v.s) = __ldg(reinterpret_cast<const uint4*>(px) + i);
-                        w.load(s_w + t9 * p.c + i * 8);
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) acc[j][k] = fmaf(v.get(k), w.get(k), acc[j][k]);
-                    }
-                }
-            }
-            const int64_t qq = (int64_t)base + srcl;
-            const int64_t off = qq * p.c;
-            if (!p.fused) {
-                if (on) {
-#pragma unroll
-                    for (int j = 0; j < NV; ++j) {
-                        const int i = lig + j * g;
-                        if (i >= npk) continue;
-                        Pack<__half, 8> o;
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) o.set(k, acc[j][k]);
-                        o.store(p.out + off + i * 8);
-                    }
-                }
-                continue;
-            }
-            Pack<__half, 8> pe[NV], pu[NV], pr[NV];
-            bool hit = false;
-            if (on) {
-#pragma unroll
-                for (int j = 0; j < NV; ++j) {
-                    const int i = lig + j * g;
-                    if (i >= npk) continue;
-                    pu[j].load(p.prev + off + i * 8);
-                    pr[j].load(p.trunc + off + i * 8);
-                }
-#pragma unroll
-                for (int j = 0; j < NV; ++j) {
-                    const int i = lig + j * g;
-                    if (i >= npk) continue;
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const float yo = pu[j].get(k);
-                        const float rr = rnd<__half>(pr[j].get(k) + rnd<__half>(acc[j][k]));
-                        const float u = rnd<__half>(yo + rr);
-                        const float ee = rnd<__half>(act_apply(u, p.act) - act_apply(yo, p.act));
-                        pr[j].set(k, rr); pu[j].set(k, u); pe[j].set(k, ee);
-                        hit |= fabsf(ee) > p.thr;
-                    }
-                }
-            }
-            const bool active = group_any(hit, g, lane);
-            if (!on) continue;
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int i = lig + j * g;
-                if (i >= npk) continue;
-                if (active) {
-                    Pack<__half, 8> z; z.zero();
-                    pu[j].store(p.prev + off + i * 8);
-                    pe[j].store(p.out + off + i * 8);
-                    z.store(p.trunc + off + i * 8);
-                } else {
-                    pr[j].store(p.trunc + off + i * 8);
-                }
-            }
-            if (lig == 0) p.mo[qq] = active ? 1 : 0;
+            dw_pixel<NV>(p, s_w, s_b, src >= 0, tb, (int64_t)base + srcl, sb, soy, sox, lig, g, npk, lane);
         }
     }
 }
 
 // Depthwise 3x3 (stride 1 or 2, dilation 1) in fp16 with in- and out-mask; DC_ERR_UNSUPPORTED tells the
 // caller to use the generic kernels.
+int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
+
 int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
-                    int32_t* mo, const dc_epilogue* ep, cudaStream_t st) {
+                    int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
     const bool ok = d->dtype == DC_F16 && d->kh == 3 && d->kw == 3 && d->dil_h == 1 && d->dil_w == 1 &&
                     d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) && d->groups == d->c_in &&
                     d->c_in == d->c_out && d->c_in % 8 == 0 && d->c_in <= 1024 && mi != nullptr && mo != nullptr &&
@@ -191,6 +236,22 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     const int npk = p.c / 8;
     const int nv = divup(npk, 32);
     const size_t smem = (size_t)10 * p.c * 2;
+    if (ws != nullptr) {            // work-list form: one scan pass, then persistent warps over the active pixels
+        int rc = scan_conv_mask(d, mi, mo, ws, ws_bytes, p.fused, st);
+        if (rc != DC_OK) return rc;
+        const int32_t* count = reinterpret_cast<const int32_t*>(ws);
+        const uint32_t* list = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(ws) + 16);
+        const uint32_t* taps = list + npix;
+        const size_t smem_l = (size_t)10 * p.c * 2;
+        const unsigned grid = (unsigned)sm_count() * (nv >= 3 ? 2 : 4);
+        switch (nv) {
+            case 1: k_dw3x3_list<1><<<grid, 256, smem_l, st>>>(p, count, list, taps); break;
+            case 2: k_dw3x3_list<2><<<grid, 256, smem_l, st>>>(p, count, list, taps); break;
+            case 3: k_dw3x3_list<3><<<grid, 256, smem_l, st>>>(p, count, list, taps); break;
+            default: k_dw3x3_list<4><<<grid, 256, smem_l, st>>>(p, count, list, taps); break;
+        }
+        return check_launch();
+    }
     // wide pixels keep a whole warp busy, so give every warp few of them; narrow pixels share a warp
     int g = 1;
     while (g < npk && g < 32) g <<= 1;

@@ -1,0 +1,95 @@
+// Active-pixel work list of a convolution: one light pass dilates the in-mask by the receptive field,
+// writes the out-mask and appends every active output pixel (with the bit set of its active taps) to a
+// compacted list in caller-provided scratch memory. The convolution kernels then size their work by the
+// list (persistent CTAs pulling entries), so inactive regions cost one coalesced mask read and the active
+// pixels are spread evenly over the SMs however they cluster in the image.
+//
+// Scratch layout (dc_conv_workspace_bytes): [0] int32 count, [4..16) padding, then npix_out uint32 pixel
+// indices, then npix_out uint32 tap bit sets.
+#include "dc_common.cuh"
+
+namespace dc {
+
+struct ScanParams {
+    const int32_t* mi; int32_t* mo; int32_t* count; uint32_t* list; uint32_t* taps;
+    int n, hi, wi, ho, wo, kh, kw, sh, sw, pt, pl, dh, dw;
+    int defer_active;      // fused epilogue: the out-mask of active pixels is written by the epilogue
+};
+
+__global__ void __launch_bounds__(256) k_scan_conv_mask(ScanParams p) {
+    __shared__ int s_warp[8];
+    __shared__ int s_base;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
+    for (uint32_t start = blockIdx.x * 256u; start < npix; start += gridDim.x * 256u) {
+        const uint32_t q = start + threadIdx.x;
+        unsigned bits = 0;
+        if (q < npix) {
+            const int ox = (int)(q % (uint32_t)p.wo);
+            const uint32_t t = q / (uint32_t)p.wo;
+            const int oy = (int)(t % (uint32_t)p.ho);
+            const int b = (int)(t / (uint32_t)p.ho);
+            const int32_t* m = p.mi + (int64_t)b * p.hi * p.wi;
+            if (p.kh == 1 && p.kw == 1) {
+                const int iy = oy * p.sh - p.pt, ix = ox * p.sw - p.pl;
+                if (iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi && m[iy * p.wi + ix] != 0) bits = 1u;
+            } else {
+                for (int ky = 0; ky < p.kh; ++ky) {
+                    const int iy = oy * p.sh - p.pt + ky * p.dh;
+                    if (iy < 0 || iy >= p.hi) continue;
+                    for (int kx = 0; kx < p.kw; ++kx) {
+                        const int ix = ox * p.sw - p.pl + kx * p.dw;
+                        if (ix < 0 || ix >= p.wi) continue;
+                        if (m[iy * p.wi + ix] != 0) bits |= 1u << ((ky * p.kw + kx) & 31);
+                    }
+                }
+            }
+            if (!p.defer_active || bits == 0) p.mo[q] = bits != 0 ? 1 : 0;
+        }
+        const unsigned bal = __ballot_sync(DC_FULL, bits != 0);
+        if (lane == 0) s_warp[warp] = __popc(bal);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { const int c = s_warp[i]; s_warp[i] = tot; tot += c; }
+            s_base = tot ? atomicAdd(p.count, tot) : 0;
+        }
+        __syncthreads();
+        if (bits) {
+            const int slot = s_base + s_warp[warp] + __popc(bal & ((1u << lane) - 1u));
+            p.list[slot] = q;
+            p.taps[slot] = bits;
+        }
+        __syncthreads();
+    }
+}
+
+size_t conv_workspace_bytes(const dc_conv_desc* d) {
+    const int64_t npix = (int64_t)d->n * d->h_out * d->w_out;
+    return 16 + (size_t)npix * 8;
+}
+
+// Fills the work list for `d`; taps beyond 32 per pixel are not representable (kernels up to 5x5).
+int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active,
+                   cudaStream_t st) {
+    const int64_t npix = (int64_t)d->n * d->h_out * d->w_out;
+    if (ws == nullptr || ws_bytes < conv_workspace_bytes(d)) return DC_ERR_WORKSPACE;
+    if (npix > 0x7fffffffLL || d->kh * d->kw > 32) return DC_ERR_UNSUPPORTED;
+    ScanParams p{};
+    p.mi = mi; p.mo = mo;
+    p.count = reinterpret_cast<int32_t*>(ws);
+    p.list = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ws) + 16);
+    p.taps = p.list + npix;
+    p.n = d->n; p.hi = d->h_in; p.wi = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.kh = d->kh; p.kw = d->kw;
+    p.sh = d->stride_h; p.sw = d->stride_w; p.pt = d->pad_top; p.pl = d->pad_left; p.dh = d->dil_h; p.dw = d->dil_w;
+    p.defer_active = defer_active;
+    if (cudaMemsetAsync(ws, 0, 16, st) != cudaSuccess) return check_launch();
+    int64_t blocks = divup64(npix, 256);
+    const int64_t cap = (int64_t)sm_count() * 32;
+    if (blocks > cap) blocks = cap;
+    k_scan_conv_mask<<<(unsigned)blocks, 256, 0, st>>>(p);
+    return check_launch();
+}
+
+}  // namespace dc

@@ -76,6 +76,11 @@ def conv_out_hw(h, w, kernel, stride, padding, dilation):
     return out_h, out_w
 
 
+def conv_workspace_bytes(desc):
+    """Scratch bytes the work-list kernels want for this geometry."""
+    return int(lib.dc_conv_workspace_bytes(desc))
+
+
 def make_epilogue(prev_out, truncated, threshold, activation, truncation_mode):
     e = Epilogue()
     e.prev_out = _ptr(prev_out)
@@ -88,12 +93,13 @@ def make_epilogue(prev_out, truncated, threshold, activation, truncation_mode):
 
 def sparse_conv(x, filter, mask=None, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, c_out: int = None,
                 create_out_mask=False, sub_tile_sparsity=True, out_mask=None, out_shape=None, out=None,
-                filter_umma=None, epilogue=None, desc=None):
+                filter_umma=None, epilogue=None, desc=None, workspace=None):
     """Delta convolution (reference: cuda_kernels.py:13-45). Returns ``out`` or ``(out, out_mask)``.
 
     ``out`` / ``out_mask`` may be passed to reuse buffers; ``filter_umma`` is the packed
     tensor-core image of the same filter (optional); ``epilogue`` a ``make_epilogue`` result
-    fusing activation + truncation; ``desc`` a cached ``make_conv_desc`` result.
+    fusing activation + truncation; ``desc`` a cached ``make_conv_desc`` result; ``workspace`` a uint8
+    scratch tensor of at least ``conv_workspace_bytes(desc)`` bytes enabling the work-list kernels.
     """
     _check_feature(x, "x")
     _check_mask(mask, x, "mask")
@@ -117,8 +123,12 @@ def sparse_conv(x, filter, mask=None, bias=None, stride=(1, 1), padding=(0, 0), 
         filt, layout = filter, _lib.DC_FILTER_HWIO
         if filter.dtype != x.dtype:
             raise RuntimeError("deltacnn_b200.sparse_conv: filter dtype differs from input dtype")
-    check(lib.dc_conv2d(desc, x.data_ptr(), _ptr(mask), filt.data_ptr(), layout, _ptr(bias), out.data_ptr(), _ptr(out_mask),
-                        epilogue, _stream()), "sparse_conv")
+    if workspace is not None and mask is not None and out_mask is not None:
+        check(lib.dc_conv2d_ws(desc, x.data_ptr(), _ptr(mask), filt.data_ptr(), layout, _ptr(bias), out.data_ptr(),
+                               _ptr(out_mask), epilogue, workspace.data_ptr(), workspace.numel(), _stream()), "sparse_conv")
+    else:
+        check(lib.dc_conv2d(desc, x.data_ptr(), _ptr(mask), filt.data_ptr(), layout, _ptr(bias), out.data_ptr(), _ptr(out_mask),
+                            epilogue, _stream()), "sparse_conv")
     if create_out_mask and mask is not None:
         return out, out_mask
     return out

@@ -204,6 +204,7 @@ class _DeltaConvMixin:
         self._out = None
         self._desc = None
         self._epilogue = None
+        self._workspace = None
         self.fuse_activation = True
         assert kwargs.get("leaky_relu_negative_slope", 0.1) == 0.1, "Leaky ReLU implementation uses hard coded negative slope of 0.1"
 
@@ -261,7 +262,7 @@ class _DeltaConvMixin:
             # resolution or batch change: forget the cached geometry and buffers
             self.in_shape = x.shape
             self.out_shape = []
-            self._out = self.out_mask = self._desc = None
+            self._out = self.out_mask = self._desc = self._workspace = None
 
         epilogue = None
         act = self.activation_layer
@@ -277,7 +278,11 @@ class _DeltaConvMixin:
             self._desc = K.make_conv_desc(tuple(x.shape), self.out_channels, hw, tuple(self.kernel_size), self.stride,
                                           self.padding, self.dilation, self.groups, K._dtype(x))
         op = K.sparse_deconv if self._transposed else K.sparse_conv
-        extra = {} if self._transposed else {"filter_umma": self.weight_umma}
+        extra = {}
+        if not self._transposed:
+            if DCConv2d.use_worklist and self._workspace is None and self.frame_idx > 0:
+                self._workspace = torch.empty(K.conv_workspace_bytes(self._desc), dtype=torch.uint8, device=x.device)
+            extra = {"filter_umma": self.weight_umma, "workspace": self._workspace if self.frame_idx > 0 else None}
         out, out_mask = op(
             x=x, filter=self.weight, mask=mask, bias=self.bias if self.frame_idx <= 0 else None, stride=self.stride,
             padding=self.padding, dilation=self.dilation, groups=self.groups, c_out=self.out_channels, create_out_mask=True,
@@ -304,6 +309,7 @@ class _DeltaConvMixin:
         self.out_shape = []
         self._out = None
         self._desc = None
+        self._workspace = None
         DCConv2d.conv_idx = -1
         DCConv2d.n_dense_output, DCConv2d.n_sparse_output = 0, 0
         DCConv2d.n_dense_inputs, DCConv2d.n_sparse_inputs = 0, 0
@@ -358,6 +364,7 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
     flops_sum = 0
     measure_flops = False
     reuse_buffers = True      # keep per-layer output buffers across frames
+    use_worklist = True       # steady-state frames: active-pixel work lists in per-layer scratch memory
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1, groups: int = 1,
                  bias: bool = True, padding_mode: str = "zeros", delta_threshold: float = None, name: str = None,

@@ -105,6 +105,21 @@ int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in,
               const void* filter, int32_t filter_layout, const void* bias,
               void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream);
 
+/* Scratch bytes dc_conv2d_ws wants for this geometry (16 + 8 bytes per output pixel). */
+size_t dc_conv_workspace_bytes(const dc_conv_desc* desc);
+
+/* dc_conv2d with caller-provided scratch memory for the active-pixel work list: a light pass
+ * writes the out-mask and compacts the active output pixels into `workspace`, and the convolution
+ * kernel then sizes its work by that list (persistent CTAs), which is what makes sparse frames
+ * cheap however the active pixels cluster. Same results as dc_conv2d. The scratch is only
+ * meaningful during the call; calls on different streams need different scratch. Shapes without a
+ * list-driven kernel fall back to dc_conv2d. No reference counterpart (the reference re-derives
+ * activity inside every tile, src/cuda/conv_kernel.cu:46-108). */
+int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_in,
+                 const void* filter, int32_t filter_layout, const void* bias,
+                 void* out, int32_t* mask_out, const dc_epilogue* epilogue,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
 /* Delta transposed convolution (4x4 stride 2, 6x6 stride 4 and any k = m*stride, groups 1).
  * Replaces sparse_deconv_bias_wrapper_masked (src/cuda/conv_torch_wrapper.cpp:136-210 ->
  * delta_deconv / delta_deconv_hp, src/cuda/deconv_kernel.cu:854-932). Filter HWIO:

@@ -453,3 +453,45 @@ def test_stem_conv_fused_epilogue_equals_two_kernels(dtype, cout, k, s, p):
     assert 0 < int(m2.sum())
     sel = (m1 != 0).expand_as(o1)
     assert torch.equal(o1[sel], o2[sel])
+
+
+@pytest.mark.parametrize("kind,cin,cout,h,w,s", [("pw", 16, 96, 40, 44, 1), ("pw", 144, 24, 28, 28, 1), ("pw", 960, 320, 7, 7, 1), ("pw", 64, 384, 14, 14, 1),
+                                                  ("pw", 256, 512, 16, 16, 2), ("dw", 96, 96, 40, 44, 2), ("dw", 32, 32, 50, 50, 1), ("dw", 960, 960, 7, 7, 1)])
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("density", [0.0, 0.1, 1.0])
+def test_worklist_kernels_equal_the_plain_ones(kind, cin, cout, h, w, s, fused, density):
+    """dc_conv2d_ws (active-pixel work list in caller scratch) must give exactly what dc_conv2d gives."""
+    import deltacnn_b200.cuda_kernels as k
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(51)
+    n = 3
+    x = rand_feat(g, n, cin, h, w, dtype, 0.3).cuda()
+    mask = rand_mask(g, n, h, w, density)
+    mask[0, :, : h // 2] = 0
+    mask = mask.cuda()
+    groups = cin if kind == "dw" else 1
+    ksz, pad = (3, 1) if kind == "dw" else (1, 0)
+    wt = (torch.randn(cout, cin // groups, ksz, ksz, generator=g) * (0.4 if kind == "dw" else cin ** -0.5)).to(dtype)
+    f = convert_filter_out_channels_last(wt).cuda()
+    packed = _pack_umma(f, cin, cout, s) if kind == "pw" else None
+    ho, wo = k.conv_out_hw(h, w, (ksz, ksz), (s, s), (pad, pad), (1, 1))
+    prev = rand_feat(g, n, cout, ho, wo, dtype, 1.0)
+    trunc = rand_feat(g, n, cout, ho, wo, dtype, 0.02)
+    desc = k.make_conv_desc(tuple(x.shape), cout, (ho, wo), (ksz, ksz), (s, s), (pad, pad), (1, 1), groups, 1)
+    ws = torch.full((k.conv_workspace_bytes(desc) + 64,), 0xAB, dtype=torch.uint8, device="cuda")
+    res = []
+    for workspace in (None, ws):
+        p_, t_ = prev.cuda(), trunc.cuda()
+        ep = k.make_epilogue(p_, t_, 0.7, 2, 0) if fused else None
+        out = torch.full((n, cout, ho, wo), float("nan"), dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last)
+        o, m = k.sparse_conv(x, f, mask, None, (s, s), (pad, pad), (1, 1), groups, create_out_mask=True, out=out,
+                             filter_umma=packed, epilogue=ep, workspace=workspace)
+        res.append((o.clone(), m.clone(), p_, t_))
+    assert _lib.lib.dc_umma_error() == 0
+    (o1, m1, p1, t1), (o2, m2, p2, t2) = res
+    assert torch.equal(m1, m2) and torch.equal(p1, p2) and torch.equal(t1, t2)
+    sel = (m1 != 0).expand_as(o1)
+    assert torch.equal(o1[sel], o2[sel])
+    assert torch.isnan(o2[~sel]).all()
