@@ -93,3 +93,49 @@ int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* 
 }
 
 }  // namespace dc
+
+// ---------------------------------------------------------------------------------------------
+// Entry point for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library may not call cudaMalloc at all: a plugin that runs inside another
+// application's fixed device-memory budget, or a real-time loop that must stay away from the allocator
+// (and its implicit synchronisation) once it has started. dc_conv2d_ws wants scratch memory for its work
+// list; dc_conv2d_static keeps that scratch in the image of this library instead: a fixed array in device
+// global memory that every GPU loading the library holds until the process exits.
+namespace dc {
+
+constexpr size_t kStaticWsBytes = 16 + 8u * 524288u;      // work lists of up to 524288 output pixels (4 MiB)
+static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
+
+// In host code `g_static_ws` is only a stand-in for the symbol; the device address has to be asked for,
+// per device, with that device current.
+static void* static_ws_address(int* err) {
+    constexpr int kMaxDevices = 64;
+    static void* cached[kMaxDevices] = {};
+    *err = DC_OK;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { *err = DC_ERR_LAUNCH; return nullptr; }
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_ws) != cudaSuccess || ptr == nullptr) { (void)check_launch(); *err = DC_ERR_LAUNCH; return nullptr; }
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+
+}  // namespace dc
+
+extern "C" size_t dc_static_workspace_max_pixels(void) { return (dc::kStaticWsBytes - 16) / 8; }
+
+extern "C" int dc_conv2d_static(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter,
+                                int32_t filter_layout, const void* bias, void* out, int32_t* mask_out,
+                                const dc_epilogue* epilogue, void* stream) {
+    if (desc == nullptr) return DC_ERR_NULL_POINTER;
+    const int64_t npix = (int64_t)desc->n * desc->h_out * desc->w_out;
+    if (npix < 0) return DC_ERR_SHAPE;
+    if ((uint64_t)npix > dc_static_workspace_max_pixels()) return DC_ERR_WORKSPACE;   // more output pixels than the built-in scratch holds
+    int err = DC_OK;
+    void* ws = dc::static_ws_address(&err);
+    if (ws == nullptr) return err;
+    return dc_conv2d_ws(desc, in, mask_in, filter, filter_layout, bias, out, mask_out, epilogue, ws, dc::kStaticWsBytes, stream);
+}

@@ -120,6 +120,23 @@ int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_i
                  void* out, int32_t* mask_out, const dc_epilogue* epilogue,
                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* dc_conv2d_ws without any allocation on the caller's side or inside the library. No counterpart in the
+ * reference. It exists for hosts that are not allowed to allocate device memory when they call: a
+ * plugin that lives inside another application's fixed device-memory budget, or a control loop that
+ * must stay away from the allocator (and the synchronisation it implies) once it runs. The work-list scratch
+ * is a fixed array inside this library's device image (4 MiB per GPU that loads the library, held until
+ * the process exits), so the call handles at most dc_static_workspace_max_pixels() = 524288 output
+ * pixels (n*h_out*w_out) and returns DC_ERR_WORKSPACE beyond that. The first call on a device looks up
+ * the array's device address (cudaGetSymbolAddress, with that device current); make that first call
+ * before any stream capture. All calls share the one array, which keeps the previous call's list: the
+ * counter is cleared at the start of every call, and two calls that overlap on the GPU (different
+ * streams, or different threads) race on it -- serialise them or use dc_conv2d_ws with separate scratch.
+ * Results are those of dc_conv2d. */
+int dc_conv2d_static(const dc_conv_desc* desc, const void* in, const int32_t* mask_in,
+                     const void* filter, int32_t filter_layout, const void* bias,
+                     void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream);
+size_t dc_static_workspace_max_pixels(void);
+
 /* Delta transposed convolution (4x4 stride 2, 6x6 stride 4 and any k = m*stride, groups 1).
  * Replaces sparse_deconv_bias_wrapper_masked (src/cuda/conv_torch_wrapper.cpp:136-210 ->
  * delta_deconv / delta_deconv_hp, src/cuda/deconv_kernel.cu:854-932). Filter HWIO:
