@@ -88,3 +88,56 @@ class MultiBranchStep:
             self.load(frames)
         self.graph.replay()
         return self.static_out
+
+
+class PipelinedStep:
+    """End-to-end stepping from host memory: two input buffers and two captured graphs of the same model,
+    so that the host->device copy of frame t+1 (on a copy stream) overlaps the delta step of frame t, and
+    the result of frame t is copied back to pinned host memory behind it. The model must be warmed up
+    (first frame and one steady-state frame done) before construction."""
+
+    def __init__(self, model, example_input, compute_stream):
+        self.compute = compute_stream
+        self.copy = torch.cuda.Stream()
+        self.inputs = [example_input.clone(), example_input.clone()]
+        self.graphs, self.outputs = [], []
+        torch.cuda.synchronize()
+        pool = None
+        with torch.no_grad():
+            for buf in self.inputs:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=torch.cuda.Stream(), pool=pool):
+                    out = model(buf)
+                pool = g.pool()
+                self.graphs.append(g)
+                self.outputs.append(out)
+        self.host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in self.outputs]
+        self.copied = [torch.cuda.Event(), torch.cuda.Event()]
+        self.consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        for e in self.consumed:
+            e.record(self.compute)
+        self.uploaded = 0      # frames uploaded so far
+        self.stepped = 0       # frames processed so far
+
+    def upload(self, host_frame):
+        """Start the upload of the next frame (at most one frame ahead of step())."""
+        assert self.uploaded - self.stepped < 2
+        i = self.uploaded % 2
+        self.copy.wait_event(self.consumed[i])            # the graph that last read this buffer is done
+        with torch.cuda.stream(self.copy):
+            self.inputs[i].copy_(host_frame, non_blocking=True)
+            self.copied[i].record(self.copy)
+        self.uploaded += 1
+
+    def step(self):
+        """Run the delta step on the oldest uploaded frame; returns the pinned host tensor the result is
+        being copied to (valid once the compute stream has been synchronised)."""
+        assert self.stepped < self.uploaded
+        i = self.stepped % 2
+        self.compute.wait_event(self.copied[i])
+        with torch.cuda.stream(self.compute):
+            self.graphs[i].replay()
+            self.consumed[i].record(self.compute)
+            self.host_out[i].copy_(self.outputs[i], non_blocking=True)
+        self.stepped += 1
+        return self.host_out[i]
