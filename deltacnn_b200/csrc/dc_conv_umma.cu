@@ -38,11 +38,14 @@ struct PwParams {
     float thr; int act; int fused;
     int64_t npix_out;
     int hi, wi, ho, wo, sh, sw;
+    int kh, kw, dh, dw, pt, pl;     // kernel geometry; taps = kh * kw (K runs tap-major, then input channels)
+    int taps, ncb;                  // ncb = K blocks of 64 input channels per tap; nkb = taps * ncb
     int cin, cout;
     int nkb, bn, span, b_resident, tmem_cols, nslots;
     uint32_t b_kb_stride;           // bytes between consecutive K blocks of the packed filter
     const int32_t* wl_count;        // work-list mode (else nullptr): number of active output pixels
-    const uint32_t* wl_list;        //   and their indices, written by k_scan_conv_mask
+    const uint32_t* wl_list;        //   their indices
+    const uint32_t* wl_taps;        //   and the bit sets of their active taps, written by k_scan_conv_mask
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
 
@@ -140,7 +143,7 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     uint8_t* sStage = smem;                                        // aliases the A ring (dead once a tile's MMAs are done)
     uint8_t* sB = smem + p.off_b;
     int* s_out = reinterpret_cast<int*>(smem + p.off_list);        // [span] output pixel (relative) of every active row
-    int* s_in = s_out + p.span;                                    // [span] input pixel of every active row
+    int* s_in = s_out + p.span;                                    // [span][taps] input pixel of every (active row, tap), -1 = inactive or out of bounds
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_misc);
     // bars[0..kStages)            slot_free   (tcgen05.commit of the MMAs that read stage s)
     // bars[kStages..+16)          b_full      (bulk copy of a filter block landed)
@@ -254,16 +257,18 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     const int nse = p.nslots;
     auto issue_block = [&](int t0_, int cnt_t_, int kb_, int I) {
         const int slot_ = I % nse;
-        const int kk = kb_ * kKBlock + chunk * 8;
-        const int ksteps_ = (min(p.cin - kb_ * kKBlock, kKBlock) + 15) >> 4;
+        const int tap_ = kb_ / p.ncb, cb_ = kb_ - tap_ * p.ncb;
+        const int kk = cb_ * kKBlock + chunk * 8;
+        const int ksteps_ = (min(p.cin - cb_ * kKBlock, kKBlock) + 15) >> 4;
         if (chunk < ksteps_ * 2) {
             const uint32_t dst0 = smem_u32(sA + (size_t)slot_ * kABytes) + a_thread_off;
 #pragma unroll
             for (int j = 0; j < kPasses; ++j) {
                 const int r = row_in_pass + kRowsPerPass * j;
                 if (r < cnt_t_) {
-                    const bool real = kk < p.cin;
-                    const __half* src = real ? p.in + (int64_t)s_in[t0_ + r] * p.cin + kk : p.in;
+                    const int pin_ = s_in[(t0_ + r) * p.taps + tap_];
+                    const bool real = kk < p.cin && pin_ >= 0;
+                    const __half* src = real ? p.in + (int64_t)pin_ * p.cin + kk : p.in;
                     cp_async16(dst0 + j * (kRowsPerPass / 8) * 1024, src, real ? 16u : 0u);
                 }
             }
@@ -288,14 +293,19 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
             __syncthreads();                                        // previous tile's epilogue has read the lists
             for (int r = tid; r < cnt_t; r += kPwThreads) {
                 const uint32_t q = p.wl_list[(size_t)tg * kRows + r];
+                const uint32_t tb = p.wl_taps[(size_t)tg * kRows + r];
                 s_out[r] = (int)q;
-                int pin_ = (int)q;
-                if (p.sh != 1 || p.sw != 1) {
-                    const uint32_t b = q / (uint32_t)hw_out;
-                    const uint32_t rr = q - b * (uint32_t)hw_out;
-                    pin_ = (int)((b * p.hi + (rr / p.wo) * p.sh) * p.wi + (rr % p.wo) * p.sw);
+                const uint32_t b = q / (uint32_t)hw_out;
+                const uint32_t rr = q - b * (uint32_t)hw_out;
+                const int oy = (int)(rr / (uint32_t)p.wo), ox = (int)(rr % (uint32_t)p.wo);
+                for (int t = 0; t < p.taps; ++t) {
+                    int pin_ = -1;
+                    if (tb & (1u << t)) {
+                        const int iy = oy * p.sh - p.pt + (t / p.kw) * p.dh, ix = ox * p.sw - p.pl + (t % p.kw) * p.dw;
+                        pin_ = (int)((b * p.hi + iy) * p.wi + ix);
+                    }
+                    s_in[r * p.taps + t] = pin_;
                 }
-                s_in[r] = pin_;
             }
             __syncthreads();
         }
@@ -309,7 +319,7 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
             fence_proxy_async();
             __syncthreads();
             if (s_u32[1] == 0) { ok = false; break; }
-            const int ksteps = (min(p.cin - kb * kKBlock, kKBlock) + 15) >> 4;
+            const int ksteps = (min(p.cin - (kb % p.ncb) * kKBlock, kKBlock) + 15) >> 4;
             if (tid == 0) {
                 bool bok = true;
                 if (!p.b_resident) bok = mbar_wait(bar_bfull(slot), (uint32_t)((I / nse) & 1));
@@ -442,33 +452,36 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
 // HWIO (1,1,cin,cout) fp16 -> [K block][row = output channel, padded][64 K values], K-major, 128-byte
 // swizzled per 8-row group. An N tile of any width (multiple of 16) is a contiguous run of rows inside
 // every K block, so the launch can choose its N tiling without repacking.
-__global__ void k_pack_pw(const __half* __restrict__ w, __half* __restrict__ img, int cin, int cout, int rows, int nkb) {
-    const int64_t total = (int64_t)nkb * rows * 64;
+__global__ void k_pack_pw(const __half* __restrict__ w, __half* __restrict__ img, int cin, int cout, int rows, int taps, int ncb) {
+    const int64_t total = (int64_t)taps * ncb * rows * 64;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int e = (int)(i & 7);
         const int cpos = (int)((i >> 3) & 7);       // swizzled chunk position inside the 128-byte row
         const int64_t rowi = i >> 6;
         const int n = (int)(rowi % rows);
-        const int kb = (int)(rowi / rows);
+        const int kb = (int)(rowi / rows);          // K block = (tap, block of 64 input channels)
+        const int tap = kb / ncb, cb = kb - tap * ncb;
         const int c = cpos ^ (n & 7);               // logical chunk stored at this position
-        const int k = kb * 64 + c * 8 + e;
-        img[i] = (k < cin && n < cout) ? w[(int64_t)k * cout + n] : __float2half(0.f);
+        const int k = cb * 64 + c * 8 + e;          // input channel
+        img[i] = (k < cin && n < cout) ? w[((int64_t)tap * cin + k) * cout + n] : __float2half(0.f);
     }
 }
 
 struct PwPlan {
     bool ok;
-    int bn, ntiles, nkb, rows, tmem_cols, b_resident, span, nslots;
+    int bn, ntiles, nkb, ncb, taps, rows, tmem_cols, b_resident, span, nslots;
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
     size_t smem, img_bytes;
 };
 
 static PwPlan plan_pw(const dc_conv_desc* d) {
     PwPlan pl{};
-    pl.ok = d->dtype == DC_F16 && d->kh == 1 && d->kw == 1 && d->groups == 1 && d->pad_top == 0 && d->pad_left == 0 &&
-            d->pad_bottom == 0 && d->pad_right == 0 && d->c_in % 8 == 0 && d->c_out % 8 == 0 && d->c_in >= 16 && d->c_out >= 16;
+    pl.taps = d->kh * d->kw;
+    pl.ok = d->dtype == DC_F16 && d->groups == 1 && pl.taps <= 25 && d->c_in % 8 == 0 && d->c_out % 8 == 0 &&
+            d->c_in >= 16 && d->c_out >= 16;
     if (!pl.ok) return pl;
-    pl.nkb = divup(d->c_in, kKBlock);
+    pl.ncb = divup(d->c_in, kKBlock);
+    pl.nkb = pl.taps * pl.ncb;
     pl.rows = divup(d->c_out, 256) * 256 + 256;     // room for a ragged last N tile of any width
     pl.img_bytes = (size_t)pl.nkb * pl.rows * 128;
     return pl;
@@ -507,7 +520,7 @@ static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, boo
     pl.off_stage = 0;
     pl.off_b = ((ring > staging ? ring : staging) + 1023) & ~1023u;
     pl.off_list = (pl.off_b + (uint32_t)b_bytes + 15) & ~15u;
-    pl.off_misc = (pl.off_list + 2u * (uint32_t)span * 4u + 15) & ~15u;
+    pl.off_misc = (pl.off_list + (1u + (uint32_t)pl.taps) * (uint32_t)span * 4u + 15) & ~15u;
     pl.smem = pl.off_misc + 8 * (kStages + kMaxResidentKB + 1) + 48 + 4 * (size_t)pl.bn + 1024 /* alignment slack */;
 }
 
@@ -525,7 +538,7 @@ int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, vo
     const int64_t total = (int64_t)pl.img_bytes / 2;
     int64_t blocks = divup64(total, 256);
     if (blocks > 4096) blocks = 4096;
-    k_pack_pw<<<(unsigned)blocks, 256, 0, st>>>((const __half*)hwio, (__half*)packed, d->c_in, d->c_out, pl.rows, pl.nkb);
+    k_pack_pw<<<(unsigned)blocks, 256, 0, st>>>((const __half*)hwio, (__half*)packed, d->c_in, d->c_out, pl.rows, pl.taps, pl.ncb);
     return check_launch();
 }
 
@@ -535,6 +548,8 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
                 int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
     PwPlan pl = plan_pw(d);
     if (!pl.ok || mi == nullptr || mo == nullptr) return DC_ERR_UNSUPPORTED;
+    // without scratch for a work list only 1x1 kernels (no receptive field to dilate) have a tensor-core path
+    if (ws == nullptr && (pl.taps != 1 || d->pad_top != 0 || d->pad_left != 0)) return DC_ERR_UNSUPPORTED;
     if (!aligned16(in) || !aligned16(out) || !aligned16(filt)) return DC_ERR_ALIGNMENT;
     const int64_t npix_out = (int64_t)d->n * d->h_out * d->w_out;
     if (npix_out == 0) return DC_OK;
@@ -553,6 +568,8 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     p.npix_out = npix_out;
     p.hi = d->h_in; p.wi = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.sh = d->stride_h; p.sw = d->stride_w;
     p.cin = d->c_in; p.cout = d->c_out;
+    p.kh = d->kh; p.kw = d->kw; p.dh = d->dil_h; p.dw = d->dil_w; p.pt = d->pad_top; p.pl = d->pad_left;
+    p.taps = pl.taps; p.ncb = pl.ncb;
     p.nkb = pl.nkb; p.bn = pl.bn; p.span = pl.span; p.b_resident = pl.b_resident; p.tmem_cols = pl.tmem_cols;
     p.nslots = pl.nslots;
     p.b_kb_stride = (uint32_t)pl.rows * 128u;
@@ -569,6 +586,7 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
         if (rc != DC_OK) return rc;
         p.wl_count = reinterpret_cast<const int32_t*>(ws);
         p.wl_list = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(ws) + 16);
+        p.wl_taps = p.wl_list + npix_out;
         int64_t persistent = (int64_t)sm_count() * 4 / pl.ntiles;
         if (persistent < 1) persistent = 1;
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;

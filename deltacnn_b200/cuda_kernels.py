@@ -123,12 +123,16 @@ def sparse_conv(x, filter, mask=None, bias=None, stride=(1, 1), padding=(0, 0), 
         filt, layout = filter, _lib.DC_FILTER_HWIO
         if filter.dtype != x.dtype:
             raise RuntimeError("deltacnn_b200.sparse_conv: filter dtype differs from input dtype")
-    if workspace is not None and mask is not None and out_mask is not None:
-        check(lib.dc_conv2d_ws(desc, x.data_ptr(), _ptr(mask), filt.data_ptr(), layout, _ptr(bias), out.data_ptr(),
-                               _ptr(out_mask), epilogue, workspace.data_ptr(), workspace.numel(), _stream()), "sparse_conv")
-    else:
-        check(lib.dc_conv2d(desc, x.data_ptr(), _ptr(mask), filt.data_ptr(), layout, _ptr(bias), out.data_ptr(), _ptr(out_mask),
-                            epilogue, _stream()), "sparse_conv")
+    ws_ptr, ws_len = (workspace.data_ptr(), workspace.numel()) if (workspace is not None and mask is not None and out_mask is not None) else (None, 0)
+    status = lib.dc_conv2d_ws(desc, x.data_ptr(), _ptr(mask), filt.data_ptr(), layout, _ptr(bias), out.data_ptr(), _ptr(out_mask),
+                              epilogue, ws_ptr, ws_len, _stream())
+    if status == 2 and layout == _lib.DC_FILTER_UMMA:
+        # no tensor-core kernel for this call (e.g. a KxK filter without scratch): CUDA-core kernel, same result
+        if filter.dtype != x.dtype:
+            raise RuntimeError("deltacnn_b200.sparse_conv: filter dtype differs from input dtype")
+        status = lib.dc_conv2d_ws(desc, x.data_ptr(), _ptr(mask), filter.data_ptr(), _lib.DC_FILTER_HWIO, _ptr(bias), out.data_ptr(),
+                                  _ptr(out_mask), epilogue, ws_ptr, ws_len, _stream())
+    check(status, "sparse_conv")
     if create_out_mask and mask is not None:
         return out, out_mask
     return out

@@ -280,9 +280,11 @@ class _DeltaConvMixin:
         op = K.sparse_deconv if self._transposed else K.sparse_conv
         extra = {}
         if not self._transposed:
-            if DCConv2d.use_worklist and self._workspace is None and self.frame_idx > 0:
+            if DCConv2d.use_worklist and self._workspace is None:
                 self._workspace = torch.empty(K.conv_workspace_bytes(self._desc), dtype=torch.uint8, device=x.device)
-            extra = {"filter_umma": self.weight_umma, "workspace": self._workspace if self.frame_idx > 0 else None}
+            # kernels larger than 1x1 have a tensor-core path only with a work list
+            umma = self.weight_umma if (self._workspace is not None or self.kernel_size == (1, 1)) else None
+            extra = {"filter_umma": umma, "workspace": self._workspace}
         out, out_mask = op(
             x=x, filter=self.weight, mask=mask, bias=self.bias if self.frame_idx <= 0 else None, stride=self.stride,
             padding=self.padding, dilation=self.dilation, groups=self.groups, c_out=self.out_channels, create_out_mask=True,

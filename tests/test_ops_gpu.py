@@ -496,3 +496,67 @@ def test_worklist_kernels_equal_the_plain_ones(kind, cin, cout, h, w, s, fused, 
     assert torch.equal(o1[sel], o2[sel])
     if not fused:
         assert torch.isnan(o2[~sel]).all(), "pixels outside the out-mask must not be written"
+
+
+KXK_CASES = [
+    # cin, cout, k, stride, pad, dil, n, h, w
+    (64, 64, 3, 1, 1, 1, 2, 20, 24), (64, 128, 3, 2, 1, 1, 2, 21, 19), (128, 128, 3, 1, 1, 1, 2, 16, 16), (32, 32, 3, 1, 2, 2, 2, 15, 15),
+    (256, 256, 3, 1, 1, 1, 1, 12, 12), (512, 512, 3, 1, 1, 1, 1, 8, 8), (24, 40, 5, 1, 2, 1, 2, 13, 13), (256, 64, 3, 1, 1, 1, 2, 17, 30),
+]
+
+
+def _pack_umma_kxk(wt_hwio, cin, cout, k, stride, pad, dil):
+    from deltacnn_b200 import _lib
+    import deltacnn_b200.cuda_kernels as kk
+    desc = kk.make_conv_desc((1, cin, 8, 8), cout, (8, 8), (k, k), (stride, stride), (pad, pad), (dil, dil), 1, 1)
+    nbytes = _lib.lib.dc_filter_umma_bytes(desc, 0)
+    assert nbytes > 0
+    packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    _lib.check(_lib.lib.dc_pack_filter_umma(desc, 0, wt_hwio.data_ptr(), packed.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+    return packed
+
+
+@pytest.mark.parametrize("case", KXK_CASES)
+@pytest.mark.parametrize("density", [0.0, 0.1, 1.0])
+@pytest.mark.parametrize("fused", [False, True])
+def test_kxk_conv_umma_matches_oracle_and_cuda_core_kernel(case, density, fused):
+    """3x3 / 5x5 convolutions as implicit GEMM on tcgen05 (work-list mode) against the oracle, and the
+    fused epilogue against convolution + stand-alone activation kernel."""
+    import deltacnn_b200.cuda_kernels as kk
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    cin, cout, k, s, p, d, n, h, w = case
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(61)
+    x = rand_feat(g, n, cin, h, w, dtype, 0.5)
+    mask = rand_mask(g, n, h, w, density)
+    wt = (torch.randn(cout, cin, k, k, generator=g) / (k * cin ** 0.5)).to(dtype)
+    bias = torch.randn(cout, generator=g).to(dtype)
+    ref, m_ref = O.conv(x, mask, wt, bias, (s, s), (p, p), (d, d), 1)
+    f = convert_filter_out_channels_last(wt).cuda()
+    packed = _pack_umma_kxk(f, cin, cout, k, s, p, d)
+    xd, md = x.cuda(), mask.cuda()
+    xd[(mask == 0).expand_as(x)] = float("nan")
+    ho, wo = ref.shape[2:]
+    desc = kk.make_conv_desc(tuple(x.shape), cout, (ho, wo), (k, k), (s, s), (p, p), (d, d), 1, 1)
+    ws = torch.empty(kk.conv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
+    if not fused:
+        out = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last)
+        out, om = kk.sparse_conv(xd, f, md, bias.cuda(), (s, s), (p, p), (d, d), 1, create_out_mask=True, out=out, filter_umma=packed, workspace=ws)
+        assert _lib.lib.dc_umma_error() == 0
+        assert torch.equal(om.cpu(), m_ref)
+        assert_close_masked(out, ref, m_ref, dtype, "kxk umma")
+        assert torch.isnan(out.cpu()[(m_ref == 0).expand_as(ref)]).all()
+        return
+    prev = rand_feat(g, n, cout, ho, wo, dtype, 1.0)
+    trunc = rand_feat(g, n, cout, ho, wo, dtype, 0.02)
+    o1, m1 = kk.sparse_conv(xd, f, md, None, (s, s), (p, p), (d, d), 1, create_out_mask=True, filter_umma=packed, workspace=ws)
+    p1, t1 = prev.cuda(), trunc.cuda()
+    kk.sparse_activation(o1, p1, t1, m1, 0.8, 1, 0)
+    p2, t2 = prev.cuda(), trunc.cuda()
+    o2, m2 = kk.sparse_conv(xd, f, md, None, (s, s), (p, p), (d, d), 1, create_out_mask=True, filter_umma=packed, workspace=ws,
+                            epilogue=kk.make_epilogue(p2, t2, 0.8, 1, 0))
+    assert _lib.lib.dc_umma_error() == 0
+    assert torch.equal(m1, m2) and torch.equal(p1, p2) and torch.equal(t1, t2)
+    sel = (m1 != 0).expand_as(o1)
+    assert torch.equal(o1[sel], o2[sel])
