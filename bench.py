@@ -289,7 +289,7 @@ def count_launches(delta, frames_dev, t_next, F):
     import torch
     from deltacnn_b200 import _lib
     counts = [0]
-    names = [n for n in _lib.EXPORTED_SYMBOLS if n not in ("dc_version", "dc_status_string", "dc_last_cuda_error", "dc_filter_umma_bytes", "dc_umma_error", "dc_conv_workspace_bytes", "dc_static_workspace_max_pixels")]
+    names = [n for n in _lib.EXPORTED_SYMBOLS if n not in ("dc_version", "dc_status_string", "dc_last_cuda_error", "dc_filter_umma_bytes", "dc_umma_error", "dc_conv_workspace_bytes", "dc_deconv_workspace_bytes", "dc_static_workspace_max_pixels")]
     originals = {}
 
     def wrap(name, fn):

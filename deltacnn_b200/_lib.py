@@ -49,6 +49,8 @@ _SIGNATURES = {
     "dc_conv2d_static": (c_int, [ctypes.POINTER(ConvDesc), _P, _P, _P, c_int, _P, _P, _P, ctypes.POINTER(Epilogue), _P]),
     "dc_static_workspace_max_pixels": (c_size_t, []),
     "dc_deconv2d": (c_int, [ctypes.POINTER(ConvDesc), _P, _P, _P, c_int, _P, _P, _P, ctypes.POINTER(Epilogue), _P]),
+    "dc_deconv2d_ws": (c_int, [ctypes.POINTER(ConvDesc), _P, _P, _P, c_int, _P, _P, _P, ctypes.POINTER(Epilogue), _P, c_size_t, _P]),
+    "dc_deconv_workspace_bytes": (c_size_t, [ctypes.POINTER(ConvDesc)]),
     "dc_filter_umma_bytes": (c_size_t, [ctypes.POINTER(ConvDesc), c_int]),
     "dc_pack_filter_umma": (c_int, [ctypes.POINTER(ConvDesc), c_int, _P, _P, _P]),
     "dc_activate_truncate": (c_int, [_P, _P, _P, _P, c_i64, c_int, c_int, c_float, c_int, c_int, _P]),

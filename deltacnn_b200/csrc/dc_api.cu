@@ -41,6 +41,9 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
 int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
                     int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t conv_workspace_bytes(const dc_conv_desc* d);
+size_t deconv_workspace_bytes(const dc_conv_desc* d);
+int deconv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+                  int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st);
 
 static int run_epilogue(const dc_conv_desc* d, void* out, int32_t* mo, const dc_epilogue* ep, void* stream) {
     if (ep == nullptr) return DC_OK;
@@ -102,17 +105,29 @@ int dc_conv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, 
 
 size_t dc_conv_workspace_bytes(const dc_conv_desc* desc) { return desc == nullptr ? 0 : conv_workspace_bytes(desc); }
 
-int dc_deconv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
-                const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream) {
+int dc_deconv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
+                   const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* workspace,
+                   size_t workspace_bytes, void* stream) {
     if (desc == nullptr || in == nullptr || filter == nullptr || out == nullptr) return DC_ERR_NULL_POINTER;
     if (epilogue != nullptr && (epilogue->prev_out == nullptr || (epilogue->truncation >= 0 && epilogue->truncated == nullptr)))
         return DC_ERR_NULL_POINTER;
-    if (filter_layout != DC_FILTER_HWIO) return DC_ERR_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
+    if (filter_layout == DC_FILTER_UMMA) {
+        if (workspace != nullptr && workspace_bytes < deconv_workspace_bytes(desc)) return DC_ERR_WORKSPACE;
+        return deconv2d_umma(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
+    }
+    if (filter_layout != DC_FILTER_HWIO) return DC_ERR_UNSUPPORTED;
     int rc = deconv2d_simt(desc, in, mask_in, filter, bias, out, mask_out, st);
     if (rc != DC_OK) return rc;
     return run_epilogue(desc, out, mask_out, epilogue, stream);
 }
+
+int dc_deconv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
+                const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream) {
+    return dc_deconv2d_ws(desc, in, mask_in, filter, filter_layout, bias, out, mask_out, epilogue, nullptr, 0, stream);
+}
+
+size_t dc_deconv_workspace_bytes(const dc_conv_desc* desc) { return desc == nullptr ? 0 : deconv_workspace_bytes(desc); }
 
 size_t dc_filter_umma_bytes(const dc_conv_desc* desc, int32_t transposed) {
     if (desc == nullptr) return 0;

@@ -46,6 +46,9 @@ struct PwParams {
     const int32_t* wl_count;        // work-list mode (else nullptr): number of active output pixels
     const uint32_t* wl_list;        //   their indices
     const uint32_t* wl_taps;        //   and the bit sets of their active taps, written by k_scan_conv_mask
+    int transposed;                 // transposed convolution with stride sh == sw: blockIdx.z = output phase,
+    int m;                          //   m x m taps per phase (kh = m * stride); lists are per phase
+    int64_t wl_stride;              //   entries between the per-phase list segments
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
 
@@ -161,6 +164,14 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     const int n0 = blockIdx.y * p.bn;                              // first output channel of this CTA
     const int ncols = min(p.bn, p.cout - n0);                      // real output channels here
     const uint8_t* wimg = p.wimg + (size_t)blockIdx.y * p.bn * 128;   // this CTA's rows inside every K block
+    // transposed convolution: this CTA's output phase (py, px) uses the taps ky = py + s*a, kx = px + s*b
+    const int ph_y = p.transposed ? (int)blockIdx.z / p.sw : 0, ph_x = p.transposed ? (int)blockIdx.z % p.sw : 0;
+    auto filter_block = [&](int kb_) -> size_t {                  // K block of this CTA -> K block of the packed filter
+        if (!p.transposed) return (size_t)kb_;
+        const int j = kb_ / p.ncb, cb = kb_ - j * p.ncb;
+        const int t = (ph_y + p.sh * (j / p.m)) * p.kw + ph_x + p.sw * (j % p.m);
+        return (size_t)t * p.ncb + cb;
+    };
 
     // ---- compaction of the span's active pixels, one pass (order preserved) ----
     const bool list_mode = p.wl_list != nullptr;
@@ -168,7 +179,7 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     const int64_t q0 = list_mode ? 0 : (int64_t)blockIdx.x * p.span;
     int cnt = 0;
     if (list_mode) {
-        cnt = *p.wl_count;
+        cnt = p.wl_count[blockIdx.z];
         if ((int64_t)blockIdx.x * kRows >= cnt) return;            // persistent CTAs beyond the work
     } else {
     const int spt = max(1, p.span / kPwThreads);                   // consecutive pixels per thread (1..8)
@@ -232,7 +243,7 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
         if (p.b_resident) {               // the whole filter slab of this CTA, one bulk copy per K block
             for (int kb = 0; kb < p.nkb; ++kb) {
                 mbar_expect_tx(bar_bfull(kb), b_block_bytes);
-                bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + (size_t)kb * p.b_kb_stride, b_block_bytes, bar_bfull(kb));
+                bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(kb));
             }
         }
     }
@@ -276,7 +287,7 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
         cp_async_commit();
         if (tid == 0 && !p.b_resident) {
             mbar_expect_tx(bar_bfull(slot_), b_block_bytes);
-            bulk_g2s(smem_u32(sB + (size_t)slot_ * b_block_bytes), wimg + (size_t)kb_ * p.b_kb_stride, b_block_bytes, bar_bfull(slot_));
+            bulk_g2s(smem_u32(sB + (size_t)slot_ * b_block_bytes), wimg + filter_block(kb_) * p.b_kb_stride, b_block_bytes, bar_bfull(slot_));
         }
     };
     __syncthreads();                  // row lists complete
@@ -292,8 +303,9 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
         if (list_mode) {
             __syncthreads();                                        // previous tile's epilogue has read the lists
             for (int r = tid; r < cnt_t; r += kPwThreads) {
-                const uint32_t q = p.wl_list[(size_t)tg * kRows + r];
-                const uint32_t tb = p.wl_taps[(size_t)tg * kRows + r];
+                const size_t e_ = (size_t)blockIdx.z * p.wl_stride + (size_t)tg * kRows + r;
+                const uint32_t q = p.wl_list[e_];
+                const uint32_t tb = p.wl_taps[e_];
                 s_out[r] = (int)q;
                 const uint32_t b = q / (uint32_t)hw_out;
                 const uint32_t rr = q - b * (uint32_t)hw_out;
@@ -301,7 +313,9 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
                 for (int t = 0; t < p.taps; ++t) {
                     int pin_ = -1;
                     if (tb & (1u << t)) {
-                        const int iy = oy * p.sh - p.pt + (t / p.kw) * p.dh, ix = ox * p.sw - p.pl + (t % p.kw) * p.dw;
+                        int iy, ix;
+                        if (p.transposed) { iy = (oy + p.pt) / p.sh - t / p.m; ix = (ox + p.pl) / p.sw - t % p.m; }
+                        else { iy = oy * p.sh - p.pt + (t / p.kw) * p.dh; ix = ox * p.sw - p.pl + (t % p.kw) * p.dw; }
                         pin_ = (int)((b * p.hi + iy) * p.wi + ix);
                     }
                     s_in[r * p.taps + t] = pin_;
@@ -474,11 +488,13 @@ struct PwPlan {
     size_t smem, img_bytes;
 };
 
-static PwPlan plan_pw(const dc_conv_desc* d) {
+static PwPlan plan_pw(const dc_conv_desc* d, int transposed = 0) {
     PwPlan pl{};
     pl.taps = d->kh * d->kw;
     pl.ok = d->dtype == DC_F16 && d->groups == 1 && pl.taps <= 25 && d->c_in % 8 == 0 && d->c_out % 8 == 0 &&
             d->c_in >= 16 && d->c_out >= 16;
+    if (transposed)     // stride 2, kernel 2m x 2m, no dilation: four output phases of m x m taps each
+        pl.ok = pl.ok && d->stride_h == 2 && d->stride_w == 2 && d->kh == d->kw && d->kh % 2 == 0 && d->dil_h == 1 && d->dil_w == 1;
     if (!pl.ok) return pl;
     pl.ncb = divup(d->c_in, kKBlock);
     pl.nkb = pl.taps * pl.ncb;
@@ -525,14 +541,12 @@ static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, boo
 }
 
 size_t filter_umma_bytes(const dc_conv_desc* d, int transposed) {
-    if (transposed) return 0;
-    PwPlan pl = plan_pw(d);
+    PwPlan pl = plan_pw(d, transposed);
     return pl.ok ? pl.img_bytes : 0;
 }
 
 int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, void* packed, cudaStream_t st) {
-    if (transposed) return DC_ERR_UNSUPPORTED;
-    PwPlan pl = plan_pw(d);
+    PwPlan pl = plan_pw(d, transposed);
     if (!pl.ok) return DC_ERR_UNSUPPORTED;
     if (!aligned16(packed)) return DC_ERR_ALIGNMENT;
     const int64_t total = (int64_t)pl.img_bytes / 2;
@@ -544,9 +558,12 @@ int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, vo
 
 int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
 
-int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
-                int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
-    PwPlan pl = plan_pw(d);
+int scan_deconv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
+
+static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in, const int32_t* mi, const void* filt, const void* bias,
+                          void* out, int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
+    PwPlan pl = plan_pw(d, transposed);
+    if (transposed && ws == nullptr) return DC_ERR_UNSUPPORTED;
     if (!pl.ok || mi == nullptr || mo == nullptr) return DC_ERR_UNSUPPORTED;
     // without scratch for a work list only 1x1 kernels (no receptive field to dilate) have a tensor-core path
     if (ws == nullptr && (pl.taps != 1 || d->pad_top != 0 || d->pad_left != 0)) return DC_ERR_UNSUPPORTED;
@@ -555,6 +572,10 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     if (npix_out == 0) return DC_OK;
     if ((int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
     const bool want_fused = ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
+    if (transposed) {                 // the kernel sees one phase: m x m taps
+        pl.taps = (d->kh / 2) * (d->kw / 2);
+        pl.nkb = pl.taps * pl.ncb;
+    }
     finish_plan(pl, d, npix_out, want_fused, ws != nullptr);
     const bool fused = want_fused && pl.ntiles == 1;
     PwParams p{};
@@ -570,6 +591,7 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     p.cin = d->c_in; p.cout = d->c_out;
     p.kh = d->kh; p.kw = d->kw; p.dh = d->dil_h; p.dw = d->dil_w; p.pt = d->pad_top; p.pl = d->pad_left;
     p.taps = pl.taps; p.ncb = pl.ncb;
+    p.transposed = transposed; p.m = transposed ? d->kh / 2 : 0; p.wl_stride = transposed ? npix_out : 0;
     p.nkb = pl.nkb; p.bn = pl.bn; p.span = pl.span; p.b_resident = pl.b_resident; p.tmem_cols = pl.tmem_cols;
     p.nslots = pl.nslots;
     p.b_kb_stride = (uint32_t)pl.rows * 128u;
@@ -582,11 +604,13 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
     if (pl.smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
     dim3 grid((unsigned)divup64(npix_out, pl.span), (unsigned)pl.ntiles);
     if (ws != nullptr) {              // work-list mode: scan pass, then persistent CTAs over the active rows
-        int rc = scan_conv_mask(d, mi, mo, ws, ws_bytes, fused ? 1 : 0, st);
+        int rc = transposed ? scan_deconv_mask(d, mi, mo, ws, ws_bytes, fused ? 1 : 0, st)
+                            : scan_conv_mask(d, mi, mo, ws, ws_bytes, fused ? 1 : 0, st);
         if (rc != DC_OK) return rc;
         p.wl_count = reinterpret_cast<const int32_t*>(ws);
         p.wl_list = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(ws) + 16);
-        p.wl_taps = p.wl_list + npix_out;
+        p.wl_taps = p.wl_list + (transposed ? 4 * npix_out : npix_out);
+        if (transposed) grid.z = 4;
         int64_t persistent = (int64_t)sm_count() * 4 / pl.ntiles;
         if (persistent < 1) persistent = 1;
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
@@ -598,6 +622,16 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
         return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,
                                     ep->activation, ep->truncation, (void*)st);
     return DC_OK;
+}
+
+int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+                int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
+    return conv_umma_impl(d, 0, in, mi, filt, bias, out, mo, ep, ws, ws_bytes, st);
+}
+
+int deconv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+                  int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
+    return conv_umma_impl(d, 1, in, mi, filt, bias, out, mo, ep, ws, ws_bytes, st);
 }
 
 int umma_error_code() {

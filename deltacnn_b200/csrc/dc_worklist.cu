@@ -94,6 +94,97 @@ int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* 
 
 }  // namespace dc
 
+namespace dc {
+
+// Transposed convolution, stride 2, kernel 2m x 2m: an output pixel (oy, ox) belongs to the phase
+// ((oy + pad) % 2, (ox + pad) % 2) and only the m x m taps of that phase reach it, from the input pixels
+// ((oy + pad) / 2 - a, (ox + pad) / 2 - b). The active output pixels are listed per phase (four lists of
+// npix_out entries each, four counters in the header), so that a tile of rows shares one tap set.
+struct ScanDeconvParams {
+    const int32_t* mi; int32_t* mo; int32_t* count; uint32_t* list; uint32_t* taps;
+    int n, hi, wi, ho, wo, m, pt, pl;
+    int defer_active;
+};
+
+__global__ void __launch_bounds__(256) k_scan_deconv_mask(ScanDeconvParams p) {
+    __shared__ int s_warp[4][8];
+    __shared__ int s_base[4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
+    for (uint32_t start = blockIdx.x * 256u; start < npix; start += gridDim.x * 256u) {
+        const uint32_t q = start + threadIdx.x;
+        unsigned bits = 0;
+        int phase = 0;
+        if (q < npix) {
+            const int ox = (int)(q % (uint32_t)p.wo);
+            const uint32_t t = q / (uint32_t)p.wo;
+            const int oy = (int)(t % (uint32_t)p.ho);
+            const int b = (int)(t / (uint32_t)p.ho);
+            phase = ((oy + p.pt) & 1) * 2 + ((ox + p.pl) & 1);
+            const int by = (oy + p.pt) >> 1, bx = (ox + p.pl) >> 1;
+            const int32_t* m = p.mi + (int64_t)b * p.hi * p.wi;
+            for (int a = 0; a < p.m; ++a) {
+                const int iy = by - a;
+                if (iy < 0 || iy >= p.hi) continue;
+                for (int c = 0; c < p.m; ++c) {
+                    const int ix = bx - c;
+                    if (ix < 0 || ix >= p.wi) continue;
+                    if (m[iy * p.wi + ix] != 0) bits |= 1u << (a * p.m + c);
+                }
+            }
+            if (!p.defer_active || bits == 0) p.mo[q] = bits != 0 ? 1 : 0;
+        }
+        unsigned bal[4];
+#pragma unroll
+        for (int ph = 0; ph < 4; ++ph) {
+            bal[ph] = __ballot_sync(DC_FULL, bits != 0 && phase == ph);
+            if (lane == 0) s_warp[ph][warp] = __popc(bal[ph]);
+        }
+        __syncthreads();
+        if (threadIdx.x < 4) {
+            const int ph = threadIdx.x;
+            int tot = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { const int c = s_warp[ph][i]; s_warp[ph][i] = tot; tot += c; }
+            s_base[ph] = tot ? atomicAdd(p.count + ph, tot) : 0;
+        }
+        __syncthreads();
+        if (bits) {
+            const size_t slot = (size_t)phase * npix + s_base[phase] + s_warp[phase][warp] + __popc(bal[phase] & ((1u << lane) - 1u));
+            p.list[slot] = q;
+            p.taps[slot] = bits;
+        }
+        __syncthreads();
+    }
+}
+
+size_t deconv_workspace_bytes(const dc_conv_desc* d) {
+    const int64_t npix = (int64_t)d->n * d->h_out * d->w_out;
+    return 16 + (size_t)npix * 8 * 4;
+}
+
+int scan_deconv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active,
+                     cudaStream_t st) {
+    const int64_t npix = (int64_t)d->n * d->h_out * d->w_out;
+    if (ws == nullptr || ws_bytes < deconv_workspace_bytes(d)) return DC_ERR_WORKSPACE;
+    if (npix > 0x3fffffffLL || d->stride_h != 2 || d->stride_w != 2 || d->kh != d->kw || d->kh % 2 != 0 || d->kh > 10) return DC_ERR_UNSUPPORTED;
+    ScanDeconvParams p{};
+    p.mi = mi; p.mo = mo;
+    p.count = reinterpret_cast<int32_t*>(ws);
+    p.list = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ws) + 16);
+    p.taps = p.list + 4 * npix;
+    p.n = d->n; p.hi = d->h_in; p.wi = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.m = d->kh / 2; p.pt = d->pad_top; p.pl = d->pad_left;
+    p.defer_active = defer_active;
+    if (cudaMemsetAsync(ws, 0, 16, st) != cudaSuccess) return check_launch();
+    int64_t blocks = divup64(npix, 256);
+    const int64_t cap = (int64_t)sm_count() * 32;
+    if (blocks > cap) blocks = cap;
+    k_scan_deconv_mask<<<(unsigned)blocks, 256, 0, st>>>(p);
+    return check_launch();
+}
+
+}  // namespace dc
+
 // ---------------------------------------------------------------------------------------------
 // Entry point for callers that cannot allocate device memory
 // ---------------------------------------------------------------------------------------------

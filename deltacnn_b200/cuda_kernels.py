@@ -146,7 +146,7 @@ def deconv_out_hw(h, w, kernel, stride, padding, dilation):
 
 def sparse_deconv(x, filter, mask=None, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, c_out: int = None,
                   create_out_mask=False, sub_tile_sparsity=True, out_mask=None, out_shape=None, out=None, epilogue=None,
-                  desc=None):
+                  desc=None, filter_umma=None, workspace=None):
     """Delta transposed convolution (reference: cuda_kernels.py:47-78); output_padding is not applied."""
     _check_feature(x, "x")
     _check_mask(mask, x, "mask")
@@ -168,11 +168,23 @@ def sparse_deconv(x, filter, mask=None, bias=None, stride=(1, 1), padding=(0, 0)
         desc = make_conv_desc(tuple(x.shape), out_c, (out_h, out_w), kernel, stride, padding, dilation, groups, _dtype(x))
     if filter.dtype != x.dtype:
         raise RuntimeError("deltacnn_b200.sparse_deconv: filter dtype differs from input dtype")
-    check(lib.dc_deconv2d(desc, x.data_ptr(), _ptr(mask), filter.data_ptr(), _lib.DC_FILTER_HWIO, _ptr(bias), out.data_ptr(),
-                          _ptr(out_mask), epilogue, _stream()), "sparse_deconv")
+    ws_ptr, ws_len = (workspace.data_ptr(), workspace.numel()) if (workspace is not None and mask is not None and out_mask is not None) else (None, 0)
+    status = 2
+    if filter_umma is not None and ws_ptr is not None:
+        status = lib.dc_deconv2d_ws(desc, x.data_ptr(), _ptr(mask), filter_umma.data_ptr(), _lib.DC_FILTER_UMMA, _ptr(bias),
+                                    out.data_ptr(), _ptr(out_mask), epilogue, ws_ptr, ws_len, _stream())
+    if status == 2:     # no tensor-core kernel for this call: CUDA-core kernel, same result
+        status = lib.dc_deconv2d(desc, x.data_ptr(), _ptr(mask), filter.data_ptr(), _lib.DC_FILTER_HWIO, _ptr(bias), out.data_ptr(),
+                                 _ptr(out_mask), epilogue, _stream())
+    check(status, "sparse_deconv")
     if create_out_mask and mask is not None:
         return out, out_mask
     return out
+
+
+def deconv_workspace_bytes(desc):
+    """Scratch bytes the work-list transposed convolution wants for this geometry."""
+    return int(lib.dc_deconv_workspace_bytes(desc))
 
 
 def sparse_pooling(x, prev_x, kernel_size, mask=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), create_out_mask=True,

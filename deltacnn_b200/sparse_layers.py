@@ -279,7 +279,11 @@ class _DeltaConvMixin:
                                           self.padding, self.dilation, self.groups, K._dtype(x))
         op = K.sparse_deconv if self._transposed else K.sparse_conv
         extra = {}
-        if not self._transposed:
+        if self._transposed:
+            if DCConv2d.use_worklist and self._workspace is None and self.weight_umma is not None:
+                self._workspace = torch.empty(K.deconv_workspace_bytes(self._desc), dtype=torch.uint8, device=x.device)
+            extra = {"filter_umma": self.weight_umma, "workspace": self._workspace}
+        else:
             if DCConv2d.use_worklist and self._workspace is None:
                 self._workspace = torch.empty(K.conv_workspace_bytes(self._desc), dtype=torch.uint8, device=x.device)
             # kernels larger than 1x1 have a tensor-core path only with a work list
@@ -333,17 +337,18 @@ class _DeltaConvMixin:
     def _pack_umma(self):
         """Build the tensor-core image of the filter when the shape has a tcgen05 kernel."""
         self.weight_umma = None
-        if self._transposed or self.weight.dtype != torch.float16 or not self.weight.is_cuda:
+        if self.weight.dtype != torch.float16 or not self.weight.is_cuda:
             return
         from ._lib import lib, check
         kh, kw = self.kernel_size
         desc = K.make_conv_desc((1, self.in_channels, 8, 8), self.out_channels, (8, 8), (kh, kw), self.stride,
                                 self.padding, self.dilation, self.groups, 1)
-        nbytes = lib.dc_filter_umma_bytes(desc, 0)
+        tr = 1 if self._transposed else 0
+        nbytes = lib.dc_filter_umma_bytes(desc, tr)
         if nbytes == 0:
             return
         packed = torch.empty(nbytes, dtype=torch.uint8, device=self.weight.device)
-        check(lib.dc_pack_filter_umma(desc, 0, self.weight.data_ptr(), packed.data_ptr(),
+        check(lib.dc_pack_filter_umma(desc, tr, self.weight.data_ptr(), packed.data_ptr(),
                                       torch.cuda.current_stream().cuda_stream), "pack_filter_umma")
         self.weight_umma = packed
 

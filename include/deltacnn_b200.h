@@ -145,6 +145,16 @@ int dc_deconv2d(const dc_conv_desc* desc, const void* in, const int32_t* mask_in
                 const void* filter, int32_t filter_layout, const void* bias,
                 void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* stream);
 
+/* dc_deconv2d with caller-provided scratch for per-phase active-pixel work lists (16 + 32 bytes per
+ * output pixel, dc_deconv_workspace_bytes). With a DC_FILTER_UMMA filter image (stride 2, kernel 2m x 2m,
+ * fp16) the four output phases run as m x m implicit GEMMs on the tensor cores. Same results as
+ * dc_deconv2d. No reference counterpart. */
+int dc_deconv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_in,
+                   const void* filter, int32_t filter_layout, const void* bias,
+                   void* out, int32_t* mask_out, const dc_epilogue* epilogue,
+                   void* workspace, size_t workspace_bytes, void* stream);
+size_t dc_deconv_workspace_bytes(const dc_conv_desc* desc);
+
 /* Bytes of the DC_FILTER_UMMA image of a filter (0 if the shape has no tensor-core kernel). */
 size_t dc_filter_umma_bytes(const dc_conv_desc* desc, int32_t transposed);
 /* Repack an fp16 HWIO filter on the device into the DC_FILTER_UMMA layout. */

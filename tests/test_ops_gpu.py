@@ -560,3 +560,49 @@ def test_kxk_conv_umma_matches_oracle_and_cuda_core_kernel(case, density, fused)
     assert torch.equal(m1, m2) and torch.equal(p1, p2) and torch.equal(t1, t2)
     sel = (m1 != 0).expand_as(o1)
     assert torch.equal(o1[sel], o2[sel])
+
+
+@pytest.mark.parametrize("cin,cout,k,p,n,h,w", [(64, 64, 4, 1, 2, 9, 11), (512, 256, 4, 1, 1, 6, 7), (256, 256, 4, 1, 2, 12, 10), (32, 48, 2, 0, 2, 8, 8)])
+@pytest.mark.parametrize("density", [0.0, 0.15, 1.0])
+@pytest.mark.parametrize("fused", [False, True])
+def test_deconv_umma_matches_oracle(cin, cout, k, p, n, h, w, density, fused):
+    """Transposed convolution (stride 2) as four per-phase implicit GEMMs on tcgen05, work-list mode."""
+    import deltacnn_b200.cuda_kernels as kk
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(71)
+    x = rand_feat(g, n, cin, h, w, dtype, 0.5)
+    mask = rand_mask(g, n, h, w, density)
+    wt = (torch.randn(cin, cout, k, k, generator=g) / cin ** 0.5).to(dtype)
+    bias = torch.randn(cout, generator=g).to(dtype)
+    ref, m_ref = O.deconv(x, mask, wt, bias, (2, 2), (p, p))
+    f = convert_filter_out_channels_last(wt, transposed=True).cuda()
+    ho, wo = ref.shape[2:]
+    desc = kk.make_conv_desc(tuple(x.shape), cout, (ho, wo), (k, k), (2, 2), (p, p), (1, 1), 1, 1)
+    nbytes = _lib.lib.dc_filter_umma_bytes(desc, 1)
+    assert nbytes > 0
+    packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    _lib.check(_lib.lib.dc_pack_filter_umma(desc, 1, f.data_ptr(), packed.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+    ws = torch.empty(kk.deconv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
+    xd, md = x.cuda(), mask.cuda()
+    xd[(mask == 0).expand_as(x)] = float("nan")
+    if not fused:
+        out = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last)
+        out, om = kk.sparse_deconv(xd, f, md, bias.cuda(), (2, 2), (p, p), (1, 1), 1, create_out_mask=True, out=out, filter_umma=packed, workspace=ws)
+        assert _lib.lib.dc_umma_error() == 0
+        assert torch.equal(om.cpu(), m_ref)
+        assert_close_masked(out, ref, m_ref, dtype, "deconv umma")
+        assert torch.isnan(out.cpu()[(m_ref == 0).expand_as(ref)]).all()
+        return
+    prev = rand_feat(g, n, cout, ho, wo, dtype, 1.0)
+    trunc = rand_feat(g, n, cout, ho, wo, dtype, 0.02)
+    o1, m1 = kk.sparse_deconv(xd, f, md, None, (2, 2), (p, p), (1, 1), 1, create_out_mask=True, filter_umma=packed, workspace=ws)
+    p1, t1 = prev.cuda(), trunc.cuda()
+    kk.sparse_activation(o1, p1, t1, m1, 0.8, 1, 0)
+    p2, t2 = prev.cuda(), trunc.cuda()
+    o2, m2 = kk.sparse_deconv(xd, f, md, None, (2, 2), (p, p), (1, 1), 1, create_out_mask=True, filter_umma=packed, workspace=ws,
+                              epilogue=kk.make_epilogue(p2, t2, 0.8, 1, 0))
+    assert torch.equal(m1, m2) and torch.equal(p1, p2) and torch.equal(t1, t2)
+    sel = (m1 != 0).expand_as(o1)
+    assert torch.equal(o1[sel], o2[sel])
