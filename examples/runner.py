@@ -49,35 +49,42 @@ class GraphedStep:
         return self.static_out
 
 
+def capture_groups(models, inputs, pool=None):
+    """Capture one CUDA graph that runs ``models[g](inputs[g])`` for every group g, each group on its own
+    stream inside the capture (fork from / join into the capturing stream), so kernels of different
+    groups may overlap. Returns (graph, outputs)."""
+    main = torch.cuda.Stream()
+    side = [torch.cuda.Stream() for _ in models[1:]]
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.no_grad(), torch.cuda.graph(graph, stream=main, pool=pool):
+        fork = torch.cuda.Event()
+        fork.record(main)
+        outs = [None] * len(models)
+        joins = []
+        for i, st in enumerate(side):
+            st.wait_event(fork)
+            with torch.cuda.stream(st):
+                outs[i + 1] = models[i + 1](inputs[i + 1])
+                ev = torch.cuda.Event()
+                ev.record(st)
+                joins.append(ev)
+        outs[0] = models[0](inputs[0])
+        for ev in joins:
+            main.wait_event(ev)
+    return graph, outs
+
+
 class MultiBranchStep:
     """One CUDA graph that steps several groups of streams concurrently: every group has its own model
-    instance (own caches) and its own CUDA stream inside the capture, so the kernels of different groups
-    overlap on the GPU. Streams of a video never interact, so the groups share nothing but the weights'
-    values. Each model must already have processed its first frame and one steady-state frame."""
+    instance (own caches) and its own CUDA stream inside the capture. Streams of a video never interact,
+    so the groups share nothing but the weights' values. Each model must already have processed its first
+    frame and one steady-state frame."""
 
     def __init__(self, models, example_inputs):
         self.models = models
         self.static_in = [x.clone() for x in example_inputs]
-        self.main = torch.cuda.Stream()
-        self.side = [torch.cuda.Stream() for _ in models[1:]]
-        torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.no_grad(), torch.cuda.graph(self.graph, stream=self.main):
-            fork = torch.cuda.Event()
-            fork.record(self.main)
-            outs = [None] * len(models)
-            joins = []
-            for i, s in enumerate(self.side):
-                s.wait_event(fork)
-                with torch.cuda.stream(s):
-                    outs[i + 1] = models[i + 1](self.static_in[i + 1])
-                    ev = torch.cuda.Event()
-                    ev.record(s)
-                    joins.append(ev)
-            outs[0] = models[0](self.static_in[0])
-            for ev in joins:
-                self.main.wait_event(ev)
-        self.static_out = outs
+        self.graph, self.static_out = capture_groups(models, self.static_in)
 
     def load(self, frames, non_blocking=True):
         for dst, src in zip(self.static_in, frames):
@@ -91,27 +98,25 @@ class MultiBranchStep:
 
 
 class PipelinedStep:
-    """End-to-end stepping from host memory: two input buffers and two captured graphs of the same model,
-    so that the host->device copy of frame t+1 (on a copy stream) overlaps the delta step of frame t, and
-    the result of frame t is copied back to pinned host memory behind it. The model must be warmed up
-    (first frame and one steady-state frame done) before construction."""
+    """End-to-end stepping from host memory: two sets of input buffers and two captured graphs of the
+    same model group(s), so that the host->device copy of frame t+1 (on a copy stream) overlaps the delta
+    step of frame t, and the result of frame t is copied back to pinned host memory behind it. The models
+    must be warmed up (first frame and one steady-state frame done) before construction. ``bounds`` are
+    the batch offsets of the groups inside a full frame batch."""
 
-    def __init__(self, model, example_input, compute_stream):
+    def __init__(self, models, example_inputs, bounds, compute_stream):
         self.compute = compute_stream
         self.copy = torch.cuda.Stream()
-        self.inputs = [example_input.clone(), example_input.clone()]
+        self.bounds = bounds
+        self.inputs = [[x.clone() for x in example_inputs] for _ in range(2)]
         self.graphs, self.outputs = [], []
-        torch.cuda.synchronize()
         pool = None
-        with torch.no_grad():
-            for buf in self.inputs:
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=torch.cuda.Stream(), pool=pool):
-                    out = model(buf)
-                pool = g.pool()
-                self.graphs.append(g)
-                self.outputs.append(out)
-        self.host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in self.outputs]
+        for bufs in self.inputs:
+            g, outs = capture_groups(models, bufs, pool=pool)
+            pool = g.pool()
+            self.graphs.append(g)
+            self.outputs.append(outs)
+        self.host_out = [[torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs] for outs in self.outputs]
         self.copied = [torch.cuda.Event(), torch.cuda.Event()]
         self.consumed = [torch.cuda.Event(), torch.cuda.Event()]
         for e in self.consumed:
@@ -120,24 +125,26 @@ class PipelinedStep:
         self.stepped = 0       # frames processed so far
 
     def upload(self, host_frame):
-        """Start the upload of the next frame (at most one frame ahead of step())."""
+        """Start the upload of the next frame batch (at most one ahead of step())."""
         assert self.uploaded - self.stepped < 2
         i = self.uploaded % 2
-        self.copy.wait_event(self.consumed[i])            # the graph that last read this buffer is done
+        self.copy.wait_event(self.consumed[i])            # the graph that last read these buffers is done
         with torch.cuda.stream(self.copy):
-            self.inputs[i].copy_(host_frame, non_blocking=True)
+            for g, buf in enumerate(self.inputs[i]):
+                buf.copy_(host_frame[self.bounds[g]:self.bounds[g + 1]], non_blocking=True)
             self.copied[i].record(self.copy)
         self.uploaded += 1
 
     def step(self):
-        """Run the delta step on the oldest uploaded frame; returns the pinned host tensor the result is
-        being copied to (valid once the compute stream has been synchronised)."""
+        """Run the delta step on the oldest uploaded frame batch; returns the pinned host tensors the results
+        are being copied to (valid once the compute stream has been synchronised)."""
         assert self.stepped < self.uploaded
         i = self.stepped % 2
         self.compute.wait_event(self.copied[i])
         with torch.cuda.stream(self.compute):
             self.graphs[i].replay()
             self.consumed[i].record(self.compute)
-            self.host_out[i].copy_(self.outputs[i], non_blocking=True)
+            for dst, src in zip(self.host_out[i], self.outputs[i]):
+                dst.copy_(src, non_blocking=True)
         self.stepped += 1
         return self.host_out[i]
