@@ -94,6 +94,28 @@ __device__ __forceinline__ bool group_any(bool p, int g, int lane) {
     return (b & gm) != 0;
 }
 
+// Programmatic dependent launch: a kernel launched through launch_pdl may start while the previous kernel on
+// the stream is still draining; everything it does before grid_dep_wait() (shared-memory set-up, loading
+// constant filters) overlaps that tail, everything that reads the previous kernel's results comes after it.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    return check_launch();
+}
+
 // Sum-reduce over an aligned group of g lanes.
 __device__ __forceinline__ float group_sum(float x, int g) {
     for (int o = g >> 1; o > 0; o >>= 1) x += __shfl_xor_sync(DC_FULL, x, o);

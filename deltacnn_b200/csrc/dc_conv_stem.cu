@@ -23,11 +23,13 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
     T* out = reinterpret_cast<T*>(p.out);
     T* prev = reinterpret_cast<T*>(p.prev);
     T* trunc = reinterpret_cast<T*>(p.trunc);
+    grid_dep_launch();
     const int taps = p.kh * p.kw;
     const int kdim = taps * p.ci;
     for (int i = threadIdx.x; i < kdim * p.co; i += 256) s_w[i] = to_f<T>(reinterpret_cast<const T*>(p.w)[i]);
     float* s_b = s_w + kdim * p.co;
     for (int i = threadIdx.x; i < p.co; i += 256) s_b[i] = p.bias ? to_f<T>(reinterpret_cast<const T*>(p.bias)[i]) : 0.f;
+    grid_dep_wait();
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
@@ -162,12 +164,12 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
         p.thr = p.fused ? host_round_threshold<__half>(ep->threshold) : 0.f;
         static thread_local bool set16 = false;
         if (smem > 48 * 1024 && !set16) { cudaFuncSetAttribute(k_conv_stem<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set16 = true; }
-        k_conv_stem<__half><<<(unsigned)blocks, 256, smem, st>>>(p);
+        return launch_pdl(k_conv_stem<__half>, dim3((unsigned)blocks), dim3(256), smem, st, p);
     } else {
         p.thr = p.fused ? ep->threshold : 0.f;
         static thread_local bool set32 = false;
         if (smem > 48 * 1024 && !set32) { cudaFuncSetAttribute(k_conv_stem<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set32 = true; }
-        k_conv_stem<float><<<(unsigned)blocks, 256, smem, st>>>(p);
+        return launch_pdl(k_conv_stem<float>, dim3((unsigned)blocks), dim3(256), smem, st, p);
     }
     return check_launch();
 }

@@ -155,6 +155,8 @@ __global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
     // s_u32[0] tmem base, [1] ok flag, [3..3+warps) warp totals
     float* s_bias = reinterpret_cast<float*>(s_u32 + 12);          // [bn]
 
+    grid_dep_launch();
+    grid_dep_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar0 = smem_u32(bars);
     auto bar_slot = [&](int s) { return bar0 + 8u * s; };
@@ -615,8 +617,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         if (persistent < 1) persistent = 1;
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
     }
-    k_pw_umma<<<grid, kPwThreads, pl.smem, st>>>(p);
-    int rc = check_launch();
+    int rc = launch_pdl(k_pw_umma, grid, dim3(kPwThreads), pl.smem, st, p);
     if (rc != DC_OK) return rc;
     if (ep != nullptr && !fused)
         return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,

@@ -120,13 +120,16 @@ __global__ void __launch_bounds__(256) k_dw3x3_list(DwStripParams p, const int32
     extern __shared__ __align__(16) uint8_t smem[];
     __half* s_w = reinterpret_cast<__half*>(smem);                    // [9][C]
     __half* s_b = s_w + 9 * p.c;                                      // [C]
-    const int cnt = *count;
-    if (cnt == 0) return;
+    grid_dep_launch();
     const int npk = p.c >> 3;
+    // the filter is constant: stage it while the previous kernel (the mask scan) is still finishing
     for (int i = threadIdx.x; i < 9 * npk; i += 256)
         reinterpret_cast<uint4*>(s_w)[i] = __ldg(reinterpret_cast<const uint4*>(p.w) + i);
     for (int i = threadIdx.x; i < npk; i += 256)
         reinterpret_cast<uint4*>(s_b)[i] = p.bias ? __ldg(reinterpret_cast<const uint4*>(p.bias) + i) : make_uint4(0, 0, 0, 0);
+    grid_dep_wait();
+    const int cnt = *count;
+    if (cnt == 0) return;
     __syncthreads();
     const int lane = threadIdx.x & 31;
     int g = 1;
@@ -154,11 +157,13 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     __half* s_w = reinterpret_cast<__half*>(smem);                    // [9][C]
     __half* s_b = s_w + 9 * p.c;                                      // [C]
+    grid_dep_launch();
     const int npk = p.c >> 3;
     for (int i = threadIdx.x; i < 9 * npk; i += 256)
         reinterpret_cast<uint4*>(s_w)[i] = __ldg(reinterpret_cast<const uint4*>(p.w) + i);
     for (int i = threadIdx.x; i < npk; i += 256)
         reinterpret_cast<uint4*>(s_b)[i] = p.bias ? __ldg(reinterpret_cast<const uint4*>(p.bias) + i) : make_uint4(0, 0, 0, 0);
+    grid_dep_wait();
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
@@ -245,10 +250,10 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
         const size_t smem_l = (size_t)10 * p.c * 2;
         const unsigned grid = (unsigned)sm_count() * (nv >= 3 ? 2 : 4);
         switch (nv) {
-            case 1: k_dw3x3_list<1><<<grid, 256, smem_l, st>>>(p, count, list, taps); break;
-            case 2: k_dw3x3_list<2><<<grid, 256, smem_l, st>>>(p, count, list, taps); break;
-            case 3: k_dw3x3_list<3><<<grid, 256, smem_l, st>>>(p, count, list, taps); break;
-            default: k_dw3x3_list<4><<<grid, 256, smem_l, st>>>(p, count, list, taps); break;
+            case 1: launch_pdl(k_dw3x3_list<1>, dim3(grid), dim3(256), smem_l, st, p, count, list, taps); break;
+            case 2: launch_pdl(k_dw3x3_list<2>, dim3(grid), dim3(256), smem_l, st, p, count, list, taps); break;
+            case 3: launch_pdl(k_dw3x3_list<3>, dim3(grid), dim3(256), smem_l, st, p, count, list, taps); break;
+            default: launch_pdl(k_dw3x3_list<4>, dim3(grid), dim3(256), smem_l, st, p, count, list, taps); break;
         }
         return check_launch();
     }
@@ -263,10 +268,10 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     const int64_t cap = (int64_t)sm_count() * 8;
     if (blocks > cap) blocks = cap;
     switch (nv) {
-        case 1: k_dw3x3_strip<1><<<(unsigned)blocks, 256, smem, st>>>(p); break;
-        case 2: k_dw3x3_strip<2><<<(unsigned)blocks, 256, smem, st>>>(p); break;
-        case 3: k_dw3x3_strip<3><<<(unsigned)blocks, 256, smem, st>>>(p); break;
-        default: k_dw3x3_strip<4><<<(unsigned)blocks, 256, smem, st>>>(p); break;
+        case 1: launch_pdl(k_dw3x3_strip<1>, dim3((unsigned)blocks), dim3(256), smem, st, p); break;
+        case 2: launch_pdl(k_dw3x3_strip<2>, dim3((unsigned)blocks), dim3(256), smem, st, p); break;
+        case 3: launch_pdl(k_dw3x3_strip<3>, dim3((unsigned)blocks), dim3(256), smem, st, p); break;
+        default: launch_pdl(k_dw3x3_strip<4>, dim3((unsigned)blocks), dim3(256), smem, st, p); break;
     }
     return check_launch();
 }

@@ -11,6 +11,8 @@
 namespace dc {
 
 #define DC_PIXEL_LOOP(npix, g)                                                              \
+    grid_dep_launch();                                                                      \
+    grid_dep_wait();                                                                        \
     const int lane = threadIdx.x & 31;                                                      \
     const int lig = lane & ((g) - 1);                                                       \
     const int ppw = 32 / (g);                                                               \
@@ -74,6 +76,8 @@ __global__ void __launch_bounds__(256) k_sparsify_c3(const T* __restrict__ x, T*
                                                      int32_t* __restrict__ mask, int64_t npix, float thr) {
     constexpr int PPT = sizeof(T) == 2 ? 8 : 4;                         // pixels per thread
     constexpr int NE = PPT * 3;                                         // elements per thread (3 x 16 bytes)
+    grid_dep_launch();
+    grid_dep_wait();
     const int64_t ngroups = npix / PPT;
     for (int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gi < ngroups; gi += (int64_t)gridDim.x * blockDim.x) {
         alignas(16) T xa[NE];
@@ -432,6 +436,8 @@ __global__ void __launch_bounds__(256) k_compact_mask(const int32_t* __restrict_
                                                       int32_t* __restrict__ indices, int32_t* __restrict__ count) {
     __shared__ int warp_cnt[8];
     __shared__ int block_base;
+    grid_dep_launch();
+    grid_dep_wait();
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     for (int64_t start = (int64_t)blockIdx.x * 256; start < npix; start += (int64_t)gridDim.x * 256) {
         const int64_t px = start + threadIdx.x;
@@ -475,21 +481,21 @@ static int sparsify_t(const T* x, T* prev, T* delta, int32_t* mask, int64_t npix
             int64_t blocks = divup64(ngroups, 256);
             const int64_t cap = (int64_t)sm_count() * 16;
             if (blocks > cap) blocks = cap;
-            k_sparsify_c3<T><<<(unsigned)blocks, 256, 0, st>>>(x, prev, delta, mask, npix, t);
+            launch_pdl(k_sparsify_c3<T>, (unsigned)blocks, dim3(256), 0, st, x, prev, delta, mask, npix, t);
         }
         const int64_t done = ngroups * PPT;
         if (done < npix) {      // ragged tail: the generic kernel on the last few pixels
             const int g = lanes_per_pixel(C);
-            k_sparsify<T, 1><<<1, 256, 0, st>>>(x + done * 3, prev + done * 3, delta + done * 3, mask + done, npix - done, C, g, t);
+            launch_pdl(k_sparsify<T, 1>, 1, dim3(256), 0, st, x + done * 3, prev + done * 3, delta + done * 3, mask + done, npix - done, C, g, t);
         }
         return check_launch();
     }
     if (W == V) {
         const int g = lanes_per_pixel(C / V);
-        k_sparsify<T, V><<<pixel_grid(npix, g), 256, 0, st>>>(x, prev, delta, mask, npix, C, g, t);
+        launch_pdl(k_sparsify<T, V>, pixel_grid(npix, g), dim3(256), 0, st, x, prev, delta, mask, npix, C, g, t);
     } else {
         const int g = lanes_per_pixel(C);
-        k_sparsify<T, 1><<<pixel_grid(npix, g), 256, 0, st>>>(x, prev, delta, mask, npix, C, g, t);
+        launch_pdl(k_sparsify<T, 1>, pixel_grid(npix, g), dim3(256), 0, st, x, prev, delta, mask, npix, C, g, t);
     }
     return check_launch();
 }
@@ -505,7 +511,7 @@ static int act_trunc_t(T* delta, T* prev, T* trunc, int32_t* mask, int64_t npix,
         const int g = lanes_per_pixel(nvec);
         const int per_lane = divup(nvec, g);
         dim3 grid = pixel_grid(npix, g);
-#define DC_AT(NV) k_act_trunc<T, V, NV><<<grid, 256, 0, st>>>(delta, prev, trunc, mask, npix, C, g, t, act, mode)
+#define DC_AT(NV) launch_pdl(k_act_trunc<T, V, NV>, grid, dim3(256), 0, st, delta, prev, trunc, mask, npix, C, g, t, act, mode)
         if (per_lane <= 1) DC_AT(1);
         else if (per_lane <= 2) DC_AT(2);
         else if (per_lane <= 4) DC_AT(4);
@@ -515,8 +521,8 @@ static int act_trunc_t(T* delta, T* prev, T* trunc, int32_t* mask, int64_t npix,
     } else {
         const int g = lanes_per_pixel(C);
         dim3 grid = pixel_grid(npix, g);
-        if (divup(C, g) <= 4) k_act_trunc<T, 1, 4><<<grid, 256, 0, st>>>(delta, prev, trunc, mask, npix, C, g, t, act, mode);
-        else k_act_trunc<T, 1, 0><<<grid, 256, 0, st>>>(delta, prev, trunc, mask, npix, C, g, t, act, mode);
+        if (divup(C, g) <= 4) launch_pdl(k_act_trunc<T, 1, 4>, grid, dim3(256), 0, st, delta, prev, trunc, mask, npix, C, g, t, act, mode);
+        else launch_pdl(k_act_trunc<T, 1, 0>, grid, dim3(256), 0, st, delta, prev, trunc, mask, npix, C, g, t, act, mode);
     }
     return check_launch();
 }
@@ -526,10 +532,10 @@ static int act_trunc_t(T* delta, T* prev, T* trunc, int32_t* mask, int64_t npix,
         constexpr int V = VecTraits<T>::kVec;                                                 \
         if (pick_w<T>(C, ptrs) == V) {                                                        \
             const int g = lanes_per_pixel((C) / V);                                           \
-            KERNEL<T, V><<<pixel_grid(npix_, g), 256, 0, st>>>(__VA_ARGS__, g);               \
+            launch_pdl(KERNEL<T, V>, pixel_grid(npix_, g), dim3(256), 0, st, __VA_ARGS__, g);               \
         } else {                                                                              \
             const int g = lanes_per_pixel(C);                                                 \
-            KERNEL<T, 1><<<pixel_grid(npix_, g), 256, 0, st>>>(__VA_ARGS__, g);               \
+            launch_pdl(KERNEL<T, 1>, pixel_grid(npix_, g), dim3(256), 0, st, __VA_ARGS__, g);               \
         }                                                                                     \
     } while (0)
 
@@ -560,9 +566,9 @@ int dc_sparsify_u8(const uint8_t* x_u8, const float* scale, const float* offset,
     cudaStream_t st = (cudaStream_t)stream;
     const int g = lanes_per_pixel(channels);
     if (dtype == DC_F32)
-        k_sparsify_u8<float><<<pixel_grid(npix, g), 256, 0, st>>>(x_u8, scale, offset, (float*)prev_in, (float*)delta, mask, npix, channels, g, threshold);
+        launch_pdl(k_sparsify_u8<float>, pixel_grid(npix, g), dim3(256), 0, st, x_u8, scale, offset, (float*)prev_in, (float*)delta, mask, npix, channels, g, threshold);
     else if (dtype == DC_F16)
-        k_sparsify_u8<__half><<<pixel_grid(npix, g), 256, 0, st>>>(x_u8, scale, offset, (__half*)prev_in, (__half*)delta, mask, npix, channels, g, host_round_threshold<__half>(threshold));
+        launch_pdl(k_sparsify_u8<__half>, pixel_grid(npix, g), dim3(256), 0, st, x_u8, scale, offset, (__half*)prev_in, (__half*)delta, mask, npix, channels, g, host_round_threshold<__half>(threshold));
     else return DC_ERR_DTYPE;
     return check_launch();
 }
@@ -642,11 +648,11 @@ int dc_concat(const void* a, const void* b, void* out, const int32_t* mask_a, co
     // the vector path needs both halves to be whole packs
     if (dtype == DC_F32) {
         const int cc = (channels_a % 4 == 0 && channels_b % 4 == 0) ? ctot : 1;
-        if (cc == 1) { const int g = lanes_per_pixel(ctot); k_concat<float, 1><<<pixel_grid(npix, g), 256, 0, st>>>((const float*)a, (const float*)b, (float*)out, mask_a, mask_b, mask_out, npix, channels_a, channels_b, g); }
+        if (cc == 1) { const int g = lanes_per_pixel(ctot); launch_pdl(k_concat<float, 1>, pixel_grid(npix, g), dim3(256), 0, st, (const float*)a, (const float*)b, (float*)out, mask_a, mask_b, mask_out, npix, channels_a, channels_b, g); }
         else DC_DISPATCH_W(float, ctot, DC_PTRS(a, b, out), k_concat, npix, (const float*)a, (const float*)b, (float*)out, mask_a, mask_b, mask_out, npix, channels_a, channels_b);
     } else if (dtype == DC_F16) {
         const int cc = (channels_a % 8 == 0 && channels_b % 8 == 0) ? ctot : 1;
-        if (cc == 1) { const int g = lanes_per_pixel(ctot); k_concat<__half, 1><<<pixel_grid(npix, g), 256, 0, st>>>((const __half*)a, (const __half*)b, (__half*)out, mask_a, mask_b, mask_out, npix, channels_a, channels_b, g); }
+        if (cc == 1) { const int g = lanes_per_pixel(ctot); launch_pdl(k_concat<__half, 1>, pixel_grid(npix, g), dim3(256), 0, st, (const __half*)a, (const __half*)b, (__half*)out, mask_a, mask_b, mask_out, npix, channels_a, channels_b, g); }
         else DC_DISPATCH_W(__half, ctot, DC_PTRS(a, b, out), k_concat, npix, (const __half*)a, (const __half*)b, (__half*)out, mask_a, mask_b, mask_out, npix, channels_a, channels_b);
     } else return DC_ERR_DTYPE;
     return check_launch();
@@ -692,7 +698,7 @@ int dc_compact_mask(const int32_t* mask, int64_t npix, int32_t* indices, int32_t
     int64_t blocks = divup64(npix, 256);
     const int64_t cap = (int64_t)sm_count() * 8;
     if (blocks > cap) blocks = cap;
-    k_compact_mask<<<(unsigned)blocks, 256, 0, st>>>(mask, npix, indices, count);
+    launch_pdl(k_compact_mask, dim3((unsigned)blocks), dim3(256), 0, st, mask, npix, indices, count);
     return check_launch();
 }
 

@@ -16,6 +16,8 @@ template <typename T, int W>
 __global__ void __launch_bounds__(256) k_pool(const T* __restrict__ in, const T* __restrict__ prev,
                                               const int32_t* __restrict__ mi, T* __restrict__ out,
                                               int32_t* __restrict__ mo, PoolGeom p, int mode, int g) {
+    grid_dep_launch();
+    grid_dep_wait();
     const int nvec = p.c / W;
     const int64_t npix = (int64_t)p.n * p.ho * p.wo;
     const int lane = threadIdx.x & 31;
@@ -112,6 +114,8 @@ __global__ void __launch_bounds__(128) k_global_avg(const T* __restrict__ in, co
                                                     T* __restrict__ out, int32_t* __restrict__ mo, int hw, int C) {
     __shared__ int32_t s_mask[1024];
     __shared__ int s_any;
+    grid_dep_launch();
+    grid_dep_wait();
     const int b = blockIdx.y;
     const int nvec = C / W;
     const int vec = blockIdx.x * blockDim.x + threadIdx.x;
@@ -164,10 +168,10 @@ static int pool_t(const dc_conv_desc* d, const T* in, T* prev, const int32_t* mi
         const int hw = d->h_in * d->w_in;
         if (vec_ok) {
             dim3 grid(divup(C / V, 128), d->n);
-            k_global_avg<T, V><<<grid, 128, 0, st>>>(in, mi, out, mo, hw, C);
+            launch_pdl(k_global_avg<T, V>, grid, dim3(128), 0, st, in, mi, out, mo, hw, C);
         } else {
             dim3 grid(divup(C, 128), d->n);
-            k_global_avg<T, 1><<<grid, 128, 0, st>>>(in, mi, out, mo, hw, C);
+            launch_pdl(k_global_avg<T, 1>, grid, dim3(128), 0, st, in, mi, out, mo, hw, C);
         }
         return check_launch();
     }
@@ -178,8 +182,8 @@ static int pool_t(const dc_conv_desc* d, const T* in, T* prev, const int32_t* mi
     int64_t blocks = divup64(divup64(npix, 32 / g), 8);
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    if (vec_ok) k_pool<T, V><<<(unsigned)blocks, 256, 0, st>>>(in, prev, mi, out, mo, p, mode, g);
-    else k_pool<T, 1><<<(unsigned)blocks, 256, 0, st>>>(in, prev, mi, out, mo, p, mode, g);
+    if (vec_ok) launch_pdl(k_pool<T, V>, dim3((unsigned)blocks), dim3(256), 0, st, in, prev, mi, out, mo, p, mode, g);
+    else launch_pdl(k_pool<T, 1>, dim3((unsigned)blocks), dim3(256), 0, st, in, prev, mi, out, mo, p, mode, g);
     return check_launch();
 }
 

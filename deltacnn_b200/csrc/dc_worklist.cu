@@ -19,6 +19,8 @@ struct ScanParams {
 __global__ void __launch_bounds__(256) k_scan_conv_mask(ScanParams p) {
     __shared__ int s_warp[8];
     __shared__ int s_base;
+    grid_dep_launch();
+    grid_dep_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
     for (uint32_t start = blockIdx.x * 256u; start < npix; start += gridDim.x * 256u) {
@@ -88,8 +90,7 @@ int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* 
     int64_t blocks = divup64(npix, 256);
     const int64_t cap = (int64_t)sm_count() * 32;
     if (blocks > cap) blocks = cap;
-    k_scan_conv_mask<<<(unsigned)blocks, 256, 0, st>>>(p);
-    return check_launch();
+    return launch_pdl(k_scan_conv_mask, dim3((unsigned)blocks), dim3(256), 0, st, p);
 }
 
 }  // namespace dc
@@ -109,6 +110,8 @@ struct ScanDeconvParams {
 __global__ void __launch_bounds__(256) k_scan_deconv_mask(ScanDeconvParams p) {
     __shared__ int s_warp[4][8];
     __shared__ int s_base[4];
+    grid_dep_launch();
+    grid_dep_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
     for (uint32_t start = blockIdx.x * 256u; start < npix; start += gridDim.x * 256u) {
@@ -179,8 +182,7 @@ int scan_deconv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void
     int64_t blocks = divup64(npix, 256);
     const int64_t cap = (int64_t)sm_count() * 32;
     if (blocks > cap) blocks = cap;
-    k_scan_deconv_mask<<<(unsigned)blocks, 256, 0, st>>>(p);
-    return check_launch();
+    return launch_pdl(k_scan_deconv_mask, dim3((unsigned)blocks), dim3(256), 0, st, p);
 }
 
 }  // namespace dc
