@@ -1,7 +1,7 @@
 """One kernel of the delta path on a fixed, seeded, benchmark-shaped input, a few launches: the
 small case that profiler captures are taken on (inputs larger than L2, well under 1 GB on the device).
 
-    python examples/kernel_case.py pw     # tcgen05 pointwise 16->96 @112x112, fused ReLU6 + truncation, 32 streams
+    python examples/kernel_case.py pw     # tcgen05 pointwise 16->96 @112x112, fused ReLU6 + truncation, 32 streams (work-list mode)
     python examples/kernel_case.py dw     # depthwise 3x3 96 ch @112x112 stride 2, fused ReLU6 + truncation, 32 streams
     python examples/kernel_case.py act    # stand-alone activation/truncation, 96 ch @112x112, 32 streams
 Prints the CUDA-event time per launch (L2 flushed between launches) and the algorithmic GB/s.
@@ -50,8 +50,10 @@ def main():
         out = torch.empty_like(prev)
         om = torch.empty(n, 1, h, w, dtype=torch.int32, device="cuda")
         ep = K.make_epilogue(prev, trunc, 0.02, 2, 0)
+        d2 = K.make_conv_desc(tuple(x.shape), cout, (h, w), (1, 1), (1, 1), (0, 0), (1, 1), 1, 1)
+        ws = torch.zeros(K.conv_workspace_bytes(d2), dtype=torch.uint8, device="cuda")
         run = lambda: K.sparse_conv(x, f, mask, None, (1, 1), (0, 0), (1, 1), 1, create_out_mask=True, out=out, out_mask=om,
-                                    filter_umma=packed, epilogue=ep)
+                                    filter_umma=packed, epilogue=ep, workspace=ws)
         act_px = int(mask.sum())
         nbytes = 2 * (act_px * cin + cin * cout) + 2 * cout * 5 * act_px + 8 * mask.numel()
     elif which == "dw":
@@ -66,7 +68,10 @@ def main():
         out = torch.empty_like(prev)
         om = torch.empty(n, 1, ho, ho, dtype=torch.int32, device="cuda")
         ep = K.make_epilogue(prev, trunc, 0.02, 2, 0)
-        run = lambda: K.sparse_conv(x, f, mask, None, (s, s), (1, 1), (1, 1), c, create_out_mask=True, out=out, out_mask=om, epilogue=ep)
+        d2 = K.make_conv_desc(tuple(x.shape), c, (ho, ho), (3, 3), (s, s), (1, 1), (1, 1), c, 1)
+        ws = torch.zeros(K.conv_workspace_bytes(d2), dtype=torch.uint8, device="cuda")
+        run = lambda: K.sparse_conv(x, f, mask, None, (s, s), (1, 1), (1, 1), c, create_out_mask=True, out=out, out_mask=om, epilogue=ep,
+                                    workspace=ws)
         run()
         nbytes = 2 * c * (int(mask.sum()) + 5 * int((torch.nn.functional.max_pool2d(mask.float(), 3, s, 1) > 0).sum())) + 4 * (mask.numel() + om.numel())
     else:
