@@ -106,19 +106,22 @@ __global__ void __launch_bounds__(256) k_pool(const T* __restrict__ in, const T*
     }
 }
 
-// Global average pool: one CTA per (image, slab of channel packs); every thread owns one
-// pack of channels and walks the image's active pixels in index order, so the fp32 sum is
-// reproducible. The image's mask is staged in shared memory in chunks.
+// Global average pool: one CTA per (image, slab of 32 channel packs). The 256 threads are 8 pixel lanes x 32
+// packs: lane j sums the active pixels j, j+8, ... of its pack in fp32, then the eight partial sums are
+// added in a fixed order through shared memory, so the result is reproducible (the reference uses float
+// atomics). The image's mask is staged in shared memory in chunks.
 template <typename T, int W>
-__global__ void __launch_bounds__(128) k_global_avg(const T* __restrict__ in, const int32_t* __restrict__ mi,
+__global__ void __launch_bounds__(256) k_global_avg(const T* __restrict__ in, const int32_t* __restrict__ mi,
                                                     T* __restrict__ out, int32_t* __restrict__ mo, int hw, int C) {
     __shared__ int32_t s_mask[1024];
+    __shared__ float s_part[8][32][W];
     __shared__ int s_any;
     grid_dep_launch();
     grid_dep_wait();
     const int b = blockIdx.y;
     const int nvec = C / W;
-    const int vec = blockIdx.x * blockDim.x + threadIdx.x;
+    const int pk = threadIdx.x & 31, pl = threadIdx.x >> 5;           // pack inside the slab, pixel lane
+    const int vec = blockIdx.x * 32 + pk;
     float acc[W];
 #pragma unroll
     for (int k = 0; k < W; ++k) acc[k] = 0.f;
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(128) k_global_avg(const T* __restrict__ in, co
         if (any) s_any = 1;
         __syncthreads();
         if (vec < nvec) {
-            for (int i = 0; i < cnt; ++i) {
+            for (int i = pl; i < cnt; i += 8) {
                 if (s_mask[i] == 0) continue;
                 Pack<T, W> v;
                 v.load(in + ((int64_t)b * hw + p0 + i) * C + vec * W);
@@ -144,12 +147,19 @@ __global__ void __launch_bounds__(128) k_global_avg(const T* __restrict__ in, co
             }
         }
     }
+#pragma unroll
+    for (int k = 0; k < W; ++k) s_part[pl][pk][k] = acc[k];
     __syncthreads();
-    if (vec < nvec) {
+    if (pl == 0 && vec < nvec) {
         Pack<T, W> o;
         const float inv = 1.f / (float)hw;
 #pragma unroll
-        for (int k = 0; k < W; ++k) o.set(k, acc[k] * inv);
+        for (int k = 0; k < W; ++k) {
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += s_part[j][pk][k];
+            o.set(k, sum * inv);
+        }
         o.store(out + (int64_t)b * C + vec * W);
     }
     if (mo != nullptr && blockIdx.x == 0 && threadIdx.x == 0) mo[b] = s_any;
@@ -167,11 +177,11 @@ static int pool_t(const dc_conv_desc* d, const T* in, T* prev, const int32_t* mi
     if (global) {
         const int hw = d->h_in * d->w_in;
         if (vec_ok) {
-            dim3 grid(divup(C / V, 128), d->n);
-            launch_pdl(k_global_avg<T, V>, grid, dim3(128), 0, st, in, mi, out, mo, hw, C);
+            dim3 grid(divup(C / V, 32), d->n);
+            launch_pdl(k_global_avg<T, V>, grid, dim3(256), 0, st, in, mi, out, mo, hw, C);
         } else {
-            dim3 grid(divup(C, 128), d->n);
-            launch_pdl(k_global_avg<T, 1>, grid, dim3(128), 0, st, in, mi, out, mo, hw, C);
+            dim3 grid(divup(C, 32), d->n);
+            launch_pdl(k_global_avg<T, 1>, grid, dim3(256), 0, st, in, mi, out, mo, hw, C);
         }
         return check_launch();
     }

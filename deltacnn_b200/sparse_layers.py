@@ -487,8 +487,41 @@ class DCSparsify(DCModule):
         self.frame_idx = -1
         self.mask = None
         self._delta = None
+        self._u8 = None
+
+    def set_u8_input(self, scale=1.0 / 255.0, offset=0.0, dtype=torch.float16, channels=3):
+        """Accept 8-bit frames: ``forward`` then takes a contiguous uint8 tensor of shape (N, H, W, C) and
+        the value compared and cached is ``frame * scale[c] + offset[c]`` in ``dtype``; normalisation, delta
+        and mask are one kernel. ``scale`` / ``offset`` are numbers or per-channel sequences."""
+        def vec(v):
+            t = torch.as_tensor(v, dtype=torch.float32).flatten()
+            return t.expand(channels).contiguous() if t.numel() == 1 else t.contiguous()
+        self._u8 = (vec(scale), vec(offset), dtype)
+        return self
+
+    def _u8_to_float(self, frame):
+        scale, offset, dtype = self._u8
+        if scale.device != frame.device:
+            scale, offset = scale.to(frame.device), offset.to(frame.device)
+            self._u8 = (scale, offset, dtype)
+        x = (frame.float() * scale + offset).to(dtype)                 # N,H,W,C contiguous
+        return x.permute(0, 3, 1, 2)                                   # logical NCHW, channels-last memory
 
     def forward(self, input):
+        if input.dtype == torch.uint8:
+            if self._u8 is None:
+                raise RuntimeError("DCSparsify got a uint8 frame: call set_u8_input() first")
+            if DCConv2d.backend != DCBackend.deltacnn or self.idx == -1 or self.dilation > 1:
+                return self.forward(self._u8_to_float(input))
+            self.frame_idx += 1
+            n, h, w, c = input.shape
+            if self.mask is None or self.mask.shape[0] != n:
+                self.mask = torch.empty((n, 1, h, w), dtype=torch.int, device=input.device)
+            if self._delta is None or self._delta.shape[0] != n or not DCConv2d.reuse_buffers:
+                self._delta = torch.empty_like(self.prev_in)
+            scale, offset, _ = self._u8
+            K.sparsify_u8(input, scale, offset, self.prev_in, self._delta, self.mask, DCThreshold.get(self))
+            return self._delta, self.mask
         if DCConv2d.backend == DCBackend.cudnn:
             return input
         if DCConv2d.backend != DCBackend.deltacnn:

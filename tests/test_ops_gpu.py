@@ -606,3 +606,31 @@ def test_deconv_umma_matches_oracle(cin, cout, k, p, n, h, w, density, fused):
     assert torch.equal(m1, m2) and torch.equal(p1, p2) and torch.equal(t1, t2)
     sel = (m1 != 0).expand_as(o1)
     assert torch.equal(o1[sel], o2[sel])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sparsify_u8_ingest_matches_float_path(dtype):
+    """8-bit frames through DCSparsify.set_u8_input(): same masks, deltas and cache as normalising with
+    torch first and feeding the float frame."""
+    from deltacnn_b200 import DCSparsify, DCThreshold
+    g = torch.Generator().manual_seed(81)
+    n, h, w = 3, 30, 34
+    frames = torch.randint(0, 256, (4, n, h, w, 3), generator=g, dtype=torch.uint8)
+    frames[1:] = frames[0]
+    frames[1, :, 5:12, 7:20] += 40
+    frames[2] = frames[1]
+    frames[2, :, 15:18, :] -= 9
+    frames[3] = frames[2]
+    frames = frames.cuda()
+    a, b = DCSparsify(delta_threshold=0.05).set_u8_input(1.0 / 255.0, 0.0, dtype), DCSparsify(delta_threshold=0.05)
+    for t in range(4):
+        xf = (frames[t].float() * (1.0 / 255.0)).to(dtype).permute(0, 3, 1, 2)
+        d1, m1 = a(frames[t])
+        d2, m2 = b(xf)
+        assert torch.equal(m1, m2), t
+        sel = (m2 != 0).expand_as(d2)
+        assert torch.equal(d1[sel], d2[sel])
+        assert torch.equal(a.prev_in, b.prev_in)
+        if t > 0:
+            assert 0 < int(m1.sum()) < m1.numel() or t == 3
+    assert len(DCThreshold.t) == 2
