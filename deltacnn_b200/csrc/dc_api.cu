@@ -36,6 +36,8 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
 size_t filter_umma_bytes(const dc_conv_desc* d, int transposed);
 int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, void* packed, cudaStream_t st);
 int umma_error_code();
+int conv_thin(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+              int32_t* mo, cudaStream_t st);
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
@@ -93,7 +95,8 @@ int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_i
     if (rc != DC_ERR_UNSUPPORTED) return rc;
     rc = conv_stem(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;
-    rc = conv2d_simt(desc, in, mask_in, filter, bias, out, mask_out, st);
+    rc = conv_thin(desc, in, mask_in, filter, bias, out, mask_out, st);
+    if (rc == DC_ERR_UNSUPPORTED) rc = conv2d_simt(desc, in, mask_in, filter, bias, out, mask_out, st);
     if (rc != DC_OK) return rc;
     return run_epilogue(desc, out, mask_out, epilogue, stream);
 }

@@ -1,0 +1,91 @@
+// Pointwise delta convolution with very few output channels (detection / pose heads: 64 -> 1, 64 -> 2,
+// 32 -> 17): too thin for a tensor-core tile, pure bandwidth. An aligned lane group per active pixel reads
+// the pixel's channel packs (16 bytes per lane), every lane forms its partial dot products with the filter
+// held in shared memory as fp32, and the group reduces them with shuffles.
+#include "dc_common.cuh"
+
+namespace dc {
+
+constexpr int kThinMaxCout = 32;
+
+template <typename T, int W>
+__global__ void __launch_bounds__(256) k_conv_thin(const T* __restrict__ in, const int32_t* __restrict__ mi,
+                                                   const T* __restrict__ filt, const T* __restrict__ bias,
+                                                   T* __restrict__ out, int32_t* __restrict__ mo, int64_t npix, int cin,
+                                                   int cout, int g) {
+    extern __shared__ float s_w[];                               // [cin][cout], then bias [cout]
+    grid_dep_launch();
+    for (int i = threadIdx.x; i < cin * cout; i += 256) s_w[i] = to_f<T>(filt[i]);
+    float* s_b = s_w + cin * cout;
+    for (int i = threadIdx.x; i < cout; i += 256) s_b[i] = bias ? to_f<T>(bias[i]) : 0.f;
+    grid_dep_wait();
+    __syncthreads();
+    const int nvec = cin / W;
+    const int lane = threadIdx.x & 31;
+    const int lig = lane & (g - 1);
+    const int ppw = 32 / g;
+    const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * 8;
+    for (int64_t base = warp0 * ppw; base < npix; base += nwarps * ppw) {
+        const int64_t px = base + lane / g;
+        const bool on = px < npix && mi[px] != 0;
+        if (px < npix && lig == 0) mo[px] = on ? 1 : 0;
+        if (__ballot_sync(DC_FULL, on) == 0) continue;
+        float acc[kThinMaxCout];
+#pragma unroll
+        for (int co = 0; co < kThinMaxCout; ++co) acc[co] = 0.f;
+        if (on) {
+            for (int i = lig; i < nvec; i += g) {
+                Pack<T, W> v;
+                v.load(in + px * cin + i * W);
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    const float a = v.get(k);
+                    const float* wr = s_w + (i * W + k) * cout;
+#pragma unroll
+                    for (int co = 0; co < kThinMaxCout; ++co)
+                        if (co < cout) acc[co] = fmaf(a, wr[co], acc[co]);
+                }
+            }
+        }
+#pragma unroll
+        for (int co = 0; co < kThinMaxCout; ++co) {
+            if (co >= cout) break;
+            const float s = group_sum(acc[co], g);
+            if (on && (co % g) == lig) out[px * cout + co] = from_f<T>(s + s_b[co]);
+        }
+    }
+}
+
+// 1x1, stride 1, no padding, groups 1, at most 32 output channels, with in- and out-mask.
+int conv_thin(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+              int32_t* mo, cudaStream_t st) {
+    const bool ok = d->kh == 1 && d->kw == 1 && d->stride_h == 1 && d->stride_w == 1 && d->groups == 1 && d->pad_top == 0 &&
+                    d->pad_left == 0 && d->pad_bottom == 0 && d->pad_right == 0 && d->c_out <= kThinMaxCout &&
+                    (d->c_out % 8 != 0 || d->c_out < 16) && d->c_in >= 8 && mi != nullptr && mo != nullptr;
+    if (!ok) return DC_ERR_UNSUPPORTED;
+    const int64_t npix = (int64_t)d->n * d->h_out * d->w_out;
+    if (npix == 0) return DC_OK;
+    const size_t smem = sizeof(float) * ((size_t)d->c_in * d->c_out + d->c_out);
+    if (smem > 48 * 1024) return DC_ERR_UNSUPPORTED;
+    auto launch = [&](auto kernel, int nvec, auto* tin, auto* tf, auto* tb, auto* tout) {
+        const int g = lanes_per_pixel(nvec);
+        int64_t blocks = divup64(divup64(npix, 32 / g), 8);
+        const int64_t cap = (int64_t)sm_count() * 16;
+        if (blocks > cap) blocks = cap;
+        return launch_pdl(kernel, dim3((unsigned)blocks), dim3(256), smem, st, tin, mi, tf, tb, tout, mo, npix, d->c_in, d->c_out, g);
+    };
+    if (d->dtype == DC_F16) {
+        const bool vec = d->c_in % 8 == 0 && aligned16(in);
+        if (vec) return launch(k_conv_thin<__half, 8>, d->c_in / 8, (const __half*)in, (const __half*)filt, (const __half*)bias, (__half*)out);
+        return launch(k_conv_thin<__half, 1>, d->c_in, (const __half*)in, (const __half*)filt, (const __half*)bias, (__half*)out);
+    }
+    if (d->dtype == DC_F32) {
+        const bool vec = d->c_in % 4 == 0 && aligned16(in);
+        if (vec) return launch(k_conv_thin<float, 4>, d->c_in / 4, (const float*)in, (const float*)filt, (const float*)bias, (float*)out);
+        return launch(k_conv_thin<float, 1>, d->c_in, (const float*)in, (const float*)filt, (const float*)bias, (float*)out);
+    }
+    return DC_ERR_DTYPE;
+}
+
+}  // namespace dc

@@ -634,3 +634,23 @@ def test_sparsify_u8_ingest_matches_float_path(dtype):
         if t > 0:
             assert 0 < int(m1.sum()) < m1.numel() or t == 3
     assert len(DCThreshold.t) == 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cin,cout", [(64, 1), (64, 2), (32, 17), (256, 5), (20, 3)])
+@pytest.mark.parametrize("density", [0.0, 0.2, 1.0])
+def test_thin_pointwise_conv(dtype, cin, cout, density):
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    g = torch.Generator().manual_seed(91)
+    n, h, w = 2, 17, 23
+    x = rand_feat(g, n, cin, h, w, dtype)
+    mask = rand_mask(g, n, h, w, density)
+    wt = (torch.randn(cout, cin, 1, 1, generator=g) / cin ** 0.5).to(dtype)
+    bias = torch.randn(cout, generator=g).to(dtype)
+    ref, m_ref = O.conv(x, mask, wt, bias, (1, 1), (0, 0), (1, 1), 1)
+    xd = x.cuda()
+    xd[(mask == 0).expand_as(x)] = float("nan")
+    out, om = K().sparse_conv(xd, convert_filter_out_channels_last(wt).cuda(), mask.cuda(), bias.cuda(), (1, 1), (0, 0), (1, 1), 1,
+                              create_out_mask=True)
+    assert torch.equal(om.cpu(), m_ref)
+    assert_close_masked(out, ref, m_ref, dtype, "thin conv")
