@@ -31,6 +31,7 @@ constexpr int kMaxResidentKB = 16;
 constexpr int kPwThreads = 256;
 constexpr int kPwWarps = kPwThreads / 32;
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr int64_t kListMinPixels = 40000;    // below this many output pixels 1x1 layers skip the work list
 
 struct PwParams {
     const __half* in; const int32_t* mi; const uint8_t* wimg; const __half* bias;
@@ -139,7 +140,7 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 // ---- kernel -----------------------------------------------------------------------------------
 // Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
 //                [ row lists ][ mbarriers, scalars, bias ]
-__global__ void __launch_bounds__(kPwThreads, 2) k_pw_umma(PwParams p) {
+__global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
@@ -574,6 +575,9 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     if (npix_out == 0) return DC_OK;
     if ((int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
     const bool want_fused = ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
+    // A work list costs two extra launches (counter reset + scan). It pays when the active set is large and
+    // clustered; small maps keep the single-kernel form (1x1 only: each CTA compacts its own span of pixels).
+    if (ws != nullptr && !transposed && pl.taps == 1 && d->pad_top == 0 && d->pad_left == 0 && npix_out < kListMinPixels) ws = nullptr;
     if (transposed) {                 // the kernel sees one phase: m x m taps
         pl.taps = (d->kh / 2) * (d->kw / 2);
         pl.nkb = pl.taps * pl.ncb;
@@ -613,7 +617,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         p.wl_list = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(ws) + 16);
         p.wl_taps = p.wl_list + (transposed ? 4 * npix_out : npix_out);
         if (transposed) grid.z = 4;
-        int64_t persistent = (int64_t)sm_count() * 4 / pl.ntiles;
+        int64_t persistent = (int64_t)sm_count() * 3 / pl.ntiles;     // three CTAs of this kernel fit on an SM
         if (persistent < 1) persistent = 1;
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
     }

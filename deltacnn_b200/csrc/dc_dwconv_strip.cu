@@ -241,7 +241,8 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     const int npk = p.c / 8;
     const int nv = divup(npk, 32);
     const size_t smem = (size_t)10 * p.c * 2;
-    if (ws != nullptr) {            // work-list form: one scan pass, then persistent warps over the active pixels
+    // the work list costs two extra launches; it pays on large maps where the active pixels cluster
+    if (ws != nullptr && npix >= 40000) {             // work-list form: one scan pass, then persistent warps over the active pixels
         int rc = scan_conv_mask(d, mi, mo, ws, ws_bytes, p.fused, st);
         if (rc != DC_OK) return rc;
         const int32_t* count = reinterpret_cast<const int32_t*>(ws);
