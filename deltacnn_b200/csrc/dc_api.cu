@@ -1,5 +1,6 @@
 // C-ABI plumbing: status strings, launch-error bookkeeping, and the convolution entry
 // points that choose between the tensor-core and the CUDA-core kernels.
+#include <cstdlib>
 #include "dc_common.cuh"
 
 namespace dc {
@@ -17,6 +18,11 @@ int sm_count() {
         cached_dev = dev;
     }
     return cached;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] { const char* e = getenv("DC_NO_PDL"); return !(e != nullptr && e[0] == '1'); }();
+    return on;
 }
 
 int check_launch() {

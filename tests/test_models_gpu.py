@@ -126,3 +126,59 @@ def test_nonzero_thresholds_bounded_error_and_graph_replay():
             assert _rel(out, eager[t - 1]) < 1e-3
         ref = dense(xs[3])
         assert _rel(eager[2], ref) < 0.5, "thresholded output drifted far from the dense network"
+
+
+def test_config1_mobilenet_fp32_64_frames_no_drift_and_threshold_005():
+    """The reference-runnable configuration: MobileNetV2 fp32, batch 1, 64 frames of the seeded video.
+    Threshold 0: every frame within 1e-4 of the dense network (no error accumulation over the stream).
+    Threshold 0.05 everywhere: masks become sparse and the output stays close to the dense network;
+    the CUDA path tracks the CPU oracle network on the same frames."""
+    from deltacnn_b200 import DCThreshold
+    from examples.nets import build_pair
+    from oracle.delta_net import build_oracle_net, Thresholds
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    frames = _frames("mobilenet", 0, 64)
+    dense_cpu, _ = build_pair("mobilenet", frames[:8], device="cpu")
+    dense, delta = build_pair("mobilenet", frames[:8], device="cuda")
+    worst = 0.0
+    with torch.no_grad():
+        for t in range(64):
+            x = frames[t:t + 1].cuda().contiguous(memory_format=torch.channels_last)
+            e = _rel(delta(x), dense(x))
+            worst = max(worst, e)
+            assert e <= 1e-4, f"frame {t}: {e:.3e}"
+    # threshold 0.05 on every layer
+    DCThreshold.reset()
+    DCThreshold.t_default = 0.05
+    _, delta2 = build_pair("mobilenet", frames[:8], device="cuda")
+    oracle = build_oracle_net("mobilenet", dense_cpu.state_dict())
+    Thresholds.default = 0.05
+    errs, dens, vs_oracle = [], [], []
+    with torch.no_grad():
+        for t in range(12):
+            x = frames[t:t + 1]
+            got = delta2(x.cuda().contiguous(memory_format=torch.channels_last))
+            ref = dense_cpu(x)
+            want = oracle(x)
+            errs.append(_rel(got.cpu(), ref))
+            vs_oracle.append(_rel(got.cpu(), want))
+            if t > 0:
+                dens.append(float(delta2.sparsify.mask.float().mean().item()))
+                assert torch.equal(delta2.sparsify.mask.cpu(), (oracle.sparsify.prev_in is not None) and _oracle_input_mask(oracle, frames, t))
+    assert 0.02 < sum(dens) / len(dens) < 0.3
+    assert max(errs) < 0.5
+    assert max(vs_oracle) < 5e-2, f"CUDA path vs CPU oracle network at threshold 0.05: {max(vs_oracle):.3e}"
+    DCThreshold.t_default = 0.0
+
+
+def _oracle_input_mask(oracle, frames, t):
+    """Input update mask of frame t recomputed from the oracle's rule on the frames themselves."""
+    prev = frames[0:1].clone()
+    mask = None
+    for k in range(1, t + 1):
+        d = frames[k:k + 1] - prev
+        mask = (d.abs() > 0.05).any(dim=1, keepdim=True)
+        sel = mask.expand_as(prev)
+        prev[sel] = frames[k:k + 1][sel]
+    return mask.to(torch.int32)
