@@ -15,6 +15,10 @@ int sm_count() {
     if (dev != cached_dev) {
         int v = 0;
         if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) cached = v;
+        // DC_GRID_SHARE=k sizes every grid for 1/k of the SMs, for callers that run k kernels side by side
+        const char* e = getenv("DC_GRID_SHARE");
+        const int share = e != nullptr ? atoi(e) : 1;
+        if (share > 1 && cached / share >= 1) cached /= share;
         cached_dev = dev;
     }
     return cached;

@@ -157,7 +157,6 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     float* s_bias = reinterpret_cast<float*>(s_u32 + 12);          // [bn]
 
     grid_dep_launch();
-    grid_dep_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar0 = smem_u32(bars);
     auto bar_slot = [&](int s) { return bar0 + 8u * s; };
@@ -176,6 +175,24 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
         return (size_t)t * p.ncb + cb;
     };
 
+    // ---- set-up that reads nothing the previous kernel wrote: overlaps that kernel's tail ----
+    if (tid == 0) {
+        for (int i = 0; i < kStages + kMaxResidentKB + 1; ++i) mbar_init(bar0 + 8u * i, 1);
+        fence_barrier_init();
+        s_u32[1] = 1;
+    }
+    for (int i = tid; i < p.bn; i += kPwThreads) s_bias[i] = (p.bias != nullptr && i < ncols) ? __half2float(p.bias[n0 + i]) : 0.f;
+    if (warp == 0) tmem_alloc(smem_u32(&s_u32[0]), (uint32_t)p.tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_u32[0];
+    auto leave = [&]() {                   // nothing to do for this CTA: give the tensor memory back
+        __syncthreads();
+        if (warp == 0) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    };
+    grid_dep_wait();
+
     // ---- compaction of the span's active pixels, one pass (order preserved) ----
     const bool list_mode = p.wl_list != nullptr;
     const int64_t hw_out = (int64_t)p.ho * p.wo;
@@ -183,7 +200,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     int cnt = 0;
     if (list_mode) {
         cnt = p.wl_count[blockIdx.z];
-        if ((int64_t)blockIdx.x * kRows >= cnt) return;            // persistent CTAs beyond the work
+        if ((int64_t)blockIdx.x * kRows >= cnt) { leave(); return; }   // persistent CTAs beyond the work
     } else {
     const int spt = max(1, p.span / kPwThreads);                   // consecutive pixels per thread (1..8)
     int pin[8];
@@ -227,7 +244,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     int slot0 = incl - mine_cnt;
     for (int w = 0; w < warp; ++w) slot0 += s_u32[3 + w];
     for (int w = 0; w < kPwWarps; ++w) cnt += (int)s_u32[3 + w];
-    if (cnt == 0) return;                 // nothing active in this span: no barriers, no tensor memory
+    if (cnt == 0) { leave(); return; }    // nothing active in this span
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         if (bits & (1u << j)) {
@@ -239,23 +256,12 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     }   // span mode
 
     const uint32_t b_block_bytes = (uint32_t)p.bn * 128u;
-    if (tid == 0) {
-        for (int i = 0; i < kStages + kMaxResidentKB + 1; ++i) mbar_init(bar0 + 8u * i, 1);
-        fence_barrier_init();
-        s_u32[1] = 1;
-        if (p.b_resident) {               // the whole filter slab of this CTA, one bulk copy per K block
-            for (int kb = 0; kb < p.nkb; ++kb) {
-                mbar_expect_tx(bar_bfull(kb), b_block_bytes);
-                bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(kb));
-            }
+    if (tid == 0 && p.b_resident) {       // the whole filter slab of this CTA, one bulk copy per K block
+        for (int kb = 0; kb < p.nkb; ++kb) {
+            mbar_expect_tx(bar_bfull(kb), b_block_bytes);
+            bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(kb));
         }
     }
-    for (int i = tid; i < p.bn; i += kPwThreads) s_bias[i] = (p.bias != nullptr && i < ncols) ? __half2float(p.bias[n0 + i]) : 0.f;
-    if (warp == 0) tmem_alloc(smem_u32(&s_u32[0]), (uint32_t)p.tmem_cols);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = s_u32[0];
 
     const uint32_t idesc = make_idesc(p.bn);
     const int row_in_pass = tid >> 3, chunk = tid & 7;
@@ -456,7 +462,8 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
         tc_fence_after();
     }
 
-    // drain: every MMA that was issued has to finish before tensor memory is released
+    // drain: copies in flight and every MMA that was issued have to finish before shared and tensor memory are released
+    cp_async_wait_pending(0);
     if (!ok && tid == 0) {
         for (int s = 0; s < kStages; ++s) { (void)mbar_try_wait(bar_slot(s), 0); }
     }
