@@ -332,6 +332,17 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
             }
             __syncthreads();
         }
+        if (p.fused) {
+            // the epilogue will read the two cache rows of every active pixel: start pulling them towards L2 now,
+            // so that those reads do not wait on HBM after the accumulator is ready
+            const int lines = (ncols * 2 + 127) >> 7;                 // 128-byte lines per row
+            for (int i = tid; i < cnt_t * lines; i += kPwThreads) {
+                const int r = i / lines, l = i - r * lines;
+                const int64_t e_off = (q0 + s_out[t0 + r]) * p.cout + n0 + l * 64;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p.prev + e_off));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p.trunc + e_off));
+            }
+        }
         const int it0 = tile * p.nkb;
         // every MMA of the previous tile has completed (accumulator barrier), so the first stages are free
         for (int d = 0; d < kPrefetch && d < p.nkb; ++d) issue_block(t0, cnt_t, d, it0 + d);

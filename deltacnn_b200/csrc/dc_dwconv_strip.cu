@@ -37,6 +37,19 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const __half* s
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[j][k] = bb.get(k);
     }
+    const int64_t off = qq * p.c;
+    // the two cache reads do not depend on the convolution: issue them first so that they are in flight
+    // while the taps are loaded and multiplied
+    Pack<__half, 8> pe[NV], pu[NV], pr[NV];
+    if (p.fused && on) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = lig + j * g;
+            if (i >= npk) continue;
+            pu[j].load(p.prev + off + i * 8);
+            pr[j].load(p.trunc + off + i * 8);
+        }
+    }
     if (on) {
 #pragma unroll
         for (int t9 = 0; t9 < 9; ++t9) {
@@ -54,7 +67,6 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const __half* s
             }
         }
     }
-    const int64_t off = qq * p.c;
     if (!p.fused) {
         if (on) {
 #pragma unroll
@@ -69,16 +81,8 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const __half* s
         }
         return;
     }
-    Pack<__half, 8> pe[NV], pu[NV], pr[NV];
     bool hit = false;
     if (on) {
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int i = lig + j * g;
-            if (i >= npk) continue;
-            pu[j].load(p.prev + off + i * 8);
-            pr[j].load(p.trunc + off + i * 8);
-        }
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             const int i = lig + j * g;
