@@ -70,6 +70,62 @@ __device__ __forceinline__ float act_apply(float x, int code) {
     }
 }
 
+// Activations whose value at a half-precision argument is itself a half: their deltas can be formed in
+// packed half arithmetic without changing a bit (identity, ReLU, ReLU6).
+__device__ __forceinline__ bool act_exact_in_half(int code) { return code >= DC_ACT_NONE && code <= DC_ACT_RELU6; }
+
+// Accumulate + activation delta + threshold test of one 16-byte pack of fp16 channels.
+//   in:  d = incoming delta, y = accumulated pre-activation value, tr = carried residual
+//   out: tr = residual + delta, y = y + tr, d = f(y_new) - f(y_old); returns |d| > thr for any channel.
+// Packed-half form: adding or subtracting two halves in fp32 and rounding once gives the correctly rounded
+// half result, max and min are exact, so this equals truncate_pack_f32 bit for bit for the activations of
+// act_exact_in_half at a fifth of the instructions.
+__device__ __forceinline__ bool truncate_pack_h2(Pack<__half, 8>& d, Pack<__half, 8>& y, Pack<__half, 8>& tr, int act, __half2 thr2) {
+    __half2* dh = reinterpret_cast<__half2*>(d.s);
+    __half2* yh = reinterpret_cast<__half2*>(y.s);
+    __half2* th = reinterpret_cast<__half2*>(tr.s);
+    const __half2 zero = __float2half2_rn(0.f), six = __float2half2_rn(6.f);
+    unsigned any = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const __half2 r = __hadd2(th[k], dh[k]);
+        const __half2 yo = yh[k];
+        const __half2 u = __hadd2(yo, r);
+        __half2 fu = u, fy = yo;
+        if (act != DC_ACT_NONE) {
+            fu = __hmax2(fu, zero);
+            fy = __hmax2(fy, zero);
+            if (act == DC_ACT_RELU6) {
+                fu = __hmin2(fu, six);
+                fy = __hmin2(fy, six);
+            }
+        }
+        const __half2 e = __hsub2(fu, fy);
+        th[k] = r;
+        yh[k] = u;
+        dh[k] = e;
+        any |= __hgt2_mask(__habs2(e), thr2);
+    }
+    return any != 0;
+}
+// The same step in fp32 with one rounding per stored value, for every activation and storage type.
+template <typename T, int W>
+__device__ __forceinline__ bool truncate_pack_f32(Pack<T, W>& d, Pack<T, W>& y, Pack<T, W>& tr, int act, float thr) {
+    bool hit = false;
+#pragma unroll
+    for (int k = 0; k < W; ++k) {
+        const float yo = y.get(k);
+        const float rr = rnd<T>(tr.get(k) + d.get(k));
+        const float uu = rnd<T>(yo + rr);
+        const float ee = rnd<T>(act_apply(uu, act) - act_apply(yo, act));
+        tr.set(k, rr);
+        y.set(k, uu);
+        d.set(k, ee);
+        hit |= fabsf(ee) > thr;
+    }
+    return hit;
+}
+
 // Threshold as the storage type sees it (the half kernels compare against the
 // threshold rounded to half).
 template <typename T> inline float host_round_threshold(float t);

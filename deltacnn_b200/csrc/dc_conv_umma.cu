@@ -14,6 +14,14 @@
 //                             dc_activate_truncate is applied here, so the convolution result never
 //                             makes a round trip through HBM
 //
+// Roles inside a CTA of 8 warps: warps 0-6 gather rows (cp.async into the swizzled stage ring, running up to
+// four K blocks ahead; a block is handed over through a "full" mbarrier once the copies have landed and a
+// proxy fence has made them visible to the tensor core), one thread of warp 7 waits on those barriers and
+// issues the MMAs, tcgen05.commit hands stages back ("empty" barriers); all 8 warps run the epilogue.
+// The kernel is bound by instruction issue and dependent latency, not by bandwidth (few warps walk a long
+// path once per tile), so the per-tile path is kept short: no integer division (multiply-shift with host
+// constants), tap offsets tabulated once, and the truncation step in packed half arithmetic.
+//
 // Every wait on an mbarrier is bounded; a wait that gives up sets a sticky device-side error code
 // (dc_umma_error) and the CTA frees its tensor memory and returns.
 #include "dc_common.cuh"
@@ -26,10 +34,13 @@ constexpr int kRows = 128;            // M of one MMA tile
 constexpr int kKBlock = 64;           // fp16 elements per K block (one 128-byte swizzle row)
 constexpr int kABytes = kRows * 128;  // one A stage
 constexpr int kStages = 4;           // shared-memory ring depth
-constexpr int kPrefetch = 3;         // K blocks in flight ahead of the tensor core
-constexpr int kMaxResidentKB = 16;
+constexpr int kDelay = 2;            // a producer signals a K block after issuing kDelay more (copies in flight per thread)
 constexpr int kPwThreads = 256;
 constexpr int kPwWarps = kPwThreads / 32;
+constexpr int kProducerWarps = kPwWarps - 1;                  // the last warp feeds the tensor core
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kRowStep = kProducerThreads / 8;                // rows between a producer thread's chunks
+constexpr int kChunkPasses = (kRows + kRowStep - 1) / kRowStep;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int64_t kListMinPixels = 40000;    // below this many output pixels 1x1 layers skip the work list
 
@@ -50,6 +61,7 @@ struct PwParams {
     int transposed;                 // transposed convolution with stride sh == sw: blockIdx.z = output phase,
     int m;                          //   m x m taps per phase (kh = m * stride); lists are per phase
     int64_t wl_stride;              //   entries between the per-phase list segments
+    uint32_t hw_mul, hw_shift, wo_mul, wo_shift;   // division by h_out*w_out and by w_out (fast_div)
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
 
@@ -71,11 +83,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the phase did not complete within the iteration limit.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i)
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: false when the phase did not complete within the iteration limit, or when another thread of
+// the CTA has cleared the ok flag in the meantime (a wait elsewhere gave up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* ok_flag) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *ok_flag == 0) return false;
+    }
     return false;
+}
+// One lane polls, the warp shares the result (the whole warp calls this converged).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* ok_flag) {
+    int got = 1;
+    if ((threadIdx.x & 31) == 0) got = mbar_wait(bar, parity, ok_flag) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, got, 0) != 0;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -86,10 +110,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_pending(int n) {      // at most n groups still in flight
-    if (n <= 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
-    else if (n == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
-    else asm volatile("cp.async.wait_group 2;" ::: "memory");
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {            // at most N of this thread's groups still in flight
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -137,6 +160,17 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
 }
 
+// n / d for n < 2^31 with (mul, shift) from fast_div_init(d): exact, no division instruction.
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift) {
+    return (uint32_t)(((uint64_t)n * mul) >> shift);
+}
+static void fast_div_init(uint32_t d, uint32_t* mul, uint32_t* shift) {
+    uint32_t s = 0;
+    while ((1ull << s) < d) ++s;
+    *mul = (uint32_t)((((uint64_t)1 << (31 + s)) + d - 1) / d);   // ceil(2^(31+s) / d) < 2^32
+    *shift = 31 + s;
+}
+
 // ---- kernel -----------------------------------------------------------------------------------
 // Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
 //                [ row lists ][ mbarriers, scalars, bias ]
@@ -147,21 +181,26 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     uint8_t* sStage = smem;                                        // aliases the A ring (dead once a tile's MMAs are done)
     uint8_t* sB = smem + p.off_b;
     int* s_out = reinterpret_cast<int*>(smem + p.off_list);        // [span] output pixel (relative) of every active row
-    int* s_in = s_out + p.span;                                    // [span][taps] input pixel of every (active row, tap), -1 = inactive or out of bounds
+    int* s_base = s_out + p.span;                                  // [span] input pixel of tap 0 of the row (may lie in the padding)
+    uint32_t* s_tb = reinterpret_cast<uint32_t*>(s_base + p.span); // [span] bit set of the row's active taps
+    int* s_toff = reinterpret_cast<int*>(s_tb + p.span);           // [32] input pixel of every tap relative to the base pixel
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_misc);
-    // bars[0..kStages)            slot_free   (tcgen05.commit of the MMAs that read stage s)
-    // bars[kStages..+16)          b_full      (bulk copy of a filter block landed)
-    // bars[kStages+16]            accum_full  (all MMAs of a tile done)
-    uint32_t* s_u32 = reinterpret_cast<uint32_t*>(bars + kStages + kMaxResidentKB + 1);
+    // bars[0..kStages)            empty   (tcgen05.commit of the MMAs that read stage s)
+    // bars[kStages..2*kStages)    full    (every producer warp's copies into stage s have landed)
+    // bars[2*kStages..3*kStages)  b_full  (bulk copy of the filter block of stage s landed; [0]: the resident filter)
+    // bars[3*kStages]             accum   (all MMAs of a tile done)
+    uint32_t* s_u32 = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
     // s_u32[0] tmem base, [1] ok flag, [3..3+warps) warp totals
     float* s_bias = reinterpret_cast<float*>(s_u32 + 12);          // [bn]
 
     grid_dep_launch();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar0 = smem_u32(bars);
-    auto bar_slot = [&](int s) { return bar0 + 8u * s; };
-    auto bar_bfull = [&](int s) { return bar0 + 8u * (kStages + s); };
-    const uint32_t bar_accum = bar0 + 8u * (kStages + kMaxResidentKB);
+    auto bar_empty = [&](int s) { return bar0 + 8u * s; };
+    auto bar_full = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto bar_bfull = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
+    const uint32_t bar_accum = bar0 + 8u * (3 * kStages);
+    const uint32_t idesc = make_idesc(p.bn);
 
     const int n0 = blockIdx.y * p.bn;                              // first output channel of this CTA
     const int ncols = min(p.bn, p.cout - n0);                      // real output channels here
@@ -176,10 +215,10 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     };
 
     // ---- set-up that reads nothing the previous kernel wrote: overlaps that kernel's tail ----
-    if (tid == 0) {
-        for (int i = 0; i < kStages + kMaxResidentKB + 1; ++i) mbar_init(bar0 + 8u * i, 1);
+    if (tid <= 3 * kStages) {
+        mbar_init(bar0 + 8u * tid, (tid >= kStages && tid < 2 * kStages) ? (uint32_t)kProducerWarps : 1u);
         fence_barrier_init();
-        s_u32[1] = 1;
+        if (tid == 0) s_u32[1] = 1;
     }
     for (int i = tid; i < p.bn; i += kPwThreads) s_bias[i] = (p.bias != nullptr && i < ncols) ? __half2float(p.bias[n0 + i]) : 0.f;
     if (warp == 0) tmem_alloc(smem_u32(&s_u32[0]), (uint32_t)p.tmem_cols);
@@ -193,194 +232,201 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     };
     grid_dep_wait();
 
-    // ---- compaction of the span's active pixels, one pass (order preserved) ----
+    // ---- the rows of this CTA ----
     const bool list_mode = p.wl_list != nullptr;
-    const int64_t hw_out = (int64_t)p.ho * p.wo;
     const int64_t q0 = list_mode ? 0 : (int64_t)blockIdx.x * p.span;
     int cnt = 0;
     if (list_mode) {
         cnt = p.wl_count[blockIdx.z];
         if ((int64_t)blockIdx.x * kRows >= cnt) { leave(); return; }   // persistent CTAs beyond the work
+        if (tid < p.taps)                                           // input pixel of tap t relative to a row's base pixel
+            s_toff[tid] = p.transposed ? -((tid / p.m) * p.wi + tid % p.m) : (tid / p.kw) * p.dh * p.wi + (tid % p.kw) * p.dw;
     } else {
-    const int spt = max(1, p.span / kPwThreads);                   // consecutive pixels per thread (1..8)
-    int pin[8];
-    unsigned bits = 0;
-    {
-        int m[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            m[j] = 0;
-            pin[j] = 0;
-            const int64_t q = q0 + (int64_t)tid * spt + j;
-            if (j < spt && tid * spt + j < p.span && q < p.npix_out) {
-                if (p.sh == 1 && p.sw == 1) {
-                    pin[j] = (int)q;
-                } else {
-                    const int64_t b = q / hw_out;
-                    const int r = (int)(q - b * hw_out);
-                    pin[j] = (int)((b * p.hi + (int64_t)(r / p.wo) * p.sh) * p.wi + (int64_t)(r % p.wo) * p.sw);
-                }
-                m[j] = p.mi[pin[j]];
+        // span mode (1x1 kernels, no padding): thread t owns pixel q0 + t; the active ones are compacted in
+        // order with a ballot per warp and a prefix over the warp totals
+        int pin = 0;
+        bool on = false;
+        const int64_t q = q0 + tid;
+        if (tid < p.span && q < p.npix_out) {
+            if (p.sh == 1 && p.sw == 1) {
+                pin = (int)q;
+            } else {
+                const uint32_t b = fast_div((uint32_t)q, p.hw_mul, p.hw_shift);
+                const uint32_t r = (uint32_t)q - b * (uint32_t)(p.ho * p.wo);
+                const uint32_t oy = fast_div(r, p.wo_mul, p.wo_shift);
+                pin = (int)((b * p.hi + oy * p.sh) * p.wi + (r - oy * p.wo) * p.sw);
             }
+            on = p.mi[pin] != 0;
+            if (blockIdx.y == 0 && (!p.fused || !on)) p.mo[q] = on ? 1 : 0;
         }
+        const unsigned bal = __ballot_sync(DC_FULL, on);
+        if (lane == 0) s_u32[3 + warp] = (uint32_t)__popc(bal);
+        if (tid == 0) s_toff[0] = 0;
+        __syncthreads();
+        int slot = __popc(bal & ((1u << lane) - 1u));
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int64_t q = q0 + (int64_t)tid * spt + j;
-            if (j < spt && tid * spt + j < p.span && q < p.npix_out) {
-                if (m[j] != 0) bits |= 1u << j;
-                if (blockIdx.y == 0 && (!p.fused || m[j] == 0)) p.mo[q] = m[j] != 0 ? 1 : 0;
-            }
+        for (int w = 0; w < kPwWarps; ++w) {
+            const int c = (int)s_u32[3 + w];
+            if (w < warp) slot += c;
+            cnt += c;
         }
-    }
-    const int mine_cnt = __popc(bits);
-    int incl = mine_cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(DC_FULL, incl, o);
-        if (lane >= o) incl += v;
-    }
-    if (lane == 31) s_u32[3 + warp] = incl;
-    __syncthreads();
-    int slot0 = incl - mine_cnt;
-    for (int w = 0; w < warp; ++w) slot0 += s_u32[3 + w];
-    for (int w = 0; w < kPwWarps; ++w) cnt += (int)s_u32[3 + w];
-    if (cnt == 0) { leave(); return; }    // nothing active in this span
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        if (bits & (1u << j)) {
-            s_out[slot0] = tid * spt + j;
-            s_in[slot0] = pin[j];
-            ++slot0;
+        if (cnt == 0) { leave(); return; }    // nothing active in this span
+        if (on) {
+            s_out[slot] = tid;
+            s_base[slot] = pin;
+            s_tb[slot] = 1u;
         }
     }
-    }   // span mode
 
     const uint32_t b_block_bytes = (uint32_t)p.bn * 128u;
-    if (tid == 0 && p.b_resident) {       // the whole filter slab of this CTA, one bulk copy per K block
-        for (int kb = 0; kb < p.nkb; ++kb) {
-            mbar_expect_tx(bar_bfull(kb), b_block_bytes);
-            bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(kb));
-        }
-    }
-
-    const uint32_t idesc = make_idesc(p.bn);
-    const int row_in_pass = tid >> 3, chunk = tid & 7;
-    const uint32_t a_thread_off = (uint32_t)((row_in_pass >> 3) * 1024 + (row_in_pass & 7) * 128 + ((chunk ^ (row_in_pass & 7)) << 4));
-    constexpr int kPasses = kRows / (kPwThreads / 8);            // row passes per K block
-    constexpr int kRowsPerPass = kPwThreads / 8;
-    int it = 0;                       // global K-block iteration counter (ring position)
+    const bool is_mma_warp = warp == kPwWarps - 1;
+    volatile uint32_t* ok_flag = &s_u32[1];
     bool ok = true;
 
-    // one K block of one tile: every thread copies its 16-byte chunks of the gathered rows straight into the
-    // swizzled stage (cp.async, zero fill beyond the last input channel); thread 0 adds the filter block when
-    // the filter is streamed. I = global block index (ring position and mbarrier phase derive from it).
-    const int nse = p.nslots;
-    auto issue_block = [&](int t0_, int cnt_t_, int kb_, int I) {
-        const int slot_ = I % nse;
-        const int tap_ = kb_ / p.ncb, cb_ = kb_ - tap_ * p.ncb;
-        const int kk = cb_ * kKBlock + chunk * 8;
-        const int ksteps_ = (min(p.cin - cb_ * kKBlock, kKBlock) + 15) >> 4;
-        if (chunk < ksteps_ * 2) {
-            const uint32_t dst0 = smem_u32(sA + (size_t)slot_ * kABytes) + a_thread_off;
-#pragma unroll
-            for (int j = 0; j < kPasses; ++j) {
-                const int r = row_in_pass + kRowsPerPass * j;
-                if (r < cnt_t_) {
-                    const int pin_ = s_in[(t0_ + r) * p.taps + tap_];
-                    const bool real = kk < p.cin && pin_ >= 0;
-                    const __half* src = real ? p.in + (int64_t)pin_ * p.cin + kk : p.in;
-                    cp_async16(dst0 + j * (kRowsPerPass / 8) * 1024, src, real ? 16u : 0u);
-                }
-            }
-        }
-        cp_async_commit();
-        if (tid == 0 && !p.b_resident) {
-            mbar_expect_tx(bar_bfull(slot_), b_block_bytes);
-            bulk_g2s(smem_u32(sB + (size_t)slot_ * b_block_bytes), wimg + filter_block(kb_) * p.b_kb_stride, b_block_bytes, bar_bfull(slot_));
-        }
+    // Producer threads (warps 0 .. kProducerWarps-1): thread t owns 16-byte chunk (t & 7) of the rows
+    // (t >> 3) + kRowStep * j of every K block and copies it straight into the swizzled stage (cp.async, zero
+    // fill for inactive or out-of-bounds taps and beyond the last input channel).
+    const int chunk = tid & 7, row0 = tid >> 3;
+    auto dst_off = [&](int j) {           // byte offset of this thread's chunk of its j-th row inside a swizzled stage
+        const int r = row0 + kRowStep * j;
+        return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4));
     };
+    const uint32_t sA_u32 = smem_u32(sA);
+    const int last_ksteps = (p.cin - (p.ncb - 1) * kKBlock + 15) >> 4;      // MMAs (K = 16) in the last channel block of a tap
+    const int nse = p.nslots;
+    // ring positions: producers fill (pslot, pwrap) and signal (sslot); the MMA thread consumes (mslot, mwrap).
+    // The wrap counters give the mbarrier phases: use k of a slot completes phase k of its barriers.
+    int pslot = 0, pwrap = 0, sslot = 0, mslot = 0, mwrap = 0;
+    auto signal_block = [&]() {           // this thread's copies of the oldest unsignalled block have landed
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full(sslot));
+        if (++sslot == nse) sslot = 0;
+    };
+    // epilogue geometry: an aligned group of g lanes per row, 16 bytes per lane
+    const int nch = ncols >> 3;                                   // 16-byte packs per row
+    int g = 1;
+    while (g < nch && g < 32) g <<= 1;
+    const int lig = lane & (g - 1), ppw = 32 / g;
+    const bool half_exact = act_exact_in_half(p.act);
+    const __half2 thr2 = __float2half2_rn(p.thr);
     __syncthreads();                  // row lists complete
 
     // span mode: the tiles of this CTA's own list; list mode: every gridDim.x-th tile of the global list
     const int tile_first = list_mode ? (int)blockIdx.x : 0;
     const int tile_step = list_mode ? (int)gridDim.x : 1;
     const int tiles_total = (cnt + kRows - 1) / kRows;
-    int tile = 0;                     // tiles processed by this CTA (mbarrier phases count these)
+    const bool plain_1x1 = p.taps == 1 && p.sh == 1 && p.sw == 1 && p.pt == 0 && p.pl == 0 && !p.transposed;
+    int tile = 0;                     // tiles processed by this CTA (the accumulator barrier's phase counts these)
     for (int tg = tile_first; tg < tiles_total && ok; tg += tile_step, ++tile) {
         const int cnt_t = min(kRows, cnt - tg * kRows);
         const int t0 = list_mode ? 0 : tg * kRows;                  // offset of the tile's rows in the shared lists
         if (list_mode) {
             __syncthreads();                                        // previous tile's epilogue has read the lists
-            for (int r = tid; r < cnt_t; r += kPwThreads) {
-                const size_t e_ = (size_t)blockIdx.z * p.wl_stride + (size_t)tg * kRows + r;
+            if (tid < cnt_t) {
+                const size_t e_ = (size_t)blockIdx.z * p.wl_stride + (size_t)tg * kRows + tid;
                 const uint32_t q = p.wl_list[e_];
-                const uint32_t tb = p.wl_taps[e_];
-                s_out[r] = (int)q;
-                const uint32_t b = q / (uint32_t)hw_out;
-                const uint32_t rr = q - b * (uint32_t)hw_out;
-                const int oy = (int)(rr / (uint32_t)p.wo), ox = (int)(rr % (uint32_t)p.wo);
-                for (int t = 0; t < p.taps; ++t) {
-                    int pin_ = -1;
-                    if (tb & (1u << t)) {
-                        int iy, ix;
-                        if (p.transposed) { iy = (oy + p.pt) / p.sh - t / p.m; ix = (ox + p.pl) / p.sw - t % p.m; }
-                        else { iy = oy * p.sh - p.pt + (t / p.kw) * p.dh; ix = ox * p.sw - p.pl + (t % p.kw) * p.dw; }
-                        pin_ = (int)((b * p.hi + iy) * p.wi + ix);
+                s_out[tid] = (int)q;
+                s_tb[tid] = p.wl_taps[e_];
+                int base = (int)q;
+                if (!plain_1x1) {
+                    const uint32_t b = fast_div(q, p.hw_mul, p.hw_shift);
+                    const uint32_t rr = q - b * (uint32_t)(p.ho * p.wo);
+                    const int oy = (int)fast_div(rr, p.wo_mul, p.wo_shift);
+                    const int ox = (int)rr - oy * p.wo;
+                    if (p.transposed) base = ((int)b * p.hi + ((oy + p.pt) >> 1)) * p.wi + ((ox + p.pl) >> 1);   // stride 2
+                    else base = ((int)b * p.hi + oy * p.sh - p.pt) * p.wi + ox * p.sw - p.pl;
+                }
+                s_base[tid] = base;
+            }
+            __syncthreads();
+        }
+
+        if (!is_mma_warp) {
+            // ---- producers: run up to nse K blocks ahead of the tensor core; a block is signalled (full
+            //      barrier, one arrival per warp) kDelay blocks after it was issued ----
+            int rbase[kChunkPasses];
+            uint32_t rtb[kChunkPasses];          // tap bit set of the row; bit 31 marks a row that exists
+#pragma unroll
+            for (int j = 0; j < kChunkPasses; ++j) {
+                const int r = row0 + kRowStep * j;
+                const bool v = r < cnt_t;
+                rbase[j] = v ? s_base[t0 + r] : 0;
+                rtb[j] = v ? (s_tb[t0 + r] | 0x80000000u) : 0u;
+            }
+            int tap = 0, cb = 0, toff = s_toff[0];
+            for (int kb = 0; kb < p.nkb; ++kb) {
+                if (pwrap > 0 && !mbar_wait_warp(bar_empty(pslot), (uint32_t)((pwrap - 1) & 1), ok_flag)) {
+                    *ok_flag = 0; atomicExch(&g_umma_error, 1);
+                    break;
+                }
+                const int kk = cb * kKBlock + chunk * 8;
+                const int ksteps_ = cb == p.ncb - 1 ? last_ksteps : kKBlock / 16;
+                if (chunk < ksteps_ * 2) {
+                    const uint32_t dst0 = sA_u32 + (uint32_t)pslot * kABytes;
+                    const bool in_k = kk < p.cin;
+#pragma unroll
+                    for (int j = 0; j < kChunkPasses; ++j) {
+                        if (rtb[j] != 0u) {
+                            const bool real = in_k && ((rtb[j] >> tap) & 1u) != 0u;
+                            const __half* src = real ? p.in + (int64_t)(rbase[j] + toff) * p.cin + kk : p.in;
+                            cp_async16(dst0 + dst_off(j), src, real ? 16u : 0u);
+                        }
                     }
-                    s_in[r * p.taps + t] = pin_;
+                }
+                cp_async_commit();
+                if (tid == 0 && !p.b_resident) {
+                    mbar_expect_tx(bar_bfull(pslot), b_block_bytes);
+                    bulk_g2s(smem_u32(sB + (size_t)pslot * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(pslot));
+                }
+                if (++pslot == nse) { pslot = 0; ++pwrap; }
+                if (++cb == p.ncb) {
+                    cb = 0;
+                    if (++tap < p.taps) toff = s_toff[tap];
+                }
+                if (kb >= kDelay) {
+                    cp_async_wait_group<kDelay>();
+                    signal_block();
                 }
             }
-            __syncthreads();
-        }
-        if (p.fused) {
-            // the epilogue will read the two cache rows of every active pixel: start pulling them towards L2 now,
-            // so that those reads do not wait on HBM after the accumulator is ready
-            const int lines = (ncols * 2 + 127) >> 7;                 // 128-byte lines per row
-            for (int i = tid; i < cnt_t * lines; i += kPwThreads) {
-                const int r = i / lines, l = i - r * lines;
-                const int64_t e_off = (q0 + s_out[t0 + r]) * p.cout + n0 + l * 64;
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(p.prev + e_off));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(p.trunc + e_off));
-            }
-        }
-        const int it0 = tile * p.nkb;
-        // every MMA of the previous tile has completed (accumulator barrier), so the first stages are free
-        for (int d = 0; d < kPrefetch && d < p.nkb; ++d) issue_block(t0, cnt_t, d, it0 + d);
-        for (int kb = 0; kb < p.nkb; ++kb) {
-            const int I = it0 + kb;
-            const int slot = I % nse;
-            cp_async_wait_pending(min(kPrefetch - 1, p.nkb - 1 - kb));
-            fence_proxy_async();
-            __syncthreads();
-            if (s_u32[1] == 0) { ok = false; break; }
-            const int ksteps = (min(p.cin - (kb % p.ncb) * kKBlock, kKBlock) + 15) >> 4;
-            if (tid == 0) {
-                bool bok = true;
-                if (!p.b_resident) bok = mbar_wait(bar_bfull(slot), (uint32_t)((I / nse) & 1));
-                else if (tile == 0) bok = mbar_wait(bar_bfull(kb), 0u);
-                if (!bok) { s_u32[1] = 0; atomicExch(&g_umma_error, 2); }
-                else {
+            if (p.nkb >= 2) { cp_async_wait_group<1>(); signal_block(); }
+            cp_async_wait_group<0>();
+            signal_block();
+        } else {
+            // ---- one thread feeds the tensor core ----
+            if (lane == 0) {
+                if (tile == 0 && p.b_resident) {       // the whole filter slab of this CTA: one bulk copy per K block, one barrier
+                    mbar_expect_tx(bar_bfull(0), (uint32_t)p.nkb * b_block_bytes);
+                    for (int kb = 0; kb < p.nkb; ++kb)
+                        bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(0));
+                }
+                const uint64_t ad0 = make_smem_desc(sA_u32);
+                const uint64_t bd0 = make_smem_desc(smem_u32(sB));
+                const uint32_t b_step = b_block_bytes >> 4;
+                int cb = 0;
+                for (int kb = 0; kb < p.nkb; ++kb) {
+                    bool got = mbar_wait(bar_full(mslot), (uint32_t)(mwrap & 1), ok_flag);
+                    if (got) {
+                        if (!p.b_resident) got = mbar_wait(bar_bfull(mslot), (uint32_t)(mwrap & 1), ok_flag);
+                        else if (tile == 0 && kb == 0) got = mbar_wait(bar_bfull(0), 0u, ok_flag);
+                    }
+                    if (!got) { *ok_flag = 0; atomicExch(&g_umma_error, 2); break; }
                     tc_fence_after();
-                    const uint64_t ad = make_smem_desc(smem_u32(sA + (size_t)slot * kABytes));
-                    const uint64_t bd = make_smem_desc(smem_u32(sB + (size_t)(p.b_resident ? kb : slot) * b_block_bytes));
+                    const int ksteps = cb == p.ncb - 1 ? last_ksteps : kKBlock / 16;
+                    const uint64_t ad = ad0 + (uint64_t)((uint32_t)mslot * (kABytes >> 4));
+                    const uint64_t bd = bd0 + (uint64_t)((uint32_t)(p.b_resident ? kb : mslot) * b_step);
                     for (int ks = 0; ks < ksteps; ++ks)
                         umma_f16(tmem_base, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(bar_slot(slot));
+                    umma_commit(bar_empty(mslot));
+                    if (++mslot == nse) { mslot = 0; ++mwrap; }
+                    if (++cb == p.ncb) cb = 0;
                 }
+                if (*ok_flag != 0) umma_commit(bar_accum);
             }
-            const int nxt = kb + kPrefetch;
-            if (nxt < p.nkb) {
-                // the stage block `nxt` goes into was last read by the MMAs of block nxt - nse
-                const int Ip = it0 + nxt - nse;
-                if (Ip >= 0 && !mbar_wait(bar_slot((it0 + nxt) % nse), (uint32_t)((Ip / nse) & 1))) { s_u32[1] = 0; atomicExch(&g_umma_error, 1); }
-                issue_block(t0, cnt_t, nxt, it0 + nxt);
-            }
+            __syncwarp();
         }
-        if (!ok) break;
-        if (tid == 0) {
-            umma_commit(bar_accum);
-            if (!mbar_wait(bar_accum, (uint32_t)(tile & 1))) { s_u32[1] = 0; atomicExch(&g_umma_error, 3); }
-        }
+        // every MMA of the tile has completed: the accumulator is final and the stage ring is free
+        if (!mbar_wait_warp(bar_accum, (uint32_t)(tile & 1), ok_flag)) { *ok_flag = 0; atomicExch(&g_umma_error, 3); }
         __syncthreads();
         if (s_u32[1] == 0) { ok = false; break; }
         tc_fence_after();
@@ -390,6 +436,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
             const int quarter = warp & 3;                          // TMEM lanes a warp may read: 32 * (warp % 4) ...
             const int r = quarter * 32 + lane;
             uint8_t* srow = sStage + (size_t)r * p.stage_pitch;
+#pragma unroll 1
             for (int c0 = (warp >> 2) * 16; c0 < p.bn; c0 += 16 * (kPwWarps / 4)) {
                 uint32_t acc[16];
                 tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, acc);
@@ -411,11 +458,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
         //      activation delta + any-channel truncation against the two caches ----
         {
             constexpr int kU = 2;
-            const int nch = ncols >> 3;                           // 16-byte packs per row
-            int g = 1;
-            while (g < nch && g < 32) g <<= 1;
-            const int lig = lane & (g - 1);
-            const int ppw = 32 / g;
+#pragma unroll 1
             for (int rb = warp * ppw * kU; rb < cnt_t; rb += kPwWarps * ppw * kU) {
                 Pack<__half, 8> d[kU], y[kU], tr[kU];
                 int64_t off[kU];
@@ -440,25 +483,16 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
                         if (mine[u]) d[u].store(p.out + off[u]);
                         continue;
                     }
-                    Pack<__half, 8> e;
                     bool hit = false;
-                    if (mine[u]) {
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const float yo = y[u].get(k);
-                            const float rr = rnd<__half>(tr[u].get(k) + d[u].get(k));
-                            const float uu = rnd<__half>(yo + rr);
-                            const float ee = rnd<__half>(act_apply(uu, p.act) - act_apply(yo, p.act));
-                            tr[u].set(k, rr); y[u].set(k, uu); e.set(k, ee);
-                            hit |= fabsf(ee) > p.thr;
-                        }
-                    }
+                    if (mine[u])
+                        hit = half_exact ? truncate_pack_h2(d[u], y[u], tr[u], p.act, thr2)
+                                         : truncate_pack_f32(d[u], y[u], tr[u], p.act, p.thr);
                     const bool active = group_any(hit, g, lane);
                     if (mine[u]) {
                         if (active) {
                             Pack<__half, 8> z; z.zero();
                             y[u].store(p.prev + off[u]);
-                            e.store(p.out + off[u]);
+                            d[u].store(p.out + off[u]);
                             z.store(p.trunc + off[u]);
                         } else {
                             tr[u].store(p.trunc + off[u]);
@@ -474,9 +508,9 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     }
 
     // drain: copies in flight and every MMA that was issued have to finish before shared and tensor memory are released
-    cp_async_wait_pending(0);
+    cp_async_wait_group<0>();
     if (!ok && tid == 0) {
-        for (int s = 0; s < kStages; ++s) { (void)mbar_try_wait(bar_slot(s), 0); }
+        for (int s = 0; s < kStages; ++s) { (void)mbar_try_wait(bar_empty(s), 0); }
     }
     tc_fence_before();
     __syncthreads();
@@ -542,11 +576,11 @@ static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, boo
     pl.tmem_cols = 32;
     while (pl.tmem_cols < pl.bn) pl.tmem_cols <<= 1;
     const size_t b_block = (size_t)pl.bn * 128;
-    pl.b_resident = (pl.nkb <= kMaxResidentKB && pl.nkb * b_block <= 64 * 1024) ? 1 : 0;
+    pl.b_resident = pl.nkb * b_block <= 64 * 1024 ? 1 : 0;
     pl.nslots = pl.nkb < kStages ? pl.nkb : kStages;
     const size_t b_bytes = (pl.b_resident ? pl.nkb : pl.nslots) * b_block;
     // spans small enough to give every SM several CTAs, large enough to fill an MMA tile when sparse
-    int span = 1024;
+    int span = 256;                   // a thread of the CTA looks at one pixel of the span
     const int64_t want = (int64_t)sms * 6;
     while (span > 128 && divup64(npix_out, span) * pl.ntiles < want) span >>= 1;
     if (list_mode) span = kRows;      // the shared row lists hold one tile
@@ -557,8 +591,8 @@ static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, boo
     pl.off_stage = 0;
     pl.off_b = ((ring > staging ? ring : staging) + 1023) & ~1023u;
     pl.off_list = (pl.off_b + (uint32_t)b_bytes + 15) & ~15u;
-    pl.off_misc = (pl.off_list + (1u + (uint32_t)pl.taps) * (uint32_t)span * 4u + 15) & ~15u;
-    pl.smem = pl.off_misc + 8 * (kStages + kMaxResidentKB + 1) + 48 + 4 * (size_t)pl.bn + 1024 /* alignment slack */;
+    pl.off_misc = (pl.off_list + (3u * (uint32_t)span + 32u) * 4u + 15) & ~15u;
+    pl.smem = pl.off_misc + 8 * (3 * kStages + 1) + 48 + 4 * (size_t)pl.bn + 1024 /* alignment slack */;
 }
 
 size_t filter_umma_bytes(const dc_conv_desc* d, int transposed) {
@@ -619,6 +653,8 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     p.nkb = pl.nkb; p.bn = pl.bn; p.span = pl.span; p.b_resident = pl.b_resident; p.tmem_cols = pl.tmem_cols;
     p.nslots = pl.nslots;
     p.b_kb_stride = (uint32_t)pl.rows * 128u;
+    fast_div_init((uint32_t)(d->h_out * d->w_out), &p.hw_mul, &p.hw_shift);
+    fast_div_init((uint32_t)d->w_out, &p.wo_mul, &p.wo_shift);
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_list = pl.off_list; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
     static thread_local bool attr_set = false;
     if (!attr_set) {
