@@ -13,6 +13,17 @@ namespace dc {
 __host__ __device__ constexpr inline int64_t divup64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 __host__ __device__ constexpr inline int divup(int a, int b) { return (a + b - 1) / b; }
 
+// n / d for n < 2^31 with (mul, shift) from fast_div_init(d): exact, no division instruction sequence.
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift) {
+    return (uint32_t)(((uint64_t)n * mul) >> shift);
+}
+inline void fast_div_init(uint32_t d, uint32_t* mul, uint32_t* shift) {
+    uint32_t s = 0;
+    while ((1ull << s) < d) ++s;
+    *mul = (uint32_t)((((uint64_t)1 << (31 + s)) + d - 1) / d);   // ceil(2^(31+s) / d) < 2^32
+    *shift = 31 + s;
+}
+
 // Number of SMs of the current device (cached per thread), for grid sizing.
 int sm_count();
 // Record a launch failure for dc_last_cuda_error(); returns DC_OK or DC_ERR_LAUNCH.

@@ -160,17 +160,6 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
 }
 
-// n / d for n < 2^31 with (mul, shift) from fast_div_init(d): exact, no division instruction.
-__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift) {
-    return (uint32_t)(((uint64_t)n * mul) >> shift);
-}
-static void fast_div_init(uint32_t d, uint32_t* mul, uint32_t* shift) {
-    uint32_t s = 0;
-    while ((1ull << s) < d) ++s;
-    *mul = (uint32_t)((((uint64_t)1 << (31 + s)) + d - 1) / d);   // ceil(2^(31+s) / d) < 2^32
-    *shift = 31 + s;
-}
-
 // ---- kernel -----------------------------------------------------------------------------------
 // Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
 //                [ row lists ][ mbarriers, scalars, bias ]

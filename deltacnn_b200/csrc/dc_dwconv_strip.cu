@@ -18,86 +18,64 @@ struct DwStripParams {
     float thr; int act; int fused;
     int n, hi, wi, c, ho, wo, s, pt, pl;
     int strip;          // output pixels per warp and iteration: a multiple of the pixels a warp processes at once, <= 32
+    uint32_t wo_mul, wo_shift, ho_mul, ho_shift;      // fast_div constants for w_out and h_out
 };
 
 // One output pixel per aligned lane group: depthwise taps -> fp32 accumulators -> epilogue in registers.
 // Must be called by all 32 lanes of a warp (the any-channel decision ballots across the warp).
+// `in0` is the element offset of tap (0,0)'s input pixel (it may lie in the padding: only taps whose bit is
+// set in `tb` are read). All tap loads of a channel pack are issued before the first is used, so a lane has
+// up to eleven 16-byte reads in flight; inactive taps contribute zeros instead of branches.
 template <int NV>
-__device__ __forceinline__ void dw_pixel(const DwStripParams& p, const __half* s_w, const __half* s_b, bool on, unsigned tb,
-                                         int64_t qq, int sb, int soy, int sox, int lig, int g, int npk, int lane) {
-    const int y0 = soy * p.s - p.pt, x0 = sox * p.s - p.pl;
-    const __half* img = p.in + (int64_t)sb * p.hi * p.wi * p.c;
-    float acc[NV][8];
+__device__ __forceinline__ void dw_pixel(const DwStripParams& p, const float* s_w, const float* s_b, bool on, unsigned tb,
+                                         int64_t qq, int64_t in0, int lig, int g, int npk, int lane) {
+    const int64_t off = qq * p.c;
+    Pack<__half, 8> pd[NV], pu[NV], pr[NV];
+    const bool half_exact = act_exact_in_half(p.act);
+    const __half2 thr2 = __float2half2_rn(p.thr);
+    bool hit = false;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const int i = lig + j * g;
-        Pack<__half, 8> bb;
-        bb.zero();
-        if (on && i < npk) bb.load(s_b + i * 8);
+        const bool mine = on && i < npk;
+        uint4 v[9];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[j][k] = bb.get(k);
-    }
-    const int64_t off = qq * p.c;
-    // the two cache reads do not depend on the convolution: issue them first so that they are in flight
-    // while the taps are loaded and multiplied
-    Pack<__half, 8> pe[NV], pu[NV], pr[NV];
-    if (p.fused && on) {
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int i = lig + j * g;
-            if (i >= npk) continue;
+        for (int t9 = 0; t9 < 9; ++t9) {
+            v[t9] = make_uint4(0u, 0u, 0u, 0u);
+            if (mine && (tb & (1u << t9)))
+                v[t9] = __ldg(reinterpret_cast<const uint4*>(p.in + in0 + (int64_t)((t9 / 3) * p.wi + t9 % 3) * p.c) + i);
+        }
+        if (p.fused && mine) {
             pu[j].load(p.prev + off + i * 8);
             pr[j].load(p.trunc + off + i * 8);
         }
-    }
-    if (on) {
+        float acc[8];
+        const int ci = mine ? i * 8 : 0;
+        {
+            const float4 b0 = *reinterpret_cast<const float4*>(s_b + ci), b1 = *reinterpret_cast<const float4*>(s_b + ci + 4);
+            acc[0] = b0.x; acc[1] = b0.y; acc[2] = b0.z; acc[3] = b0.w; acc[4] = b1.x; acc[5] = b1.y; acc[6] = b1.z; acc[7] = b1.w;
+        }
 #pragma unroll
         for (int t9 = 0; t9 < 9; ++t9) {
-            if (!(tb & (1u << t9))) continue;
-            const __half* px = img + ((int64_t)(y0 + t9 / 3) * p.wi + (x0 + t9 % 3)) * p.c;
+            const float4 w0 = *reinterpret_cast<const float4*>(s_w + t9 * p.c + ci), w1 = *reinterpret_cast<const float4*>(s_w + t9 * p.c + ci + 4);
+            const __half2* h = reinterpret_cast<const __half2*>(&v[t9]);
+            const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+            acc[0] = fmaf(f0.x, w0.x, acc[0]); acc[1] = fmaf(f0.y, w0.y, acc[1]);
+            acc[2] = fmaf(f1.x, w0.z, acc[2]); acc[3] = fmaf(f1.y, w0.w, acc[3]);
+            acc[4] = fmaf(f2.x, w1.x, acc[4]); acc[5] = fmaf(f2.y, w1.y, acc[5]);
+            acc[6] = fmaf(f3.x, w1.z, acc[6]); acc[7] = fmaf(f3.y, w1.w, acc[7]);
+        }
+        __half2* dh = reinterpret_cast<__half2*>(pd[j].s);
 #pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int i = lig + j * g;
-                if (i >= npk) continue;
-                Pack<__half, 8> v, w;
-                *reinterpret_cast<uint4*>(v.s) = __ldg(reinterpret_cast<const uint4*>(px) + i);
-                w.load(s_w + t9 * p.c + i * 8);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) acc[j][k] = fmaf(v.get(k), w.get(k), acc[j][k]);
-            }
+        for (int k = 0; k < 4; ++k) dh[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+        if (!p.fused) {
+            if (mine) pd[j].store(p.out + off + i * 8);
+        } else if (mine) {
+            hit |= half_exact ? truncate_pack_h2(pd[j], pu[j], pr[j], p.act, thr2)
+                              : truncate_pack_f32(pd[j], pu[j], pr[j], p.act, p.thr);
         }
     }
-    if (!p.fused) {
-        if (on) {
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int i = lig + j * g;
-                if (i >= npk) continue;
-                Pack<__half, 8> o;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) o.set(k, acc[j][k]);
-                o.store(p.out + off + i * 8);
-            }
-        }
-        return;
-    }
-    bool hit = false;
-    if (on) {
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int i = lig + j * g;
-            if (i >= npk) continue;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float yo = pu[j].get(k);
-                const float rr = rnd<__half>(pr[j].get(k) + rnd<__half>(acc[j][k]));
-                const float u = rnd<__half>(yo + rr);
-                const float ee = rnd<__half>(act_apply(u, p.act) - act_apply(yo, p.act));
-                pr[j].set(k, rr); pu[j].set(k, u); pe[j].set(k, ee);
-                hit |= fabsf(ee) > p.thr;
-            }
-        }
-    }
+    if (!p.fused) return;
     const bool active = group_any(hit, g, lane);
     if (!on) return;
 #pragma unroll
@@ -107,7 +85,7 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const __half* s
         if (active) {
             Pack<__half, 8> z; z.zero();
             pu[j].store(p.prev + off + i * 8);
-            pe[j].store(p.out + off + i * 8);
+            pd[j].store(p.out + off + i * 8);
             z.store(p.trunc + off + i * 8);
         } else {
             pr[j].store(p.trunc + off + i * 8);
@@ -116,21 +94,34 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const __half* s
     if (lig == 0) p.mo[qq] = active ? 1 : 0;
 }
 
+// The filter and the bias as fp32 in shared memory ([9][C] and [C]): converted once per CTA, so that the taps
+// cost one conversion (the input) instead of two.
+__device__ __forceinline__ void dw_stage_filter(const DwStripParams& p, float* s_w, float* s_b) {
+    const int npk = p.c >> 3;
+    for (int i = threadIdx.x; i < 10 * npk; i += 256) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (i < 9 * npk) raw = __ldg(reinterpret_cast<const uint4*>(p.w) + i);
+        else if (p.bias != nullptr) raw = __ldg(reinterpret_cast<const uint4*>(p.bias) + (i - 9 * npk));
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+        float* dst = i < 9 * npk ? s_w + i * 8 : s_b + (i - 9 * npk) * 8;
+        *reinterpret_cast<float4*>(dst) = make_float4(f0.x, f0.y, f1.x, f1.y);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(f2.x, f2.y, f3.x, f3.y);
+    }
+}
+
 // List-driven form: persistent warps pull active output pixels from the work list written by
 // k_scan_conv_mask, so the active set is spread evenly over the SMs however it clusters in the image.
 template <int NV>
 __global__ void __launch_bounds__(256) k_dw3x3_list(DwStripParams p, const int32_t* __restrict__ count,
                                                     const uint32_t* __restrict__ list, const uint32_t* __restrict__ taps) {
     extern __shared__ __align__(16) uint8_t smem[];
-    __half* s_w = reinterpret_cast<__half*>(smem);                    // [9][C]
-    __half* s_b = s_w + 9 * p.c;                                      // [C]
+    float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
+    float* s_b = s_w + 9 * p.c;                                       // [C]
     grid_dep_launch();
     const int npk = p.c >> 3;
     // the filter is constant: stage it while the previous kernel (the mask scan) is still finishing
-    for (int i = threadIdx.x; i < 9 * npk; i += 256)
-        reinterpret_cast<uint4*>(s_w)[i] = __ldg(reinterpret_cast<const uint4*>(p.w) + i);
-    for (int i = threadIdx.x; i < npk; i += 256)
-        reinterpret_cast<uint4*>(s_b)[i] = p.bias ? __ldg(reinterpret_cast<const uint4*>(p.bias) + i) : make_uint4(0, 0, 0, 0);
+    dw_stage_filter(p, s_w, s_b);
     grid_dep_wait();
     const int cnt = *count;
     if (cnt == 0) return;
@@ -148,25 +139,23 @@ __global__ void __launch_bounds__(256) k_dw3x3_list(DwStripParams p, const int32
         const bool on = idx < cnt;
         const uint32_t q = on ? list[idx] : 0u;
         const unsigned tb = on ? taps[idx] : 0u;
-        const int ox = (int)(q % (uint32_t)p.wo);
-        const uint32_t t = q / (uint32_t)p.wo;
-        const int oy = (int)(t % (uint32_t)p.ho);
-        const int b = (int)(t / (uint32_t)p.ho);
-        dw_pixel<NV>(p, s_w, s_b, on, tb, (int64_t)q, b, oy, ox, lig, g, npk, lane);
+        const uint32_t t = fast_div(q, p.wo_mul, p.wo_shift);
+        const int ox = (int)(q - t * (uint32_t)p.wo);
+        const uint32_t b = fast_div(t, p.ho_mul, p.ho_shift);
+        const int oy = (int)(t - b * (uint32_t)p.ho);
+        const int64_t in0 = (((int64_t)b * p.hi + (oy * p.s - p.pt)) * p.wi + (ox * p.s - p.pl)) * p.c;
+        dw_pixel<NV>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
     }
 }
 
 template <int NV>   // channel packs per lane: ceil(C / 8 / lanes-per-pixel)
 __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
-    __half* s_w = reinterpret_cast<__half*>(smem);                    // [9][C]
-    __half* s_b = s_w + 9 * p.c;                                      // [C]
+    float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
+    float* s_b = s_w + 9 * p.c;                                       // [C]
     grid_dep_launch();
     const int npk = p.c >> 3;
-    for (int i = threadIdx.x; i < 9 * npk; i += 256)
-        reinterpret_cast<uint4*>(s_w)[i] = __ldg(reinterpret_cast<const uint4*>(p.w) + i);
-    for (int i = threadIdx.x; i < npk; i += 256)
-        reinterpret_cast<uint4*>(s_b)[i] = p.bias ? __ldg(reinterpret_cast<const uint4*>(p.bias) + i) : make_uint4(0, 0, 0, 0);
+    dw_stage_filter(p, s_w, s_b);
     grid_dep_wait();
     __syncthreads();
 
@@ -185,10 +174,10 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
         unsigned taps = 0;                                            // bit t: tap t in bounds and active
         int oy = 0, ox = 0, b = 0;
         if (lane < p.strip && q < npix) {
-            ox = (int)(q % (uint32_t)p.wo);
-            const uint32_t t = q / (uint32_t)p.wo;
-            oy = (int)(t % (uint32_t)p.ho);
-            b = (int)(t / (uint32_t)p.ho);
+            const uint32_t t = fast_div(q, p.wo_mul, p.wo_shift);
+            ox = (int)(q - t * (uint32_t)p.wo);
+            b = (int)fast_div(t, p.ho_mul, p.ho_shift);
+            oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
             const int y0 = oy * p.s - p.pt, x0 = ox * p.s - p.pl;
             const int32_t* mrow = p.mi + (int64_t)b * p.hi * p.wi;
 #pragma unroll
@@ -212,7 +201,8 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
             const int srcl = src < 0 ? 0 : src;
             const unsigned tb = __shfl_sync(DC_FULL, taps, srcl);
             const int soy = __shfl_sync(DC_FULL, oy, srcl), sox = __shfl_sync(DC_FULL, ox, srcl), sb = __shfl_sync(DC_FULL, b, srcl);
-            dw_pixel<NV>(p, s_w, s_b, src >= 0, tb, (int64_t)base + srcl, sb, soy, sox, lig, g, npk, lane);
+            const int64_t in0 = (((int64_t)sb * p.hi + (soy * p.s - p.pt)) * p.wi + (sox * p.s - p.pl)) * p.c;
+            dw_pixel<NV>(p, s_w, s_b, src >= 0, tb, (int64_t)base + srcl, in0, lig, g, npk, lane);
         }
     }
 }
@@ -242,9 +232,11 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     p.act = p.fused ? ep->activation : 0;
     p.n = d->n; p.hi = d->h_in; p.wi = d->w_in; p.c = d->c_in; p.ho = d->h_out; p.wo = d->w_out; p.s = d->stride_h;
     p.pt = d->pad_top; p.pl = d->pad_left;
+    fast_div_init((uint32_t)p.wo, &p.wo_mul, &p.wo_shift);
+    fast_div_init((uint32_t)p.ho, &p.ho_mul, &p.ho_shift);
     const int npk = p.c / 8;
     const int nv = divup(npk, 32);
-    const size_t smem = (size_t)10 * p.c * 2;
+    const size_t smem = (size_t)10 * p.c * 4;         // filter and bias as fp32
     // the work list costs two extra launches; it pays on large maps where the active pixels cluster
     if (ws != nullptr && npix >= 40000) {             // work-list form: one scan pass, then persistent warps over the active pixels
         int rc = scan_conv_mask(d, mi, mo, ws, ws_bytes, p.fused, st);
@@ -252,7 +244,7 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
         const int32_t* count = reinterpret_cast<const int32_t*>(ws);
         const uint32_t* list = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(ws) + 16);
         const uint32_t* taps = list + npix;
-        const size_t smem_l = (size_t)10 * p.c * 2;
+        const size_t smem_l = smem;
         const unsigned grid = (unsigned)sm_count() * (nv >= 3 ? 2 : 4);
         switch (nv) {
             case 1: launch_pdl(k_dw3x3_list<1>, dim3(grid), dim3(256), smem_l, st, p, count, list, taps); break;
