@@ -14,11 +14,13 @@ struct StemParams {
     const void* in; const int32_t* mi; const void* w; const void* bias; void* out; int32_t* mo;
     void* prev; void* trunc; float thr; int act; int fused;
     int n, hi, wi, ci, ho, wo, co, kh, kw, sh, sw, pt, pl, dh, dw;
+    uint32_t wo_mul, wo_shift, ho_mul, ho_shift;                 // fast_div constants for w_out and h_out
 };
 
 template <typename T>
 __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
-    extern __shared__ float s_w[];                               // [kh*kw*ci][co] fp32, then bias [co]
+    extern __shared__ float s_w[];                               // [kh*kw*ci][co] fp32, bias [co], tap offsets [kh*kw]
+    constexpr int W = VecTraits<T>::kVec, NP = 8 / W;            // a lane's 8 output channels as NP 16-byte packs
     const T* in = reinterpret_cast<const T*>(p.in);
     T* out = reinterpret_cast<T*>(p.out);
     T* prev = reinterpret_cast<T*>(p.prev);
@@ -29,6 +31,8 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
     for (int i = threadIdx.x; i < kdim * p.co; i += 256) s_w[i] = to_f<T>(reinterpret_cast<const T*>(p.w)[i]);
     float* s_b = s_w + kdim * p.co;
     for (int i = threadIdx.x; i < p.co; i += 256) s_b[i] = p.bias ? to_f<T>(reinterpret_cast<const T*>(p.bias)[i]) : 0.f;
+    int* s_toff = reinterpret_cast<int*>(s_b + p.co);            // input pixel of tap t relative to tap 0
+    for (int i = threadIdx.x; i < taps; i += 256) s_toff[i] = (i / p.kw) * p.dh * p.wi + (i % p.kw) * p.dw;
     grid_dep_wait();
     __syncthreads();
 
@@ -36,29 +40,32 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
     const int npk = p.co >> 3;                                   // 8 output channels per lane
     int g = 1;
     while (g < npk) g <<= 1;                                     // npk <= 32
-    const int lig = lane & (g - 1);
+    const int lig = lane & (g - 1), gi = lane / g;
     const int ppw = 32 / g;
-    const int64_t npix = (int64_t)p.n * p.ho * p.wo;
-    const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int64_t nwarps = (int64_t)gridDim.x * 8;
-    for (int64_t base = warp0 * 32; base < npix; base += nwarps * 32) {
+    const bool half_exact = sizeof(T) == 2 && act_exact_in_half(p.act);
+    const __half2 thr2 = __float2half2_rn(p.thr);
+    const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
+    const uint32_t warp0 = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const uint32_t nwarps = gridDim.x * 8;
+    for (uint32_t base = warp0 * 32u; base < npix; base += nwarps * 32u) {
         // phase 1: lane = pixel
-        const int64_t q = base + lane;
+        const uint32_t q = base + lane;
         unsigned long long tapbits = 0ull;                       // taps in bounds and active (taps <= 64)
-        int ox = 0, oy = 0;
-        int64_t b = 0;
+        int in0 = 0;                                             // input pixel of tap 0 (may lie in the padding)
         if (q < npix) {
-            ox = (int)(q % p.wo);
-            const int64_t t = q / p.wo;
-            oy = (int)(t % p.ho);
-            b = t / p.ho;
+            const uint32_t t = fast_div(q, p.wo_mul, p.wo_shift);
+            const int ox = (int)(q - t * (uint32_t)p.wo);
+            const int b = (int)fast_div(t, p.ho_mul, p.ho_shift);
+            const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
+            const int y0 = oy * p.sh - p.pt, x0 = ox * p.sw - p.pl;
+            in0 = (b * p.hi + y0) * p.wi + x0;
             for (int ky = 0; ky < p.kh; ++ky) {
-                const int iy = oy * p.sh - p.pt + ky * p.dh;
+                const int iy = y0 + ky * p.dh;
                 if (iy < 0 || iy >= p.hi) continue;
                 for (int kx = 0; kx < p.kw; ++kx) {
-                    const int ix = ox * p.sw - p.pl + kx * p.dw;
+                    const int ix = x0 + kx * p.dw;
                     if (ix < 0 || ix >= p.wi) continue;
-                    if (p.mi[(b * p.hi + iy) * p.wi + ix] != 0) tapbits |= 1ull << (ky * p.kw + kx);
+                    if (p.mi[in0 + ky * p.dh * p.wi + kx * p.dw] != 0) tapbits |= 1ull << (ky * p.kw + kx);
                 }
             }
             if (!p.fused || tapbits == 0ull) p.mo[q] = tapbits != 0ull ? 1 : 0;
@@ -66,70 +73,85 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
         unsigned todo = __ballot_sync(DC_FULL, tapbits != 0ull);
         // phase 2: ppw active pixels per round
         while (todo) {
-            // the (lane / g)-th set bit of todo, if any
+            // the gi-th set bit of todo, if any
             unsigned rem = todo;
             int src = -1;
-            for (int k = 0; k <= lane / g && rem; ++k) {
-                src = __ffs(rem) - 1;
+            for (int k = 0; k <= gi && rem; ++k) {
+                const int bpos = __ffs(rem) - 1;
                 rem &= rem - 1;
-                if (k < lane / g) src = -1;
+                if (k == gi) src = bpos;
             }
             // drop the ppw lowest set bits
             for (int k = 0; k < ppw && todo; ++k) todo &= todo - 1;
             const int srcl = src < 0 ? 0 : src;
             const unsigned long long tb = __shfl_sync(DC_FULL, tapbits, srcl);
-            const int sox = __shfl_sync(DC_FULL, ox, srcl), soy = __shfl_sync(DC_FULL, oy, srcl);
-            const long long sb = __shfl_sync(DC_FULL, (long long)b, srcl);
+            const int sin0 = __shfl_sync(DC_FULL, in0, srcl);
             const bool mine = src >= 0 && lig < npk;
-            const int64_t qq = base + srcl;
+            const int64_t qq = (int64_t)base + srcl;
+            const int cl = mine ? lig * 8 : 0;
             float acc[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = mine ? s_b[lig * 8 + k] : 0.f;
-            if (mine) {
-                unsigned long long r2 = tb;
-                while (r2) {
-                    const int tp = __ffsll((long long)r2) - 1;
-                    r2 &= r2 - 1;
-                    const int iy = soy * p.sh - p.pt + (tp / p.kw) * p.dh, ix = sox * p.sw - p.pl + (tp % p.kw) * p.dw;
-                    const T* px = in + ((sb * p.hi + iy) * p.wi + ix) * (int64_t)p.ci;
-                    for (int c = 0; c < p.ci; ++c) {
-                        const float a = to_f<T>(px[c]);
-                        const float* wr = s_w + (tp * p.ci + c) * p.co + lig * 8;
+            for (int k = 0; k < 8; ++k) acc[k] = s_b[cl + k];
+            // uniform loop over the taps: the reads of a few taps are issued together, inactive taps add zeros
+#pragma unroll 3
+            for (int tp = 0; tp < taps; ++tp) {
+                const bool a = mine && ((tb >> tp) & 1ull) != 0ull;
+                const T* px = in + (int64_t)(sin0 + s_toff[tp]) * p.ci;
+                float x[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) x[c] = (a && c < p.ci) ? to_f<T>(px[c]) : 0.f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    if (c < p.ci) {
+                        const float* wr = s_w + (tp * p.ci + c) * p.co + cl;
                         const float4 w0 = *reinterpret_cast<const float4*>(wr), w1 = *reinterpret_cast<const float4*>(wr + 4);
-                        acc[0] = fmaf(a, w0.x, acc[0]); acc[1] = fmaf(a, w0.y, acc[1]);
-                        acc[2] = fmaf(a, w0.z, acc[2]); acc[3] = fmaf(a, w0.w, acc[3]);
-                        acc[4] = fmaf(a, w1.x, acc[4]); acc[5] = fmaf(a, w1.y, acc[5]);
-                        acc[6] = fmaf(a, w1.z, acc[6]); acc[7] = fmaf(a, w1.w, acc[7]);
+                        acc[0] = fmaf(x[c], w0.x, acc[0]); acc[1] = fmaf(x[c], w0.y, acc[1]);
+                        acc[2] = fmaf(x[c], w0.z, acc[2]); acc[3] = fmaf(x[c], w0.w, acc[3]);
+                        acc[4] = fmaf(x[c], w1.x, acc[4]); acc[5] = fmaf(x[c], w1.y, acc[5]);
+                        acc[6] = fmaf(x[c], w1.z, acc[6]); acc[7] = fmaf(x[c], w1.w, acc[7]);
                     }
                 }
             }
-            const int64_t off = qq * p.co + lig * 8;
+            const int64_t off = qq * p.co + cl;
+            Pack<T, W> d[NP], y[NP], r[NP];
+#pragma unroll
+            for (int h = 0; h < NP; ++h)
+#pragma unroll
+                for (int k = 0; k < W; ++k) d[h].set(k, acc[h * W + k]);
             if (!p.fused) {
                 if (mine) {
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) out[off + k] = from_f<T>(acc[k]);
+                    for (int h = 0; h < NP; ++h) d[h].store(out + off + h * W);
                 }
                 continue;
             }
-            float yv[8], rv[8], ev[8];
             bool hit = false;
             if (mine) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const float yo = to_f<T>(prev[off + k]);
-                    const float rr = rnd<T>(to_f<T>(trunc[off + k]) + rnd<T>(acc[k]));
-                    const float u = rnd<T>(yo + rr);
-                    const float ee = rnd<T>(act_apply(u, p.act) - act_apply(yo, p.act));
-                    yv[k] = u; rv[k] = rr; ev[k] = ee;
-                    hit |= fabsf(ee) > p.thr;
+                for (int h = 0; h < NP; ++h) {
+                    y[h].load(prev + off + h * W);
+                    r[h].load(trunc + off + h * W);
+                }
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    if constexpr (sizeof(T) == 2) {
+                        if (half_exact) { hit |= truncate_pack_h2(d[h], y[h], r[h], p.act, thr2); continue; }
+                    }
+                    hit |= truncate_pack_f32(d[h], y[h], r[h], p.act, p.thr);
                 }
             }
             const bool active = group_any(hit, g, lane);
             if (mine) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    if (active) { prev[off + k] = from_f<T>(yv[k]); out[off + k] = from_f<T>(ev[k]); trunc[off + k] = from_f<T>(0.f); }
-                    else trunc[off + k] = from_f<T>(rv[k]);
+                for (int h = 0; h < NP; ++h) {
+                    if (active) {
+                        Pack<T, W> z; z.zero();
+                        y[h].store(prev + off + h * W);
+                        d[h].store(out + off + h * W);
+                        z.store(trunc + off + h * W);
+                    } else {
+                        r[h].store(trunc + off + h * W);
+                    }
                 }
             }
             if (src >= 0 && lig == 0) p.mo[qq] = active ? 1 : 0;
@@ -141,12 +163,13 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, const dc_epilogue* ep, cudaStream_t st) {
     const bool ok = d->groups == 1 && d->c_in <= 4 && d->c_out % 8 == 0 && d->c_out <= 256 && d->kh * d->kw <= 64 &&
-                    mi != nullptr && mo != nullptr && (d->dtype == DC_F16 || d->dtype == DC_F32) &&
-                    (ep == nullptr || ep->truncation == DC_TRUNC_MAX);
+                    mi != nullptr && mo != nullptr && (d->dtype == DC_F16 || d->dtype == DC_F32) && aligned16(out) &&
+                    (ep == nullptr || (ep->truncation == DC_TRUNC_MAX && aligned16(ep->prev_out) && aligned16(ep->truncated)));
     if (!ok) return DC_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(float) * ((size_t)d->kh * d->kw * d->c_in * d->c_out + d->c_out);
+    const size_t smem = sizeof(float) * ((size_t)d->kh * d->kw * d->c_in * d->c_out + d->c_out + (size_t)d->kh * d->kw);
     if (smem > 96 * 1024) return DC_ERR_UNSUPPORTED;
     if (d->n == 0) return DC_OK;
+    if ((int64_t)d->n * d->h_out * d->w_out > 0x7fffffffLL || (int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
     StemParams p{};
     p.in = in; p.mi = mi; p.w = filt; p.bias = bias; p.out = out; p.mo = mo;
     p.fused = ep != nullptr;
@@ -156,6 +179,8 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
     p.n = d->n; p.hi = d->h_in; p.wi = d->w_in; p.ci = d->c_in; p.ho = d->h_out; p.wo = d->w_out; p.co = d->c_out;
     p.kh = d->kh; p.kw = d->kw; p.sh = d->stride_h; p.sw = d->stride_w; p.pt = d->pad_top; p.pl = d->pad_left;
     p.dh = d->dil_h; p.dw = d->dil_w;
+    fast_div_init((uint32_t)p.wo, &p.wo_mul, &p.wo_shift);
+    fast_div_init((uint32_t)p.ho, &p.ho_mul, &p.ho_shift);
     const int64_t npix = (int64_t)d->n * d->h_out * d->w_out;
     int64_t blocks = divup64(npix, 256);
     const int64_t cap = (int64_t)sm_count() * 16;

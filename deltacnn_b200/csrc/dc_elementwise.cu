@@ -149,6 +149,8 @@ __global__ void __launch_bounds__(256) k_act_trunc(T* __restrict__ delta, T* __r
                                                    int32_t* __restrict__ mask, int64_t npix, int C, int g, float thr,
                                                    int act, int mode) {
     const int nvec = C / W;
+    const bool half_fast = mode == DC_TRUNC_MAX && act_exact_in_half(act);
+    const __half2 thr2 = __float2half2_rn(thr);
     DC_PIXEL_LOOP(npix, g) {
         const int64_t px = base + lane / g;
         const bool on = (px < npix) && (mask[px] != 0);
@@ -182,6 +184,13 @@ __global__ void __launch_bounds__(256) k_act_trunc(T* __restrict__ delta, T* __r
             d.load(delta + off + i * W);
             y.load(prev + off + i * W);
             r.load(trunc + off + i * W);
+            if constexpr (sizeof(T) == 2 && W == 8) {
+                if (half_fast) {                 // packed half arithmetic, bit-identical (see truncate_pack_h2)
+                    hit |= truncate_pack_h2(d, y, r, act, thr2);
+                    e = d;
+                    return;
+                }
+            }
 #pragma unroll
             for (int k = 0; k < W; ++k) {
                 float yo = y.get(k);
