@@ -49,7 +49,7 @@ int umma_error_code();
 int conv_thin(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, cudaStream_t st);
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
-              int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
+              int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st);
 int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
                     int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t conv_workspace_bytes(const dc_conv_desc* d);
@@ -103,7 +103,7 @@ int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_i
     if (filter_layout != DC_FILTER_HWIO) return DC_ERR_UNSUPPORTED;
     int rc = dwconv3x3_strip(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;
-    rc = conv_stem(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);
+    rc = conv_stem(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;
     rc = conv_thin(desc, in, mask_in, filter, bias, out, mask_out, st);
     if (rc == DC_ERR_UNSUPPORTED) rc = conv2d_simt(desc, in, mask_in, filter, bias, out, mask_out, st);

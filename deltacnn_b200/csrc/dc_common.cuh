@@ -170,20 +170,37 @@ __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol
 // DC_NO_PDL=1 in the environment turns programmatic dependent launch off (plain stream order).
 bool pdl_enabled();
 
+// cluster_y > 1 launches thread-block clusters of (1, cluster_y, 1) CTAs (grid.y must be a multiple of it).
 template <typename... KArgs, typename... Args>
-inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_y, Args... args) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_y > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = (unsigned)cluster_y;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = n;
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     return check_launch();
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    return launch_pdl_cluster(kernel, grid, block, smem, st, 1, args...);
 }
 
 // Sum-reduce over an aligned group of g lanes.

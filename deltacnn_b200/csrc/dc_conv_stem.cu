@@ -17,22 +17,147 @@ struct StemParams {
     uint32_t wo_mul, wo_shift, ho_mul, ho_shift;                 // fast_div constants for w_out and h_out
 };
 
+// One output pixel per aligned lane group (8 output channels per lane): taps x input channels against the fp32
+// filter in shared memory, epilogue in registers. Called by all 32 lanes of a warp.
 template <typename T>
-__global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
-    extern __shared__ float s_w[];                               // [kh*kw*ci][co] fp32, bias [co], tap offsets [kh*kw]
+__device__ __forceinline__ void stem_pixel(const StemParams& p, const float* s_w, const float* s_b, const int* s_toff, bool on,
+                                           unsigned long long tb, int sin0, int64_t qq, int lig, int g, int npk, int lane,
+                                           bool half_exact, __half2 thr2) {
     constexpr int W = VecTraits<T>::kVec, NP = 8 / W;            // a lane's 8 output channels as NP 16-byte packs
     const T* in = reinterpret_cast<const T*>(p.in);
     T* out = reinterpret_cast<T*>(p.out);
     T* prev = reinterpret_cast<T*>(p.prev);
     T* trunc = reinterpret_cast<T*>(p.trunc);
-    grid_dep_launch();
+    const int taps = p.kh * p.kw;
+    const bool mine = on && lig < npk;
+    const int cl = mine ? lig * 8 : 0;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = s_b[cl + k];
+    // uniform loop over the taps: the reads of a few taps are issued together, inactive taps add zeros
+#pragma unroll 3
+    for (int tp = 0; tp < taps; ++tp) {
+        const bool a = mine && ((tb >> tp) & 1ull) != 0ull;
+        const T* px = in + (int64_t)(sin0 + s_toff[tp]) * p.ci;
+        float x[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) x[c] = (a && c < p.ci) ? to_f<T>(px[c]) : 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (c < p.ci) {
+                const float* wr = s_w + (tp * p.ci + c) * p.co + cl;
+                const float4 w0 = *reinterpret_cast<const float4*>(wr), w1 = *reinterpret_cast<const float4*>(wr + 4);
+                acc[0] = fmaf(x[c], w0.x, acc[0]); acc[1] = fmaf(x[c], w0.y, acc[1]);
+                acc[2] = fmaf(x[c], w0.z, acc[2]); acc[3] = fmaf(x[c], w0.w, acc[3]);
+                acc[4] = fmaf(x[c], w1.x, acc[4]); acc[5] = fmaf(x[c], w1.y, acc[5]);
+                acc[6] = fmaf(x[c], w1.z, acc[6]); acc[7] = fmaf(x[c], w1.w, acc[7]);
+            }
+        }
+    }
+    const int64_t off = qq * p.co + cl;
+    Pack<T, W> d[NP], y[NP], r[NP];
+#pragma unroll
+    for (int h = 0; h < NP; ++h)
+#pragma unroll
+        for (int k = 0; k < W; ++k) d[h].set(k, acc[h * W + k]);
+    if (!p.fused) {
+        if (mine) {
+#pragma unroll
+            for (int h = 0; h < NP; ++h) d[h].store(out + off + h * W);
+        }
+        return;
+    }
+    bool hit = false;
+    if (mine) {
+#pragma unroll
+        for (int h = 0; h < NP; ++h) {
+            y[h].load(prev + off + h * W);
+            r[h].load(trunc + off + h * W);
+        }
+#pragma unroll
+        for (int h = 0; h < NP; ++h) {
+            if constexpr (sizeof(T) == 2) {
+                if (half_exact) { hit |= truncate_pack_h2(d[h], y[h], r[h], p.act, thr2); continue; }
+            }
+            hit |= truncate_pack_f32(d[h], y[h], r[h], p.act, p.thr);
+        }
+    }
+    const bool active = group_any(hit, g, lane);
+    if (mine) {
+#pragma unroll
+        for (int h = 0; h < NP; ++h) {
+            if (active) {
+                Pack<T, W> z; z.zero();
+                y[h].store(prev + off + h * W);
+                d[h].store(out + off + h * W);
+                z.store(trunc + off + h * W);
+            } else {
+                r[h].store(trunc + off + h * W);
+            }
+        }
+    }
+    if (on && lig == 0) p.mo[qq] = active ? 1 : 0;
+}
+
+// Filter [kh*kw*ci][co] and bias [co] as fp32 plus the input-pixel offset of every tap, in shared memory.
+template <typename T>
+__device__ __forceinline__ void stem_stage_filter(const StemParams& p, float* s_w, float** s_b_out, int** s_toff_out) {
     const int taps = p.kh * p.kw;
     const int kdim = taps * p.ci;
     for (int i = threadIdx.x; i < kdim * p.co; i += 256) s_w[i] = to_f<T>(reinterpret_cast<const T*>(p.w)[i]);
     float* s_b = s_w + kdim * p.co;
     for (int i = threadIdx.x; i < p.co; i += 256) s_b[i] = p.bias ? to_f<T>(reinterpret_cast<const T*>(p.bias)[i]) : 0.f;
-    int* s_toff = reinterpret_cast<int*>(s_b + p.co);            // input pixel of tap t relative to tap 0
+    int* s_toff = reinterpret_cast<int*>(s_b + p.co);
     for (int i = threadIdx.x; i < taps; i += 256) s_toff[i] = (i / p.kw) * p.dh * p.wi + (i % p.kw) * p.dw;
+    *s_b_out = s_b;
+    *s_toff_out = s_toff;
+}
+
+// List-driven form: persistent warps pull active output pixels (with the bit set of their active taps) from the
+// work list written by k_scan_conv_mask, so clustered active regions are spread evenly over the SMs.
+template <typename T>
+__global__ void __launch_bounds__(256) k_conv_stem_list(StemParams p, const int32_t* __restrict__ count,
+                                                        const uint32_t* __restrict__ list, const uint32_t* __restrict__ tapl) {
+    extern __shared__ float s_w[];
+    grid_dep_launch();
+    float* s_b;
+    int* s_toff;
+    stem_stage_filter<T>(p, s_w, &s_b, &s_toff);
+    grid_dep_wait();
+    const int cnt = *count;
+    if (cnt == 0) return;
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int npk = p.co >> 3;
+    int g = 1;
+    while (g < npk) g <<= 1;
+    const int lig = lane & (g - 1), gi = lane / g;
+    const int ppw = 32 / g;
+    const bool half_exact = sizeof(T) == 2 && act_exact_in_half(p.act);
+    const __half2 thr2 = __float2half2_rn(p.thr);
+    const int warp0 = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int nwarps = gridDim.x * 8;
+    for (int r = warp0 * ppw; r < cnt; r += nwarps * ppw) {
+        const int idx = r + gi;
+        const bool on = idx < cnt;
+        const uint32_t q = on ? list[idx] : 0u;
+        const unsigned long long tb = on ? (unsigned long long)tapl[idx] : 0ull;
+        const uint32_t t = fast_div(q, p.wo_mul, p.wo_shift);
+        const int ox = (int)(q - t * (uint32_t)p.wo);
+        const int b = (int)fast_div(t, p.ho_mul, p.ho_shift);
+        const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
+        const int in0 = (b * p.hi + oy * p.sh - p.pt) * p.wi + ox * p.sw - p.pl;
+        stem_pixel<T>(p, s_w, s_b, s_toff, on, tb, in0, (int64_t)q, lig, g, npk, lane, half_exact, thr2);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
+    extern __shared__ float s_w[];                               // [kh*kw*ci][co] fp32, bias [co], tap offsets [kh*kw]
+    grid_dep_launch();
+    float* s_b;
+    int* s_toff;
+    stem_stage_filter<T>(p, s_w, &s_b, &s_toff);
     grid_dep_wait();
     __syncthreads();
 
@@ -86,82 +211,16 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
             const int srcl = src < 0 ? 0 : src;
             const unsigned long long tb = __shfl_sync(DC_FULL, tapbits, srcl);
             const int sin0 = __shfl_sync(DC_FULL, in0, srcl);
-            const bool mine = src >= 0 && lig < npk;
-            const int64_t qq = (int64_t)base + srcl;
-            const int cl = mine ? lig * 8 : 0;
-            float acc[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = s_b[cl + k];
-            // uniform loop over the taps: the reads of a few taps are issued together, inactive taps add zeros
-#pragma unroll 3
-            for (int tp = 0; tp < taps; ++tp) {
-                const bool a = mine && ((tb >> tp) & 1ull) != 0ull;
-                const T* px = in + (int64_t)(sin0 + s_toff[tp]) * p.ci;
-                float x[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) x[c] = (a && c < p.ci) ? to_f<T>(px[c]) : 0.f;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    if (c < p.ci) {
-                        const float* wr = s_w + (tp * p.ci + c) * p.co + cl;
-                        const float4 w0 = *reinterpret_cast<const float4*>(wr), w1 = *reinterpret_cast<const float4*>(wr + 4);
-                        acc[0] = fmaf(x[c], w0.x, acc[0]); acc[1] = fmaf(x[c], w0.y, acc[1]);
-                        acc[2] = fmaf(x[c], w0.z, acc[2]); acc[3] = fmaf(x[c], w0.w, acc[3]);
-                        acc[4] = fmaf(x[c], w1.x, acc[4]); acc[5] = fmaf(x[c], w1.y, acc[5]);
-                        acc[6] = fmaf(x[c], w1.z, acc[6]); acc[7] = fmaf(x[c], w1.w, acc[7]);
-                    }
-                }
-            }
-            const int64_t off = qq * p.co + cl;
-            Pack<T, W> d[NP], y[NP], r[NP];
-#pragma unroll
-            for (int h = 0; h < NP; ++h)
-#pragma unroll
-                for (int k = 0; k < W; ++k) d[h].set(k, acc[h * W + k]);
-            if (!p.fused) {
-                if (mine) {
-#pragma unroll
-                    for (int h = 0; h < NP; ++h) d[h].store(out + off + h * W);
-                }
-                continue;
-            }
-            bool hit = false;
-            if (mine) {
-#pragma unroll
-                for (int h = 0; h < NP; ++h) {
-                    y[h].load(prev + off + h * W);
-                    r[h].load(trunc + off + h * W);
-                }
-#pragma unroll
-                for (int h = 0; h < NP; ++h) {
-                    if constexpr (sizeof(T) == 2) {
-                        if (half_exact) { hit |= truncate_pack_h2(d[h], y[h], r[h], p.act, thr2); continue; }
-                    }
-                    hit |= truncate_pack_f32(d[h], y[h], r[h], p.act, p.thr);
-                }
-            }
-            const bool active = group_any(hit, g, lane);
-            if (mine) {
-#pragma unroll
-                for (int h = 0; h < NP; ++h) {
-                    if (active) {
-                        Pack<T, W> z; z.zero();
-                        y[h].store(prev + off + h * W);
-                        d[h].store(out + off + h * W);
-                        z.store(trunc + off + h * W);
-                    } else {
-                        r[h].store(trunc + off + h * W);
-                    }
-                }
-            }
-            if (src >= 0 && lig == 0) p.mo[qq] = active ? 1 : 0;
+            stem_pixel<T>(p, s_w, s_b, s_toff, src >= 0, tb, sin0, (int64_t)base + srcl, lig, g, npk, lane, half_exact, thr2);
         }
     }
 }
 
 // groups == 1, c_in <= 4, c_out a multiple of 8 up to 256, at most 64 taps, with in- and out-mask.
+int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
+
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
-              int32_t* mo, const dc_epilogue* ep, cudaStream_t st) {
+              int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
     const bool ok = d->groups == 1 && d->c_in <= 4 && d->c_out % 8 == 0 && d->c_out <= 256 && d->kh * d->kw <= 64 &&
                     mi != nullptr && mo != nullptr && (d->dtype == DC_F16 || d->dtype == DC_F32) && aligned16(out) &&
                     (ep == nullptr || (ep->truncation == DC_TRUNC_MAX && aligned16(ep->prev_out) && aligned16(ep->truncated)));
@@ -185,18 +244,29 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
     int64_t blocks = divup64(npix, 256);
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    if (d->dtype == DC_F16) {
-        p.thr = p.fused ? host_round_threshold<__half>(ep->threshold) : 0.f;
-        static thread_local bool set16 = false;
-        if (smem > 48 * 1024 && !set16) { cudaFuncSetAttribute(k_conv_stem<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set16 = true; }
-        return launch_pdl(k_conv_stem<__half>, dim3((unsigned)blocks), dim3(256), smem, st, p);
-    } else {
-        p.thr = p.fused ? ep->threshold : 0.f;
-        static thread_local bool set32 = false;
-        if (smem > 48 * 1024 && !set32) { cudaFuncSetAttribute(k_conv_stem<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set32 = true; }
-        return launch_pdl(k_conv_stem<float>, dim3((unsigned)blocks), dim3(256), smem, st, p);
+    p.thr = !p.fused ? 0.f : d->dtype == DC_F16 ? host_round_threshold<__half>(ep->threshold) : ep->threshold;
+    static thread_local bool attr_set = false;
+    if (smem > 48 * 1024 && !attr_set) {
+        cudaFuncSetAttribute(k_conv_stem<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_conv_stem<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_conv_stem_list<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_conv_stem_list<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        attr_set = true;
     }
-    return check_launch();
+    // large maps with scratch: one scan pass writes the active pixels (tap bit sets fit 32 bits up to 5x5), then
+    // persistent warps share them evenly
+    if (ws != nullptr && d->kh * d->kw <= 32 && npix >= 40000) {
+        int rc = scan_conv_mask(d, mi, mo, ws, ws_bytes, p.fused, st);
+        if (rc != DC_OK) return rc;
+        const int32_t* count = reinterpret_cast<const int32_t*>(ws);
+        const uint32_t* list = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(ws) + 16);
+        const uint32_t* tapl = list + npix;
+        const unsigned grid = (unsigned)sm_count() * 8;
+        if (d->dtype == DC_F16) return launch_pdl(k_conv_stem_list<__half>, dim3(grid), dim3(256), smem, st, p, count, list, tapl);
+        return launch_pdl(k_conv_stem_list<float>, dim3(grid), dim3(256), smem, st, p, count, list, tapl);
+    }
+    if (d->dtype == DC_F16) return launch_pdl(k_conv_stem<__half>, dim3((unsigned)blocks), dim3(256), smem, st, p);
+    return launch_pdl(k_conv_stem<float>, dim3((unsigned)blocks), dim3(256), smem, st, p);
 }
 
 }  // namespace dc

@@ -361,7 +361,8 @@ def test_pointwise_umma_matches_oracle(case, density):
     assert_close_masked(out2, out.cpu(), m_ref, dtype, "umma vs simt")
 
 
-@pytest.mark.parametrize("case", [c for c in PW_CASES if c[1] <= 256] + [(64, 384, 1, 2, 14, 14)])
+@pytest.mark.parametrize("case", PW_CASES + [(64, 384, 1, 2, 14, 14), (96, 576, 1, 3, 14, 14), (160, 960, 1, 2, 7, 7), (320, 1280, 1, 2, 7, 7),
+                                             (256, 2048, 1, 1, 9, 9), (32, 272, 1, 3, 30, 30)])
 @pytest.mark.parametrize("act", [2, 0])
 def test_pointwise_umma_fused_epilogue_equals_two_kernels(case, act):
     from deltacnn_b200 import _lib
@@ -378,7 +379,7 @@ def test_pointwise_umma_fused_epilogue_equals_two_kernels(case, act):
     ho, wo = k.conv_out_hw(h, w, (1, 1), (s, s), (0, 0), (1, 1))
     prev = rand_feat(g, n, cout, ho, wo, dtype, 1.0).cuda()
     trunc = rand_feat(g, n, cout, ho, wo, dtype, 0.02).cuda()
-    thr = 0.6 if cout <= 64 else 0.9       # drops some pixels and keeps others
+    thr = 0.6 if cout <= 64 else 0.9 if cout <= 300 else 0.75       # drops some pixels and keeps others
     # two kernels: convolution, then activation/truncation
     o1, m1 = k.sparse_conv(x, f, mask, None, (s, s), (0, 0), (1, 1), 1, create_out_mask=True, filter_umma=packed)
     p1, t1 = prev.clone(), trunc.clone()
@@ -389,7 +390,9 @@ def test_pointwise_umma_fused_epilogue_equals_two_kernels(case, act):
     o2, m2 = k.sparse_conv(x, f, mask, None, (s, s), (0, 0), (1, 1), 1, create_out_mask=True, filter_umma=packed, epilogue=ep)
     assert _lib.lib.dc_umma_error() == 0
     assert torch.equal(m1, m2)
-    assert int(m2.sum()) <= int(m1.numel())
+    assert int(m2.sum()) <= int(mask[:, :, ::s, ::s].sum())
+    if cout > 300:
+        assert 0 < int(m2.sum()) < int(mask[:, :, ::s, ::s].sum()), "the threshold must keep some active pixels and drop others"
     assert torch.equal(p1, p2) and torch.equal(t1, t2)
     sel = (m1 != 0).expand_as(o1)
     assert torch.equal(o1[sel], o2[sel])
@@ -456,7 +459,10 @@ def test_stem_conv_fused_epilogue_equals_two_kernels(dtype, cout, k, s, p):
 
 
 @pytest.mark.parametrize("kind,cin,cout,h,w,s", [("pw", 16, 96, 40, 44, 1), ("pw", 144, 24, 28, 28, 1), ("pw", 960, 320, 7, 7, 1), ("pw", 64, 384, 14, 14, 1),
-                                                  ("pw", 256, 512, 16, 16, 2), ("dw", 96, 96, 40, 44, 2), ("dw", 32, 32, 50, 50, 1), ("dw", 960, 960, 7, 7, 1)])
+                                                  ("pw", 256, 512, 16, 16, 2), ("dw", 96, 96, 40, 44, 2), ("dw", 32, 32, 50, 50, 1), ("dw", 960, 960, 7, 7, 1),
+                                                  # maps large enough for the list-driven kernels to be chosen
+                                                  ("pw", 16, 96, 120, 121, 1), ("pw", 96, 24, 120, 121, 1), ("dw", 32, 32, 120, 121, 1),
+                                                  ("dw", 96, 96, 240, 236, 2), ("stem", 3, 32, 240, 236, 2), ("stem", 3, 32, 45, 47, 2)])
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("density", [0.0, 0.1, 1.0])
 def test_worklist_kernels_equal_the_plain_ones(kind, cin, cout, h, w, s, fused, density):
@@ -472,7 +478,7 @@ def test_worklist_kernels_equal_the_plain_ones(kind, cin, cout, h, w, s, fused, 
     mask[0, :, : h // 2] = 0
     mask = mask.cuda()
     groups = cin if kind == "dw" else 1
-    ksz, pad = (3, 1) if kind == "dw" else (1, 0)
+    ksz, pad = (1, 0) if kind == "pw" else (3, 1)
     wt = (torch.randn(cout, cin // groups, ksz, ksz, generator=g) * (0.4 if kind == "dw" else cin ** -0.5)).to(dtype)
     f = convert_filter_out_channels_last(wt).cuda()
     packed = _pack_umma(f, cin, cout, s) if kind == "pw" else None
