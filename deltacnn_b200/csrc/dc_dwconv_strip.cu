@@ -207,6 +207,107 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
     }
 }
 
+// Wide pixels (more than 256 channels): a warp owns one slice of 32 channel packs of one output pixel, the S
+// slices of a pixel sit in neighbouring warps of the CTA, and the any-channel decision of the fused epilogue
+// goes through shared memory. Compared with one warp walking all slices of a pixel in turn this gives S times
+// the warps to hide the read latency with, and a per-warp chain of one round of reads instead of S.
+// Persistent CTAs: the filter is staged once per CTA.
+__global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
+    float* s_b = s_w + 9 * p.c;                                       // [C]
+    __shared__ int s_flag[2][8];                                      // [iteration parity][warp]: slice passed the threshold
+    grid_dep_launch();
+    const int npk = p.c >> 3;
+    dw_stage_filter(p, s_w, s_b);
+    grid_dep_wait();
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ppi = 8 / S;                                            // pixels per CTA and iteration
+    const int my_px = warp / S, my_slice = warp - my_px * S;
+    const bool worker = warp < ppi * S;
+    const int i = my_slice * 32 + lane;                               // this lane's channel pack
+    const bool half_exact = act_exact_in_half(p.act);
+    const __half2 thr2 = __float2half2_rn(p.thr);
+    const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
+    int par = 0;
+    for (uint32_t base = blockIdx.x * (uint32_t)ppi; base < npix; base += gridDim.x * (uint32_t)ppi, par ^= 1) {
+        const uint32_t q = base + (uint32_t)my_px;
+        const bool on = worker && q < npix;
+        // the pixel's active taps: lane t < 9 looks at tap t
+        const uint32_t t = fast_div(on ? q : 0u, p.wo_mul, p.wo_shift);
+        const int ox = (int)((on ? q : 0u) - t * (uint32_t)p.wo);
+        const int b = (int)fast_div(t, p.ho_mul, p.ho_shift);
+        const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
+        const int y0 = oy * p.s - p.pt, x0 = ox * p.s - p.pl;
+        bool tap_on = false;
+        if (on && lane < 9) {
+            const int iy = y0 + lane / 3, ix = x0 + lane % 3;
+            tap_on = iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi && p.mi[((int64_t)b * p.hi + iy) * p.wi + ix] != 0;
+        }
+        const unsigned tb = __ballot_sync(DC_FULL, tap_on) & 0x1ffu;
+        if (on && my_slice == 0 && lane == 0 && (!p.fused || tb == 0u)) p.mo[q] = tb != 0u ? 1 : 0;
+        const bool mine = on && tb != 0u && i < npk;
+        const int64_t in0 = (((int64_t)b * p.hi + y0) * p.wi + x0) * p.c;
+        const int64_t off = (int64_t)q * p.c + i * 8;
+        uint4 v[9];
+#pragma unroll
+        for (int t9 = 0; t9 < 9; ++t9) {
+            v[t9] = make_uint4(0u, 0u, 0u, 0u);
+            if (mine && (tb & (1u << t9)))
+                v[t9] = __ldg(reinterpret_cast<const uint4*>(p.in + in0 + (int64_t)((t9 / 3) * p.wi + t9 % 3) * p.c) + i);
+        }
+        Pack<__half, 8> pd, pu, pr;
+        if (p.fused && mine) {
+            pu.load(p.prev + off);
+            pr.load(p.trunc + off);
+        }
+        float acc[8];
+        const int ci = mine ? i * 8 : 0;
+        {
+            const float4 b0 = *reinterpret_cast<const float4*>(s_b + ci), b1 = *reinterpret_cast<const float4*>(s_b + ci + 4);
+            acc[0] = b0.x; acc[1] = b0.y; acc[2] = b0.z; acc[3] = b0.w; acc[4] = b1.x; acc[5] = b1.y; acc[6] = b1.z; acc[7] = b1.w;
+        }
+#pragma unroll
+        for (int t9 = 0; t9 < 9; ++t9) {
+            const float4 w0 = *reinterpret_cast<const float4*>(s_w + t9 * p.c + ci), w1 = *reinterpret_cast<const float4*>(s_w + t9 * p.c + ci + 4);
+            const __half2* h = reinterpret_cast<const __half2*>(&v[t9]);
+            const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+            acc[0] = fmaf(f0.x, w0.x, acc[0]); acc[1] = fmaf(f0.y, w0.y, acc[1]);
+            acc[2] = fmaf(f1.x, w0.z, acc[2]); acc[3] = fmaf(f1.y, w0.w, acc[3]);
+            acc[4] = fmaf(f2.x, w1.x, acc[4]); acc[5] = fmaf(f2.y, w1.y, acc[5]);
+            acc[6] = fmaf(f3.x, w1.z, acc[6]); acc[7] = fmaf(f3.y, w1.w, acc[7]);
+        }
+        __half2* dh = reinterpret_cast<__half2*>(pd.s);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) dh[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+        if (!p.fused) {                                               // uniform over the CTA
+            if (mine) pd.store(p.out + off);
+            continue;
+        }
+        bool hit = false;
+        if (mine) hit = half_exact ? truncate_pack_h2(pd, pu, pr, p.act, thr2) : truncate_pack_f32(pd, pu, pr, p.act, p.thr);
+        const bool whit = __any_sync(DC_FULL, hit);
+        if (lane == 0) s_flag[par][warp] = whit ? 1 : 0;
+        __syncthreads();          // the flags of iteration parity `par` are next written two iterations (two barriers) later
+        bool active = false;
+        if (worker)
+            for (int sl = 0; sl < S; ++sl) active |= s_flag[par][my_px * S + sl] != 0;
+        if (mine) {
+            if (active) {
+                Pack<__half, 8> z; z.zero();
+                pu.store(p.prev + off);
+                pd.store(p.out + off);
+                z.store(p.trunc + off);
+            } else {
+                pr.store(p.trunc + off);
+            }
+        }
+        if (on && tb != 0u && my_slice == 0 && lane == 0) p.mo[q] = active ? 1 : 0;
+    }
+}
+
 // Depthwise 3x3 (stride 1 or 2, dilation 1) in fp16 with in- and out-mask; DC_ERR_UNSUPPORTED tells the
 // caller to use the generic kernels.
 int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
@@ -253,6 +354,14 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
             default: launch_pdl(k_dw3x3_list<4>, dim3(grid), dim3(256), smem_l, st, p, count, list, taps); break;
         }
         return check_launch();
+    }
+    if (nv >= 2) {                                    // wide pixels: one warp per slice of 32 channel packs, persistent CTAs
+        const int S = nv;                             // c_in <= 1024: at most 4 slices
+        const int ppi = 8 / S;
+        int64_t blocks_s = divup64(npix, ppi);
+        const int64_t cap_s = (int64_t)sm_count() * 4;
+        if (blocks_s > cap_s) blocks_s = cap_s;
+        return launch_pdl(k_dw3x3_sliced, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S);
     }
     // wide pixels keep a whole warp busy, so give every warp few of them; narrow pixels share a warp
     int g = 1;
