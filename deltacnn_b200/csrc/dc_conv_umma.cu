@@ -34,7 +34,7 @@ constexpr int kRows = 128;            // M of one MMA tile
 constexpr int kKBlock = 64;           // fp16 elements per K block (one 128-byte swizzle row)
 constexpr int kABytes = kRows * 128;  // one A stage
 constexpr int kStages = 4;           // shared-memory ring depth
-constexpr int kDelay = 2;            // a producer signals a K block after issuing kDelay more (copies in flight per thread)
+constexpr int kDelay = 1;            // a producer signals a K block after issuing kDelay more (copies in flight per thread)
 constexpr int kPwThreads = 256;
 constexpr int kPwWarps = kPwThreads / 32;
 constexpr int kProducerWarps = kPwWarps - 1;                  // the last warp feeds the tensor core
@@ -378,7 +378,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
                     signal_block();
                 }
             }
-            if (p.nkb >= 2) { cp_async_wait_group<1>(); signal_block(); }
+            if (kDelay >= 2 && p.nkb >= 2) { cp_async_wait_group<1>(); signal_block(); }
             cp_async_wait_group<0>();
             signal_block();
         } else {
