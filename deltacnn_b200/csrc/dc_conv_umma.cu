@@ -24,6 +24,8 @@
 //
 // Every wait on an mbarrier is bounded; a wait that gives up sets a sticky device-side error code
 // (dc_umma_error) and the CTA frees its tensor memory and returns.
+#include <cstring>
+#include <cuda.h>          // CUtensorMap and its enums (the encoder is fetched through cudaGetDriverEntryPoint)
 #include "dc_common.cuh"
 
 namespace dc {
@@ -62,6 +64,7 @@ struct PwParams {
     int m;                          //   m x m taps per phase (kh = m * stride); lists are per phase
     int64_t wl_stride;              //   entries between the per-phase list segments
     uint32_t hw_mul, hw_shift, wo_mul, wo_shift;   // division by h_out*w_out and by w_out (fast_div)
+    int tma_rows;                   // 1: the kernel got a tensor map of the input as [pixels][channels] and may load whole spans with it
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
 
@@ -143,6 +146,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
+// One tiled TMA load: box {64 channels, 128 pixels} of the [pixels][channels] input at (channel x, pixel y) into a
+// stage, written by the copy engine in the 128-byte-swizzled K-major layout; coordinates beyond the tensor read zeros.
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
@@ -163,7 +172,7 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 // ---- kernel -----------------------------------------------------------------------------------
 // Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
 //                [ row lists ][ mbarriers, scalars, bias ]
-__global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
+__global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, const __grid_constant__ CUtensorMap tmap_in) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
@@ -204,8 +213,8 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     };
 
     // ---- set-up that reads nothing the previous kernel wrote: overlaps that kernel's tail ----
-    if (tid <= 3 * kStages) {
-        mbar_init(bar0 + 8u * tid, (tid >= kStages && tid < 2 * kStages) ? (uint32_t)kProducerWarps : 1u);
+    if (tid <= 3 * kStages && (tid < kStages || tid >= 2 * kStages)) {     // the "full" barriers follow once the row mode is known
+        mbar_init(bar0 + 8u * tid, 1u);
         fence_barrier_init();
         if (tid == 0) s_u32[1] = 1;
     }
@@ -225,6 +234,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
     const bool list_mode = p.wl_list != nullptr;
     const int64_t q0 = list_mode ? 0 : (int64_t)blockIdx.x * p.span;
     int cnt = 0;
+    bool dense_rows = false;          // span mode: rows = all pixels of the span, loaded by TMA
     if (list_mode) {
         cnt = p.wl_count[blockIdx.z];
         if ((int64_t)blockIdx.x * kRows >= cnt) { leave(); return; }   // persistent CTAs beyond the work
@@ -260,11 +270,27 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
             cnt += c;
         }
         if (cnt == 0) { leave(); return; }    // nothing active in this span
-        if (on) {
+        // Mostly active span of a stride-1 layer: its pixels are consecutive rows of the input, so a tile is ONE tiled
+        // TMA load per K block instead of a gather; every pixel of the span becomes a row, the inactive ones are
+        // computed and dropped in the epilogue.
+        const int span_valid = (int)min((int64_t)p.span, p.npix_out - q0);
+        dense_rows = p.tma_rows != 0 && 2 * cnt >= span_valid;
+        if (dense_rows) {
+            cnt = span_valid;
+            if (tid < span_valid) {
+                s_out[tid] = tid;
+                s_base[tid] = pin;
+                s_tb[tid] = on ? 1u : 0u;
+            }
+        } else if (on) {
             s_out[slot] = tid;
             s_base[slot] = pin;
             s_tb[slot] = 1u;
         }
+    }
+    if (tid >= kStages && tid < 2 * kStages) {
+        mbar_init(bar0 + 8u * tid, dense_rows ? 1u : (uint32_t)kProducerWarps);
+        fence_barrier_init();
     }
 
     const uint32_t b_block_bytes = (uint32_t)p.bn * 128u;
@@ -331,7 +357,26 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
             __syncthreads();
         }
 
-        if (!is_mma_warp) {
+        if (!is_mma_warp && dense_rows) {
+            // ---- one thread asks the copy engine for the tile's rows, a K block per request ----
+            if (tid == 0) {
+                const int y0 = (int)q0 + t0;                           // first pixel of the tile (stride 1: pixel = input row)
+                for (int kb = 0; kb < p.nkb; ++kb) {
+                    if (pwrap > 0 && !mbar_wait(bar_empty(pslot), (uint32_t)((pwrap - 1) & 1), ok_flag)) {
+                        *ok_flag = 0; atomicExch(&g_umma_error, 1);
+                        break;
+                    }
+                    mbar_expect_tx(bar_full(pslot), (uint32_t)kABytes);
+                    tma_load_rows(sA_u32 + (uint32_t)pslot * kABytes, &tmap_in, kb * kKBlock, y0, bar_full(pslot));
+                    if (!p.b_resident) {
+                        mbar_expect_tx(bar_bfull(pslot), b_block_bytes);
+                        bulk_g2s(smem_u32(sB + (size_t)pslot * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(pslot));
+                    }
+                    if (++pslot == nse) { pslot = 0; ++pwrap; }
+                }
+            }
+            __syncwarp();
+        } else if (!is_mma_warp) {
             // ---- producers: run up to nse K blocks ahead of the tensor core; a block is signalled (full
             //      barrier, one arrival per warp) kDelay blocks after it was issued ----
             int rbase[kChunkPasses];
@@ -455,7 +500,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
 #pragma unroll
                 for (int u = 0; u < kU; ++u) {
                     const int r = rb + u * ppw + lane / g;
-                    mine[u] = r < cnt_t && lig < nch;
+                    mine[u] = r < cnt_t && lig < nch && (!dense_rows || s_tb[t0 + r] != 0u);
                     off[u] = 0;
                     if (mine[u]) {
                         off[u] = (q0 + s_out[t0 + r]) * p.cout + n0 + lig * 8;
@@ -488,7 +533,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(PwParams p) {
                         }
                     }
                     const int r = rb + u * ppw + lane / g;
-                    if (r < cnt_t && lig == 0) p.mo[q0 + s_out[t0 + r]] = active ? 1 : 0;
+                    if (r < cnt_t && lig == 0 && (!dense_rows || s_tb[t0 + r] != 0u)) p.mo[q0 + s_out[t0 + r]] = active ? 1 : 0;
                 }
             }
         }
@@ -604,6 +649,34 @@ int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* 
 
 int scan_deconv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
 
+// Tensor map of the input seen as a matrix [pixels][channels] (fp16), box {64 channels, 128 pixels}, 128-byte
+// swizzle: what tma_load_rows reads. The encoder lives in the driver; it is looked up once through the runtime.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static bool encode_rows_map(CUtensorMap* map, const void* in, int64_t npix_in, int cin) {
+    static EncodeTiledFn fn = nullptr;
+    static bool looked_up = false;
+    if (!looked_up) {
+        looked_up = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        else
+            (void)cudaGetLastError();
+    }
+    if (fn == nullptr) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)cin, (cuuint64_t)npix_in};
+    const cuuint64_t gstride[1] = {(cuuint64_t)cin * 2u};          // bytes between pixels: a multiple of 16 (cin % 8 == 0)
+    const cuuint32_t box[2] = {(cuuint32_t)kKBlock, (cuuint32_t)kRows};
+    const cuuint32_t estride[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(in), gdim, gstride, box, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in, const int32_t* mi, const void* filt, const void* bias,
                           void* out, int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
     PwPlan pl = plan_pw(d, transposed);
@@ -644,6 +717,13 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     p.b_kb_stride = (uint32_t)pl.rows * 128u;
     fast_div_init((uint32_t)(d->h_out * d->w_out), &p.hw_mul, &p.hw_shift);
     fast_div_init((uint32_t)d->w_out, &p.wo_mul, &p.wo_shift);
+    // span mode on a stride-1 pointwise layer: mostly active spans are loaded as whole tiles by TMA
+    alignas(64) CUtensorMap tmap;
+    memset(&tmap, 0, sizeof(tmap));
+    p.tma_rows = 0;
+    if (ws == nullptr && !transposed && pl.taps == 1 && d->stride_h == 1 && d->stride_w == 1 && d->pad_top == 0 && d->pad_left == 0 &&
+        d->c_in >= kKBlock && encode_rows_map(&tmap, in, (int64_t)d->n * d->h_in * d->w_in, d->c_in))
+        p.tma_rows = 1;
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_list = pl.off_list; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
     static thread_local bool attr_set = false;
     if (!attr_set) {
@@ -664,7 +744,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         if (persistent < 1) persistent = 1;
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
     }
-    int rc = launch_pdl(k_pw_umma, grid, dim3(kPwThreads), pl.smem, st, p);
+    int rc = launch_pdl(k_pw_umma, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
     if (rc != DC_OK) return rc;
     if (ep != nullptr && !fused)
         return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,
