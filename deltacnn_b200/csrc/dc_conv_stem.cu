@@ -113,21 +113,22 @@ __device__ __forceinline__ void stem_stage_filter(const StemParams& p, float* s_
     *s_toff_out = s_toff;
 }
 
-// List-driven form: persistent warps pull active output pixels (with the bit set of their active taps) from the
-// work list written by k_scan_conv_mask, so clustered active regions are spread evenly over the SMs.
+// Large maps without a work list in global memory: persistent CTAs own the 256-pixel spans blockIdx.x + j * gridDim.x,
+// dilate the mask of kStemSpans spans per round (thread = output pixel), compact the active pixels with their tap
+// bit sets into shared memory and let the eight warps share them. No scan pass, no counter to reset.
+constexpr int kStemSpans = 2;
 template <typename T>
-__global__ void __launch_bounds__(256) k_conv_stem_list(StemParams p, const int32_t* __restrict__ count,
-                                                        const uint32_t* __restrict__ list, const uint32_t* __restrict__ tapl) {
+__global__ void __launch_bounds__(256) k_conv_stem_cta(StemParams p, int64_t nspans, int rounds) {
     extern __shared__ float s_w[];
+    __shared__ uint32_t s_q[kStemSpans * 256];
+    __shared__ unsigned long long s_t[kStemSpans * 256];
+    __shared__ int s_cnt;
     grid_dep_launch();
     float* s_b;
     int* s_toff;
     stem_stage_filter<T>(p, s_w, &s_b, &s_toff);
     grid_dep_wait();
-    const int cnt = *count;
-    if (cnt == 0) return;
-    __syncthreads();
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int npk = p.co >> 3;
     int g = 1;
     while (g < npk) g <<= 1;
@@ -135,19 +136,61 @@ __global__ void __launch_bounds__(256) k_conv_stem_list(StemParams p, const int3
     const int ppw = 32 / g;
     const bool half_exact = sizeof(T) == 2 && act_exact_in_half(p.act);
     const __half2 thr2 = __float2half2_rn(p.thr);
-    const int warp0 = blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int nwarps = gridDim.x * 8;
-    for (int r = warp0 * ppw; r < cnt; r += nwarps * ppw) {
-        const int idx = r + gi;
-        const bool on = idx < cnt;
-        const uint32_t q = on ? list[idx] : 0u;
-        const unsigned long long tb = on ? (unsigned long long)tapl[idx] : 0ull;
+    const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
+    auto in0_of = [&](uint32_t q) {
         const uint32_t t = fast_div(q, p.wo_mul, p.wo_shift);
         const int ox = (int)(q - t * (uint32_t)p.wo);
         const int b = (int)fast_div(t, p.ho_mul, p.ho_shift);
         const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
-        const int in0 = (b * p.hi + oy * p.sh - p.pt) * p.wi + ox * p.sw - p.pl;
-        stem_pixel<T>(p, s_w, s_b, s_toff, on, tb, in0, (int64_t)q, lig, g, npk, lane, half_exact, thr2);
+        return (b * p.hi + oy * p.sh - p.pt) * p.wi + ox * p.sw - p.pl;
+    };
+    for (int round = 0; round < rounds; ++round) {
+        if (threadIdx.x == 0) s_cnt = 0;
+        __syncthreads();              // also: the filter is staged, the previous round's list has been consumed
+#pragma unroll
+        for (int j = 0; j < kStemSpans; ++j) {
+            const int64_t sid = (int64_t)blockIdx.x + (int64_t)(round * kStemSpans + j) * gridDim.x;
+            const int64_t q64 = sid * 256 + threadIdx.x;
+            const bool valid = sid < nspans && q64 < (int64_t)npix;
+            const uint32_t q = valid ? (uint32_t)q64 : 0u;
+            unsigned long long tapbits = 0ull;
+            if (valid) {
+                const uint32_t t = fast_div(q, p.wo_mul, p.wo_shift);
+                const int ox = (int)(q - t * (uint32_t)p.wo);
+                const int b = (int)fast_div(t, p.ho_mul, p.ho_shift);
+                const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
+                const int y0 = oy * p.sh - p.pt, x0 = ox * p.sw - p.pl;
+                const int in0 = (b * p.hi + y0) * p.wi + x0;
+                for (int ky = 0; ky < p.kh; ++ky) {
+                    const int iy = y0 + ky * p.dh;
+                    if (iy < 0 || iy >= p.hi) continue;
+                    for (int kx = 0; kx < p.kw; ++kx) {
+                        const int ix = x0 + kx * p.dw;
+                        if (ix < 0 || ix >= p.wi) continue;
+                        if (p.mi[in0 + ky * p.dh * p.wi + kx * p.dw] != 0) tapbits |= 1ull << (ky * p.kw + kx);
+                    }
+                }
+                if (!p.fused || tapbits == 0ull) p.mo[q] = tapbits != 0ull ? 1 : 0;
+            }
+            const unsigned bal = __ballot_sync(DC_FULL, tapbits != 0ull);
+            int base = 0;
+            if (lane == 0 && bal != 0u) base = atomicAdd(&s_cnt, __popc(bal));
+            base = __shfl_sync(DC_FULL, base, 0);
+            if (tapbits != 0ull) {
+                const int slot = base + __popc(bal & ((1u << lane) - 1u));
+                s_q[slot] = q;
+                s_t[slot] = tapbits;
+            }
+        }
+        __syncthreads();
+        const int cnt = s_cnt;
+        for (int r = warp * ppw; r < cnt; r += 8 * ppw) {
+            const int idx = r + gi;
+            const bool on = idx < cnt;
+            const uint32_t q = on ? s_q[idx] : 0u;
+            const unsigned long long tb = on ? s_t[idx] : 0ull;
+            stem_pixel<T>(p, s_w, s_b, s_toff, on, tb, in0_of(q), (int64_t)q, lig, g, npk, lane, half_exact, thr2);
+        }
     }
 }
 
@@ -217,8 +260,6 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
 }
 
 // groups == 1, c_in <= 4, c_out a multiple of 8 up to 256, at most 64 taps, with in- and out-mask.
-int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
-
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
     const bool ok = d->groups == 1 && d->c_in <= 4 && d->c_out % 8 == 0 && d->c_out <= 256 && d->kh * d->kw <= 64 &&
@@ -249,21 +290,19 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
     if (smem > 48 * 1024 && !attr_set) {
         cudaFuncSetAttribute(k_conv_stem<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         cudaFuncSetAttribute(k_conv_stem<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(k_conv_stem_list<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(k_conv_stem_list<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_conv_stem_cta<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_conv_stem_cta<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         attr_set = true;
     }
-    // large maps with scratch: one scan pass writes the active pixels (tap bit sets fit 32 bits up to 5x5), then
-    // persistent warps share them evenly
-    if (ws != nullptr && d->kh * d->kw <= 32 && npix >= 40000) {
-        int rc = scan_conv_mask(d, mi, mo, ws, ws_bytes, p.fused, st);
-        if (rc != DC_OK) return rc;
-        const int32_t* count = reinterpret_cast<const int32_t*>(ws);
-        const uint32_t* list = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(ws) + 16);
-        const uint32_t* tapl = list + npix;
-        const unsigned grid = (unsigned)sm_count() * 8;
-        if (d->dtype == DC_F16) return launch_pdl(k_conv_stem_list<__half>, dim3(grid), dim3(256), smem, st, p, count, list, tapl);
-        return launch_pdl(k_conv_stem_list<float>, dim3(grid), dim3(256), smem, st, p, count, list, tapl);
+    // large maps: persistent CTAs compact the active pixels of their spans themselves (no scan pass, no scratch)
+    (void)ws; (void)ws_bytes;
+    if (npix >= 40000) {
+        const int64_t nspans = divup64(npix, 256);
+        int64_t grid_c = (int64_t)sm_count() * (d->dtype == DC_F16 ? 4 : 3);    // resident CTAs (registers)
+        if (grid_c > nspans) grid_c = nspans;
+        const int rounds = (int)divup64(divup64(nspans, grid_c), kStemSpans);
+        if (d->dtype == DC_F16) return launch_pdl(k_conv_stem_cta<__half>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
+        return launch_pdl(k_conv_stem_cta<float>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
     }
     if (d->dtype == DC_F16) return launch_pdl(k_conv_stem<__half>, dim3((unsigned)blocks), dim3(256), smem, st, p);
     return launch_pdl(k_conv_stem<float>, dim3((unsigned)blocks), dim3(256), smem, st, p);

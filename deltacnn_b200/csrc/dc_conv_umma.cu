@@ -44,6 +44,7 @@ constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kRowStep = kProducerThreads / 8;                // rows between a producer thread's chunks
 constexpr int kChunkPasses = (kRows + kRowStep - 1) / kRowStep;
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr int kMsSpans = 8;                  // spans whose active pixels a persistent CTA compacts together
 constexpr int64_t kListMinPixels = 40000;    // below this many output pixels 1x1 layers skip the work list
 
 struct PwParams {
@@ -64,6 +65,8 @@ struct PwParams {
     int m;                          //   m x m taps per phase (kh = m * stride); lists are per phase
     int64_t wl_stride;              //   entries between the per-phase list segments
     uint32_t hw_mul, hw_shift, wo_mul, wo_shift;   // division by h_out*w_out and by w_out (fast_div)
+    int ms_rounds;                  // > 0: persistent CTAs over strided 128-pixel spans, kMsSpans of them per round
+    int64_t ms_nspans;              //      number of 128-pixel spans of the output
     int tma_rows;                   // 1: the kernel got a tensor map of the input as [pixels][channels] and may load whole spans with it
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
@@ -232,7 +235,8 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
 
     // ---- the rows of this CTA ----
     const bool list_mode = p.wl_list != nullptr;
-    const int64_t q0 = list_mode ? 0 : (int64_t)blockIdx.x * p.span;
+    const bool multi = p.ms_rounds > 0;                               // span mode over several strided spans per CTA
+    const int64_t q0 = (list_mode || multi) ? 0 : (int64_t)blockIdx.x * p.span;
     int cnt = 0;
     bool dense_rows = false;          // span mode: rows = all pixels of the span, loaded by TMA
     if (list_mode) {
@@ -240,6 +244,8 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         if ((int64_t)blockIdx.x * kRows >= cnt) { leave(); return; }   // persistent CTAs beyond the work
         if (tid < p.taps)                                           // input pixel of tap t relative to a row's base pixel
             s_toff[tid] = p.transposed ? -((tid / p.m) * p.wi + tid % p.m) : (tid / p.kw) * p.dh * p.wi + (tid % p.kw) * p.dw;
+    } else if (multi) {
+        if (tid == 0) s_toff[0] = 0;
     } else {
         // span mode (1x1 kernels, no padding): thread t owns pixel q0 + t; the active ones are compacted in
         // order with a ballot per warp and a prefix over the warp totals
@@ -327,12 +333,48 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     const __half2 thr2 = __float2half2_rn(p.thr);
     __syncthreads();                  // row lists complete
 
+    const bool plain_1x1 = p.taps == 1 && p.sh == 1 && p.sw == 1 && p.pt == 0 && p.pl == 0 && !p.transposed;
+    int tile = 0;                     // tiles processed by this CTA (the accumulator barrier's phase counts these)
+    const int nrounds = multi ? p.ms_rounds : 1;
+    for (int round = 0; round < nrounds && ok; ++round) {
+    if (multi) {
+        // Large maps of 1x1 layers without a work list: a persistent CTA owns the spans blockIdx.x + j * gridDim.x
+        // (so clustered active regions are dealt round-robin to all CTAs) and compacts the active pixels of kMsSpans
+        // of them into one row list. All mask reads of a round are in flight together.
+        if (tid == 0) s_u32[2] = 0u;
+        __syncthreads();
+        int64_t q4[4];
+        bool on4[4], valid4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int v = tid + kPwThreads * i;                      // 0 .. kMsSpans * 128 - 1
+            const int64_t sid = (int64_t)blockIdx.x + (int64_t)(round * kMsSpans + (v >> 7)) * gridDim.x;
+            q4[i] = sid * kRows + (v & 127);
+            valid4[i] = sid < p.ms_nspans && q4[i] < p.npix_out;
+            on4[i] = valid4[i] && p.mi[valid4[i] ? q4[i] : 0] != 0;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (valid4[i] && blockIdx.y == 0 && (!p.fused || !on4[i])) p.mo[q4[i]] = on4[i] ? 1 : 0;
+            const unsigned bal = __ballot_sync(DC_FULL, on4[i]);
+            int base = 0;
+            if (lane == 0 && bal != 0u) base = (int)atomicAdd(&s_u32[2], (uint32_t)__popc(bal));
+            base = __shfl_sync(DC_FULL, base, 0);
+            if (on4[i]) {
+                const int slot = base + __popc(bal & ((1u << lane) - 1u));
+                s_out[slot] = (int)q4[i];
+                s_base[slot] = (int)q4[i];
+                s_tb[slot] = 1u;
+            }
+        }
+        __syncthreads();
+        cnt = (int)s_u32[2];
+        if (cnt == 0) continue;
+    }
     // span mode: the tiles of this CTA's own list; list mode: every gridDim.x-th tile of the global list
     const int tile_first = list_mode ? (int)blockIdx.x : 0;
     const int tile_step = list_mode ? (int)gridDim.x : 1;
     const int tiles_total = (cnt + kRows - 1) / kRows;
-    const bool plain_1x1 = p.taps == 1 && p.sh == 1 && p.sw == 1 && p.pt == 0 && p.pl == 0 && !p.transposed;
-    int tile = 0;                     // tiles processed by this CTA (the accumulator barrier's phase counts these)
     for (int tg = tile_first; tg < tiles_total && ok; tg += tile_step, ++tile) {
         const int cnt_t = min(kRows, cnt - tg * kRows);
         const int t0 = list_mode ? 0 : tg * kRows;                  // offset of the tile's rows in the shared lists
@@ -540,6 +582,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         __syncthreads();
         tc_fence_after();
     }
+    }   // rounds
 
     // drain: copies in flight and every MMA that was issued have to finish before shared and tensor memory are released
     cp_async_wait_group<0>();
@@ -593,7 +636,7 @@ static PwPlan plan_pw(const dc_conv_desc* d, int transposed = 0) {
 }
 
 // Launch-time choices: N tiling, span of pixels per CTA, shared-memory layout.
-static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, bool want_fused, bool list_mode) {
+static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, bool want_fused, bool list_mode, bool multi_span) {
     const int sms = sm_count();
     pl.ntiles = divup(d->c_out, 256);
     pl.bn = divup(divup(d->c_out, pl.ntiles), 16) * 16;
@@ -618,6 +661,7 @@ static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, boo
     const int64_t want = (int64_t)sms * 6;
     while (span > 128 && divup64(npix_out, span) * pl.ntiles < want) span >>= 1;
     if (list_mode) span = kRows;      // the shared row lists hold one tile
+    if (multi_span) span = kMsSpans * kRows;   // ... or the active pixels of a round of spans
     pl.span = span;
     pl.stage_pitch = (uint32_t)pl.bn * 2 + 16;
     const uint32_t ring = (uint32_t)pl.nslots * kABytes;
@@ -689,14 +733,16 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     if (npix_out == 0) return DC_OK;
     if ((int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
     const bool want_fused = ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
-    // A work list costs two extra launches (counter reset + scan). It pays when the active set is large and
-    // clustered; small maps keep the single-kernel form (1x1 only: each CTA compacts its own span of pixels).
-    if (ws != nullptr && !transposed && pl.taps == 1 && d->pad_top == 0 && d->pad_left == 0 && npix_out < kListMinPixels) ws = nullptr;
+    // 1x1 layers without padding never need a work list: each CTA compacts its own pixels. On small maps a CTA owns
+    // one contiguous span; on large maps persistent CTAs own strided spans (multi-span mode).
+    const bool pointwise = !transposed && pl.taps == 1 && d->pad_top == 0 && d->pad_left == 0;
+    if (pointwise && ((d->stride_h == 1 && d->stride_w == 1) || npix_out < kListMinPixels)) ws = nullptr;
+    const bool multi_span = ws == nullptr && pointwise && d->stride_h == 1 && d->stride_w == 1 && npix_out >= kListMinPixels;
     if (transposed) {                 // the kernel sees one phase: m x m taps
         pl.taps = (d->kh / 2) * (d->kw / 2);
         pl.nkb = pl.taps * pl.ncb;
     }
-    finish_plan(pl, d, npix_out, want_fused, ws != nullptr);
+    finish_plan(pl, d, npix_out, want_fused, ws != nullptr, multi_span);
     const bool fused = want_fused && pl.ntiles == 1;
     PwParams p{};
     p.in = (const __half*)in; p.mi = mi; p.wimg = (const uint8_t*)filt; p.bias = (const __half*)bias;
@@ -732,6 +778,15 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     }
     if (pl.smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
     dim3 grid((unsigned)divup64(npix_out, pl.span), (unsigned)pl.ntiles);
+    p.ms_rounds = 0;
+    p.ms_nspans = divup64(npix_out, kRows);
+    if (multi_span) {
+        int64_t persistent = (int64_t)sm_count() * 3 / pl.ntiles;     // three CTAs of this kernel fit on an SM
+        if (persistent < 1) persistent = 1;
+        grid.x = (unsigned)(p.ms_nspans < persistent ? p.ms_nspans : persistent);
+        p.ms_rounds = (int)divup64(divup64(p.ms_nspans, grid.x), kMsSpans);
+        p.tma_rows = 0;
+    }
     if (ws != nullptr) {              // work-list mode: scan pass, then persistent CTAs over the active rows
         int rc = transposed ? scan_deconv_mask(d, mi, mo, ws, ws_bytes, fused ? 1 : 0, st)
                             : scan_conv_mask(d, mi, mo, ws, ws_bytes, fused ? 1 : 0, st);

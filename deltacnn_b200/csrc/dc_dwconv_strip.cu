@@ -207,6 +207,90 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
     }
 }
 
+// Large maps without a work list in global memory: persistent CTAs own the 256-pixel spans blockIdx.x + j * gridDim.x
+// (clustered active regions are dealt round-robin to all CTAs). Per round a CTA dilates the mask of kCtaSpans spans
+// (thread = output pixel, all mask reads in flight together), compacts the active pixels with their tap bit sets
+// into shared memory and lets its eight warps share them, so one active run of pixels is spread over the whole CTA
+// instead of being walked by one warp. No scan pass, no counter to reset.
+constexpr int kCtaSpans = 4;
+template <int NV>
+__global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t nspans, int rounds) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
+    float* s_b = s_w + 9 * p.c;                                       // [C]
+    __shared__ uint32_t s_q[kCtaSpans * 256], s_t[kCtaSpans * 256];
+    __shared__ int s_cnt;
+    grid_dep_launch();
+    const int npk = p.c >> 3;
+    dw_stage_filter(p, s_w, s_b);
+    grid_dep_wait();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int g = 1;
+    while (g < npk && g < 32) g <<= 1;
+    const int lig = lane & (g - 1);
+    const int gi = lane / g;
+    const int ppw = 32 / g;
+    const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
+    for (int round = 0; round < rounds; ++round) {
+        if (threadIdx.x == 0) s_cnt = 0;
+        __syncthreads();              // also: the filter is staged, the previous round's list has been consumed
+        // ---- phase 1: thread = output pixel of each of the round's spans ----
+        unsigned tb4[kCtaSpans];
+        uint32_t q4[kCtaSpans];
+        bool valid4[kCtaSpans];
+#pragma unroll
+        for (int j = 0; j < kCtaSpans; ++j) {
+            const int64_t sid = (int64_t)blockIdx.x + (int64_t)(round * kCtaSpans + j) * gridDim.x;
+            const int64_t q64 = sid * 256 + threadIdx.x;
+            valid4[j] = sid < nspans && q64 < (int64_t)npix;
+            q4[j] = valid4[j] ? (uint32_t)q64 : 0u;
+            tb4[j] = 0u;
+            if (valid4[j]) {
+                const uint32_t t = fast_div(q4[j], p.wo_mul, p.wo_shift);
+                const int ox = (int)(q4[j] - t * (uint32_t)p.wo);
+                const int b = (int)fast_div(t, p.ho_mul, p.ho_shift);
+                const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
+                const int y0 = oy * p.s - p.pt, x0 = ox * p.s - p.pl;
+                const int32_t* mrow = p.mi + (int64_t)b * p.hi * p.wi;
+#pragma unroll
+                for (int t9 = 0; t9 < 9; ++t9) {
+                    const int iy = y0 + t9 / 3, ix = x0 + t9 % 3;
+                    if (iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi && mrow[iy * p.wi + ix] != 0) tb4[j] |= 1u << t9;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kCtaSpans; ++j) {
+            if (valid4[j] && (!p.fused || tb4[j] == 0u)) p.mo[q4[j]] = tb4[j] != 0u ? 1 : 0;
+            const unsigned bal = __ballot_sync(DC_FULL, tb4[j] != 0u);
+            int base = 0;
+            if (lane == 0 && bal != 0u) base = atomicAdd(&s_cnt, __popc(bal));
+            base = __shfl_sync(DC_FULL, base, 0);
+            if (tb4[j] != 0u) {
+                const int slot = base + __popc(bal & ((1u << lane) - 1u));
+                s_q[slot] = q4[j];
+                s_t[slot] = tb4[j];
+            }
+        }
+        __syncthreads();
+        const int cnt = s_cnt;
+        // ---- phase 2: the CTA's warps share the active pixels ----
+        for (int r = warp * ppw; r < cnt; r += 8 * ppw) {
+            const int idx = r + gi;
+            const bool on = idx < cnt;
+            const uint32_t q = on ? s_q[idx] : 0u;
+            const unsigned tb = on ? s_t[idx] : 0u;
+            const uint32_t t = fast_div(q, p.wo_mul, p.wo_shift);
+            const int ox = (int)(q - t * (uint32_t)p.wo);
+            const uint32_t b = fast_div(t, p.ho_mul, p.ho_shift);
+            const int oy = (int)(t - b * (uint32_t)p.ho);
+            const int64_t in0 = (((int64_t)b * p.hi + (oy * p.s - p.pt)) * p.wi + (ox * p.s - p.pl)) * p.c;
+            dw_pixel<NV>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
+        }
+    }
+}
+
 // Wide pixels (more than 256 channels): a warp owns one slice of 32 channel packs of one output pixel, the S
 // slices of a pixel sit in neighbouring warps of the CTA, and the any-channel decision of the fused epilogue
 // goes through shared memory. Compared with one warp walking all slices of a pixel in turn this gives S times
@@ -338,6 +422,13 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     const int npk = p.c / 8;
     const int nv = divup(npk, 32);
     const size_t smem = (size_t)10 * p.c * 4;         // filter and bias as fp32
+    if (nv == 1 && npix >= 40000) {                    // large map, narrow pixels: CTA-level compaction, no scan pass
+        const int64_t nspans = divup64(npix, 256);
+        int64_t grid_c = (int64_t)sm_count() * 4;
+        if (grid_c > nspans) grid_c = nspans;
+        const int rounds = (int)divup64(divup64(nspans, grid_c), kCtaSpans);
+        return launch_pdl(k_dw3x3_cta<1>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
+    }
     // the work list costs two extra launches; it pays on large maps where the active pixels cluster
     if (ws != nullptr && npix >= 40000) {             // work-list form: one scan pass, then persistent warps over the active pixels
         int rc = scan_conv_mask(d, mi, mo, ws, ws_bytes, p.fused, st);

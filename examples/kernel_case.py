@@ -1,7 +1,7 @@
 """One kernel of the delta path on a fixed, seeded, benchmark-shaped input, a few launches: the
 small case that profiler captures are taken on (inputs larger than L2, well under 1 GB on the device).
 
-    python examples/kernel_case.py pw     # tcgen05 pointwise 16->96 @112x112, fused ReLU6 + truncation, 32 streams (work-list mode)
+    python examples/kernel_case.py pw     # tcgen05 pointwise 16->96 @112x112, fused ReLU6 + truncation, 32 streams (persistent CTAs over strided spans)
     python examples/kernel_case.py dw     # depthwise 3x3 96 ch @112x112 stride 2, fused ReLU6 + truncation, 32 streams
     python examples/kernel_case.py act    # stand-alone activation/truncation, 96 ch @112x112, 32 streams
 Prints the CUDA-event time per launch (L2 flushed between launches) and the algorithmic GB/s.

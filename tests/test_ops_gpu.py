@@ -115,6 +115,8 @@ CONV_CASES = [
     (96, 96, 3, 2, 1, 1, 96, 12, 12),
     (12, 12, 5, 1, 2, 1, 12, 8, 8),
     (7, 7, 3, 1, 1, 1, 7, 8, 8),
+    # maps large enough for the persistent kernels that compact the active pixels per CTA
+    (3, 32, 3, 2, 1, 1, 1, 320, 330), (3, 16, 7, 2, 3, 1, 1, 300, 300), (32, 32, 3, 1, 1, 1, 32, 150, 151), (96, 96, 3, 2, 1, 1, 96, 300, 302),
 ]
 
 
@@ -317,6 +319,8 @@ PW_CASES = [
     (32, 16, 1, 2, 20, 24), (16, 96, 1, 2, 24, 20), (96, 24, 1, 2, 16, 16), (24, 144, 1, 2, 16, 12), (144, 32, 1, 3, 9, 9),
     (192, 64, 1, 2, 14, 14), (64, 384, 1, 2, 14, 14), (576, 160, 1, 2, 7, 7), (960, 320, 1, 2, 7, 7), (320, 1280, 1, 3, 7, 7),
     (256, 512, 2, 2, 16, 16), (64, 256, 1, 1, 40, 40), (1024, 2048, 2, 1, 8, 8),
+    # large maps: persistent CTAs over strided spans, one and several rounds
+    (16, 96, 1, 3, 120, 121), (96, 24, 1, 4, 112, 112), (16, 32, 1, 10, 224, 224),
 ]
 
 
