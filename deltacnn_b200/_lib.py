@@ -25,7 +25,8 @@ class ConvDesc(ctypes.Structure):
 class Epilogue(ctypes.Structure):
     """dc_epilogue."""
     _fields_ = [("prev_out", c_void_p), ("truncated", c_void_p), ("threshold", c_float),
-                ("activation", c_int), ("truncation", c_int)]
+                ("activation", c_int), ("truncation", c_int),
+                ("residual", c_void_p), ("residual_mask", c_void_p)]
 
 
 if not os.path.exists(LIB_PATH):

@@ -94,8 +94,10 @@ int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_i
                  const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* workspace,
                  size_t workspace_bytes, void* stream) {
     if (desc == nullptr || in == nullptr || filter == nullptr || out == nullptr) return DC_ERR_NULL_POINTER;
-    if (epilogue != nullptr && (epilogue->prev_out == nullptr || (epilogue->truncation >= 0 && epilogue->truncated == nullptr)))
+    const bool residual_only = epilogue != nullptr && epilogue->residual != nullptr;
+    if (epilogue != nullptr && !residual_only && (epilogue->prev_out == nullptr || (epilogue->truncation >= 0 && epilogue->truncated == nullptr)))
         return DC_ERR_NULL_POINTER;
+    if (residual_only && filter_layout != DC_FILTER_UMMA) return DC_ERR_UNSUPPORTED;   // the caller adds with dc_add
     if (workspace != nullptr && workspace_bytes < conv_workspace_bytes(desc)) return DC_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     if (filter_layout == DC_FILTER_UMMA)
@@ -122,6 +124,7 @@ int dc_deconv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask
                    const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* workspace,
                    size_t workspace_bytes, void* stream) {
     if (desc == nullptr || in == nullptr || filter == nullptr || out == nullptr) return DC_ERR_NULL_POINTER;
+    if (epilogue != nullptr && epilogue->residual != nullptr) return DC_ERR_UNSUPPORTED;   // residual connections: 1x1 convolutions only
     if (epilogue != nullptr && (epilogue->prev_out == nullptr || (epilogue->truncation >= 0 && epilogue->truncated == nullptr)))
         return DC_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;

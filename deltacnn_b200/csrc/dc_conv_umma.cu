@@ -44,6 +44,7 @@ constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kRowStep = kProducerThreads / 8;                // rows between a producer thread's chunks
 constexpr int kChunkPasses = (kRows + kRowStep - 1) / kRowStep;
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr uint32_t kRowHasResidual = 0x40000000u;   // bit of a row's tap word: the residual is active at this pixel
 constexpr int kMsSpans = 8;                  // spans whose active pixels a persistent CTA compacts together
 constexpr int64_t kListMinPixels = 40000;    // below this many output pixels 1x1 layers skip the work list
 
@@ -51,6 +52,7 @@ struct PwParams {
     const __half* in; const int32_t* mi; const uint8_t* wimg; const __half* bias;
     __half* out; int32_t* mo; __half* prev; __half* trunc;
     float thr; int act; int fused;
+    const __half* res; const int32_t* res_mask;   // optional residual (delta, mask) added to a linear 1x1 result
     int64_t npix_out;
     int hi, wi, ho, wo, sh, sw;
     int kh, kw, dh, dw, pt, pl;     // kernel geometry; taps = kh * kw (K runs tap-major, then input channels)
@@ -250,7 +252,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         // span mode (1x1 kernels, no padding): thread t owns pixel q0 + t; the active ones are compacted in
         // order with a ballot per warp and a prefix over the warp totals
         int pin = 0;
-        bool on = false;
+        bool on = false, ron = false;
         const int64_t q = q0 + tid;
         if (tid < p.span && q < p.npix_out) {
             if (p.sh == 1 && p.sw == 1) {
@@ -262,9 +264,11 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                 pin = (int)((b * p.hi + oy * p.sh) * p.wi + (r - oy * p.wo) * p.sw);
             }
             on = p.mi[pin] != 0;
-            if (blockIdx.y == 0 && (!p.fused || !on)) p.mo[q] = on ? 1 : 0;
+            ron = p.res_mask != nullptr && p.res_mask[q] != 0;
+            if (blockIdx.y == 0 && (!p.fused || !(on || ron))) p.mo[q] = (on || ron) ? 1 : 0;
         }
-        const unsigned bal = __ballot_sync(DC_FULL, on);
+        const uint32_t tbw = (on ? 1u : 0u) | (ron ? kRowHasResidual : 0u);
+        const unsigned bal = __ballot_sync(DC_FULL, tbw != 0u);
         if (lane == 0) s_u32[3 + warp] = (uint32_t)__popc(bal);
         if (tid == 0) s_toff[0] = 0;
         __syncthreads();
@@ -286,12 +290,12 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
             if (tid < span_valid) {
                 s_out[tid] = tid;
                 s_base[tid] = pin;
-                s_tb[tid] = on ? 1u : 0u;
+                s_tb[tid] = tbw;
             }
-        } else if (on) {
+        } else if (tbw != 0u) {
             s_out[slot] = tid;
             s_base[slot] = pin;
-            s_tb[slot] = 1u;
+            s_tb[slot] = tbw;
         }
     }
     if (tid >= kStages && tid < 2 * kStages) {
@@ -336,45 +340,50 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     const bool plain_1x1 = p.taps == 1 && p.sh == 1 && p.sw == 1 && p.pt == 0 && p.pl == 0 && !p.transposed;
     int tile = 0;                     // tiles processed by this CTA (the accumulator barrier's phase counts these)
     const int nrounds = multi ? p.ms_rounds : 1;
+    int carry = 0;                    // multi-span mode: rows of a partly filled tile, kept for the next round
     for (int round = 0; round < nrounds && ok; ++round) {
     if (multi) {
         // Large maps of 1x1 layers without a work list: a persistent CTA owns the spans blockIdx.x + j * gridDim.x
         // (so clustered active regions are dealt round-robin to all CTAs) and compacts the active pixels of kMsSpans
         // of them into one row list. All mask reads of a round are in flight together.
-        if (tid == 0) s_u32[2] = 0u;
+        if (tid == 0) s_u32[2] = (uint32_t)carry;
         __syncthreads();
         int64_t q4[4];
-        bool on4[4], valid4[4];
+        bool valid4[4];
+        uint32_t tb4[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int v = tid + kPwThreads * i;                      // 0 .. kMsSpans * 128 - 1
             const int64_t sid = (int64_t)blockIdx.x + (int64_t)(round * kMsSpans + (v >> 7)) * gridDim.x;
             q4[i] = sid * kRows + (v & 127);
             valid4[i] = sid < p.ms_nspans && q4[i] < p.npix_out;
-            on4[i] = valid4[i] && p.mi[valid4[i] ? q4[i] : 0] != 0;
+            tb4[i] = (valid4[i] && p.mi[valid4[i] ? q4[i] : 0] != 0) ? 1u : 0u;
+            if (valid4[i] && p.res_mask != nullptr && p.res_mask[q4[i]] != 0) tb4[i] |= kRowHasResidual;
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            if (valid4[i] && blockIdx.y == 0 && (!p.fused || !on4[i])) p.mo[q4[i]] = on4[i] ? 1 : 0;
-            const unsigned bal = __ballot_sync(DC_FULL, on4[i]);
+            if (valid4[i] && blockIdx.y == 0 && (!p.fused || tb4[i] == 0u)) p.mo[q4[i]] = tb4[i] != 0u ? 1 : 0;
+            const unsigned bal = __ballot_sync(DC_FULL, tb4[i] != 0u);
             int base = 0;
             if (lane == 0 && bal != 0u) base = (int)atomicAdd(&s_u32[2], (uint32_t)__popc(bal));
             base = __shfl_sync(DC_FULL, base, 0);
-            if (on4[i]) {
+            if (tb4[i] != 0u) {
                 const int slot = base + __popc(bal & ((1u << lane) - 1u));
                 s_out[slot] = (int)q4[i];
                 s_base[slot] = (int)q4[i];
-                s_tb[slot] = 1u;
+                s_tb[slot] = tb4[i];
             }
         }
         __syncthreads();
         cnt = (int)s_u32[2];
         if (cnt == 0) continue;
     }
+    // only the last round runs a partly filled tile; before that the remainder waits for more rows
+    const bool full_tiles_only = multi && round + 1 < nrounds;
     // span mode: the tiles of this CTA's own list; list mode: every gridDim.x-th tile of the global list
     const int tile_first = list_mode ? (int)blockIdx.x : 0;
     const int tile_step = list_mode ? (int)gridDim.x : 1;
-    const int tiles_total = (cnt + kRows - 1) / kRows;
+    const int tiles_total = full_tiles_only ? cnt / kRows : (cnt + kRows - 1) / kRows;
     for (int tg = tile_first; tg < tiles_total && ok; tg += tile_step, ++tile) {
         const int cnt_t = min(kRows, cnt - tg * kRows);
         const int t0 = list_mode ? 0 : tg * kRows;                  // offset of the tile's rows in the shared lists
@@ -556,7 +565,21 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
 #pragma unroll
                 for (int u = 0; u < kU; ++u) {
                     if (!p.fused) {
-                        if (mine[u]) d[u].store(p.out + off[u]);
+                        if (mine[u]) {
+                            if (p.res != nullptr) {                // linear layer with a residual connection
+                                const uint32_t tbw = s_tb[t0 + rb + u * ppw + lane / g];
+                                if (!(tbw & 1u)) d[u].zero();         // the convolution is not active here (stale or zero-filled row)
+                                if (tbw & kRowHasResidual) {
+                                    Pack<__half, 8> rr;
+                                    rr.load(p.res + off[u]);
+                                    __half2* dh = reinterpret_cast<__half2*>(d[u].s);
+                                    const __half2* rh = reinterpret_cast<const __half2*>(rr.s);
+#pragma unroll
+                                    for (int k = 0; k < 4; ++k) dh[k] = __hadd2(dh[k], rh[k]);
+                                }
+                            }
+                            d[u].store(p.out + off[u]);
+                        }
                         continue;
                     }
                     bool hit = false;
@@ -581,6 +604,16 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         }
         __syncthreads();
         tc_fence_after();
+    }
+    if (full_tiles_only) {            // move the remainder to the front of the lists (source and destination do not overlap)
+        carry = cnt - tiles_total * kRows;
+        if (tiles_total > 0 && tid < carry) {
+            const int src = tiles_total * kRows + tid;
+            s_out[tid] = s_out[src];
+            s_base[tid] = s_base[src];
+            s_tb[tid] = s_tb[src];
+        }
+        __syncthreads();
     }
     }   // rounds
 
@@ -661,7 +694,7 @@ static void finish_plan(PwPlan& pl, const dc_conv_desc* d, int64_t npix_out, boo
     const int64_t want = (int64_t)sms * 6;
     while (span > 128 && divup64(npix_out, span) * pl.ntiles < want) span >>= 1;
     if (list_mode) span = kRows;      // the shared row lists hold one tile
-    if (multi_span) span = kMsSpans * kRows;   // ... or the active pixels of a round of spans
+    if (multi_span) span = kMsSpans * kRows + kRows;   // ... or the active pixels of a round of spans plus a carried remainder
     pl.span = span;
     pl.stage_pitch = (uint32_t)pl.bn * 2 + 16;
     const uint32_t ring = (uint32_t)pl.nslots * kABytes;
@@ -732,7 +765,14 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     const int64_t npix_out = (int64_t)d->n * d->h_out * d->w_out;
     if (npix_out == 0) return DC_OK;
     if ((int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
-    const bool want_fused = ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
+    const bool has_res = ep != nullptr && ep->residual != nullptr;
+    if (has_res) {        // residual connection: linear stride-1 pointwise layers only (each CTA compacts its own rows)
+        const bool ok_res = !transposed && pl.taps == 1 && d->pad_top == 0 && d->pad_left == 0 && d->stride_h == 1 && d->stride_w == 1 &&
+                            ep->truncation == DC_TRUNC_NONE && ep->activation == DC_ACT_NONE && ep->residual_mask != nullptr &&
+                            aligned16(ep->residual);
+        if (!ok_res) return DC_ERR_UNSUPPORTED;
+    }
+    const bool want_fused = !has_res && ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
     // 1x1 layers without padding never need a work list: each CTA compacts its own pixels. On small maps a CTA owns
     // one contiguous span; on large maps persistent CTAs own strided spans (multi-span mode).
     const bool pointwise = !transposed && pl.taps == 1 && d->pad_top == 0 && d->pad_left == 0;
@@ -752,6 +792,8 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     p.thr = fused ? host_round_threshold<__half>(ep->threshold) : 0.f;
     p.act = fused ? ep->activation : 0;
     p.fused = fused ? 1 : 0;
+    p.res = has_res ? (const __half*)ep->residual : nullptr;
+    p.res_mask = has_res ? ep->residual_mask : nullptr;
     p.npix_out = npix_out;
     p.hi = d->h_in; p.wi = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.sh = d->stride_h; p.sw = d->stride_w;
     p.cin = d->c_in; p.cout = d->c_out;
@@ -801,7 +843,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     }
     int rc = launch_pdl(k_pw_umma, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
     if (rc != DC_OK) return rc;
-    if (ep != nullptr && !fused)
+    if (ep != nullptr && !fused && !has_res)
         return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,
                                     ep->activation, ep->truncation, (void*)st);
     return DC_OK;

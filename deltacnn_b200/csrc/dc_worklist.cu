@@ -191,7 +191,7 @@ int scan_deconv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void
 // Entry point for callers that cannot allocate device memory
 // ---------------------------------------------------------------------------------------------
 // Some hosts of this library may not call cudaMalloc at all: a plugin that runs inside another
-// application's fixed device-memory budget, or a real-time loop that must stay away from the allocator
+// application's fixed device-memory allotment, or a real-time loop that must stay away from the allocator
 // (and its implicit synchronisation) once it has started. dc_conv2d_ws wants scratch memory for its work
 // list; dc_conv2d_static keeps that scratch in the image of this library instead: a fixed array in device
 // global memory that every GPU loading the library holds until the process exits.

@@ -91,6 +91,20 @@ def make_epilogue(prev_out, truncated, threshold, activation, truncation_mode):
     return e
 
 
+def make_residual_epilogue(residual, residual_mask):
+    """Epilogue of a linear 1x1 convolution that adds a residual (delta, mask) to its result, the out-mask
+    becoming the union of both masks (the DCAdd behind a projection convolution, in the same launch)."""
+    e = Epilogue()
+    e.prev_out = None
+    e.truncated = None
+    e.threshold = 0.0
+    e.activation = 0
+    e.truncation = -1
+    e.residual = _ptr(residual)
+    e.residual_mask = _ptr(residual_mask)
+    return e
+
+
 def sparse_conv(x, filter, mask=None, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, c_out: int = None,
                 create_out_mask=False, sub_tile_sparsity=True, out_mask=None, out_shape=None, out=None,
                 filter_umma=None, epilogue=None, desc=None, workspace=None):

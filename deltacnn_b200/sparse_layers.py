@@ -230,7 +230,16 @@ class _DeltaConvMixin:
     def __repr__(self):
         return f"MyConv2d{self.conv_idx} cin={self.in_channels} cout={self.out_channels}"
 
-    def _delta_forward_common(self, input):
+    def can_fuse_residual(self, input):
+        """True when forward(input, residual=(delta, mask)) adds the residual inside the convolution kernel: a linear
+        fp16 1x1 stride-1 convolution on the tensor-core path (no reference counterpart; it replaces the DCAdd that
+        follows a projection convolution, reference sparse_layers.py DCAdd.forward)."""
+        return (DCConv2d.fuse_residual and not self._transposed and self.backend == DCBackend.deltacnn and type(input) != Tensor
+                and input[0].dtype == torch.float16 and tuple(self.kernel_size) == (1, 1) and tuple(self.stride) == (1, 1)
+                and all(int(v) == 0 for v in self.padding) and self.groups == 1 and self.weight_umma is not None
+                and self.activation is None and not self.dense_out)
+
+    def _delta_forward_common(self, input, residual=None):
         DCConv2d.conv_idx += 1
         self.frame_idx += 1
         first_iter = self.conv_idx == -1
@@ -238,10 +247,13 @@ class _DeltaConvMixin:
             self.init_first_iter(input)
         if self.backend == DCBackend.cudnn:
             assert len(self.padding) == 2
-            return self._forward_cudnn(input, first_iter)
+            out = self._forward_cudnn(input, first_iter)
+            return out if residual is None else out + residual
         if self.backend != DCBackend.deltacnn:
             _unsupported_backend(self.backend)
-        return self._forward_delta_conv(input, first_iter)
+        if residual is not None and not self.can_fuse_residual(input):
+            raise RuntimeError("this convolution cannot add a residual itself (see can_fuse_residual); use DCAdd")
+        return self._forward_delta_conv(input, first_iter, residual)
 
     def _forward_cudnn(self, input, first_iter):
         out = super(_DeltaConvMixin, self).forward(input)
@@ -252,7 +264,7 @@ class _DeltaConvMixin:
             DCConv2d.flops_sum += n_updated * self.weight.numel()
         return out
 
-    def _forward_delta_conv(self, input, first_iter):
+    def _forward_delta_conv(self, input, first_iter, residual=None):
         if type(input) == Tensor:
             raise RuntimeError("delta convolutions take a (delta, mask) tuple; put a DCSparsify in front of the first layer")
         if self.orig_weights is None:
@@ -271,6 +283,9 @@ class _DeltaConvMixin:
         if fuse:
             epilogue = K.make_epilogue(act.prev_out, act.out_truncated, DCThreshold.get(act), act.activation_int,
                                        act.truncation_mode.value)
+        if residual is not None:
+            res_delta, res_mask = residual
+            epilogue = K.make_residual_epilogue(res_delta, res_mask)
         if self._desc is None:
             size_fn = K.deconv_out_hw if self._transposed else K.conv_out_hw
             hw = size_fn(x.shape[2], x.shape[3], self.kernel_size, self.stride, self.padding, self.dilation)
@@ -372,6 +387,7 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
     measure_flops = False
     reuse_buffers = True      # keep per-layer output buffers across frames
     use_worklist = True       # steady-state frames: active-pixel work lists in per-layer scratch memory
+    fuse_residual = True      # forward(input, residual=...) adds the residual inside the convolution kernel where it can
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1, groups: int = 1,
                  bias: bool = True, padding_mode: str = "zeros", delta_threshold: float = None, name: str = None,
@@ -380,8 +396,8 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
         nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias, padding_mode)
         self._init_delta_state(delta_threshold, name, activation, dense_out, backend, use_logging, kwargs)
 
-    def forward(self, input):
-        return self._delta_forward_common(input)
+    def forward(self, input, residual=None):
+        return self._delta_forward_common(input, residual)
 
 
 class DCConvTranspose2d(_DeltaConvMixin, nn.ConvTranspose2d, DCModule):

@@ -152,7 +152,18 @@ def make_mobilenet_v2(ops, num_classes=1000):
                 self.add = ops.add()
 
         def forward(self, x):
-            return self.add(x, self.conv(x)) if self.use_res else self.conv(x)
+            if not self.use_res:
+                return self.conv(x)
+            if ops.delta:
+                # the projection convolution adds the residual itself where it has a kernel for it (one launch less)
+                h = x
+                for layer in list(self.conv)[:-1]:
+                    h = layer(h)
+                proj = self.conv[-1].conv
+                if proj.can_fuse_residual(h):
+                    return proj(h, residual=x)
+                return self.add(x, proj(h))
+            return self.add(x, self.conv(x))
 
     class MobileNetV2(Base):
         def __init__(self):

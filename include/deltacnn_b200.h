@@ -69,6 +69,14 @@ typedef struct dc_epilogue {
     float threshold;
     int32_t activation;      /* dc_activation */
     int32_t truncation;      /* dc_truncation; DC_TRUNC_MAX only when fused */
+    /* Optional residual connection (no reference counterpart; replaces a DCAdd behind a linear convolution,
+     * sparse_layers.py DCAdd.forward / sparse_add_tensors_wrapper): a delta tensor of the output's shape and its
+     * update mask. out = convolution (where its out-mask is set) + residual (where residual_mask is set), the
+     * out-mask is the union. Only with activation == DC_ACT_NONE and truncation == DC_TRUNC_NONE (prev_out and
+     * truncated are then unused and may be NULL), fp16, 1x1 stride 1 without padding and the DC_FILTER_UMMA
+     * layout; anything else returns DC_ERR_UNSUPPORTED and the caller adds with dc_add. */
+    const void* residual;
+    const int32_t* residual_mask;
 } dc_epilogue;
 
 /* Filter layouts understood by dc_conv2d / dc_deconv2d. */
@@ -122,7 +130,7 @@ int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_i
 
 /* dc_conv2d_ws without any allocation on the caller's side or inside the library. No counterpart in the
  * reference. It exists for hosts that are not allowed to allocate device memory when they call: a
- * plugin that lives inside another application's fixed device-memory budget, or a control loop that
+ * plugin that lives inside another application's fixed device-memory allotment, or a control loop that
  * must stay away from the allocator (and the synchronisation it implies) once it runs. The work-list scratch
  * is a fixed array inside this library's device image (4 MiB per GPU that loads the library, held until
  * the process exits), so the call handles at most dc_static_workspace_max_pixels() = 524288 output

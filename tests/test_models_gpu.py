@@ -128,6 +128,30 @@ def test_nonzero_thresholds_bounded_error_and_graph_replay():
         assert _rel(eager[2], ref) < 0.5, "thresholded output drifted far from the dense network"
 
 
+def test_fused_residual_equals_separate_add():
+    """MobileNetV2 fp16 with the residual added inside the projection convolutions against the same network with
+    DCAdd layers: identical outputs on every frame at the benchmark's thresholds."""
+    from deltacnn_b200 import DCThreshold, DCConv2d
+    from examples.nets import build_pair
+    from examples.runner import set_depth_thresholds
+    frames = _frames("mobilenet", 2, 6)
+    xs = [frames[t:t + 1].cuda().half().repeat(2, 1, 1, 1).contiguous(memory_format=torch.channels_last) for t in range(6)]
+    outs = {}
+    try:
+        for fused in (True, False):
+            DCConv2d.fuse_residual = fused
+            DCThreshold.reset()
+            _, delta = build_pair("mobilenet", frames[:4], device="cuda", dtype=torch.float16)
+            with torch.no_grad():
+                delta(xs[0])
+                set_depth_thresholds(0.05, 0.01, 0.05)
+                outs[fused] = [delta(x).clone() for x in xs[1:]]
+    finally:
+        DCConv2d.fuse_residual = True
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.equal(a, b)
+
+
 def test_config1_mobilenet_fp32_64_frames_no_drift_and_threshold_005():
     """The reference-runnable configuration: MobileNetV2 fp32, batch 1, 64 frames of the seeded video.
     Threshold 0: every frame within 1e-4 of the dense network (no error accumulation over the stream).

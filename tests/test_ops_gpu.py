@@ -664,3 +664,42 @@ def test_thin_pointwise_conv(dtype, cin, cout, density):
                               create_out_mask=True)
     assert torch.equal(om.cpu(), m_ref)
     assert_close_masked(out, ref, m_ref, dtype, "thin conv")
+
+
+@pytest.mark.parametrize("cin,cout,n,h,w", [(144, 24, 2, 28, 28), (384, 64, 3, 14, 14), (960, 160, 2, 7, 7), (96, 24, 4, 112, 112), (192, 32, 1, 19, 23)])
+@pytest.mark.parametrize("density,res_density", [(0.1, 0.1), (0.7, 0.3), (1.0, 1.0), (0.0, 0.2), (0.3, 0.0)])
+def test_pointwise_conv_with_fused_residual_equals_conv_then_add(cin, cout, n, h, w, density, res_density):
+    """A linear 1x1 convolution that adds a residual (delta, mask) in its epilogue must give exactly what the
+    convolution followed by dc_add gives: values on the union mask, and the union mask itself."""
+    import deltacnn_b200.cuda_kernels as k
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(61)
+    x = rand_feat(g, n, cin, h, w, dtype, 0.3).cuda()
+    mask = rand_mask(g, n, h, w, density).cuda()
+    xn = x.clone()
+    xn[(mask == 0).expand_as(x)] = float("nan")              # inactive inputs must never reach the result
+    res = rand_feat(g, n, cout, h, w, dtype, 0.5).cuda()
+    rmask = rand_mask(g, n, h, w, res_density).cuda()
+    resn = res.clone()
+    resn[(rmask == 0).expand_as(res)] = float("nan")
+    wt = (torch.randn(cout, cin, 1, 1, generator=g) / cin ** 0.5).to(dtype)
+    f = convert_filter_out_channels_last(wt).cuda()
+    packed = _pack_umma(f, cin, cout, 1)
+    # reference: two calls
+    o1, m1 = k.sparse_conv(xn, f, mask, None, (1, 1), (0, 0), (1, 1), 1, create_out_mask=True, filter_umma=packed)
+    ref = torch.full_like(o1, float("nan"))
+    mref = torch.empty_like(m1)
+    k.sparse_add_tensors(resn, o1, None, ref, rmask, m1, mref, 1.0, 1.0, 0, False)
+    # fused
+    out = torch.full_like(o1, float("nan"))
+    o2, m2 = k.sparse_conv(xn, f, mask, None, (1, 1), (0, 0), (1, 1), 1, create_out_mask=True, out=out, filter_umma=packed,
+                           epilogue=k.make_residual_epilogue(resn, rmask))
+    assert _lib.lib.dc_umma_error() == 0
+    assert torch.equal(m2, mref)
+    assert torch.equal(m2, ((mask != 0) | (rmask != 0)).to(torch.int32))
+    sel = (mref != 0).expand_as(ref)
+    assert not torch.isnan(o2[sel]).any()
+    assert torch.equal(o2[sel], ref[sel])
+    assert torch.isnan(o2[~sel]).all(), "pixels outside the union mask must not be written"

@@ -1,5 +1,5 @@
 """dc_conv2d_static: the convolution entry point for callers that may not allocate device memory
-(a plugin inside another application's fixed memory budget, a loop that must not touch the allocator
+(a plugin inside another application's fixed memory allotment, a loop that must not touch the allocator
 once it runs). It keeps its work-list scratch in a fixed array inside the library, so nothing is
 allocated by the caller or by the call. Checked through the C-ABI against dc_conv2d on the same
 inputs, twice in a row (the scratch array keeps the first call's contents), bit for bit at every
