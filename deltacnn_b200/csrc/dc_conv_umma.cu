@@ -218,8 +218,10 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     };
 
     // ---- set-up that reads nothing the previous kernel wrote: overlaps that kernel's tail ----
-    if (tid <= 3 * kStages && (tid < kStages || tid >= 2 * kStages)) {     // the "full" barriers follow once the row mode is known
-        mbar_init(bar0 + 8u * tid, 1u);
+    if (tid <= 3 * kStages) {
+        // a "full" barrier takes one arrival per producer warp plus one of thread 0, which carries the byte count
+        // when the rows of a block come from the copy engine (TMA) instead of the warps' own copies
+        mbar_init(bar0 + 8u * tid, (tid >= kStages && tid < 2 * kStages) ? (uint32_t)(kProducerWarps + 1) : 1u);
         fence_barrier_init();
         if (tid == 0) s_u32[1] = 1;
     }
@@ -298,10 +300,6 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
             s_tb[slot] = tbw;
         }
     }
-    if (tid >= kStages && tid < 2 * kStages) {
-        mbar_init(bar0 + 8u * tid, dense_rows ? 1u : (uint32_t)kProducerWarps);
-        fence_barrier_init();
-    }
 
     const uint32_t b_block_bytes = (uint32_t)p.bn * 128u;
     const bool is_mma_warp = warp == kPwWarps - 1;
@@ -326,6 +324,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_full(sslot));
+        if (tid == 0) mbar_arrive(bar_full(sslot));       // the arrival that carries the byte count in TMA mode
         if (++sslot == nse) sslot = 0;
     };
     // epilogue geometry: an aligned group of g lanes per row, 16 bytes per lane
@@ -409,24 +408,26 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         }
 
         if (!is_mma_warp && dense_rows) {
-            // ---- one thread asks the copy engine for the tile's rows, a K block per request ----
-            if (tid == 0) {
-                const int y0 = (int)q0 + t0;                           // first pixel of the tile (stride 1: pixel = input row)
-                for (int kb = 0; kb < p.nkb; ++kb) {
-                    if (pwrap > 0 && !mbar_wait(bar_empty(pslot), (uint32_t)((pwrap - 1) & 1), ok_flag)) {
-                        *ok_flag = 0; atomicExch(&g_umma_error, 1);
-                        break;
-                    }
+            // ---- the copy engine loads the tile's rows, a K block per request of thread 0; every producer warp
+            //      still arrives once per block (after the stage is free), so the barriers count the same in both modes ----
+            const int y0 = (int)q0 + s_out[t0];                        // first pixel of the tile (stride 1: pixel = input row)
+            for (int kb = 0; kb < p.nkb; ++kb) {
+                if (pwrap > 0 && !mbar_wait_warp(bar_empty(pslot), (uint32_t)((pwrap - 1) & 1), ok_flag)) {
+                    *ok_flag = 0; atomicExch(&g_umma_error, 1);
+                    break;
+                }
+                if (tid == 0) {
                     mbar_expect_tx(bar_full(pslot), (uint32_t)kABytes);
                     tma_load_rows(sA_u32 + (uint32_t)pslot * kABytes, &tmap_in, kb * kKBlock, y0, bar_full(pslot));
                     if (!p.b_resident) {
                         mbar_expect_tx(bar_bfull(pslot), b_block_bytes);
                         bulk_g2s(smem_u32(sB + (size_t)pslot * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(pslot));
                     }
-                    if (++pslot == nse) { pslot = 0; ++pwrap; }
                 }
+                if (lane == 0) mbar_arrive(bar_full(pslot));
+                if (++pslot == nse) { pslot = 0; ++pwrap; }
+                if (++sslot == nse) sslot = 0;
             }
-            __syncwarp();
         } else if (!is_mma_warp) {
             // ---- producers: run up to nse K blocks ahead of the tensor core; a block is signalled (full
             //      barrier, one arrival per warp) kDelay blocks after it was issued ----
@@ -773,11 +774,15 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         if (!ok_res) return DC_ERR_UNSUPPORTED;
     }
     const bool want_fused = !has_res && ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
-    // 1x1 layers without padding never need a work list: each CTA compacts its own pixels. On small maps a CTA owns
-    // one contiguous span; on large maps persistent CTAs own strided spans (multi-span mode).
+    // 1x1 layers without padding can do without a work list: each CTA compacts its own pixels. On small maps a CTA
+    // owns one contiguous span; on large maps persistent CTAs own strided spans (multi-span mode). When the map is so
+    // large that a CTA would need several rounds of spans and the caller gave scratch memory, the work list is
+    // better: its global compaction fills every tile.
     const bool pointwise = !transposed && pl.taps == 1 && d->pad_top == 0 && d->pad_left == 0;
-    if (pointwise && ((d->stride_h == 1 && d->stride_w == 1) || npix_out < kListMinPixels)) ws = nullptr;
-    const bool multi_span = ws == nullptr && pointwise && d->stride_h == 1 && d->stride_w == 1 && npix_out >= kListMinPixels;
+    const bool unit_stride = d->stride_h == 1 && d->stride_w == 1;
+    const int64_t spans_per_cta = divup64(divup64(npix_out, kRows), (int64_t)sm_count() * 3);
+    if (pointwise && (npix_out < kListMinPixels || (unit_stride && spans_per_cta <= kMsSpans))) ws = nullptr;
+    const bool multi_span = ws == nullptr && pointwise && unit_stride && npix_out >= kListMinPixels;
     if (transposed) {                 // the kernel sees one phase: m x m taps
         pl.taps = (d->kh / 2) * (d->kw / 2);
         pl.nkb = pl.taps * pl.ncb;

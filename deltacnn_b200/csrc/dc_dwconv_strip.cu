@@ -422,11 +422,13 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     const int npk = p.c / 8;
     const int nv = divup(npk, 32);
     const size_t smem = (size_t)10 * p.c * 4;         // filter and bias as fp32
-    if (nv == 1 && npix >= 40000) {                    // large map, narrow pixels: CTA-level compaction, no scan pass
-        const int64_t nspans = divup64(npix, 256);
-        int64_t grid_c = (int64_t)sm_count() * 4;
-        if (grid_c > nspans) grid_c = nspans;
-        const int rounds = (int)divup64(divup64(nspans, grid_c), kCtaSpans);
+    // large map, narrow pixels: CTA-level compaction, no scan pass. With scratch memory and so many pixels that a CTA
+    // would need several rounds, the work list below spreads the active pixels better.
+    const int64_t nspans = divup64(npix, 256);
+    int64_t grid_c = (int64_t)sm_count() * 4;
+    if (grid_c > nspans) grid_c = nspans;
+    const int rounds = (int)divup64(divup64(nspans, grid_c), kCtaSpans);
+    if (nv == 1 && npix >= 40000 && (ws == nullptr || rounds <= 1)) {
         return launch_pdl(k_dw3x3_cta<1>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
     }
     // the work list costs two extra launches; it pays on large maps where the active pixels cluster

@@ -9,6 +9,8 @@ src/cuda/conv_kernel.cu:90-107,196-209 and src/cuda/other_nn_layers.cu:810-813):
 
   conv / deconv  esize*(A_in*Cin + U_out*Cout + kh*kw*Cin*Cout/groups) + 4*(HW_in + HW_out)
   activation     esize*C*(3*M_in + 3*M_kept) + 8*HW           (also added to a conv with fused epilogue)
+  conv + add     conv bytes + esize*Cout*(2*U_union - U_conv) + 4*HW   (residual added in the convolution's epilogue;
+                 an upper bound on the residual reads: every pixel of the union is counted once)
   sparsify       esize*C*(2*HW + 2*M) + 4*HW
   add            esize*C*(n_a + n_b + n_ab [+ 2*n_ab with activation]) + 12*HW
   pool           esize*C*(A_in [*2 for max: prev] + U_out) + 4*(HW_in + HW_out) [+ 2*esize*C*A_in cache update]
@@ -64,7 +66,13 @@ class OpProfiler:
             kind = "dwconv" if groups > 1 else ("deconv" if name == "sparse_deconv" else "conv")
             key = f"{kind}{kh}x{kw}"
             ep = kwargs.get("epilogue")
-            if ep is not None:
+            if ep is not None and getattr(ep, "residual", None):
+                # linear convolution with the residual add in its epilogue: the union mask is written, the residual
+                # is read where it is active (as many pixels as the union minus those only the convolution touches)
+                u_union = _count(om)
+                b += es * co * (u_union - u_out) + es * co * u_union + 4 * om.numel()
+                key += "+add"
+            elif ep is not None:
                 b += self._act_bytes(co, es, u_out, _count(om), om.numel())
                 key += "+act"
             return key, f"{ci}->{co} @{hi}x{wi} s{kwargs['stride'][0]}", b, flops
