@@ -24,6 +24,7 @@
 //
 // Every wait on an mbarrier is bounded; a wait that gives up sets a sticky device-side error code
 // (dc_umma_error) and the CTA frees its tensor memory and returns.
+#include <cstdlib>
 #include <cstring>
 #include <cuda.h>          // CUtensorMap and its enums (the encoder is fetched through cudaGetDriverEntryPoint)
 #include "dc_common.cuh"
@@ -69,7 +70,11 @@ struct PwParams {
     uint32_t hw_mul, hw_shift, wo_mul, wo_shift;   // division by h_out*w_out and by w_out (fast_div)
     int ms_rounds;                  // > 0: persistent CTAs over strided 128-pixel spans, kMsSpans of them per round
     int64_t ms_nspans;              //      number of 128-pixel spans of the output
-    int tma_rows;                   // 1: the kernel got a tensor map of the input as [pixels][channels] and may load whole spans with it
+    // patch mode (KxK, stride 1): a tile is a tw x th patch of output pixels (tw * th = 128), persistent CTAs walk the patches
+    int patch_mode, patch_tw_log2, patch_px, patch_py;   // patches per image row / column
+    int64_t npatches;
+    uint32_t ppx_mul, ppx_shift, ppi_mul, ppi_shift;      // division by patch_px and by patch_px * patch_py (fast_div)
+    int tma_rows;                   // 2: the tensor map is the 4-D input [n][h][w][c], box {64, tw, th, 1} (patch mode);  1: the kernel got a tensor map of the input as [pixels][channels] and may load whole spans with it
     uint32_t off_b, off_stage, off_list, off_misc, stage_pitch;
 };
 
@@ -157,6 +162,12 @@ __device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* t
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// Patch mode: box {64 channels, tw, th, 1} of the [n][h][w][c] input at (channel x, column cx, row cy, image b); the
+// 128 pixels land as 128 swizzled rows in (row, column) order, pixels outside the image read zeros (the padding).
+__device__ __forceinline__ void tma_load_patch(uint32_t dst, const CUtensorMap* tmap, int x, int cx, int cy, int b, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(cx), "r"(cy), "r"(b), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
@@ -240,7 +251,8 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     // ---- the rows of this CTA ----
     const bool list_mode = p.wl_list != nullptr;
     const bool multi = p.ms_rounds > 0;                               // span mode over several strided spans per CTA
-    const int64_t q0 = (list_mode || multi) ? 0 : (int64_t)blockIdx.x * p.span;
+    const bool patch = p.patch_mode != 0;                             // KxK stride 1: persistent CTAs over patches of output pixels
+    const int64_t q0 = (list_mode || multi || patch) ? 0 : (int64_t)blockIdx.x * p.span;
     int cnt = 0;
     bool dense_rows = false;          // span mode: rows = all pixels of the span, loaded by TMA
     if (list_mode) {
@@ -250,6 +262,8 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
             s_toff[tid] = p.transposed ? -((tid / p.m) * p.wi + tid % p.m) : (tid / p.kw) * p.dh * p.wi + (tid % p.kw) * p.dw;
     } else if (multi) {
         if (tid == 0) s_toff[0] = 0;
+    } else if (patch) {
+        if (tid < p.taps) s_toff[tid] = (tid / p.kw) * p.dh * p.wi + (tid % p.kw) * p.dw;
     } else {
         // span mode (1x1 kernels, no padding): thread t owns pixel q0 + t; the active ones are compacted in
         // order with a ballot per warp and a prefix over the warp totals
@@ -338,7 +352,8 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
 
     const bool plain_1x1 = p.taps == 1 && p.sh == 1 && p.sw == 1 && p.pt == 0 && p.pl == 0 && !p.transposed;
     int tile = 0;                     // tiles processed by this CTA (the accumulator barrier's phase counts these)
-    const int nrounds = multi ? p.ms_rounds : 1;
+    const int nrounds = multi ? p.ms_rounds : patch ? (int)((p.npatches - blockIdx.x + gridDim.x - 1) / gridDim.x) : 1;
+    // patch mode: the origin of the current patch is kept in s_toff[28..30] (x0, y0, image) for the thread that issues the loads
     int carry = 0;                    // multi-span mode: rows of a partly filled tile, kept for the next round
     for (int round = 0; round < nrounds && ok; ++round) {
     if (multi) {
@@ -376,6 +391,62 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         __syncthreads();
         cnt = (int)s_u32[2];
         if (cnt == 0) continue;
+    }
+    if (patch) {
+        // One patch of tw x th output pixels per round. Thread r < 128 looks at pixel r of the patch: ORs the in-mask
+        // over the taps (the out-mask), and notes whether every tap inside the image is active. If that holds for the
+        // whole patch the tile's rows are loaded by the copy engine, tap by tap (the delta tensor is only defined at
+        // active pixels, so a patch with an inactive input pixel in its halo gathers its active rows instead).
+        const uint32_t pid = (uint32_t)blockIdx.x + (uint32_t)round * gridDim.x;
+        const uint32_t pb = fast_div(pid, p.ppi_mul, p.ppi_shift);
+        const uint32_t prem = pid - pb * (uint32_t)(p.patch_px * p.patch_py);
+        const uint32_t pyi = fast_div(prem, p.ppx_mul, p.ppx_shift);
+        const int patch_b = (int)pb;
+        const int patch_y0 = (int)pyi << (7 - p.patch_tw_log2);
+        const int patch_x0 = (int)(prem - pyi * (uint32_t)p.patch_px) << p.patch_tw_log2;
+        if (tid == 0) { s_toff[28] = patch_x0; s_toff[29] = patch_y0; s_toff[30] = patch_b; }
+        const int oy = patch_y0 + (tid >> p.patch_tw_log2), ox = patch_x0 + (tid & ((1 << p.patch_tw_log2) - 1));
+        const bool valid = tid < kRows && oy < p.ho && ox < p.wo;
+        uint32_t tbw = 0u;
+        bool all_in = true;
+        const int in0 = (patch_b * p.hi + oy - p.pt) * p.wi + ox - p.pl;
+        if (valid) {
+            for (int t = 0; t < p.taps; ++t) {
+                const int ky = t / p.kw, kx = t - ky * p.kw;
+                const int iy = oy - p.pt + ky * p.dh, ix = ox - p.pl + kx * p.dw;
+                if (iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi) {
+                    if (p.mi[in0 + s_toff[t]] != 0) tbw |= 1u << t;
+                    else all_in = false;
+                }
+            }
+        }
+        const int q = (patch_b * p.ho + oy) * p.wo + ox;
+        if (valid && blockIdx.y == 0 && (!p.fused || tbw == 0u)) p.mo[q] = tbw != 0u ? 1 : 0;
+        if (tid == 0) s_u32[2] = 0u;
+        const int n_active = __syncthreads_count(tbw != 0u);
+        if (n_active == 0) continue;
+        dense_rows = p.tma_rows == 2 && __syncthreads_and(!valid || all_in) != 0;
+        if (dense_rows) {
+            cnt = kRows;
+            if (tid < kRows) {
+                s_out[tid] = valid ? q : 0;
+                s_base[tid] = in0;
+                s_tb[tid] = valid ? tbw : 0u;
+            }
+        } else {
+            const unsigned bal = __ballot_sync(DC_FULL, tbw != 0u);
+            int base = 0;
+            if (lane == 0 && bal != 0u) base = (int)atomicAdd(&s_u32[2], (uint32_t)__popc(bal));
+            base = __shfl_sync(DC_FULL, base, 0);
+            if (tbw != 0u) {
+                const int slot = base + __popc(bal & ((1u << lane) - 1u));
+                s_out[slot] = q;
+                s_base[slot] = in0;
+                s_tb[slot] = tbw;
+            }
+            cnt = n_active;
+        }
+        __syncthreads();
     }
     // only the last round runs a partly filled tile; before that the remainder waits for more rows
     const bool full_tiles_only = multi && round + 1 < nrounds;
@@ -418,7 +489,14 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                 }
                 if (tid == 0) {
                     mbar_expect_tx(bar_full(pslot), (uint32_t)kABytes);
-                    tma_load_rows(sA_u32 + (uint32_t)pslot * kABytes, &tmap_in, kb * kKBlock, y0, bar_full(pslot));
+                    if (patch) {
+                        const int tap_ = kb / p.ncb, cb_ = kb - tap_ * p.ncb;
+                        const int ky = tap_ / p.kw, kx = tap_ - ky * p.kw;
+                        tma_load_patch(sA_u32 + (uint32_t)pslot * kABytes, &tmap_in, cb_ * kKBlock, s_toff[28] - p.pl + kx * p.dw,
+                                       s_toff[29] - p.pt + ky * p.dh, s_toff[30], bar_full(pslot));
+                    } else {
+                        tma_load_rows(sA_u32 + (uint32_t)pslot * kABytes, &tmap_in, kb * kKBlock, y0, bar_full(pslot));
+                    }
                     if (!p.b_resident) {
                         mbar_expect_tx(bar_bfull(pslot), b_block_bytes);
                         bulk_g2s(smem_u32(sB + (size_t)pslot * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(pslot));
@@ -755,13 +833,39 @@ static bool encode_rows_map(CUtensorMap* map, const void* in, int64_t npix_in, i
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor map of the input as [n][h][w][c] (fp16), box {64 channels, tw, th, 1}, 128-byte swizzle: what tma_load_patch reads.
+static bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_desc* d, int tw, int th) {
+    CUtensorMap rows_probe;
+    if (!encode_rows_map(&rows_probe, in, (int64_t)d->n * d->h_in * d->w_in, d->c_in)) return false;   // looks the encoder up
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    const cuuint64_t c2 = (cuuint64_t)d->c_in * 2u;
+    const cuuint64_t gdim[4] = {(cuuint64_t)d->c_in, (cuuint64_t)d->w_in, (cuuint64_t)d->h_in, (cuuint64_t)d->n};
+    const cuuint64_t gstride[3] = {c2, c2 * (cuuint64_t)d->w_in, c2 * (cuuint64_t)d->w_in * (cuuint64_t)d->h_in};
+    const cuuint32_t box[4] = {(cuuint32_t)kKBlock, (cuuint32_t)tw, (cuuint32_t)th, 1u};
+    const cuuint32_t estride[4] = {1u, 1u, 1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(in), gdim, gstride, box, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in, const int32_t* mi, const void* filt, const void* bias,
                           void* out, int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
     PwPlan pl = plan_pw(d, transposed);
     if (transposed && ws == nullptr) return DC_ERR_UNSUPPORTED;
     if (!pl.ok || mi == nullptr || mo == nullptr) return DC_ERR_UNSUPPORTED;
     // without scratch for a work list only 1x1 kernels (no receptive field to dilate) have a tensor-core path
-    if (ws == nullptr && (pl.taps != 1 || d->pad_top != 0 || d->pad_left != 0)) return DC_ERR_UNSUPPORTED;
+    // KxK stride 1 without scratch memory: persistent CTAs over patches of output pixels, no scan pass (with scratch the
+    // work list is used: it fills every tile, which wins on sparse maps; patches win on mostly active maps).
+    // DC_NO_PATCH=1 turns the patch form off.
+    static const bool patch_allowed = [] { const char* e = getenv("DC_NO_PATCH"); return !(e != nullptr && e[0] == '1'); }();
+    const bool kxk_patch = patch_allowed && !transposed && pl.taps > 1 && d->stride_h == 1 && d->stride_w == 1;
+    if (ws == nullptr && !kxk_patch && (pl.taps != 1 || d->pad_top != 0 || d->pad_left != 0)) return DC_ERR_UNSUPPORTED;
     if (!aligned16(in) || !aligned16(out) || !aligned16(filt)) return DC_ERR_ALIGNMENT;
     const int64_t npix_out = (int64_t)d->n * d->h_out * d->w_out;
     if (npix_out == 0) return DC_OK;
@@ -783,6 +887,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     const int64_t spans_per_cta = divup64(divup64(npix_out, kRows), (int64_t)sm_count() * 3);
     if (pointwise && (npix_out < kListMinPixels || (unit_stride && spans_per_cta <= kMsSpans))) ws = nullptr;
     const bool multi_span = ws == nullptr && pointwise && unit_stride && npix_out >= kListMinPixels;
+    const bool patch_mode = kxk_patch && ws == nullptr;
     if (transposed) {                 // the kernel sees one phase: m x m taps
         pl.taps = (d->kh / 2) * (d->kw / 2);
         pl.nkb = pl.taps * pl.ncb;
@@ -825,6 +930,33 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     }
     if (pl.smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
     dim3 grid((unsigned)divup64(npix_out, pl.span), (unsigned)pl.ntiles);
+    p.patch_mode = 0;
+    if (patch_mode) {
+        // patch shape tw x th (tw * th = 128) with the least overhang beyond the image; wide patches on ties
+        int best_tw = 128;
+        int64_t best_area = -1;
+        for (int tw = 128; tw >= 8; tw >>= 1) {
+            const int th = kRows / tw;
+            const int64_t area = (int64_t)divup(d->w_out, tw) * tw * divup(d->h_out, th) * th;
+            if (best_area < 0 || area < best_area) { best_area = area; best_tw = tw; }
+        }
+        const int tw = best_tw, th = kRows / tw;
+        p.patch_mode = 1;
+        p.patch_tw_log2 = 0;
+        while ((1 << p.patch_tw_log2) < tw) ++p.patch_tw_log2;
+        p.patch_px = divup(d->w_out, tw);
+        p.patch_py = divup(d->h_out, th);
+        p.npatches = (int64_t)d->n * p.patch_px * p.patch_py;
+        fast_div_init((uint32_t)p.patch_px, &p.ppx_mul, &p.ppx_shift);
+        fast_div_init((uint32_t)(p.patch_px * p.patch_py), &p.ppi_mul, &p.ppi_shift);
+        p.tma_rows = encode_patch_map(&tmap, in, d, tw, th) ? 2 : 0;
+        int64_t per_sm = (int64_t)(227 * 1024) / (int64_t)(pl.smem + 1024);
+        if (per_sm > 3) per_sm = 3;
+        if (per_sm < 1) per_sm = 1;
+        int64_t persistent = (int64_t)sm_count() * per_sm / pl.ntiles;
+        if (persistent < 1) persistent = 1;
+        grid.x = (unsigned)(p.npatches < persistent ? p.npatches : persistent);
+    }
     p.ms_rounds = 0;
     p.ms_nspans = divup64(npix_out, kRows);
     if (multi_span) {

@@ -301,9 +301,12 @@ class _DeltaConvMixin:
         else:
             if DCConv2d.use_worklist and self._workspace is None:
                 self._workspace = torch.empty(K.conv_workspace_bytes(self._desc), dtype=torch.uint8, device=x.device)
-            # kernels larger than 1x1 have a tensor-core path only with a work list
-            umma = self.weight_umma if (self._workspace is not None or self.kernel_size == (1, 1)) else None
-            extra = {"filter_umma": umma, "workspace": self._workspace}
+            # with scratch memory KxK layers use a work list (best on sparse maps), without it patch tiles (best on
+            # mostly active maps); calls the tensor-core path cannot take fall back to the CUDA-core kernels
+            ws = self._workspace
+            if DCConv2d.patch_tiles and tuple(self.stride) == (1, 1) and tuple(self.kernel_size) != (1, 1):
+                ws = None
+            extra = {"filter_umma": self.weight_umma, "workspace": ws}
         out, out_mask = op(
             x=x, filter=self.weight, mask=mask, bias=self.bias if self.frame_idx <= 0 else None, stride=self.stride,
             padding=self.padding, dilation=self.dilation, groups=self.groups, c_out=self.out_channels, create_out_mask=True,
@@ -388,6 +391,7 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
     reuse_buffers = True      # keep per-layer output buffers across frames
     use_worklist = True       # steady-state frames: active-pixel work lists in per-layer scratch memory
     fuse_residual = True      # forward(input, residual=...) adds the residual inside the convolution kernel where it can
+    patch_tiles = False       # stride-1 KxK layers: patch tiles loaded by tiled TMA (mostly active maps) instead of work lists
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1, groups: int = 1,
                  bias: bool = True, padding_mode: str = "zeros", delta_threshold: float = None, name: str = None,

@@ -526,12 +526,15 @@ def _pack_umma_kxk(wt_hwio, cin, cout, k, stride, pad, dil):
     return packed
 
 
-@pytest.mark.parametrize("case", KXK_CASES)
-@pytest.mark.parametrize("density", [0.0, 0.1, 1.0])
+@pytest.mark.parametrize("case", KXK_CASES + [(64, 64, 3, 1, 1, 1, 2, 40, 48), (32, 64, 3, 1, 1, 1, 1, 70, 33), (128, 128, 3, 1, 1, 1, 3, 17, 136)])
+@pytest.mark.parametrize("density", [0.0, 0.1, 0.97, 1.0])
 @pytest.mark.parametrize("fused", [False, True])
-def test_kxk_conv_umma_matches_oracle_and_cuda_core_kernel(case, density, fused):
-    """3x3 / 5x5 convolutions as implicit GEMM on tcgen05 (work-list mode) against the oracle, and the
-    fused epilogue against convolution + stand-alone activation kernel."""
+@pytest.mark.parametrize("scratch", [True, False])
+def test_kxk_conv_umma_matches_oracle_and_cuda_core_kernel(case, density, fused, scratch):
+    """3x3 / 5x5 convolutions as implicit GEMM on tcgen05 against the oracle, and the fused epilogue against
+    convolution + stand-alone activation kernel. With scratch memory: work-list mode. Without: stride-1 layers run
+    on patch tiles (rows of a fully active patch loaded by 4-D tiled TMA, other patches gathered), strided layers
+    fall back to the CUDA-core kernel."""
     import deltacnn_b200.cuda_kernels as kk
     from deltacnn_b200 import _lib
     from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
@@ -540,6 +543,8 @@ def test_kxk_conv_umma_matches_oracle_and_cuda_core_kernel(case, density, fused)
     g = torch.Generator().manual_seed(61)
     x = rand_feat(g, n, cin, h, w, dtype, 0.5)
     mask = rand_mask(g, n, h, w, density)
+    if density == 0.97:
+        mask[0] = 1                      # one fully active image: its patches take the TMA path, the others gather
     wt = (torch.randn(cout, cin, k, k, generator=g) / (k * cin ** 0.5)).to(dtype)
     bias = torch.randn(cout, generator=g).to(dtype)
     ref, m_ref = O.conv(x, mask, wt, bias, (s, s), (p, p), (d, d), 1)
@@ -549,7 +554,7 @@ def test_kxk_conv_umma_matches_oracle_and_cuda_core_kernel(case, density, fused)
     xd[(mask == 0).expand_as(x)] = float("nan")
     ho, wo = ref.shape[2:]
     desc = kk.make_conv_desc(tuple(x.shape), cout, (ho, wo), (k, k), (s, s), (p, p), (d, d), 1, 1)
-    ws = torch.empty(kk.conv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
+    ws = torch.empty(kk.conv_workspace_bytes(desc), dtype=torch.uint8, device="cuda") if scratch else None
     if not fused:
         out = torch.full(ref.shape, float("nan"), dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last)
         out, om = kk.sparse_conv(xd, f, md, bias.cuda(), (s, s), (p, p), (d, d), 1, create_out_mask=True, out=out, filter_umma=packed, workspace=ws)
