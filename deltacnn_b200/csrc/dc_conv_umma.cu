@@ -188,6 +188,10 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 // ---- kernel -----------------------------------------------------------------------------------
 // Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
 //                [ row lists ][ mbarriers, scalars, bias ]
+// kFront selects how a CTA finds its rows: 0 = spans of a 1x1 layer (one contiguous span, or persistent CTAs over
+// strided spans), 1 = work list in global memory (KxK, strided, transposed), 2 = patches of a stride-1 KxK layer.
+// One instantiation per form keeps each kernel's code short: their speed depends on it.
+template <int kFront>
 __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, const __grid_constant__ CUtensorMap tmap_in) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -220,9 +224,10 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     const int ncols = min(p.bn, p.cout - n0);                      // real output channels here
     const uint8_t* wimg = p.wimg + (size_t)blockIdx.y * p.bn * 128;   // this CTA's rows inside every K block
     // transposed convolution: this CTA's output phase (py, px) uses the taps ky = py + s*a, kx = px + s*b
-    const int ph_y = p.transposed ? (int)blockIdx.z / p.sw : 0, ph_x = p.transposed ? (int)blockIdx.z % p.sw : 0;
+    const bool transposed = kFront == 1 && p.transposed != 0;
+    const int ph_y = transposed ? (int)blockIdx.z / p.sw : 0, ph_x = transposed ? (int)blockIdx.z % p.sw : 0;
     auto filter_block = [&](int kb_) -> size_t {                  // K block of this CTA -> K block of the packed filter
-        if (!p.transposed) return (size_t)kb_;
+        if (!transposed) return (size_t)kb_;
         const int j = kb_ / p.ncb, cb = kb_ - j * p.ncb;
         const int t = (ph_y + p.sh * (j / p.m)) * p.kw + ph_x + p.sw * (j % p.m);
         return (size_t)t * p.ncb + cb;
@@ -249,9 +254,9 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     grid_dep_wait();
 
     // ---- the rows of this CTA ----
-    const bool list_mode = p.wl_list != nullptr;
-    const bool multi = p.ms_rounds > 0;                               // span mode over several strided spans per CTA
-    const bool patch = p.patch_mode != 0;                             // KxK stride 1: persistent CTAs over patches of output pixels
+    constexpr bool list_mode = kFront == 1;
+    const bool multi = kFront == 0 && p.ms_rounds > 0;                // span mode over several strided spans per CTA
+    constexpr bool patch = kFront == 2;                               // KxK stride 1: persistent CTAs over patches of output pixels
     const int64_t q0 = (list_mode || multi || patch) ? 0 : (int64_t)blockIdx.x * p.span;
     int cnt = 0;
     bool dense_rows = false;          // span mode: rows = all pixels of the span, loaded by TMA
@@ -259,7 +264,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         cnt = p.wl_count[blockIdx.z];
         if ((int64_t)blockIdx.x * kRows >= cnt) { leave(); return; }   // persistent CTAs beyond the work
         if (tid < p.taps)                                           // input pixel of tap t relative to a row's base pixel
-            s_toff[tid] = p.transposed ? -((tid / p.m) * p.wi + tid % p.m) : (tid / p.kw) * p.dh * p.wi + (tid % p.kw) * p.dw;
+            s_toff[tid] = transposed ? -((tid / p.m) * p.wi + tid % p.m) : (tid / p.kw) * p.dh * p.wi + (tid % p.kw) * p.dw;
     } else if (multi) {
         if (tid == 0) s_toff[0] = 0;
     } else if (patch) {
@@ -350,7 +355,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     const __half2 thr2 = __float2half2_rn(p.thr);
     __syncthreads();                  // row lists complete
 
-    const bool plain_1x1 = p.taps == 1 && p.sh == 1 && p.sw == 1 && p.pt == 0 && p.pl == 0 && !p.transposed;
+    const bool plain_1x1 = p.taps == 1 && p.sh == 1 && p.sw == 1 && p.pt == 0 && p.pl == 0 && !transposed;
     int tile = 0;                     // tiles processed by this CTA (the accumulator barrier's phase counts these)
     const int nrounds = multi ? p.ms_rounds : patch ? (int)((p.npatches - blockIdx.x + gridDim.x - 1) / gridDim.x) : 1;
     // patch mode: the origin of the current patch is kept in s_toff[28..30] (x0, y0, image) for the thread that issues the loads
@@ -470,7 +475,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                     const uint32_t rr = q - b * (uint32_t)(p.ho * p.wo);
                     const int oy = (int)fast_div(rr, p.wo_mul, p.wo_shift);
                     const int ox = (int)rr - oy * p.wo;
-                    if (p.transposed) base = ((int)b * p.hi + ((oy + p.pt) >> 1)) * p.wi + ((ox + p.pl) >> 1);   // stride 2
+                    if (transposed) base = ((int)b * p.hi + ((oy + p.pt) >> 1)) * p.wi + ((ox + p.pl) >> 1);   // stride 2
                     else base = ((int)b * p.hi + oy * p.sh - p.pt) * p.wi + ox * p.sw - p.pl;
                 }
                 s_base[tid] = base;
@@ -925,7 +930,10 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_list = pl.off_list; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
     static thread_local bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(k_pw_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return check_launch();
+        if (cudaFuncSetAttribute(k_pw_umma<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(k_pw_umma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(k_pw_umma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+            return check_launch();
         attr_set = true;
     }
     if (pl.smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
@@ -978,7 +986,9 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         if (persistent < 1) persistent = 1;
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
     }
-    int rc = launch_pdl(k_pw_umma, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
+    int rc = ws != nullptr ? launch_pdl(k_pw_umma<1>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
+             : patch_mode ? launch_pdl(k_pw_umma<2>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
+                          : launch_pdl(k_pw_umma<0>, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
     if (rc != DC_OK) return rc;
     if (ep != nullptr && !fused && !has_res)
         return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,
