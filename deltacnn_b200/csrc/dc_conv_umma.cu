@@ -191,7 +191,8 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 // kFront selects how a CTA finds its rows: 0 = spans of a 1x1 layer (one contiguous span, or persistent CTAs over
 // strided spans), 1 = work list in global memory (KxK, strided, transposed), 2 = patches of a stride-1 KxK layer.
 // One instantiation per form keeps each kernel's code short: their speed depends on it.
-template <int kFront>
+// kExactAct: the fused activation is one of act_exact_in_half, so only the packed-half epilogue is compiled in.
+template <int kFront, bool kExactAct>
 __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, const __grid_constant__ CUtensorMap tmap_in) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -351,7 +352,6 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     int g = 1;
     while (g < nch && g < 32) g <<= 1;
     const int lig = lane & (g - 1), ppw = 32 / g;
-    const bool half_exact = act_exact_in_half(p.act);
     const __half2 thr2 = __float2half2_rn(p.thr);
     __syncthreads();                  // row lists complete
 
@@ -667,9 +667,10 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                         continue;
                     }
                     bool hit = false;
-                    if (mine[u])
-                        hit = half_exact ? truncate_pack_h2(d[u], y[u], tr[u], p.act, thr2)
-                                         : truncate_pack_f32(d[u], y[u], tr[u], p.act, p.thr);
+                    if (mine[u]) {
+                        if constexpr (kExactAct) hit = truncate_pack_h2(d[u], y[u], tr[u], p.act, thr2);
+                        else hit = truncate_pack_f32(d[u], y[u], tr[u], p.act, p.thr);
+                    }
                     const bool active = group_any(hit, g, lane);
                     if (mine[u]) {
                         if (active) {
@@ -930,10 +931,14 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_list = pl.off_list; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
     static thread_local bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(k_pw_umma<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(k_pw_umma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(k_pw_umma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
-            return check_launch();
+        bool ok_attr = true;
+        ok_attr &= cudaFuncSetAttribute(k_pw_umma<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        ok_attr &= cudaFuncSetAttribute(k_pw_umma<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        ok_attr &= cudaFuncSetAttribute(k_pw_umma<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        ok_attr &= cudaFuncSetAttribute(k_pw_umma<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        ok_attr &= cudaFuncSetAttribute(k_pw_umma<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        ok_attr &= cudaFuncSetAttribute(k_pw_umma<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        if (!ok_attr) return check_launch();
         attr_set = true;
     }
     if (pl.smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
@@ -986,9 +991,18 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         if (persistent < 1) persistent = 1;
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
     }
-    int rc = ws != nullptr ? launch_pdl(k_pw_umma<1>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
-             : patch_mode ? launch_pdl(k_pw_umma<2>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
-                          : launch_pdl(k_pw_umma<0>, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
+    const bool exact_act = !fused || (p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6);
+    const int front = ws != nullptr ? 1 : patch_mode ? 2 : 0;
+    int rc;
+    if (exact_act) {
+        rc = front == 1 ? launch_pdl(k_pw_umma<1, true>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
+           : front == 2 ? launch_pdl(k_pw_umma<2, true>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
+                        : launch_pdl(k_pw_umma<0, true>, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
+    } else {
+        rc = front == 1 ? launch_pdl(k_pw_umma<1, false>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
+           : front == 2 ? launch_pdl(k_pw_umma<2, false>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
+                        : launch_pdl(k_pw_umma<0, false>, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
+    }
     if (rc != DC_OK) return rc;
     if (ep != nullptr && !fused && !has_res)
         return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,
