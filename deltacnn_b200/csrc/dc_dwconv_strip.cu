@@ -26,12 +26,12 @@ struct DwStripParams {
 // `in0` is the element offset of tap (0,0)'s input pixel (it may lie in the padding: only taps whose bit is
 // set in `tb` are read). All tap loads of a channel pack are issued before the first is used, so a lane has
 // up to eleven 16-byte reads in flight; inactive taps contribute zeros instead of branches.
-template <int NV>
+// kExact: the activation is one of act_exact_in_half (only the packed-half truncation is compiled in).
+template <int NV, bool kExact>
 __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const float* s_w, const float* s_b, bool on, unsigned tb,
                                          int64_t qq, int64_t in0, int lig, int g, int npk, int lane) {
     const int64_t off = qq * p.c;
     Pack<__half, 8> pd[NV], pu[NV], pr[NV];
-    const bool half_exact = act_exact_in_half(p.act);
     const __half2 thr2 = __float2half2_rn(p.thr);
     bool hit = false;
 #pragma unroll
@@ -71,8 +71,8 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const float* s_
         if (!p.fused) {
             if (mine) pd[j].store(p.out + off + i * 8);
         } else if (mine) {
-            hit |= half_exact ? truncate_pack_h2(pd[j], pu[j], pr[j], p.act, thr2)
-                              : truncate_pack_f32(pd[j], pu[j], pr[j], p.act, p.thr);
+            if constexpr (kExact) hit |= truncate_pack_h2(pd[j], pu[j], pr[j], p.act, thr2);
+            else hit |= truncate_pack_f32(pd[j], pu[j], pr[j], p.act, p.thr);
         }
     }
     if (!p.fused) return;
@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(256) k_dw3x3_list(DwStripParams p, const int32
     const int ppw = 32 / g;
     const int warp0 = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int nwarps = gridDim.x * 8;
+    const bool exact = act_exact_in_half(p.act);
     for (int r = warp0 * ppw; r < cnt; r += nwarps * ppw) {
         const int idx = r + gi;
         const bool on = idx < cnt;
@@ -144,11 +145,12 @@ __global__ void __launch_bounds__(256) k_dw3x3_list(DwStripParams p, const int32
         const uint32_t b = fast_div(t, p.ho_mul, p.ho_shift);
         const int oy = (int)(t - b * (uint32_t)p.ho);
         const int64_t in0 = (((int64_t)b * p.hi + (oy * p.s - p.pt)) * p.wi + (ox * p.s - p.pl)) * p.c;
-        dw_pixel<NV>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
+        if (exact) dw_pixel<NV, true>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
+        else dw_pixel<NV, false>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
     }
 }
 
-template <int NV>   // channel packs per lane: ceil(C / 8 / lanes-per-pixel)
+template <int NV, bool kExact>   // channel packs per lane: ceil(C / 8 / lanes-per-pixel)
 __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
             const unsigned tb = __shfl_sync(DC_FULL, taps, srcl);
             const int soy = __shfl_sync(DC_FULL, oy, srcl), sox = __shfl_sync(DC_FULL, ox, srcl), sb = __shfl_sync(DC_FULL, b, srcl);
             const int64_t in0 = (((int64_t)sb * p.hi + (soy * p.s - p.pt)) * p.wi + (sox * p.s - p.pl)) * p.c;
-            dw_pixel<NV>(p, s_w, s_b, src >= 0, tb, (int64_t)base + srcl, in0, lig, g, npk, lane);
+            dw_pixel<NV, kExact>(p, s_w, s_b, src >= 0, tb, (int64_t)base + srcl, in0, lig, g, npk, lane);
         }
     }
 }
@@ -213,7 +215,7 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
 // into shared memory and lets its eight warps share them, so one active run of pixels is spread over the whole CTA
 // instead of being walked by one warp. No scan pass, no counter to reset.
 constexpr int kCtaSpans = 4;
-template <int NV>
+template <int NV, bool kExact>
 __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t nspans, int rounds) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t n
             const uint32_t b = fast_div(t, p.ho_mul, p.ho_shift);
             const int oy = (int)(t - b * (uint32_t)p.ho);
             const int64_t in0 = (((int64_t)b * p.hi + (oy * p.s - p.pt)) * p.wi + (ox * p.s - p.pl)) * p.c;
-            dw_pixel<NV>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
+            dw_pixel<NV, kExact>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
         }
     }
 }
@@ -296,6 +298,7 @@ __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t n
 // goes through shared memory. Compared with one warp walking all slices of a pixel in turn this gives S times
 // the warps to hide the read latency with, and a per-warp chain of one round of reads instead of S.
 // Persistent CTAs: the filter is staged once per CTA.
+template <bool kExact>
 __global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
@@ -312,7 +315,6 @@ __global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
     const int my_px = warp / S, my_slice = warp - my_px * S;
     const bool worker = warp < ppi * S;
     const int i = my_slice * 32 + lane;                               // this lane's channel pack
-    const bool half_exact = act_exact_in_half(p.act);
     const __half2 thr2 = __float2half2_rn(p.thr);
     const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
     int par = 0;
@@ -371,7 +373,10 @@ __global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
             continue;
         }
         bool hit = false;
-        if (mine) hit = half_exact ? truncate_pack_h2(pd, pu, pr, p.act, thr2) : truncate_pack_f32(pd, pu, pr, p.act, p.thr);
+        if (mine) {
+            if constexpr (kExact) hit = truncate_pack_h2(pd, pu, pr, p.act, thr2);
+            else hit = truncate_pack_f32(pd, pu, pr, p.act, p.thr);
+        }
         const bool whit = __any_sync(DC_FULL, hit);
         if (lane == 0) s_flag[par][warp] = whit ? 1 : 0;
         __syncthreads();          // the flags of iteration parity `par` are next written two iterations (two barriers) later
@@ -421,6 +426,7 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     fast_div_init((uint32_t)p.ho, &p.ho_mul, &p.ho_shift);
     const int npk = p.c / 8;
     const int nv = divup(npk, 32);
+    const bool exact = !p.fused || (p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6);
     const size_t smem = (size_t)10 * p.c * 4;         // filter and bias as fp32
     // large map, narrow pixels: CTA-level compaction, no scan pass. With scratch memory and so many pixels that a CTA
     // would need several rounds, the work list below spreads the active pixels better.
@@ -429,7 +435,8 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     if (grid_c > nspans) grid_c = nspans;
     const int rounds = (int)divup64(divup64(nspans, grid_c), kCtaSpans);
     if (nv == 1 && npix >= 40000 && (ws == nullptr || rounds <= 1)) {
-        return launch_pdl(k_dw3x3_cta<1>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
+        return exact ? launch_pdl(k_dw3x3_cta<1, true>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds)
+                     : launch_pdl(k_dw3x3_cta<1, false>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
     }
     // the work list costs two extra launches; it pays on large maps where the active pixels cluster
     if (ws != nullptr && npix >= 40000) {             // work-list form: one scan pass, then persistent warps over the active pixels
@@ -454,7 +461,8 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
         int64_t blocks_s = divup64(npix, ppi);
         const int64_t cap_s = (int64_t)sm_count() * 4;
         if (blocks_s > cap_s) blocks_s = cap_s;
-        return launch_pdl(k_dw3x3_sliced, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S);
+        return exact ? launch_pdl(k_dw3x3_sliced<true>, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S)
+                     : launch_pdl(k_dw3x3_sliced<false>, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S);
     }
     // wide pixels keep a whole warp busy, so give every warp few of them; narrow pixels share a warp
     int g = 1;
@@ -466,12 +474,9 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     int64_t blocks = divup64(divup64(npix, strip), 8);
     const int64_t cap = (int64_t)sm_count() * 8;
     if (blocks > cap) blocks = cap;
-    switch (nv) {
-        case 1: launch_pdl(k_dw3x3_strip<1>, dim3((unsigned)blocks), dim3(256), smem, st, p); break;
-        case 2: launch_pdl(k_dw3x3_strip<2>, dim3((unsigned)blocks), dim3(256), smem, st, p); break;
-        case 3: launch_pdl(k_dw3x3_strip<3>, dim3((unsigned)blocks), dim3(256), smem, st, p); break;
-        default: launch_pdl(k_dw3x3_strip<4>, dim3((unsigned)blocks), dim3(256), smem, st, p); break;
-    }
+    // wider pixels took the sliced kernel above: one channel pack per lane here
+    if (exact) launch_pdl(k_dw3x3_strip<1, true>, dim3((unsigned)blocks), dim3(256), smem, st, p);
+    else launch_pdl(k_dw3x3_strip<1, false>, dim3((unsigned)blocks), dim3(256), smem, st, p);
     return check_launch();
 }
 
