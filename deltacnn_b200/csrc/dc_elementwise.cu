@@ -144,12 +144,12 @@ __global__ void __launch_bounds__(256) k_sparsify_u8(const uint8_t* __restrict__
 // NV > 0: every lane keeps its NV packs of (e, u, r) in registers between the
 // any-channel decision and the write-back, so each state tensor is read once.
 // NV == 0: two passes, the second recomputes (used for very wide pixels).
-template <typename T, int W, int NV>
+// kHalfFast: fp16 packs, max-truncation and an activation of act_exact_in_half: only the packed-half step is compiled in.
+template <typename T, int W, int NV, bool kHalfFast = false>
 __global__ void __launch_bounds__(256) k_act_trunc(T* __restrict__ delta, T* __restrict__ prev, T* __restrict__ trunc,
                                                    int32_t* __restrict__ mask, int64_t npix, int C, int g, float thr,
                                                    int act, int mode) {
     const int nvec = C / W;
-    const bool half_fast = mode == DC_TRUNC_MAX && act_exact_in_half(act);
     const __half2 thr2 = __float2half2_rn(thr);
     DC_PIXEL_LOOP(npix, g) {
         const int64_t px = base + lane / g;
@@ -184,22 +184,20 @@ __global__ void __launch_bounds__(256) k_act_trunc(T* __restrict__ delta, T* __r
             d.load(delta + off + i * W);
             y.load(prev + off + i * W);
             r.load(trunc + off + i * W);
-            if constexpr (sizeof(T) == 2 && W == 8) {
-                if (half_fast) {                 // packed half arithmetic, bit-identical (see truncate_pack_h2)
-                    hit |= truncate_pack_h2(d, y, r, act, thr2);
-                    e = d;
-                    return;
-                }
-            }
+            if constexpr (kHalfFast && sizeof(T) == 2 && W == 8) {     // packed half arithmetic, bit-identical (see truncate_pack_h2)
+                hit |= truncate_pack_h2(d, y, r, act, thr2);
+                e = d;
+            } else {
 #pragma unroll
-            for (int k = 0; k < W; ++k) {
-                float yo = y.get(k);
-                float rr = rnd<T>(r.get(k) + d.get(k));
-                float u = rnd<T>(yo + rr);
-                float ee = rnd<T>(act_apply(u, act) - act_apply(yo, act));
-                r.set(k, rr); y.set(k, u); e.set(k, ee);
-                hit |= fabsf(ee) > thr;
-                ss = fmaf(ee, ee, ss);
+                for (int k = 0; k < W; ++k) {
+                    float yo = y.get(k);
+                    float rr = rnd<T>(r.get(k) + d.get(k));
+                    float u = rnd<T>(yo + rr);
+                    float ee = rnd<T>(act_apply(u, act) - act_apply(yo, act));
+                    r.set(k, rr); y.set(k, u); e.set(k, ee);
+                    hit |= fabsf(ee) > thr;
+                    ss = fmaf(ee, ee, ss);
+                }
             }
         };
         if (on) {
@@ -520,7 +518,12 @@ static int act_trunc_t(T* delta, T* prev, T* trunc, int32_t* mask, int64_t npix,
         const int g = lanes_per_pixel(nvec);
         const int per_lane = divup(nvec, g);
         dim3 grid = pixel_grid(npix, g);
-#define DC_AT(NV) launch_pdl(k_act_trunc<T, V, NV>, grid, dim3(256), 0, st, delta, prev, trunc, mask, npix, C, g, t, act, mode)
+        const bool fast = sizeof(T) == 2 && mode == DC_TRUNC_MAX && act >= DC_ACT_NONE && act <= DC_ACT_RELU6;
+#define DC_AT(NV)                                                                                                                        \
+    do {                                                                                                                                 \
+        if (fast) launch_pdl(k_act_trunc<T, V, NV, true>, grid, dim3(256), 0, st, delta, prev, trunc, mask, npix, C, g, t, act, mode);  \
+        else launch_pdl(k_act_trunc<T, V, NV, false>, grid, dim3(256), 0, st, delta, prev, trunc, mask, npix, C, g, t, act, mode);      \
+    } while (0)
         if (per_lane <= 1) DC_AT(1);
         else if (per_lane <= 2) DC_AT(2);
         else if (per_lane <= 4) DC_AT(4);
