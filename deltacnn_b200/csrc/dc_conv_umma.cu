@@ -192,7 +192,8 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 // strided spans), 1 = work list in global memory (KxK, strided, transposed), 2 = patches of a stride-1 KxK layer.
 // One instantiation per form keeps each kernel's code short: their speed depends on it.
 // kExactAct: the fused activation is one of act_exact_in_half, so only the packed-half epilogue is compiled in.
-template <int kFront, bool kExactAct>
+// kFused: the epilogue is the truncation step (else a plain store, optionally with a residual).
+template <int kFront, bool kExactAct, bool kFused>
 __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, const __grid_constant__ CUtensorMap tmap_in) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -287,7 +288,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
             }
             on = p.mi[pin] != 0;
             ron = p.res_mask != nullptr && p.res_mask[q] != 0;
-            if (blockIdx.y == 0 && (!p.fused || !(on || ron))) p.mo[q] = (on || ron) ? 1 : 0;
+            if (blockIdx.y == 0 && (!kFused || !(on || ron))) p.mo[q] = (on || ron) ? 1 : 0;
         }
         const uint32_t tbw = (on ? 1u : 0u) | (ron ? kRowHasResidual : 0u);
         const unsigned bal = __ballot_sync(DC_FULL, tbw != 0u);
@@ -381,7 +382,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            if (valid4[i] && blockIdx.y == 0 && (!p.fused || tb4[i] == 0u)) p.mo[q4[i]] = tb4[i] != 0u ? 1 : 0;
+            if (valid4[i] && blockIdx.y == 0 && (!kFused || tb4[i] == 0u)) p.mo[q4[i]] = tb4[i] != 0u ? 1 : 0;
             const unsigned bal = __ballot_sync(DC_FULL, tb4[i] != 0u);
             int base = 0;
             if (lane == 0 && bal != 0u) base = (int)atomicAdd(&s_u32[2], (uint32_t)__popc(bal));
@@ -426,7 +427,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
             }
         }
         const int q = (patch_b * p.ho + oy) * p.wo + ox;
-        if (valid && blockIdx.y == 0 && (!p.fused || tbw == 0u)) p.mo[q] = tbw != 0u ? 1 : 0;
+        if (valid && blockIdx.y == 0 && (!kFused || tbw == 0u)) p.mo[q] = tbw != 0u ? 1 : 0;
         if (tid == 0) s_u32[2] = 0u;
         const int n_active = __syncthreads_count(tbw != 0u);
         if (n_active == 0) continue;
@@ -640,7 +641,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                     if (mine[u]) {
                         off[u] = (q0 + s_out[t0 + r]) * p.cout + n0 + lig * 8;
                         d[u].load(reinterpret_cast<const __half*>(sStage + (size_t)r * p.stage_pitch) + lig * 8);
-                        if (p.fused) {
+                        if (kFused) {
                             y[u].load(p.prev + off[u]);
                             tr[u].load(p.trunc + off[u]);
                         }
@@ -648,7 +649,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                 }
 #pragma unroll
                 for (int u = 0; u < kU; ++u) {
-                    if (!p.fused) {
+                    if (!kFused) {
                         if (mine[u]) {
                             if (p.res != nullptr) {                // linear layer with a residual connection
                                 const uint32_t tbw = s_tb[t0 + rb + u * ppw + lane / g];
@@ -932,12 +933,11 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     static thread_local bool attr_set = false;
     if (!attr_set) {
         bool ok_attr = true;
-        ok_attr &= cudaFuncSetAttribute(k_pw_umma<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_pw_umma<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_pw_umma<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_pw_umma<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_pw_umma<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_pw_umma<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+#define DC_SET_ATTR(F, E, U) ok_attr &= cudaFuncSetAttribute(k_pw_umma<F, E, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess
+        DC_SET_ATTR(0, true, false); DC_SET_ATTR(1, true, false); DC_SET_ATTR(2, true, false);
+        DC_SET_ATTR(0, true, true); DC_SET_ATTR(1, true, true); DC_SET_ATTR(2, true, true);
+        DC_SET_ATTR(0, false, true); DC_SET_ATTR(1, false, true); DC_SET_ATTR(2, false, true);
+#undef DC_SET_ATTR
         if (!ok_attr) return check_launch();
         attr_set = true;
     }
@@ -994,15 +994,18 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     const bool exact_act = !fused || (p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6);
     const int front = ws != nullptr ? 1 : patch_mode ? 2 : 0;
     int rc;
-    if (exact_act) {
-        rc = front == 1 ? launch_pdl(k_pw_umma<1, true>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
-           : front == 2 ? launch_pdl(k_pw_umma<2, true>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
-                        : launch_pdl(k_pw_umma<0, true>, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
-    } else {
-        rc = front == 1 ? launch_pdl(k_pw_umma<1, false>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
-           : front == 2 ? launch_pdl(k_pw_umma<2, false>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
-                        : launch_pdl(k_pw_umma<0, false>, grid, dim3(kPwThreads), pl.smem, st, p, tmap);
-    }
+#define DC_LAUNCH(F, E, U) rc = launch_pdl(k_pw_umma<F, E, U>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
+#define DC_LAUNCH_FRONT(E, U)                                  \
+    do {                                                        \
+        if (front == 1) DC_LAUNCH(1, E, U);                     \
+        else if (front == 2) DC_LAUNCH(2, E, U);                \
+        else DC_LAUNCH(0, E, U);                                \
+    } while (0)
+    if (!fused) DC_LAUNCH_FRONT(true, false);
+    else if (exact_act) DC_LAUNCH_FRONT(true, true);
+    else DC_LAUNCH_FRONT(false, true);
+#undef DC_LAUNCH_FRONT
+#undef DC_LAUNCH
     if (rc != DC_OK) return rc;
     if (ep != nullptr && !fused && !has_res)
         return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,
