@@ -26,8 +26,9 @@ struct DwStripParams {
 // `in0` is the element offset of tap (0,0)'s input pixel (it may lie in the padding: only taps whose bit is
 // set in `tb` are read). All tap loads of a channel pack are issued before the first is used, so a lane has
 // up to eleven 16-byte reads in flight; inactive taps contribute zeros instead of branches.
-// kExact: the activation is one of act_exact_in_half (only the packed-half truncation is compiled in).
-template <int NV, bool kExact>
+// kEpi: 0 = plain store, 1 = fused truncation with an activation of act_exact_in_half (packed half only),
+// 2 = fused truncation, any activation.
+template <int NV, int kEpi>
 __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const float* s_w, const float* s_b, bool on, unsigned tb,
                                          int64_t qq, int64_t in0, int lig, int g, int npk, int lane) {
     const int64_t off = qq * p.c;
@@ -45,7 +46,7 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const float* s_
             if (mine && (tb & (1u << t9)))
                 v[t9] = __ldg(reinterpret_cast<const uint4*>(p.in + in0 + (int64_t)((t9 / 3) * p.wi + t9 % 3) * p.c) + i);
         }
-        if (p.fused && mine) {
+        if ((kEpi != 0) && mine) {
             pu[j].load(p.prev + off + i * 8);
             pr[j].load(p.trunc + off + i * 8);
         }
@@ -68,14 +69,14 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const float* s_
         __half2* dh = reinterpret_cast<__half2*>(pd[j].s);
 #pragma unroll
         for (int k = 0; k < 4; ++k) dh[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
-        if (!p.fused) {
+        if ((kEpi == 0)) {
             if (mine) pd[j].store(p.out + off + i * 8);
         } else if (mine) {
-            if constexpr (kExact) hit |= truncate_pack_h2(pd[j], pu[j], pr[j], p.act, thr2);
+            if constexpr (kEpi == 1) hit |= truncate_pack_h2(pd[j], pu[j], pr[j], p.act, thr2);
             else hit |= truncate_pack_f32(pd[j], pu[j], pr[j], p.act, p.thr);
         }
     }
-    if (!p.fused) return;
+    if ((kEpi == 0)) return;
     const bool active = group_any(hit, g, lane);
     if (!on) return;
 #pragma unroll
@@ -145,12 +146,13 @@ __global__ void __launch_bounds__(256) k_dw3x3_list(DwStripParams p, const int32
         const uint32_t b = fast_div(t, p.ho_mul, p.ho_shift);
         const int oy = (int)(t - b * (uint32_t)p.ho);
         const int64_t in0 = (((int64_t)b * p.hi + (oy * p.s - p.pt)) * p.wi + (ox * p.s - p.pl)) * p.c;
-        if (exact) dw_pixel<NV, true>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
-        else dw_pixel<NV, false>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
+        if (!p.fused) dw_pixel<NV, 0>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
+        else if (exact) dw_pixel<NV, 1>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
+        else dw_pixel<NV, 2>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
     }
 }
 
-template <int NV, bool kExact>   // channel packs per lane: ceil(C / 8 / lanes-per-pixel)
+template <int NV, int kEpi>   // channel packs per lane: ceil(C / 8 / lanes-per-pixel)
 __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
@@ -187,7 +189,7 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
                 const int iy = y0 + t9 / 3, ix = x0 + t9 % 3;
                 if (iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi && mrow[iy * p.wi + ix] != 0) taps |= 1u << t9;
             }
-            if (!p.fused || taps == 0) p.mo[q] = taps != 0 ? 1 : 0;
+            if ((kEpi == 0) || taps == 0) p.mo[q] = taps != 0 ? 1 : 0;
         }
         unsigned todo = __ballot_sync(DC_FULL, taps != 0);
         // ---- phase 2: ppw active pixels per round ----
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
             const unsigned tb = __shfl_sync(DC_FULL, taps, srcl);
             const int soy = __shfl_sync(DC_FULL, oy, srcl), sox = __shfl_sync(DC_FULL, ox, srcl), sb = __shfl_sync(DC_FULL, b, srcl);
             const int64_t in0 = (((int64_t)sb * p.hi + (soy * p.s - p.pt)) * p.wi + (sox * p.s - p.pl)) * p.c;
-            dw_pixel<NV, kExact>(p, s_w, s_b, src >= 0, tb, (int64_t)base + srcl, in0, lig, g, npk, lane);
+            dw_pixel<NV, kEpi>(p, s_w, s_b, src >= 0, tb, (int64_t)base + srcl, in0, lig, g, npk, lane);
         }
     }
 }
@@ -215,7 +217,7 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
 // into shared memory and lets its eight warps share them, so one active run of pixels is spread over the whole CTA
 // instead of being walked by one warp. No scan pass, no counter to reset.
 constexpr int kCtaSpans = 4;
-template <int NV, bool kExact>
+template <int NV, int kEpi>
 __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t nspans, int rounds) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t n
         }
 #pragma unroll
         for (int j = 0; j < kCtaSpans; ++j) {
-            if (valid4[j] && (!p.fused || tb4[j] == 0u)) p.mo[q4[j]] = tb4[j] != 0u ? 1 : 0;
+            if (valid4[j] && ((kEpi == 0) || tb4[j] == 0u)) p.mo[q4[j]] = tb4[j] != 0u ? 1 : 0;
             const unsigned bal = __ballot_sync(DC_FULL, tb4[j] != 0u);
             int base = 0;
             if (lane == 0 && bal != 0u) base = atomicAdd(&s_cnt, __popc(bal));
@@ -288,7 +290,7 @@ __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t n
             const uint32_t b = fast_div(t, p.ho_mul, p.ho_shift);
             const int oy = (int)(t - b * (uint32_t)p.ho);
             const int64_t in0 = (((int64_t)b * p.hi + (oy * p.s - p.pt)) * p.wi + (ox * p.s - p.pl)) * p.c;
-            dw_pixel<NV, kExact>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
+            dw_pixel<NV, kEpi>(p, s_w, s_b, on, tb, (int64_t)q, in0, lig, g, npk, lane);
         }
     }
 }
@@ -298,7 +300,7 @@ __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t n
 // goes through shared memory. Compared with one warp walking all slices of a pixel in turn this gives S times
 // the warps to hide the read latency with, and a per-warp chain of one round of reads instead of S.
 // Persistent CTAs: the filter is staged once per CTA.
-template <bool kExact>
+template <int kEpi>
 __global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* s_w = reinterpret_cast<float*>(smem);                      // [9][C]
@@ -333,7 +335,7 @@ __global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
             tap_on = iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi && p.mi[((int64_t)b * p.hi + iy) * p.wi + ix] != 0;
         }
         const unsigned tb = __ballot_sync(DC_FULL, tap_on) & 0x1ffu;
-        if (on && my_slice == 0 && lane == 0 && (!p.fused || tb == 0u)) p.mo[q] = tb != 0u ? 1 : 0;
+        if (on && my_slice == 0 && lane == 0 && ((kEpi == 0) || tb == 0u)) p.mo[q] = tb != 0u ? 1 : 0;
         const bool mine = on && tb != 0u && i < npk;
         const int64_t in0 = (((int64_t)b * p.hi + y0) * p.wi + x0) * p.c;
         const int64_t off = (int64_t)q * p.c + i * 8;
@@ -345,7 +347,7 @@ __global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
                 v[t9] = __ldg(reinterpret_cast<const uint4*>(p.in + in0 + (int64_t)((t9 / 3) * p.wi + t9 % 3) * p.c) + i);
         }
         Pack<__half, 8> pd, pu, pr;
-        if (p.fused && mine) {
+        if ((kEpi != 0) && mine) {
             pu.load(p.prev + off);
             pr.load(p.trunc + off);
         }
@@ -368,13 +370,13 @@ __global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
         __half2* dh = reinterpret_cast<__half2*>(pd.s);
 #pragma unroll
         for (int k = 0; k < 4; ++k) dh[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
-        if (!p.fused) {                                               // uniform over the CTA
+        if ((kEpi == 0)) {                                               // uniform over the CTA
             if (mine) pd.store(p.out + off);
             continue;
         }
         bool hit = false;
         if (mine) {
-            if constexpr (kExact) hit = truncate_pack_h2(pd, pu, pr, p.act, thr2);
+            if constexpr (kEpi == 1) hit = truncate_pack_h2(pd, pu, pr, p.act, thr2);
             else hit = truncate_pack_f32(pd, pu, pr, p.act, p.thr);
         }
         const bool whit = __any_sync(DC_FULL, hit);
@@ -426,7 +428,7 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     fast_div_init((uint32_t)p.ho, &p.ho_mul, &p.ho_shift);
     const int npk = p.c / 8;
     const int nv = divup(npk, 32);
-    const bool exact = !p.fused || (p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6);
+    const int epi = !p.fused ? 0 : (p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6) ? 1 : 2;     // epilogue kind of the kernels
     const size_t smem = (size_t)10 * p.c * 4;         // filter and bias as fp32
     // large map, narrow pixels: CTA-level compaction, no scan pass. With scratch memory and so many pixels that a CTA
     // would need several rounds, the work list below spreads the active pixels better.
@@ -435,8 +437,9 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     if (grid_c > nspans) grid_c = nspans;
     const int rounds = (int)divup64(divup64(nspans, grid_c), kCtaSpans);
     if (nv == 1 && npix >= 40000 && (ws == nullptr || rounds <= 1)) {
-        return exact ? launch_pdl(k_dw3x3_cta<1, true>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds)
-                     : launch_pdl(k_dw3x3_cta<1, false>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
+        return epi == 0 ? launch_pdl(k_dw3x3_cta<1, 0>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds)
+             : epi == 1 ? launch_pdl(k_dw3x3_cta<1, 1>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds)
+                        : launch_pdl(k_dw3x3_cta<1, 2>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
     }
     // the work list costs two extra launches; it pays on large maps where the active pixels cluster
     if (ws != nullptr && npix >= 40000) {             // work-list form: one scan pass, then persistent warps over the active pixels
@@ -461,8 +464,9 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
         int64_t blocks_s = divup64(npix, ppi);
         const int64_t cap_s = (int64_t)sm_count() * 4;
         if (blocks_s > cap_s) blocks_s = cap_s;
-        return exact ? launch_pdl(k_dw3x3_sliced<true>, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S)
-                     : launch_pdl(k_dw3x3_sliced<false>, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S);
+        return epi == 0 ? launch_pdl(k_dw3x3_sliced<0>, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S)
+             : epi == 1 ? launch_pdl(k_dw3x3_sliced<1>, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S)
+                        : launch_pdl(k_dw3x3_sliced<2>, dim3((unsigned)blocks_s), dim3(256), smem, st, p, S);
     }
     // wide pixels keep a whole warp busy, so give every warp few of them; narrow pixels share a warp
     int g = 1;
@@ -475,8 +479,9 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     const int64_t cap = (int64_t)sm_count() * 8;
     if (blocks > cap) blocks = cap;
     // wider pixels took the sliced kernel above: one channel pack per lane here
-    if (exact) launch_pdl(k_dw3x3_strip<1, true>, dim3((unsigned)blocks), dim3(256), smem, st, p);
-    else launch_pdl(k_dw3x3_strip<1, false>, dim3((unsigned)blocks), dim3(256), smem, st, p);
+    if (epi == 0) launch_pdl(k_dw3x3_strip<1, 0>, dim3((unsigned)blocks), dim3(256), smem, st, p);
+    else if (epi == 1) launch_pdl(k_dw3x3_strip<1, 1>, dim3((unsigned)blocks), dim3(256), smem, st, p);
+    else launch_pdl(k_dw3x3_strip<1, 2>, dim3((unsigned)blocks), dim3(256), smem, st, p);
     return check_launch();
 }
 
