@@ -188,8 +188,8 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 // ---- kernel -----------------------------------------------------------------------------------
 // Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
 //                [ row lists ][ mbarriers, scalars, bias ]
-// kFront selects how a CTA finds its rows: 0 = spans of a 1x1 layer (one contiguous span, or persistent CTAs over
-// strided spans), 1 = work list in global memory (KxK, strided, transposed), 2 = patches of a stride-1 KxK layer.
+// kFront selects how a CTA finds its rows: 0 = one contiguous span of a 1x1 layer, 3 = persistent CTAs over strided
+// spans of a 1x1 layer, 1 = work list in global memory (KxK, strided, transposed), 2 = patches of a stride-1 KxK layer.
 // One instantiation per form keeps each kernel's code short: their speed depends on it.
 // kExactAct: the fused activation is one of act_exact_in_half, so only the packed-half epilogue is compiled in.
 // kFused: the epilogue is the truncation step (else a plain store, optionally with a residual).
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
 
     // ---- the rows of this CTA ----
     constexpr bool list_mode = kFront == 1;
-    const bool multi = kFront == 0 && p.ms_rounds > 0;                // span mode over several strided spans per CTA
+    constexpr bool multi = kFront == 3;                               // span mode over several strided spans per CTA
     constexpr bool patch = kFront == 2;                               // KxK stride 1: persistent CTAs over patches of output pixels
     const int64_t q0 = (list_mode || multi || patch) ? 0 : (int64_t)blockIdx.x * p.span;
     int cnt = 0;
@@ -934,9 +934,9 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     if (!attr_set) {
         bool ok_attr = true;
 #define DC_SET_ATTR(F, E, U) ok_attr &= cudaFuncSetAttribute(k_pw_umma<F, E, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess
-        DC_SET_ATTR(0, true, false); DC_SET_ATTR(1, true, false); DC_SET_ATTR(2, true, false);
-        DC_SET_ATTR(0, true, true); DC_SET_ATTR(1, true, true); DC_SET_ATTR(2, true, true);
-        DC_SET_ATTR(0, false, true); DC_SET_ATTR(1, false, true); DC_SET_ATTR(2, false, true);
+        DC_SET_ATTR(0, true, false); DC_SET_ATTR(1, true, false); DC_SET_ATTR(2, true, false); DC_SET_ATTR(3, true, false);
+        DC_SET_ATTR(0, true, true); DC_SET_ATTR(1, true, true); DC_SET_ATTR(2, true, true); DC_SET_ATTR(3, true, true);
+        DC_SET_ATTR(0, false, true); DC_SET_ATTR(1, false, true); DC_SET_ATTR(2, false, true); DC_SET_ATTR(3, false, true);
 #undef DC_SET_ATTR
         if (!ok_attr) return check_launch();
         attr_set = true;
@@ -992,13 +992,14 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
     }
     const bool exact_act = !fused || (p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6);
-    const int front = ws != nullptr ? 1 : patch_mode ? 2 : 0;
+    const int front = ws != nullptr ? 1 : patch_mode ? 2 : multi_span ? 3 : 0;
     int rc;
 #define DC_LAUNCH(F, E, U) rc = launch_pdl(k_pw_umma<F, E, U>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
 #define DC_LAUNCH_FRONT(E, U)                                  \
     do {                                                        \
         if (front == 1) DC_LAUNCH(1, E, U);                     \
         else if (front == 2) DC_LAUNCH(2, E, U);                \
+        else if (front == 3) DC_LAUNCH(3, E, U);                \
         else DC_LAUNCH(0, E, U);                                \
     } while (0)
     if (!fused) DC_LAUNCH_FRONT(true, false);
