@@ -6,6 +6,7 @@
 // Phase 2: the active pixels are handed out to aligned lane groups (8 output channels per lane);
 // a lane reads the pixel's taps straight from global memory (the input has only a few bytes per
 // pixel, neighbours share cache lines) against the filter held in shared memory as fp32.
+#include <type_traits>
 #include "dc_common.cuh"
 
 namespace dc {
@@ -19,10 +20,11 @@ struct StemParams {
 
 // One output pixel per aligned lane group (8 output channels per lane): taps x input channels against the fp32
 // filter in shared memory, epilogue in registers. Called by all 32 lanes of a warp.
-template <typename T>
+// kEpi: 0 = plain store, 1 = fused truncation in packed half (fp16, activation of act_exact_in_half), 2 = fused, generic.
+template <typename T, int kEpi>
 __device__ __forceinline__ void stem_pixel(const StemParams& p, const float* s_w, const float* s_b, const int* s_toff, bool on,
                                            unsigned long long tb, int sin0, int64_t qq, int lig, int g, int npk, int lane,
-                                           bool half_exact, __half2 thr2) {
+                                           __half2 thr2) {
     constexpr int W = VecTraits<T>::kVec, NP = 8 / W;            // a lane's 8 output channels as NP 16-byte packs
     const T* in = reinterpret_cast<const T*>(p.in);
     T* out = reinterpret_cast<T*>(p.out);
@@ -60,7 +62,7 @@ __device__ __forceinline__ void stem_pixel(const StemParams& p, const float* s_w
     for (int h = 0; h < NP; ++h)
 #pragma unroll
         for (int k = 0; k < W; ++k) d[h].set(k, acc[h * W + k]);
-    if (!p.fused) {
+    if (kEpi == 0) {
         if (mine) {
 #pragma unroll
             for (int h = 0; h < NP; ++h) d[h].store(out + off + h * W);
@@ -76,10 +78,8 @@ __device__ __forceinline__ void stem_pixel(const StemParams& p, const float* s_w
         }
 #pragma unroll
         for (int h = 0; h < NP; ++h) {
-            if constexpr (sizeof(T) == 2) {
-                if (half_exact) { hit |= truncate_pack_h2(d[h], y[h], r[h], p.act, thr2); continue; }
-            }
-            hit |= truncate_pack_f32(d[h], y[h], r[h], p.act, p.thr);
+            if constexpr (sizeof(T) == 2 && kEpi == 1) hit |= truncate_pack_h2(d[h], y[h], r[h], p.act, thr2);
+            else hit |= truncate_pack_f32(d[h], y[h], r[h], p.act, p.thr);
         }
     }
     const bool active = group_any(hit, g, lane);
@@ -117,7 +117,7 @@ __device__ __forceinline__ void stem_stage_filter(const StemParams& p, float* s_
 // dilate the mask of kStemSpans spans per round (thread = output pixel), compact the active pixels with their tap
 // bit sets into shared memory and let the eight warps share them. No scan pass, no counter to reset.
 constexpr int kStemSpans = 2;
-template <typename T>
+template <typename T, int kEpi>
 __global__ void __launch_bounds__(256) k_conv_stem_cta(StemParams p, int64_t nspans, int rounds) {
     extern __shared__ float s_w[];
     __shared__ uint32_t s_q[kStemSpans * 256];
@@ -134,7 +134,6 @@ __global__ void __launch_bounds__(256) k_conv_stem_cta(StemParams p, int64_t nsp
     while (g < npk) g <<= 1;
     const int lig = lane & (g - 1), gi = lane / g;
     const int ppw = 32 / g;
-    const bool half_exact = sizeof(T) == 2 && act_exact_in_half(p.act);
     const __half2 thr2 = __float2half2_rn(p.thr);
     const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
     auto in0_of = [&](uint32_t q) {
@@ -170,7 +169,7 @@ __global__ void __launch_bounds__(256) k_conv_stem_cta(StemParams p, int64_t nsp
                         if (p.mi[in0 + ky * p.dh * p.wi + kx * p.dw] != 0) tapbits |= 1ull << (ky * p.kw + kx);
                     }
                 }
-                if (!p.fused || tapbits == 0ull) p.mo[q] = tapbits != 0ull ? 1 : 0;
+                if (kEpi == 0 || tapbits == 0ull) p.mo[q] = tapbits != 0ull ? 1 : 0;
             }
             const unsigned bal = __ballot_sync(DC_FULL, tapbits != 0ull);
             int base = 0;
@@ -189,12 +188,12 @@ __global__ void __launch_bounds__(256) k_conv_stem_cta(StemParams p, int64_t nsp
             const bool on = idx < cnt;
             const uint32_t q = on ? s_q[idx] : 0u;
             const unsigned long long tb = on ? s_t[idx] : 0ull;
-            stem_pixel<T>(p, s_w, s_b, s_toff, on, tb, in0_of(q), (int64_t)q, lig, g, npk, lane, half_exact, thr2);
+            stem_pixel<T, kEpi>(p, s_w, s_b, s_toff, on, tb, in0_of(q), (int64_t)q, lig, g, npk, lane, thr2);
         }
     }
 }
 
-template <typename T>
+template <typename T, int kEpi>
 __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
     extern __shared__ float s_w[];                               // [kh*kw*ci][co] fp32, bias [co], tap offsets [kh*kw]
     grid_dep_launch();
@@ -210,7 +209,6 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
     while (g < npk) g <<= 1;                                     // npk <= 32
     const int lig = lane & (g - 1), gi = lane / g;
     const int ppw = 32 / g;
-    const bool half_exact = sizeof(T) == 2 && act_exact_in_half(p.act);
     const __half2 thr2 = __float2half2_rn(p.thr);
     const uint32_t npix = (uint32_t)p.n * p.ho * p.wo;
     const uint32_t warp0 = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -236,7 +234,7 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
                     if (p.mi[in0 + ky * p.dh * p.wi + kx * p.dw] != 0) tapbits |= 1ull << (ky * p.kw + kx);
                 }
             }
-            if (!p.fused || tapbits == 0ull) p.mo[q] = tapbits != 0ull ? 1 : 0;
+            if (kEpi == 0 || tapbits == 0ull) p.mo[q] = tapbits != 0ull ? 1 : 0;
         }
         unsigned todo = __ballot_sync(DC_FULL, tapbits != 0ull);
         // phase 2: ppw active pixels per round
@@ -254,7 +252,7 @@ __global__ void __launch_bounds__(256) k_conv_stem(StemParams p) {
             const int srcl = src < 0 ? 0 : src;
             const unsigned long long tb = __shfl_sync(DC_FULL, tapbits, srcl);
             const int sin0 = __shfl_sync(DC_FULL, in0, srcl);
-            stem_pixel<T>(p, s_w, s_b, s_toff, src >= 0, tb, sin0, (int64_t)base + srcl, lig, g, npk, lane, half_exact, thr2);
+            stem_pixel<T, kEpi>(p, s_w, s_b, s_toff, src >= 0, tb, sin0, (int64_t)base + srcl, lig, g, npk, lane, thr2);
         }
     }
 }
@@ -286,12 +284,16 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
     p.thr = !p.fused ? 0.f : d->dtype == DC_F16 ? host_round_threshold<__half>(ep->threshold) : ep->threshold;
+    // epilogue kind of the kernels: plain store, fused truncation in packed half, fused truncation in fp32
+    const int epi = !p.fused ? 0 : (d->dtype == DC_F16 && p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6) ? 1 : 2;
+#define DC_STEM_KERNELS(X) X(__half, 0) X(__half, 1) X(__half, 2) X(float, 0) X(float, 2)
     static thread_local bool attr_set = false;
     if (smem > 48 * 1024 && !attr_set) {
-        cudaFuncSetAttribute(k_conv_stem<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(k_conv_stem<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(k_conv_stem_cta<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(k_conv_stem_cta<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+#define DC_STEM_ATTR(T, E)                                                                                  \
+        cudaFuncSetAttribute(k_conv_stem<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);     \
+        cudaFuncSetAttribute(k_conv_stem_cta<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        DC_STEM_KERNELS(DC_STEM_ATTR)
+#undef DC_STEM_ATTR
         attr_set = true;
     }
     // large maps: persistent CTAs compact the active pixels of their spans themselves (no scan pass, no scratch)
@@ -301,11 +303,20 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
         int64_t grid_c = (int64_t)sm_count() * (d->dtype == DC_F16 ? 4 : 3);    // resident CTAs (registers)
         if (grid_c > nspans) grid_c = nspans;
         const int rounds = (int)divup64(divup64(nspans, grid_c), kStemSpans);
-        if (d->dtype == DC_F16) return launch_pdl(k_conv_stem_cta<__half>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
-        return launch_pdl(k_conv_stem_cta<float>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
+#define DC_STEM_CTA(T, E) \
+        if (std::is_same<T, __half>::value == (d->dtype == DC_F16) && epi == E) \
+            return launch_pdl(k_conv_stem_cta<T, E>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
+        DC_STEM_KERNELS(DC_STEM_CTA)
+#undef DC_STEM_CTA
+        return DC_ERR_UNSUPPORTED;
     }
-    if (d->dtype == DC_F16) return launch_pdl(k_conv_stem<__half>, dim3((unsigned)blocks), dim3(256), smem, st, p);
-    return launch_pdl(k_conv_stem<float>, dim3((unsigned)blocks), dim3(256), smem, st, p);
+#define DC_STEM_STRIP(T, E) \
+    if (std::is_same<T, __half>::value == (d->dtype == DC_F16) && epi == E) \
+        return launch_pdl(k_conv_stem<T, E>, dim3((unsigned)blocks), dim3(256), smem, st, p);
+    DC_STEM_KERNELS(DC_STEM_STRIP)
+#undef DC_STEM_STRIP
+#undef DC_STEM_KERNELS
+    return DC_ERR_UNSUPPORTED;
 }
 
 }  // namespace dc
