@@ -8,7 +8,9 @@ namespace dc {
 
 constexpr int kThinMaxCout = 32;
 
-template <typename T, int W>
+// kCo: compile-time bound on the output channels (1, 2, 4, 8, 16, 32): the accumulators and the inner loops are sized
+// by it, so a one-channel head does not pay for thirty-two.
+template <typename T, int W, int kCo>
 __global__ void __launch_bounds__(256) k_conv_thin(const T* __restrict__ in, const int32_t* __restrict__ mi,
                                                    const T* __restrict__ filt, const T* __restrict__ bias,
                                                    T* __restrict__ out, int32_t* __restrict__ mo, int64_t npix, int cin,
@@ -31,9 +33,9 @@ __global__ void __launch_bounds__(256) k_conv_thin(const T* __restrict__ in, con
         const bool on = px < npix && mi[px] != 0;
         if (px < npix && lig == 0) mo[px] = on ? 1 : 0;
         if (__ballot_sync(DC_FULL, on) == 0) continue;
-        float acc[kThinMaxCout];
+        float acc[kCo];
 #pragma unroll
-        for (int co = 0; co < kThinMaxCout; ++co) acc[co] = 0.f;
+        for (int co = 0; co < kCo; ++co) acc[co] = 0.f;
         if (on) {
             for (int i = lig; i < nvec; i += g) {
                 Pack<T, W> v;
@@ -43,13 +45,13 @@ __global__ void __launch_bounds__(256) k_conv_thin(const T* __restrict__ in, con
                     const float a = v.get(k);
                     const float* wr = s_w + (i * W + k) * cout;
 #pragma unroll
-                    for (int co = 0; co < kThinMaxCout; ++co)
+                    for (int co = 0; co < kCo; ++co)
                         if (co < cout) acc[co] = fmaf(a, wr[co], acc[co]);
                 }
             }
         }
 #pragma unroll
-        for (int co = 0; co < kThinMaxCout; ++co) {
+        for (int co = 0; co < kCo; ++co) {
             if (co >= cout) break;
             const float s = group_sum(acc[co], g);
             if (on && (co % g) == lig) out[px * cout + co] = from_f<T>(s + s_b[co]);
@@ -75,16 +77,25 @@ int conv_thin(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
         if (blocks > cap) blocks = cap;
         return launch_pdl(kernel, dim3((unsigned)blocks), dim3(256), smem, st, tin, mi, tf, tb, tout, mo, npix, d->c_in, d->c_out, g);
     };
+#define DC_THIN(T, W, nvec)                                                                                                         \
+    do {                                                                                                                            \
+        const T* tin = (const T*)in; const T* tf = (const T*)filt; const T* tb = (const T*)bias; T* tout = (T*)out;                  \
+        if (d->c_out <= 1) return launch(k_conv_thin<T, W, 1>, nvec, tin, tf, tb, tout);                                             \
+        if (d->c_out <= 2) return launch(k_conv_thin<T, W, 2>, nvec, tin, tf, tb, tout);                                             \
+        if (d->c_out <= 4) return launch(k_conv_thin<T, W, 4>, nvec, tin, tf, tb, tout);                                             \
+        if (d->c_out <= 8) return launch(k_conv_thin<T, W, 8>, nvec, tin, tf, tb, tout);                                             \
+        if (d->c_out <= 16) return launch(k_conv_thin<T, W, 16>, nvec, tin, tf, tb, tout);                                           \
+        return launch(k_conv_thin<T, W, 32>, nvec, tin, tf, tb, tout);                                                               \
+    } while (0)
     if (d->dtype == DC_F16) {
-        const bool vec = d->c_in % 8 == 0 && aligned16(in);
-        if (vec) return launch(k_conv_thin<__half, 8>, d->c_in / 8, (const __half*)in, (const __half*)filt, (const __half*)bias, (__half*)out);
-        return launch(k_conv_thin<__half, 1>, d->c_in, (const __half*)in, (const __half*)filt, (const __half*)bias, (__half*)out);
+        if (d->c_in % 8 == 0 && aligned16(in)) DC_THIN(__half, 8, d->c_in / 8);
+        DC_THIN(__half, 1, d->c_in);
     }
     if (d->dtype == DC_F32) {
-        const bool vec = d->c_in % 4 == 0 && aligned16(in);
-        if (vec) return launch(k_conv_thin<float, 4>, d->c_in / 4, (const float*)in, (const float*)filt, (const float*)bias, (float*)out);
-        return launch(k_conv_thin<float, 1>, d->c_in, (const float*)in, (const float*)filt, (const float*)bias, (float*)out);
+        if (d->c_in % 4 == 0 && aligned16(in)) DC_THIN(float, 4, d->c_in / 4);
+        DC_THIN(float, 1, d->c_in);
     }
+#undef DC_THIN
     return DC_ERR_DTYPE;
 }
 
