@@ -216,8 +216,9 @@ __global__ void __launch_bounds__(256) k_dw3x3_strip(DwStripParams p) {
 // (thread = output pixel, all mask reads in flight together), compacts the active pixels with their tap bit sets
 // into shared memory and lets its eight warps share them, so one active run of pixels is spread over the whole CTA
 // instead of being walked by one warp. No scan pass, no counter to reset.
-constexpr int kCtaSpans = 4;                  // passes per round: a pass looks at two spans of kCtaSpanPx pixels
-constexpr int kCtaSpanPx = 128;
+constexpr int kCtaSpans = 4;                  // passes per round: a pass looks at 256 / kCtaSpanPx spans of kCtaSpanPx pixels
+constexpr int kCtaSpanPx = 64;
+constexpr int kCtaSpanLog2 = 6;
 template <int NV, int kEpi>
 __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t nspans, int rounds) {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -246,7 +247,7 @@ __global__ void __launch_bounds__(256, 4) k_dw3x3_cta(DwStripParams p, int64_t n
         bool valid4[kCtaSpans];
 #pragma unroll
         for (int j = 0; j < kCtaSpans; ++j) {
-            const int64_t sid = (int64_t)blockIdx.x + (int64_t)((round * kCtaSpans + j) * 2 + (threadIdx.x >> 7)) * gridDim.x;
+            const int64_t sid = (int64_t)blockIdx.x + (int64_t)((round * kCtaSpans + j) * (256 / kCtaSpanPx) + (threadIdx.x >> kCtaSpanLog2)) * gridDim.x;
             const int64_t q64 = sid * kCtaSpanPx + (threadIdx.x & (kCtaSpanPx - 1));
             valid4[j] = sid < nspans && q64 < (int64_t)npix;
             q4[j] = valid4[j] ? (uint32_t)q64 : 0u;
@@ -436,7 +437,7 @@ int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, co
     const int64_t nspans = divup64(npix, kCtaSpanPx);
     int64_t grid_c = (int64_t)sm_count() * 4;
     if (grid_c > nspans) grid_c = nspans;
-    const int rounds = (int)divup64(divup64(nspans, grid_c), kCtaSpans * 2);
+    const int rounds = (int)divup64(divup64(nspans, grid_c), kCtaSpans * (256 / kCtaSpanPx));
     if (nv == 1 && npix >= 40000 && (ws == nullptr || rounds <= 1)) {
         return epi == 0 ? launch_pdl(k_dw3x3_cta<1, 0>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds)
              : epi == 1 ? launch_pdl(k_dw3x3_cta<1, 1>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds)
