@@ -113,10 +113,10 @@ __device__ __forceinline__ void stem_stage_filter(const StemParams& p, float* s_
     *s_toff_out = s_toff;
 }
 
-// Large maps without a work list in global memory: persistent CTAs own the 256-pixel spans blockIdx.x + j * gridDim.x,
+// Large maps without a work list in global memory: persistent CTAs own the 64-pixel spans blockIdx.x + j * gridDim.x,
 // dilate the mask of kStemSpans spans per round (thread = output pixel), compact the active pixels with their tap
 // bit sets into shared memory and let the eight warps share them. No scan pass, no counter to reset.
-constexpr int kStemSpans = 2;
+constexpr int kStemSpans = 2;                 // passes per round: a pass looks at four spans of 64 pixels
 template <typename T, int kEpi>
 __global__ void __launch_bounds__(256) k_conv_stem_cta(StemParams p, int64_t nspans, int rounds) {
     extern __shared__ float s_w[];
@@ -148,8 +148,8 @@ __global__ void __launch_bounds__(256) k_conv_stem_cta(StemParams p, int64_t nsp
         __syncthreads();              // also: the filter is staged, the previous round's list has been consumed
 #pragma unroll
         for (int j = 0; j < kStemSpans; ++j) {
-            const int64_t sid = (int64_t)blockIdx.x + (int64_t)(round * kStemSpans + j) * gridDim.x;
-            const int64_t q64 = sid * 256 + threadIdx.x;
+            const int64_t sid = (int64_t)blockIdx.x + (int64_t)((round * kStemSpans + j) * 4 + (threadIdx.x >> 6)) * gridDim.x;
+            const int64_t q64 = sid * 64 + (threadIdx.x & 63);
             const bool valid = sid < nspans && q64 < (int64_t)npix;
             const uint32_t q = valid ? (uint32_t)q64 : 0u;
             unsigned long long tapbits = 0ull;
@@ -299,10 +299,10 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
     // large maps: persistent CTAs compact the active pixels of their spans themselves (no scan pass, no scratch)
     (void)ws; (void)ws_bytes;
     if (npix >= 40000) {
-        const int64_t nspans = divup64(npix, 256);
+        const int64_t nspans = divup64(npix, 64);
         int64_t grid_c = (int64_t)sm_count() * (d->dtype == DC_F16 ? 4 : 3);    // resident CTAs (registers)
         if (grid_c > nspans) grid_c = nspans;
-        const int rounds = (int)divup64(divup64(nspans, grid_c), kStemSpans);
+        const int rounds = (int)divup64(divup64(nspans, grid_c), kStemSpans * 4);
 #define DC_STEM_CTA(T, E) \
         if (std::is_same<T, __half>::value == (d->dtype == DC_F16) && epi == E) \
             return launch_pdl(k_conv_stem_cta<T, E>, dim3((unsigned)grid_c), dim3(256), smem, st, p, nspans, rounds);
