@@ -8,6 +8,7 @@ namespace dc {
 struct PoolGeom {
     int n, hi, wi, c, ho, wo;
     int kh, kw, sh, sw, pt, pl, pb, pr, dh, dw;
+    uint32_t wo_mul, wo_shift, ho_mul, ho_shift;      // fast_div constants for w_out and h_out (fewer than 2^31 output pixels)
 };
 
 // mode 0: out = max_win(prev + in*mask) - max_win(prev) over in-bounds taps (fp32 math);
@@ -28,10 +29,10 @@ __global__ void __launch_bounds__(256) k_pool(const T* __restrict__ in, const T*
     for (int64_t base = warp0 * ppw; base < npix; base += nwarps * ppw) {
         const int64_t px = base + lane / g;
         if (px >= npix) continue;
-        const int ox = (int)(px % p.wo);
-        const int64_t t = px / p.wo;
-        const int oy = (int)(t % p.ho);
-        const int64_t b = t / p.ho;
+        const uint32_t t = fast_div((uint32_t)px, p.wo_mul, p.wo_shift);
+        const int ox = (int)((uint32_t)px - t * (uint32_t)p.wo);
+        const int64_t b = (int64_t)fast_div(t, p.ho_mul, p.ho_shift);
+        const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
         const int y0 = oy * p.sh - p.pt, x0 = ox * p.sw - p.pl;
         bool any = false;
         for (int ky = 0; ky < p.kh; ++ky) {
@@ -186,8 +187,11 @@ static int pool_t(const dc_conv_desc* d, const T* in, T* prev, const int32_t* mi
         return check_launch();
     }
     PoolGeom p{d->n, d->h_in, d->w_in, C, d->h_out, d->w_out, d->kh, d->kw, d->stride_h, d->stride_w,
-               d->pad_top, d->pad_left, d->pad_bottom, d->pad_right, d->dil_h, d->dil_w};
+               d->pad_top, d->pad_left, d->pad_bottom, d->pad_right, d->dil_h, d->dil_w, 0u, 0u, 0u, 0u};
+    fast_div_init((uint32_t)d->w_out, &p.wo_mul, &p.wo_shift);
+    fast_div_init((uint32_t)d->h_out, &p.ho_mul, &p.ho_shift);
     const int64_t npix = (int64_t)d->n * d->h_out * d->w_out;
+    if (npix > 0x7fffffffLL) return DC_ERR_SHAPE;
     const int g = lanes_per_pixel(vec_ok ? C / V : C);
     int64_t blocks = divup64(divup64(npix, 32 / g), 8);
     const int64_t cap = (int64_t)sm_count() * 16;
