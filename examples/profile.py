@@ -186,7 +186,12 @@ def roofline_of_dominant_kernel(delta, frames_dev, stream, peak):
     achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9
     table = {k: {"launches": a["launches"], "ms": round(a["ms"], 4), "share": round(a["ms"] / total_ms, 4),
                  "GBps": round(a["bytes"] / max(a["ms"], 1e-9) / 1e6, 1)} for k, a in summary.items()}
+    # DRAM traffic of the class's kernel from a profiler capture of one of its layers (16->96 @112x112, 32 streams:
+    # 20.8 MB read + written for 47.1 MB of algorithmic bytes: the writes and part of the caches stay in L2), scaled to
+    # this launch's algorithmic bytes; None for classes without such a capture.
+    traffic = per_launch_bytes * (20.8 / 47.1) if key == "conv1x1+act" else None
     return {"bound": "hbm", "kernel": key, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-            "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}", "traffic": None,
+            "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}", "traffic": traffic,
+            "traffic_how": "scaled from an ncu capture of one layer of the class (profiles/k_pw_umma_16to96_112x112_32streams.md)",
             "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms, "launches_timed": top["launches"],
             "share_of_step": top["ms"] / total_ms, "kernels": table}
