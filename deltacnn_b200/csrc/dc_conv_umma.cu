@@ -189,7 +189,8 @@ __host__ __device__ inline uint32_t make_idesc(int n) {
 // Shared memory: [ region 0: A stage ring, later reused as the epilogue staging tile ][ filter blocks ]
 //                [ row lists ][ mbarriers, scalars, bias ]
 // kFront selects how a CTA finds its rows: 0 = one contiguous span of a 1x1 layer, 3 = persistent CTAs over strided
-// spans of a 1x1 layer, 1 = work list in global memory (KxK, strided, transposed), 2 = patches of a stride-1 KxK layer.
+// spans of a 1x1 layer, 1 = work list in global memory (KxK, strided, transposed), 2 = patches of a stride-1 KxK layer, 5 = patches of the
+// input lattice of a stride-2 transposed layer.
 // One instantiation per form keeps each kernel's code short: their speed depends on it.
 // kExactAct: the fused activation is one of act_exact_in_half, so only the packed-half epilogue is compiled in.
 // kFused: the epilogue is the truncation step (else a plain store, optionally with a residual).
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     const int ncols = min(p.bn, p.cout - n0);                      // real output channels here
     const uint8_t* wimg = p.wimg + (size_t)blockIdx.y * p.bn * 128;   // this CTA's rows inside every K block
     // transposed convolution: this CTA's output phase (py, px) uses the taps ky = py + s*a, kx = px + s*b
-    const bool transposed = kFront == 1 && p.transposed != 0;
+    const bool transposed = kFront == 5 || (kFront == 1 && p.transposed != 0);
     const int ph_y = transposed ? (int)blockIdx.z / p.sw : 0, ph_x = transposed ? (int)blockIdx.z % p.sw : 0;
     auto filter_block = [&](int kb_) -> size_t {                  // K block of this CTA -> K block of the packed filter
         if (!transposed) return (size_t)kb_;
@@ -258,7 +259,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     // ---- the rows of this CTA ----
     constexpr bool list_mode = kFront == 1;
     constexpr bool multi = kFront == 3;                               // span mode over several strided spans per CTA
-    constexpr bool patch = kFront == 2;                               // KxK stride 1: persistent CTAs over patches of output pixels
+    constexpr bool patch = kFront == 2 || kFront == 5;                             // KxK stride 1: persistent CTAs over patches of output pixels
     const int64_t q0 = (list_mode || multi || patch) ? 0 : (int64_t)blockIdx.x * p.span;
     int cnt = 0;
     bool dense_rows = false;          // span mode: rows = all pixels of the span, loaded by TMA
@@ -270,7 +271,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     } else if (multi) {
         if (tid == 0) s_toff[0] = 0;
     } else if (patch) {
-        if (tid < p.taps) s_toff[tid] = (tid / p.kw) * p.dh * p.wi + (tid % p.kw) * p.dw;
+        if (tid < p.taps) s_toff[tid] = transposed ? -((tid / p.m) * p.wi + tid % p.m) : (tid / p.kw) * p.dh * p.wi + (tid % p.kw) * p.dw;
     } else {
         // span mode (1x1 kernels, no padding): thread t owns pixel q0 + t; the active ones are compacted in
         // order with a ballot per warp and a prefix over the warp totals
@@ -411,15 +412,25 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
         const int patch_y0 = (int)pyi << (7 - p.patch_tw_log2);
         const int patch_x0 = (int)(prem - pyi * (uint32_t)p.patch_px) << p.patch_tw_log2;
         if (tid == 0) { s_toff[28] = patch_x0; s_toff[29] = patch_y0; s_toff[30] = patch_b; }
-        const int oy = patch_y0 + (tid >> p.patch_tw_log2), ox = patch_x0 + (tid & ((1 << p.patch_tw_log2) - 1));
-        const bool valid = tid < kRows && oy < p.ho && ox < p.wo;
+        // lattice point of this thread inside the patch. Convolution: the output pixel itself. Transposed convolution
+        // (stride 2): the patch tiles the lattice (by, bx) = ((oy + pad) / 2, (ox + pad) / 2) of this CTA's output phase,
+        // whose taps (a, c) read the input pixels (by - a, bx - c).
+        const int ly = patch_y0 + (tid >> p.patch_tw_log2), lx = patch_x0 + (tid & ((1 << p.patch_tw_log2) - 1));
+        const int oy = transposed ? 2 * ly + ph_y - p.pt : ly, ox = transposed ? 2 * lx + ph_x - p.pl : lx;
+        const bool valid = tid < kRows && oy >= 0 && oy < p.ho && ox >= 0 && ox < p.wo;
         uint32_t tbw = 0u;
         bool all_in = true;
-        const int in0 = (patch_b * p.hi + oy - p.pt) * p.wi + ox - p.pl;
+        const int in0 = transposed ? (patch_b * p.hi + ly) * p.wi + lx : (patch_b * p.hi + oy - p.pt) * p.wi + ox - p.pl;
         if (valid) {
             for (int t = 0; t < p.taps; ++t) {
-                const int ky = t / p.kw, kx = t - ky * p.kw;
-                const int iy = oy - p.pt + ky * p.dh, ix = ox - p.pl + kx * p.dw;
+                int iy, ix;
+                if (transposed) {
+                    const int a = t / p.m;
+                    iy = ly - a; ix = lx - (t - a * p.m);
+                } else {
+                    const int ky = t / p.kw, kx = t - ky * p.kw;
+                    iy = oy - p.pt + ky * p.dh; ix = ox - p.pl + kx * p.dw;
+                }
                 if (iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi) {
                     if (p.mi[in0 + s_toff[t]] != 0) tbw |= 1u << t;
                     else all_in = false;
@@ -497,9 +508,15 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                     mbar_expect_tx(bar_full(pslot), (uint32_t)kABytes);
                     if (patch) {
                         const int tap_ = kb / p.ncb, cb_ = kb - tap_ * p.ncb;
-                        const int ky = tap_ / p.kw, kx = tap_ - ky * p.kw;
-                        tma_load_patch(sA_u32 + (uint32_t)pslot * kABytes, &tmap_in, cb_ * kKBlock, s_toff[28] - p.pl + kx * p.dw,
-                                       s_toff[29] - p.pt + ky * p.dh, s_toff[30], bar_full(pslot));
+                        int cx, cy;
+                        if (transposed) {
+                            const int a = tap_ / p.m;
+                            cx = s_toff[28] - (tap_ - a * p.m); cy = s_toff[29] - a;
+                        } else {
+                            const int ky = tap_ / p.kw, kx = tap_ - ky * p.kw;
+                            cx = s_toff[28] - p.pl + kx * p.dw; cy = s_toff[29] - p.pt + ky * p.dh;
+                        }
+                        tma_load_patch(sA_u32 + (uint32_t)pslot * kABytes, &tmap_in, cb_ * kKBlock, cx, cy, s_toff[30], bar_full(pslot));
                     } else {
                         tma_load_rows(sA_u32 + (uint32_t)pslot * kABytes, &tmap_in, kb * kKBlock, y0, bar_full(pslot));
                     }
@@ -864,14 +881,14 @@ static bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_des
 static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in, const int32_t* mi, const void* filt, const void* bias,
                           void* out, int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st) {
     PwPlan pl = plan_pw(d, transposed);
-    if (transposed && ws == nullptr) return DC_ERR_UNSUPPORTED;
     if (!pl.ok || mi == nullptr || mo == nullptr) return DC_ERR_UNSUPPORTED;
     // without scratch for a work list only 1x1 kernels (no receptive field to dilate) have a tensor-core path
     // KxK stride 1 without scratch memory: persistent CTAs over patches of output pixels, no scan pass (with scratch the
     // work list is used: it fills every tile, which wins on sparse maps; patches win on mostly active maps).
     // DC_NO_PATCH=1 turns the patch form off.
     static const bool patch_allowed = [] { const char* e = getenv("DC_NO_PATCH"); return !(e != nullptr && e[0] == '1'); }();
-    const bool kxk_patch = patch_allowed && !transposed && pl.taps > 1 && d->stride_h == 1 && d->stride_w == 1;
+    // (a stride-2 transposed convolution is, per output phase, a 2x2- or 3x3-tap convolution over the input lattice: same form)
+    const bool kxk_patch = patch_allowed && (transposed || (pl.taps > 1 && d->stride_h == 1 && d->stride_w == 1));
     if (ws == nullptr && !kxk_patch && (pl.taps != 1 || d->pad_top != 0 || d->pad_left != 0)) return DC_ERR_UNSUPPORTED;
     if (!aligned16(in) || !aligned16(out) || !aligned16(filt)) return DC_ERR_ALIGNMENT;
     const int64_t npix_out = (int64_t)d->n * d->h_out * d->w_out;
@@ -934,9 +951,9 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     if (!attr_set) {
         bool ok_attr = true;
 #define DC_SET_ATTR(F, E, U) ok_attr &= cudaFuncSetAttribute(k_pw_umma<F, E, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess
-        DC_SET_ATTR(0, true, false); DC_SET_ATTR(1, true, false); DC_SET_ATTR(2, true, false); DC_SET_ATTR(3, true, false);
-        DC_SET_ATTR(0, true, true); DC_SET_ATTR(1, true, true); DC_SET_ATTR(2, true, true); DC_SET_ATTR(3, true, true);
-        DC_SET_ATTR(0, false, true); DC_SET_ATTR(1, false, true); DC_SET_ATTR(2, false, true); DC_SET_ATTR(3, false, true);
+        DC_SET_ATTR(0, true, false); DC_SET_ATTR(1, true, false); DC_SET_ATTR(2, true, false); DC_SET_ATTR(3, true, false); DC_SET_ATTR(5, true, false);
+        DC_SET_ATTR(0, true, true); DC_SET_ATTR(1, true, true); DC_SET_ATTR(2, true, true); DC_SET_ATTR(3, true, true); DC_SET_ATTR(5, true, true);
+        DC_SET_ATTR(0, false, true); DC_SET_ATTR(1, false, true); DC_SET_ATTR(2, false, true); DC_SET_ATTR(3, false, true); DC_SET_ATTR(5, false, true);
 #undef DC_SET_ATTR
         if (!ok_attr) return check_launch();
         attr_set = true;
@@ -948,17 +965,20 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         // patch shape tw x th (tw * th = 128) with the least overhang beyond the image; wide patches on ties
         int best_tw = 128;
         int64_t best_area = -1;
+        // extent of the lattice the patches tile: the output, or (transposed) the points ((oy + pad) / 2, (ox + pad) / 2)
+        const int lat_w = transposed ? ((d->w_out - 1 + d->pad_left) >> 1) + 1 : d->w_out;
+        const int lat_h = transposed ? ((d->h_out - 1 + d->pad_top) >> 1) + 1 : d->h_out;
         for (int tw = 128; tw >= 8; tw >>= 1) {
             const int th = kRows / tw;
-            const int64_t area = (int64_t)divup(d->w_out, tw) * tw * divup(d->h_out, th) * th;
+            const int64_t area = (int64_t)divup(lat_w, tw) * tw * divup(lat_h, th) * th;
             if (best_area < 0 || area < best_area) { best_area = area; best_tw = tw; }
         }
         const int tw = best_tw, th = kRows / tw;
         p.patch_mode = 1;
         p.patch_tw_log2 = 0;
         while ((1 << p.patch_tw_log2) < tw) ++p.patch_tw_log2;
-        p.patch_px = divup(d->w_out, tw);
-        p.patch_py = divup(d->h_out, th);
+        p.patch_px = divup(lat_w, tw);
+        p.patch_py = divup(lat_h, th);
         p.npatches = (int64_t)d->n * p.patch_px * p.patch_py;
         fast_div_init((uint32_t)p.patch_px, &p.ppx_mul, &p.ppx_shift);
         fast_div_init((uint32_t)(p.patch_px * p.patch_py), &p.ppi_mul, &p.ppi_shift);
@@ -969,6 +989,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         int64_t persistent = (int64_t)sm_count() * per_sm / pl.ntiles;
         if (persistent < 1) persistent = 1;
         grid.x = (unsigned)(p.npatches < persistent ? p.npatches : persistent);
+        if (transposed) grid.z = 4;       // one output phase per z
     }
     p.ms_rounds = 0;
     p.ms_nspans = divup64(npix_out, kRows);
@@ -992,7 +1013,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         if ((int64_t)grid.x > persistent) grid.x = (unsigned)persistent;
     }
     const bool exact_act = !fused || (p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6);
-    const int front = ws != nullptr ? 1 : patch_mode ? 2 : multi_span ? 3 : 0;
+    const int front = ws != nullptr ? 1 : patch_mode ? (transposed ? 5 : 2) : multi_span ? 3 : 0;
     int rc;
 #define DC_LAUNCH(F, E, U) rc = launch_pdl(k_pw_umma<F, E, U>, grid, dim3(kPwThreads), pl.smem, st, p, tmap)
 #define DC_LAUNCH_FRONT(E, U)                                  \
@@ -1000,6 +1021,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         if (front == 1) DC_LAUNCH(1, E, U);                     \
         else if (front == 2) DC_LAUNCH(2, E, U);                \
         else if (front == 3) DC_LAUNCH(3, E, U);                \
+        else if (front == 5) DC_LAUNCH(5, E, U);                \
         else DC_LAUNCH(0, E, U);                                \
     } while (0)
     if (!fused) DC_LAUNCH_FRONT(true, false);

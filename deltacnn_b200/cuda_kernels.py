@@ -184,7 +184,7 @@ def sparse_deconv(x, filter, mask=None, bias=None, stride=(1, 1), padding=(0, 0)
         raise RuntimeError("deltacnn_b200.sparse_deconv: filter dtype differs from input dtype")
     ws_ptr, ws_len = (workspace.data_ptr(), workspace.numel()) if (workspace is not None and mask is not None and out_mask is not None) else (None, 0)
     status = 2
-    if filter_umma is not None and ws_ptr is not None:
+    if filter_umma is not None and mask is not None and out_mask is not None:     # with scratch: work lists; without: patch tiles
         status = lib.dc_deconv2d_ws(desc, x.data_ptr(), _ptr(mask), filter_umma.data_ptr(), _lib.DC_FILTER_UMMA, _ptr(bias),
                                     out.data_ptr(), _ptr(out_mask), epilogue, ws_ptr, ws_len, _stream())
     if status == 2:     # no tensor-core kernel for this call: CUDA-core kernel, same result

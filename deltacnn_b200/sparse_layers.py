@@ -297,6 +297,8 @@ class _DeltaConvMixin:
         if self._transposed:
             if DCConv2d.use_worklist and self._workspace is None and self.weight_umma is not None:
                 self._workspace = torch.empty(K.deconv_workspace_bytes(self._desc), dtype=torch.uint8, device=x.device)
+            # stride-2 layers: per-phase work lists in scratch memory (measured faster than the patch tiles the library
+            # uses for a call without scratch)
             extra = {"filter_umma": self.weight_umma, "workspace": self._workspace}
         else:
             if DCConv2d.use_worklist and self._workspace is None:

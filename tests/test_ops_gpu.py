@@ -577,11 +577,14 @@ def test_kxk_conv_umma_matches_oracle_and_cuda_core_kernel(case, density, fused,
     assert torch.equal(o1[sel], o2[sel])
 
 
-@pytest.mark.parametrize("cin,cout,k,p,n,h,w", [(64, 64, 4, 1, 2, 9, 11), (512, 256, 4, 1, 1, 6, 7), (256, 256, 4, 1, 2, 12, 10), (32, 48, 2, 0, 2, 8, 8)])
-@pytest.mark.parametrize("density", [0.0, 0.15, 1.0])
+@pytest.mark.parametrize("cin,cout,k,p,n,h,w", [(64, 64, 4, 1, 2, 9, 11), (512, 256, 4, 1, 1, 6, 7), (256, 256, 4, 1, 2, 12, 10), (32, 48, 2, 0, 2, 8, 8),
+                                                (64, 32, 4, 1, 2, 33, 70), (128, 64, 4, 1, 1, 17, 40)])
+@pytest.mark.parametrize("density", [0.0, 0.15, 0.97, 1.0])
 @pytest.mark.parametrize("fused", [False, True])
-def test_deconv_umma_matches_oracle(cin, cout, k, p, n, h, w, density, fused):
-    """Transposed convolution (stride 2) as four per-phase implicit GEMMs on tcgen05, work-list mode."""
+@pytest.mark.parametrize("scratch", [True, False])
+def test_deconv_umma_matches_oracle(cin, cout, k, p, n, h, w, density, fused, scratch):
+    """Transposed convolution (stride 2) as four per-phase implicit GEMMs on tcgen05: per-phase work lists with
+    scratch memory, patch tiles over the input lattice without."""
     import deltacnn_b200.cuda_kernels as kk
     from deltacnn_b200 import _lib
     from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
@@ -599,7 +602,7 @@ def test_deconv_umma_matches_oracle(cin, cout, k, p, n, h, w, density, fused):
     assert nbytes > 0
     packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
     _lib.check(_lib.lib.dc_pack_filter_umma(desc, 1, f.data_ptr(), packed.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
-    ws = torch.empty(kk.deconv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
+    ws = torch.empty(kk.deconv_workspace_bytes(desc), dtype=torch.uint8, device="cuda") if scratch else None
     xd, md = x.cuda(), mask.cuda()
     xd[(mask == 0).expand_as(x)] = float("nan")
     if not fused:
