@@ -46,6 +46,9 @@ int conv2d_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const 
 size_t filter_umma_bytes(const dc_conv_desc* d, int transposed);
 int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, void* packed, cudaStream_t st);
 int umma_error_code();
+int stem_umma_error_code();
+int conv_stem_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+                   int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 int conv_thin(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, cudaStream_t st);
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
@@ -88,7 +91,10 @@ const char* dc_status_string(int status) {
 
 int dc_last_cuda_error(void) { return t_last_cuda_error; }
 
-int dc_umma_error(void) { return umma_error_code(); }
+int dc_umma_error(void) {
+    const int a = umma_error_code();
+    return a != 0 ? a : stem_umma_error_code();
+}
 
 int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,
                  const void* bias, void* out, int32_t* mask_out, const dc_epilogue* epilogue, void* workspace,
@@ -104,6 +110,8 @@ int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_i
         return conv2d_umma(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
     if (filter_layout != DC_FILTER_HWIO) return DC_ERR_UNSUPPORTED;
     int rc = dwconv3x3_strip(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
+    if (rc != DC_ERR_UNSUPPORTED) return rc;
+    rc = conv_stem_umma(desc, in, mask_in, filter, bias, out, mask_out, epilogue, st);      // RGB stems on the tensor core
     if (rc != DC_ERR_UNSUPPORTED) return rc;
     rc = conv_stem(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;

@@ -439,11 +439,12 @@ def test_depthwise_fused_epilogue_equals_two_kernels(c, h, w, s, density):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("cout,k,s,p", [(32, 3, 2, 1), (64, 7, 2, 3), (24, 3, 1, 1)])
-def test_stem_conv_fused_epilogue_equals_two_kernels(dtype, cout, k, s, p):
+@pytest.mark.parametrize("h,w", [(37, 41), (150, 161)])      # the larger map takes the tensor-core stem kernel in fp16
+def test_stem_conv_fused_epilogue_equals_two_kernels(dtype, cout, k, s, p, h, w):
     import deltacnn_b200.cuda_kernels as kk
     from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
     g = torch.Generator().manual_seed(41)
-    n, h, w = 2, 37, 41
+    n = 2
     x = rand_feat(g, n, 3, h, w, dtype, 0.5).cuda()
     mask = rand_mask(g, n, h, w, 0.15).cuda()
     wt = (torch.randn(cout, 3, k, k, generator=g) * 0.3).to(dtype)
