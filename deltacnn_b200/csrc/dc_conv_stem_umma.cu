@@ -33,6 +33,23 @@ struct StemUParams {
     uint32_t off_b, off_list, off_misc, stage_pitch;
 };
 
+// Bit kx of the result: column x0 + kx * dw of the mask row is inside the image and set (kx < min(kw, W)); the W
+// reads are issued together.
+template <int W>
+__device__ __forceinline__ unsigned mask_row_bits(const int32_t* mrow, int x0, int kw, int dw, int wi) {
+    int m[W];
+#pragma unroll
+    for (int kx = 0; kx < W; ++kx) {
+        const int ix = x0 + kx * dw;
+        m[kx] = (kx < kw && ix >= 0 && ix < wi) ? mrow[kx * dw] : 0;
+    }
+    unsigned bits = 0u;
+#pragma unroll
+    for (int kx = 0; kx < W; ++kx)
+        if (m[kx] != 0) bits |= 1u << kx;
+    return bits;
+}
+
 // kEpi: 0 = plain store, 1 = fused truncation in packed half (activation of act_exact_in_half), 2 = fused, fp32 form.
 template <int kEpi>
 __global__ void __launch_bounds__(kSuThreads, 3) k_stem_umma(const StemUParams p) {
@@ -123,10 +140,17 @@ __global__ void __launch_bounds__(kSuThreads, 3) k_stem_umma(const StemUParams p
                 for (int ky = 0; ky < p.kh; ++ky) {
                     const int iy = y0 + ky * p.dh;
                     if (iy < 0 || iy >= p.hi) continue;
-                    for (int kx = 0; kx < p.kw; ++kx) {
-                        const int ix = x0 + kx * p.dw;
-                        if (ix < 0 || ix >= p.wi) continue;
-                        if (p.mi[in0 + ky * p.dh * p.wi + kx * p.dw] != 0) tapbits |= 1ull << (ky * p.kw + kx);
+                    // the reads of a filter row are issued together: four at a time for kernels up to 4 wide, else eight
+                    const int32_t* mrow = p.mi + in0 + ky * p.dh * p.wi;
+                    if (p.kw <= 4) tapbits |= (unsigned long long)mask_row_bits<4>(mrow, x0, p.kw, p.dw, p.wi) << (ky * p.kw);
+                    else tapbits |= (unsigned long long)mask_row_bits<8>(mrow, x0, p.kw, p.dw, p.wi) << (ky * p.kw);
+                }
+                for (int kx = 8; kx < p.kw; ++kx) {               // wider rows (not used by any stem): one read at a time
+                    const int ix = x0 + kx * p.dw;
+                    if (ix < 0 || ix >= p.wi) continue;
+                    for (int ky = 0; ky < p.kh; ++ky) {
+                        const int iy = y0 + ky * p.dh;
+                        if (iy >= 0 && iy < p.hi && p.mi[in0 + ky * p.dh * p.wi + kx * p.dw] != 0) tapbits |= 1ull << (ky * p.kw + kx);
                     }
                 }
                 if (kEpi == 0 || tapbits == 0ull) p.mo[q] = tapbits != 0ull ? 1 : 0;
