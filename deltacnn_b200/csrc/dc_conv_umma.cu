@@ -49,7 +49,8 @@ struct PwParams {
     const __half* in; const int32_t* mi; const uint8_t* wimg; const __half* bias;
     __half* out; int32_t* mo; __half* prev; __half* trunc;
     float thr; int act; int fused;
-    const __half* res; const int32_t* res_mask;   // optional residual (delta, mask) added to a linear 1x1 result
+    const __half* res; const int32_t* res_mask;   // optional residual (delta, mask) added to a linear layer's result
+    __half* res_prev; int res_act;                // ... followed by DCAdd's activation: accumulated sum and activation code
     int64_t npix_out;
     int hi, wi, ho, wo, sh, sw;
     int kh, kw, dh, dw, pt, pl;     // kernel geometry; taps = kh * kw (K runs tap-major, then input channels)
@@ -82,9 +83,11 @@ struct PwParams {
 // input lattice of a stride-2 transposed layer.
 // One instantiation per form keeps each kernel's code short: their speed depends on it.
 // kExactAct: the fused activation is one of act_exact_in_half, so only the packed-half epilogue is compiled in.
-// kFused: the epilogue is the truncation step (else a plain store, optionally with a residual).
-template <int kFront, bool kExactAct, bool kFused>
+// kEpi: 0 = plain store, 1 = fused truncation step, 2 = plain store with a residual added, 3 = residual and the add
+// layer's activation.
+template <int kFront, bool kExactAct, int kEpi>
 __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, const __grid_constant__ CUtensorMap tmap_in) {
+    constexpr bool kFused = kEpi == 1;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
@@ -177,7 +180,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                 pin = (int)((b * p.hi + oy * p.sh) * p.wi + (r - oy * p.wo) * p.sw);
             }
             on = p.mi[pin] != 0;
-            ron = p.res_mask != nullptr && p.res_mask[q] != 0;
+            if constexpr (kEpi >= 2) ron = p.res_mask[q] != 0;
             if (blockIdx.y == 0 && (!kFused || !(on || ron))) p.mo[q] = (on || ron) ? 1 : 0;
         }
         const uint32_t tbw = (on ? 1u : 0u) | (ron ? kRowHasResidual : 0u);
@@ -268,7 +271,9 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
             q4[i] = sid * kRows + (v & 127);
             valid4[i] = sid < p.ms_nspans && q4[i] < p.npix_out;
             tb4[i] = (valid4[i] && p.mi[valid4[i] ? q4[i] : 0] != 0) ? 1u : 0u;
-            if (valid4[i] && p.res_mask != nullptr && p.res_mask[q4[i]] != 0) tb4[i] |= kRowHasResidual;
+            if constexpr (kEpi >= 2) {
+                if (valid4[i] && p.res_mask[q4[i]] != 0) tb4[i] |= kRowHasResidual;
+            }
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -327,6 +332,9 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
             }
         }
         const int q = (patch_b * p.ho + oy) * p.wo + ox;
+        if constexpr (kEpi >= 2) {
+            if (valid && p.res_mask[q] != 0) tbw |= kRowHasResidual;     // a row of its own even without active taps
+        }
         if (valid && blockIdx.y == 0 && (!kFused || tbw == 0u)) p.mo[q] = tbw != 0u ? 1 : 0;
         if (tid == 0) s_u32[2] = 0u;
         const int n_active = __syncthreads_count(tbw != 0u);
@@ -557,16 +565,42 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                 for (int u = 0; u < kU; ++u) {
                     if (!kFused) {
                         if (mine[u]) {
-                            if (p.res != nullptr) {                // linear layer with a residual connection
+                            if constexpr (kEpi >= 2) {             // linear layer with a residual connection
                                 const uint32_t tbw = s_tb[t0 + rb + u * ppw + lane / g];
-                                if (!(tbw & 1u)) d[u].zero();         // the convolution is not active here (stale or zero-filled row)
+                                if ((tbw & 0x3fffffffu) == 0u) d[u].zero();   // the convolution is not active here (stale or zero-filled row)
                                 if (tbw & kRowHasResidual) {
                                     Pack<__half, 8> rr;
                                     rr.load(p.res + off[u]);
                                     __half2* dh = reinterpret_cast<__half2*>(d[u].s);
                                     const __half2* rh = reinterpret_cast<const __half2*>(rr.s);
+                                    if constexpr (kEpi == 2) {
 #pragma unroll
-                                    for (int k = 0; k < 4; ++k) dh[k] = __hadd2(dh[k], rh[k]);
+                                        for (int k = 0; k < 4; ++k) dh[k] = __hadd2(dh[k], rh[k]);
+                                    } else {
+                                        // the add layer's own activation: s = a + b in fp32, u = round(y + s), out = f(u) - f(y)
+                                        // (the arithmetic of dc_add, so the result is the same bit for bit)
+                                        Pack<__half, 8> yy;
+                                        yy.load(p.res_prev + off[u]);
+#pragma unroll
+                                        for (int k = 0; k < 8; ++k) {
+                                            const float yo = yy.get(k);
+                                            const float uu = rnd<__half>(yo + (d[u].get(k) + rr.get(k)));
+                                            yy.set(k, uu);
+                                            d[u].set(k, act_apply(uu, p.res_act) - act_apply(yo, p.res_act));
+                                        }
+                                        yy.store(p.res_prev + off[u]);
+                                    }
+                                } else if constexpr (kEpi == 3) {
+                                    Pack<__half, 8> yy;
+                                    yy.load(p.res_prev + off[u]);
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k) {
+                                        const float yo = yy.get(k);
+                                        const float uu = rnd<__half>(yo + d[u].get(k));
+                                        yy.set(k, uu);
+                                        d[u].set(k, act_apply(uu, p.res_act) - act_apply(yo, p.res_act));
+                                    }
+                                    yy.store(p.res_prev + off[u]);
                                 }
                             }
                             d[u].store(p.out + off[u]);
@@ -784,10 +818,13 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     if (npix_out == 0) return DC_OK;
     if ((int64_t)d->n * d->h_in * d->w_in > 0x7fffffffLL) return DC_ERR_SHAPE;
     const bool has_res = ep != nullptr && ep->residual != nullptr;
-    if (has_res) {        // residual connection: linear stride-1 pointwise layers only (each CTA compacts its own rows)
-        const bool ok_res = !transposed && pl.taps == 1 && d->pad_top == 0 && d->pad_left == 0 && d->stride_h == 1 && d->stride_w == 1 &&
-                            ep->truncation == DC_TRUNC_NONE && ep->activation == DC_ACT_NONE && ep->residual_mask != nullptr &&
-                            aligned16(ep->residual);
+    if (has_res) {
+        // residual connection: linear stride-1 layers whose CTAs find their own rows (pointwise spans, or KxK patch tiles
+        // when no scratch is given); with an activation the add layer's accumulated sum (prev_out) is updated too
+        const bool unit = d->stride_h == 1 && d->stride_w == 1 && !transposed;
+        const bool front_ok = unit && ((pl.taps == 1 && d->pad_top == 0 && d->pad_left == 0) || (pl.taps > 1 && ws == nullptr));
+        const bool ok_res = front_ok && ep->truncation == DC_TRUNC_NONE && ep->residual_mask != nullptr && aligned16(ep->residual) &&
+                            (ep->activation == DC_ACT_NONE || (ep->prev_out != nullptr && aligned16(ep->prev_out)));
         if (!ok_res) return DC_ERR_UNSUPPORTED;
     }
     const bool want_fused = !has_res && ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
@@ -817,6 +854,8 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     p.fused = fused ? 1 : 0;
     p.res = has_res ? (const __half*)ep->residual : nullptr;
     p.res_mask = has_res ? ep->residual_mask : nullptr;
+    p.res_prev = has_res && ep->activation != DC_ACT_NONE ? (__half*)ep->prev_out : nullptr;
+    p.res_act = has_res ? ep->activation : 0;
     p.npix_out = npix_out;
     p.hi = d->h_in; p.wi = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.sh = d->stride_h; p.sw = d->stride_w;
     p.cin = d->c_in; p.cout = d->c_out;
@@ -840,9 +879,11 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     if (!attr_set) {
         bool ok_attr = true;
 #define DC_SET_ATTR(F, E, U) ok_attr &= cudaFuncSetAttribute(k_pw_umma<F, E, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess
-        DC_SET_ATTR(0, true, false); DC_SET_ATTR(1, true, false); DC_SET_ATTR(2, true, false); DC_SET_ATTR(3, true, false); DC_SET_ATTR(5, true, false);
-        DC_SET_ATTR(0, true, true); DC_SET_ATTR(1, true, true); DC_SET_ATTR(2, true, true); DC_SET_ATTR(3, true, true); DC_SET_ATTR(5, true, true);
-        DC_SET_ATTR(0, false, true); DC_SET_ATTR(1, false, true); DC_SET_ATTR(2, false, true); DC_SET_ATTR(3, false, true); DC_SET_ATTR(5, false, true);
+        DC_SET_ATTR(0, true, 0); DC_SET_ATTR(1, true, 0); DC_SET_ATTR(2, true, 0); DC_SET_ATTR(3, true, 0); DC_SET_ATTR(5, true, 0);
+        DC_SET_ATTR(0, true, 1); DC_SET_ATTR(1, true, 1); DC_SET_ATTR(2, true, 1); DC_SET_ATTR(3, true, 1); DC_SET_ATTR(5, true, 1);
+        DC_SET_ATTR(0, false, 1); DC_SET_ATTR(1, false, 1); DC_SET_ATTR(2, false, 1); DC_SET_ATTR(3, false, 1); DC_SET_ATTR(5, false, 1);
+        DC_SET_ATTR(0, true, 2); DC_SET_ATTR(2, true, 2); DC_SET_ATTR(3, true, 2);
+        DC_SET_ATTR(0, true, 3); DC_SET_ATTR(2, true, 3); DC_SET_ATTR(3, true, 3);
 #undef DC_SET_ATTR
         if (!ok_attr) return check_launch();
         attr_set = true;
@@ -913,9 +954,16 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         else if (front == 5) DC_LAUNCH(5, E, U);                \
         else DC_LAUNCH(0, E, U);                                \
     } while (0)
-    if (!fused) DC_LAUNCH_FRONT(true, false);
-    else if (exact_act) DC_LAUNCH_FRONT(true, true);
-    else DC_LAUNCH_FRONT(false, true);
+    if (has_res) {                    // residual forms exist for the fronts whose CTAs find their own rows
+        const bool with_act = p.res_prev != nullptr;
+        if (front == 2) { if (with_act) DC_LAUNCH(2, true, 3); else DC_LAUNCH(2, true, 2); }
+        else if (front == 3) { if (with_act) DC_LAUNCH(3, true, 3); else DC_LAUNCH(3, true, 2); }
+        else if (front == 0) { if (with_act) DC_LAUNCH(0, true, 3); else DC_LAUNCH(0, true, 2); }
+        else return DC_ERR_UNSUPPORTED;
+    }
+    else if (!fused) DC_LAUNCH_FRONT(true, 0);
+    else if (exact_act) DC_LAUNCH_FRONT(true, 1);
+    else DC_LAUNCH_FRONT(false, 1);
 #undef DC_LAUNCH_FRONT
 #undef DC_LAUNCH
     if (rc != DC_OK) return rc;

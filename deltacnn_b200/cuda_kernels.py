@@ -91,14 +91,15 @@ def make_epilogue(prev_out, truncated, threshold, activation, truncation_mode):
     return e
 
 
-def make_residual_epilogue(residual, residual_mask):
-    """Epilogue of a linear 1x1 convolution that adds a residual (delta, mask) to its result, the out-mask
-    becoming the union of both masks (the DCAdd behind a projection convolution, in the same launch)."""
+def make_residual_epilogue(residual, residual_mask, prev_out=None, activation=0):
+    """Epilogue of a linear convolution that adds a residual (delta, mask) to its result, the out-mask becoming the
+    union of both masks (the DCAdd behind the convolution, in the same launch). With ``activation`` > 0 the add
+    layer's activation is applied too, ``prev_out`` being that layer's accumulated sum."""
     e = Epilogue()
-    e.prev_out = None
+    e.prev_out = _ptr(prev_out) if int(activation) > 0 else None
     e.truncated = None
     e.threshold = 0.0
-    e.activation = 0
+    e.activation = max(int(activation), 0)
     e.truncation = -1
     e.residual = _ptr(residual)
     e.residual_mask = _ptr(residual_mask)

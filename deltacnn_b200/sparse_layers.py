@@ -230,16 +230,27 @@ class _DeltaConvMixin:
     def __repr__(self):
         return f"MyConv2d{self.conv_idx} cin={self.in_channels} cout={self.out_channels}"
 
-    def can_fuse_residual(self, input):
-        """True when forward(input, residual=(delta, mask)) adds the residual inside the convolution kernel: a linear
-        fp16 1x1 stride-1 convolution on the tensor-core path (no reference counterpart; it replaces the DCAdd that
-        follows a projection convolution, reference sparse_layers.py DCAdd.forward)."""
-        return (DCConv2d.fuse_residual and not self._transposed and self.backend == DCBackend.deltacnn and type(input) != Tensor
-                and input[0].dtype == torch.float16 and tuple(self.kernel_size) == (1, 1) and tuple(self.stride) == (1, 1)
-                and all(int(v) == 0 for v in self.padding) and self.groups == 1 and self.weight_umma is not None
-                and self.activation is None and not self.dense_out)
+    def can_fuse_residual(self, input, add_layer=None):
+        """True when forward(input, residual=(delta, mask), add_layer=...) adds the residual inside the convolution
+        kernel: a linear fp16 stride-1 convolution on the tensor-core path, 1x1 without padding or KxK on patch tiles
+        (no reference counterpart; it replaces the DCAdd that follows the convolution, reference sparse_layers.py
+        DCAdd.forward). ``add_layer`` is that DCAdd when it has an activation."""
+        if not (DCConv2d.fuse_residual and not self._transposed and self.backend == DCBackend.deltacnn and type(input) != Tensor
+                and input[0].dtype == torch.float16 and tuple(self.stride) == (1, 1) and self.groups == 1
+                and self.weight_umma is not None and self.activation is None and not self.dense_out):
+            return False
+        if tuple(self.kernel_size) == (1, 1):
+            if not all(int(v) == 0 for v in self.padding):
+                return False
+        elif not DCConv2d.patch_tiles or max(self.kernel_size) > 5:
+            return False
+        if add_layer is not None and (add_layer.dense_out or add_layer.weight_a != 1.0 or add_layer.weight_b != 1.0):
+            return False
+        if add_layer is not None and add_layer.activation is not None and not DCConv2d.fuse_residual_activation:
+            return False
+        return True
 
-    def _delta_forward_common(self, input, residual=None):
+    def _delta_forward_common(self, input, residual=None, add_layer=None):
         DCConv2d.conv_idx += 1
         self.frame_idx += 1
         first_iter = self.conv_idx == -1
@@ -251,9 +262,9 @@ class _DeltaConvMixin:
             return out if residual is None else out + residual
         if self.backend != DCBackend.deltacnn:
             _unsupported_backend(self.backend)
-        if residual is not None and not self.can_fuse_residual(input):
+        if residual is not None and not self.can_fuse_residual(input, add_layer):
             raise RuntimeError("this convolution cannot add a residual itself (see can_fuse_residual); use DCAdd")
-        return self._forward_delta_conv(input, first_iter, residual)
+        return self._forward_delta_conv(input, first_iter, residual, add_layer)
 
     def _forward_cudnn(self, input, first_iter):
         out = super(_DeltaConvMixin, self).forward(input)
@@ -264,7 +275,7 @@ class _DeltaConvMixin:
             DCConv2d.flops_sum += n_updated * self.weight.numel()
         return out
 
-    def _forward_delta_conv(self, input, first_iter, residual=None):
+    def _forward_delta_conv(self, input, first_iter, residual=None, add_layer=None):
         if type(input) == Tensor:
             raise RuntimeError("delta convolutions take a (delta, mask) tuple; put a DCSparsify in front of the first layer")
         if self.orig_weights is None:
@@ -285,7 +296,16 @@ class _DeltaConvMixin:
                                        act.truncation_mode.value)
         if residual is not None:
             res_delta, res_mask = residual
-            epilogue = K.make_residual_epilogue(res_delta, res_mask)
+            if add_layer is not None and add_layer.activation is not None:
+                if add_layer.first_iter:              # what DCAdd.forward does on its first call
+                    add_layer.first_iter = False
+                    DCAdd.idx += 1
+                    add_layer.idx = DCAdd.idx
+                    add_layer.prev_out = torch.zeros_like(res_delta)
+                    DCModule.temp_buffers.append(add_layer.prev_out)
+                epilogue = K.make_residual_epilogue(res_delta, res_mask, add_layer.prev_out, add_layer.activation_int)
+            else:
+                epilogue = K.make_residual_epilogue(res_delta, res_mask)
         if self._desc is None:
             size_fn = K.deconv_out_hw if self._transposed else K.conv_out_hw
             hw = size_fn(x.shape[2], x.shape[3], self.kernel_size, self.stride, self.padding, self.dilation)
@@ -393,6 +413,7 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
     reuse_buffers = True      # keep per-layer output buffers across frames
     use_worklist = True       # steady-state frames: active-pixel work lists in per-layer scratch memory
     fuse_residual = True      # forward(input, residual=...) adds the residual inside the convolution kernel where it can
+    fuse_residual_activation = False   # ... also when the add layer has an activation (its accumulated sum is updated by the convolution)
     patch_tiles = False       # stride-1 KxK layers: patch tiles loaded by tiled TMA (mostly active maps) instead of work lists
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1, groups: int = 1,
@@ -402,8 +423,8 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
         nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias, padding_mode)
         self._init_delta_state(delta_threshold, name, activation, dense_out, backend, use_logging, kwargs)
 
-    def forward(self, input, residual=None):
-        return self._delta_forward_common(input, residual)
+    def forward(self, input, residual=None, add_layer=None):
+        return self._delta_forward_common(input, residual, add_layer)
 
 
 class DCConvTranspose2d(_DeltaConvMixin, nn.ConvTranspose2d, DCModule):

@@ -67,6 +67,8 @@ if __name__ == "__main__":
     ap.add_argument("--streams", type=int, default=4)
     ap.add_argument("--frames", type=int, default=8)
     ap.add_argument("--patches", type=int, default=None)
+    ap.add_argument("--fuse-add-act", type=int, default=0, help="1: residual adds with activation run in the convolution epilogue")
     a = ap.parse_args()
+    DCConv2d.fuse_residual_activation = bool(a.fuse_add_act)
     for c in a.configs:
         print(json.dumps(run(c, a.streams, a.frames, patches=a.patches)), flush=True)

@@ -127,6 +127,16 @@ class DeltaOps:
     densify = DCDensify
 
 
+def _conv_then_add(ops, conv, h, idt, add):
+    """add(conv(h), idt). In the delta network the convolution adds the residual (and applies the add layer's
+    activation) in its own epilogue where it has a kernel for that: one launch instead of two."""
+    if ops.delta:
+        inner = conv.conv
+        if inner.can_fuse_residual(h, add):
+            return inner(h, residual=idt, add_layer=add)
+    return add(conv(h), idt)
+
+
 def _base(ops):
     return DCModule if ops.delta else nn.Module
 
@@ -208,7 +218,7 @@ def _make_resnet_parts(ops):
 
         def forward(self, x):
             idt = x if self.down is None else self.down(x)
-            return self.add(self.c3(self.c2(self.c1(x))), idt)
+            return _conv_then_add(ops, self.c3, self.c2(self.c1(x)), idt, self.add)
 
     class Basic(Base):
         def __init__(self, cin, cout, stride):
@@ -220,7 +230,7 @@ def _make_resnet_parts(ops):
 
         def forward(self, x):
             idt = x if self.down is None else self.down(x)
-            return self.add(self.c2(self.c1(x)), idt)
+            return _conv_then_add(ops, self.c2, self.c1(x), idt, self.add)
 
     return Base, Bottleneck, Basic
 

@@ -71,10 +71,12 @@ typedef struct dc_epilogue {
     int32_t truncation;      /* dc_truncation; DC_TRUNC_MAX only when fused */
     /* Optional residual connection (no reference counterpart; replaces a DCAdd behind a linear convolution,
      * sparse_layers.py DCAdd.forward / sparse_add_tensors_wrapper): a delta tensor of the output's shape and its
-     * update mask. out = convolution (where its out-mask is set) + residual (where residual_mask is set), the
-     * out-mask is the union. Only with activation == DC_ACT_NONE and truncation == DC_TRUNC_NONE (prev_out and
-     * truncated are then unused and may be NULL), fp16, 1x1 stride 1 without padding and the DC_FILTER_UMMA
-     * layout; anything else returns DC_ERR_UNSUPPORTED and the caller adds with dc_add. */
+     * update mask. sum = convolution (where its out-mask is set) + residual (where residual_mask is set), the
+     * out-mask is the union. truncation must be DC_TRUNC_NONE. With activation == DC_ACT_NONE out = sum (prev_out
+     * and truncated unused, may be NULL); with an activation, prev_out is the add layer's accumulated sum:
+     * u = prev_out + sum, out = f(u) - f(prev_out), prev_out = u (the arithmetic of dc_add). fp16, stride 1 and the
+     * DC_FILTER_UMMA layout: 1x1 without padding, or KxK called without scratch memory (patch tiles); anything else
+     * returns DC_ERR_UNSUPPORTED and the caller adds with dc_add. */
     const void* residual;
     const int32_t* residual_mask;
 } dc_epilogue;

@@ -712,3 +712,52 @@ def test_pointwise_conv_with_fused_residual_equals_conv_then_add(cin, cout, n, h
     assert not torch.isnan(o2[sel]).any()
     assert torch.equal(o2[sel], ref[sel])
     assert torch.isnan(o2[~sel]).all(), "pixels outside the union mask must not be written"
+
+
+@pytest.mark.parametrize("cin,cout,k,n,h,w", [(64, 64, 3, 2, 40, 48), (32, 32, 3, 2, 64, 64), (128, 256, 1, 2, 20, 20), (256, 64, 3, 1, 17, 33)])
+@pytest.mark.parametrize("act", [0, 1])
+@pytest.mark.parametrize("density,res_density", [(0.1, 0.1), (1.0, 1.0), (0.97, 0.5), (0.0, 0.3)])
+def test_conv_with_fused_residual_and_add_activation(cin, cout, k, n, h, w, act, density, res_density):
+    """A linear stride-1 convolution (1x1, or 3x3 on patch tiles) that adds a residual and applies the add layer's
+    activation in its epilogue against convolution followed by dc_add: same union mask, same values, same
+    accumulated sum."""
+    import deltacnn_b200.cuda_kernels as kk
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(81)
+    pad = k // 2
+    x = rand_feat(g, n, cin, h, w, dtype, 0.3).cuda()
+    mask = rand_mask(g, n, h, w, density)
+    if density == 0.97:
+        mask[0] = 1
+    mask = mask.cuda()
+    xn = x.clone()
+    xn[(mask == 0).expand_as(x)] = float("nan")
+    res = rand_feat(g, n, cout, h, w, dtype, 0.5).cuda()
+    rmask = rand_mask(g, n, h, w, res_density).cuda()
+    resn = res.clone()
+    resn[(rmask == 0).expand_as(res)] = float("nan")
+    wt = (torch.randn(cout, cin, k, k, generator=g) / (k * cin ** 0.5)).to(dtype)
+    f = convert_filter_out_channels_last(wt).cuda()
+    packed = _pack_umma_kxk(f, cin, cout, k, 1, pad, 1)
+    prev = rand_feat(g, n, cout, h, w, dtype, 1.0)
+    # reference: convolution, then dc_add
+    o1, m1 = kk.sparse_conv(xn, f, mask, None, (1, 1), (pad, pad), (1, 1), 1, create_out_mask=True, filter_umma=packed)
+    ref = torch.full_like(o1, float("nan"))
+    mref = torch.empty_like(m1)
+    p1 = prev.cuda()
+    kk.sparse_add_tensors(o1, resn, p1 if act > 0 else None, ref, m1, rmask, mref, 1.0, 1.0, act, False)
+    # fused
+    p2 = prev.cuda()
+    out = torch.full_like(o1, float("nan"))
+    o2, m2 = kk.sparse_conv(xn, f, mask, None, (1, 1), (pad, pad), (1, 1), 1, create_out_mask=True, out=out, filter_umma=packed,
+                            epilogue=kk.make_residual_epilogue(resn, rmask, p2 if act > 0 else None, act))
+    assert _lib.lib.dc_umma_error() == 0
+    assert torch.equal(m2, mref)
+    sel = (mref != 0).expand_as(ref)
+    assert not torch.isnan(o2[sel]).any()
+    assert torch.equal(o2[sel], ref[sel])
+    assert torch.isnan(o2[~sel]).all(), "pixels outside the union mask must not be written"
+    if act > 0:
+        assert torch.equal(p1, p2), "accumulated sum of the add layer differs"
