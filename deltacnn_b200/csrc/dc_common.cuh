@@ -170,6 +170,17 @@ __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol
 // DC_NO_PDL=1 in the environment turns programmatic dependent launch off (plain stream order).
 bool pdl_enabled();
 
+// "Done once" flags for set-up that the CUDA runtime keeps per device (function attributes such as the dynamic
+// shared-memory limit): slot() is the flag of the current device, or nullptr when the device cannot be queried.
+struct PerDeviceOnce {
+    bool done[64] = {};
+    bool* slot() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+        return &done[dev];
+    }
+};
+
 // cluster_y > 1 launches thread-block clusters of (1, cluster_y, 1) CTAs (grid.y must be a multiple of it).
 template <typename... KArgs, typename... Args>
 inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_y, Args... args) {

@@ -287,14 +287,16 @@ int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const vo
     // epilogue kind of the kernels: plain store, fused truncation in packed half, fused truncation in fp32
     const int epi = !p.fused ? 0 : (d->dtype == DC_F16 && p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6) ? 1 : 2;
 #define DC_STEM_KERNELS(X) X(__half, 0) X(__half, 1) X(__half, 2) X(float, 0) X(float, 2)
-    static thread_local bool attr_set = false;
-    if (smem > 48 * 1024 && !attr_set) {
+    static PerDeviceOnce attr_once;
+    bool* attr_set = attr_once.slot();
+    if (attr_set == nullptr) return DC_ERR_LAUNCH;
+    if (smem > 48 * 1024 && !*attr_set) {
 #define DC_STEM_ATTR(T, E)                                                                                  \
         cudaFuncSetAttribute(k_conv_stem<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);     \
         cudaFuncSetAttribute(k_conv_stem_cta<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         DC_STEM_KERNELS(DC_STEM_ATTR)
 #undef DC_STEM_ATTR
-        attr_set = true;
+        *attr_set = true;
     }
     // large maps: persistent CTAs compact the active pixels of their spans themselves (no scan pass, no scratch)
     (void)ws; (void)ws_bytes;

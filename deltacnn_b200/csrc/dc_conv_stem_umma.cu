@@ -65,7 +65,6 @@ __global__ void __launch_bounds__(kSuThreads, 3) k_stem_umma(const StemUParams p
     uint32_t* s_u32 = reinterpret_cast<uint32_t*>(bars + 1);       // [0] tmem base, [1] ok flag, [2] counter
     float* s_bias = reinterpret_cast<float*>(s_u32 + 4);           // [co]
 
-    grid_dep_launch();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar_done = smem_u32(bars);
 
@@ -98,6 +97,7 @@ __global__ void __launch_bounds__(kSuThreads, 3) k_stem_umma(const StemUParams p
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    grid_dep_launch();                 // only after the tensor memory is held (a dependent CTA allocates before it waits)
     const uint32_t tmem_base = s_u32[0];
     volatile uint32_t* ok_flag = &s_u32[1];
     grid_dep_wait();
@@ -316,13 +316,15 @@ int conv_stem_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, con
     p.off_misc = (p.off_list + kSuSpans * kSuSpanPx * 12u + kSuMaxK * 4u + 15) & ~15u;
     const size_t smem = p.off_misc + 8 + 16 + 4 * (size_t)p.co + 1024 /* alignment slack */;
     if (smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;
+    bool* attr_set = attr_once.slot();
+    if (attr_set == nullptr) return DC_ERR_LAUNCH;
+    if (!*attr_set) {
         bool okk = cudaFuncSetAttribute(k_stem_umma<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
         okk &= cudaFuncSetAttribute(k_stem_umma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
         okk &= cudaFuncSetAttribute(k_stem_umma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
         if (!okk) return check_launch();
-        attr_set = true;
+        *attr_set = true;
     }
     p.nspans = divup64(npix, kSuSpanPx);
     int64_t per_sm = (int64_t)(227 * 1024) / (int64_t)(smem + 1024);

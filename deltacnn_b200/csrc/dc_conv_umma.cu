@@ -106,7 +106,6 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     // s_u32[0] tmem base, [1] ok flag, [3..3+warps) warp totals
     float* s_bias = reinterpret_cast<float*>(s_u32 + 12);          // [bn]
 
-    grid_dep_launch();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar0 = smem_u32(bars);
     auto bar_empty = [&](int s) { return bar0 + 8u * s; };
@@ -141,6 +140,9 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // dependents are released only now: a CTA of the next kernel allocates tensor memory before its own
+    // grid_dep_wait(), so it must never compete for columns with a CTA of this grid that is still waiting for its own
+    grid_dep_launch();
     const uint32_t tmem_base = s_u32[0];
     auto leave = [&]() {                   // nothing to do for this CTA: give the tensor memory back
         __syncthreads();
@@ -836,6 +838,8 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     const bool unit_stride = d->stride_h == 1 && d->stride_w == 1;
     const int64_t spans_per_cta = divup64(divup64(npix_out, kRows), (int64_t)sm_count() * 3);
     if (pointwise && (npix_out < kListMinPixels || (unit_stride && spans_per_cta <= kMsSpans))) ws = nullptr;
+    // the residual forms exist for the fronts whose CTAs find their own rows; the strided-span front takes any number of rounds
+    if (pointwise && has_res) ws = nullptr;
     const bool multi_span = ws == nullptr && pointwise && unit_stride && npix_out >= kListMinPixels;
     const bool patch_mode = kxk_patch && ws == nullptr;
     if (transposed) {                 // the kernel sees one phase: m x m taps
@@ -875,8 +879,10 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         d->c_in >= kKBlock && encode_rows_map(&tmap, in, (int64_t)d->n * d->h_in * d->w_in, d->c_in))
         p.tma_rows = 1;
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_list = pl.off_list; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;
+    bool* attr_set = attr_once.slot();
+    if (attr_set == nullptr) return DC_ERR_LAUNCH;
+    if (!*attr_set) {
         bool ok_attr = true;
 #define DC_SET_ATTR(F, E, U) ok_attr &= cudaFuncSetAttribute(k_pw_umma<F, E, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess
         DC_SET_ATTR(0, true, 0); DC_SET_ATTR(1, true, 0); DC_SET_ATTR(2, true, 0); DC_SET_ATTR(3, true, 0); DC_SET_ATTR(5, true, 0);
@@ -886,7 +892,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         DC_SET_ATTR(0, true, 3); DC_SET_ATTR(2, true, 3); DC_SET_ATTR(3, true, 3);
 #undef DC_SET_ATTR
         if (!ok_attr) return check_launch();
-        attr_set = true;
+        *attr_set = true;
     }
     if (pl.smem > 227 * 1024) return DC_ERR_UNSUPPORTED;
     dim3 grid((unsigned)divup64(npix_out, pl.span), (unsigned)pl.ntiles);

@@ -86,7 +86,9 @@ __global__ void __launch_bounds__(256) k_pool(const T* __restrict__ in, const T*
                             Pack<T, W> v; v.load(in + src * p.c + i * W);
 #pragma unroll
                             for (int k = 0; k < W; ++k) {
-                                acc[k] = fmaxf(acc[k], q.get(k) + v.get(k));
+                                // the accumulated value as the cache will hold it after this call (rounded to the storage
+                                // type), so that consecutive frames' deltas telescope exactly
+                                acc[k] = fmaxf(acc[k], rnd<T>(q.get(k) + v.get(k)));
                                 pre[k] = fmaxf(pre[k], q.get(k));
                             }
                         } else {

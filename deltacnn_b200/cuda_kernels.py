@@ -42,6 +42,19 @@ def _check_mask(m, x, name):
         raise RuntimeError(f"deltacnn_b200: {name} has {m.numel()} elements, expected one per pixel")
 
 
+def _check_like(t, x, name):
+    """A cache or output tensor handed over as a raw pointer must match ``x`` in shape, dtype, device and memory
+    format: the kernels index it with x's geometry. A stale cache (batch or resolution changed without
+    ``reset_layers()``) is an error here instead of an out-of-bounds access on the device."""
+    if t is None:
+        return
+    if t.shape != x.shape or t.dtype != x.dtype or t.device != x.device:
+        raise RuntimeError(f"deltacnn_b200: {name} is {tuple(t.shape)} {t.dtype} on {t.device}, expected {tuple(x.shape)} {x.dtype} on "
+                           f"{x.device} (call reset_layers() after a batch or resolution change)")
+    if not t.is_contiguous(memory_format=torch.channels_last):
+        raise RuntimeError(f"deltacnn_b200: {name} must be channels_last contiguous")
+
+
 def _ptr(t):
     return None if t is None else t.data_ptr()
 
@@ -219,8 +232,11 @@ def sparse_pooling(x, prev_x, kernel_size, mask=None, stride=(1, 1), padding=(0,
         if type(out_shape) == list:
             out_shape.extend([out_h, out_w])
     c = x.shape[1]
+    _check_like(prev_x, x, "prev_x")
     if out is None:
         out = torch.empty((x.shape[0], c, out_h, out_w), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+    elif tuple(out.shape) != (x.shape[0], c, out_h, out_w) or out.dtype != x.dtype:
+        raise RuntimeError("deltacnn_b200.sparse_pooling: out has the wrong shape or dtype")
     if mask is not None and out_mask is None and create_out_mask:
         out_mask = torch.empty((x.shape[0], 1, out_h, out_w), dtype=torch.int32, device=x.device)
     desc = make_conv_desc(tuple(x.shape), c, (out_h, out_w), tuple(kernel_size), stride, padding, dilation, 1, _dtype(x))
@@ -239,6 +255,8 @@ def sparse_activation(x, prev_x, truncated, mask, threshold, activation, truncat
     """In-place accumulate + activation delta + truncation (reference: cuda_kernels.py:132-133)."""
     _check_feature(x, "x")
     _check_mask(mask, x, "mask")
+    _check_like(prev_x, x, "prev_x")
+    _check_like(truncated, x, "truncated")
     check(lib.dc_activate_truncate(x.data_ptr(), prev_x.data_ptr(), _ptr(truncated), mask.data_ptr(), _npix(x), x.shape[1],
                                    _dtype(x), float(threshold), max(int(activation), 0), int(truncation_mode), _stream()),
           "sparse_activation")
@@ -248,6 +266,8 @@ def sparsify(input, prev_in, delta, mask, threshold):
     """Input delta + update mask (reference: cuda_kernels.py:136-137)."""
     _check_feature(input, "input")
     _check_mask(mask, input, "mask")
+    _check_like(prev_in, input, "prev_in")
+    _check_like(delta, input, "delta")
     check(lib.dc_sparsify(input.data_ptr(), prev_in.data_ptr(), delta.data_ptr(), mask.data_ptr(), _npix(input),
                           input.shape[1], _dtype(input), float(threshold), _stream()), "sparsify")
 
@@ -255,6 +275,11 @@ def sparsify(input, prev_in, delta, mask, threshold):
 def sparsify_u8(frame_u8, scale, offset, prev_in, delta, mask, threshold):
     """``sparsify`` on an 8-bit N,H,W,C frame normalised per channel by ``scale``/``offset`` (float32)."""
     _check_feature(delta, "delta")
+    _check_like(prev_in, delta, "prev_in")
+    _check_mask(mask, delta, "mask")
+    if frame_u8.dtype != torch.uint8 or not frame_u8.is_contiguous() or \
+            tuple(frame_u8.shape) != (delta.shape[0], delta.shape[2], delta.shape[3], delta.shape[1]):
+        raise RuntimeError("deltacnn_b200.sparsify_u8: the frame must be a contiguous uint8 tensor of shape (N, H, W, C) matching delta")
     check(lib.dc_sparsify_u8(frame_u8.data_ptr(), scale.data_ptr(), offset.data_ptr(), prev_in.data_ptr(), delta.data_ptr(),
                              mask.data_ptr(), _npix(delta), delta.shape[1], _dtype(delta), float(threshold), _stream()),
           "sparsify_u8")
@@ -266,6 +291,11 @@ def sparse_add_tensors(a, b, prev_out, out, mask_a, mask_b, mask_out, weight_a, 
     _check_feature(b, "b")
     if a.shape != b.shape:
         raise RuntimeError("deltacnn_b200.sparse_add_tensors: shapes differ")
+    _check_like(prev_out, a, "prev_out")
+    _check_like(out, a, "out")
+    _check_mask(mask_a, a, "mask_a")
+    _check_mask(mask_b, a, "mask_b")
+    _check_mask(mask_out, a, "mask_out")
     check(lib.dc_add(a.data_ptr(), b.data_ptr(), _ptr(prev_out), out.data_ptr(), mask_a.data_ptr(), mask_b.data_ptr(),
                      _ptr(mask_out), float(weight_a), float(weight_b), _npix(a), a.shape[1], _dtype(a),
                      max(int(activation), 0), 1 if dense_out else 0, _stream()), "sparse_add_tensors")
@@ -274,6 +304,8 @@ def sparse_add_tensors(a, b, prev_out, out, mask_a, mask_b, mask_out, weight_a, 
 def sparse_add_to_dense_tensor(a, b, mask_a, activation=0):
     """b += a on the masked pixels of a (reference: cuda_kernels.py:144-145; the activation argument is unused there too)."""
     _check_feature(a, "a")
+    _check_like(b, a, "b")
+    _check_mask(mask_a, a, "mask_a")
     check(lib.dc_add_to_dense(a.data_ptr(), b.data_ptr(), mask_a.data_ptr(), _npix(a), a.shape[1], _dtype(a), _stream()),
           "sparse_add_to_dense_tensor")
 
@@ -323,8 +355,11 @@ def sparse_densify(delta, mask, prev_out, out=None, activation=0):
     """prev_out += delta on masked pixels; ``out`` (new tensor when None) = f(prev_out).
     One launch for the reference's accumulate + clone + activation (sparse_layers.py:1322-1329)."""
     _check_feature(delta, "delta")
+    _check_like(prev_out, delta, "prev_out")
+    _check_mask(mask, delta, "mask")
     if out is None:
         out = torch.empty_like(prev_out)
+    _check_like(out, delta, "out")
     check(lib.dc_densify(delta.data_ptr(), mask.data_ptr(), prev_out.data_ptr(), out.data_ptr(), _npix(delta), delta.shape[1],
                          _dtype(delta), max(int(activation), 0), _stream()), "sparse_densify")
     return out

@@ -287,15 +287,32 @@ class _DeltaConvMixin:
             self.out_shape = []
             self._out = self.out_mask = self._desc = self._workspace = None
 
+        if self._desc is None:
+            size_fn = K.deconv_out_hw if self._transposed else K.conv_out_hw
+            hw = size_fn(x.shape[2], x.shape[3], self.kernel_size, self.stride, self.padding, self.dilation)
+            self.out_shape = list(hw)
+            self._desc = K.make_conv_desc(tuple(x.shape), self.out_channels, hw, tuple(self.kernel_size), self.stride,
+                                          self.padding, self.dilation, self.groups, K._dtype(x))
+        out_dims = (x.shape[0], self.out_channels, self.out_shape[0], self.out_shape[1])
+
+        def check_cache(t, what):
+            # caches go to the kernel as raw pointers: a stale one must fail here, not on the device
+            if t is not None and (tuple(t.shape) != out_dims or t.dtype != x.dtype or t.device != x.device):
+                raise RuntimeError(f"deltacnn_b200: {what} of {self!r} has shape {tuple(t.shape)}, the output is {out_dims} "
+                                   "(call reset_layers() after a batch or resolution change)")
+
         epilogue = None
         act = self.activation_layer
         fuse = act is not None and self.fuse_activation and not act.first_iter and act.inplace and \
             act.truncation_mode == DCTruncation.max and self.frame_idx > 0
         if fuse:
+            check_cache(act.prev_out, "the activation cache")
+            check_cache(act.out_truncated, "the truncation cache")
             epilogue = K.make_epilogue(act.prev_out, act.out_truncated, DCThreshold.get(act), act.activation_int,
                                        act.truncation_mode.value)
         if residual is not None:
             res_delta, res_mask = residual
+            check_cache(res_delta, "the residual")
             if add_layer is not None and add_layer.activation is not None:
                 if add_layer.first_iter:              # what DCAdd.forward does on its first call
                     add_layer.first_iter = False
@@ -303,15 +320,10 @@ class _DeltaConvMixin:
                     add_layer.idx = DCAdd.idx
                     add_layer.prev_out = torch.zeros_like(res_delta)
                     DCModule.temp_buffers.append(add_layer.prev_out)
+                check_cache(add_layer.prev_out, "the add layer's cache")
                 epilogue = K.make_residual_epilogue(res_delta, res_mask, add_layer.prev_out, add_layer.activation_int)
             else:
                 epilogue = K.make_residual_epilogue(res_delta, res_mask)
-        if self._desc is None:
-            size_fn = K.deconv_out_hw if self._transposed else K.conv_out_hw
-            hw = size_fn(x.shape[2], x.shape[3], self.kernel_size, self.stride, self.padding, self.dilation)
-            self.out_shape = list(hw)
-            self._desc = K.make_conv_desc(tuple(x.shape), self.out_channels, hw, tuple(self.kernel_size), self.stride,
-                                          self.padding, self.dilation, self.groups, K._dtype(x))
         op = K.sparse_deconv if self._transposed else K.sparse_conv
         extra = {}
         if self._transposed:
@@ -558,9 +570,9 @@ class DCSparsify(DCModule):
                 return self.forward(self._u8_to_float(input))
             self.frame_idx += 1
             n, h, w, c = input.shape
-            if self.mask is None or self.mask.shape[0] != n:
+            if self.mask is None or tuple(self.mask.shape) != (n, 1, h, w):
                 self.mask = torch.empty((n, 1, h, w), dtype=torch.int, device=input.device)
-            if self._delta is None or self._delta.shape[0] != n or not DCConv2d.reuse_buffers:
+            if self._delta is None or self._delta.shape != self.prev_in.shape or not DCConv2d.reuse_buffers:
                 self._delta = torch.empty_like(self.prev_in)
             scale, offset, _ = self._u8
             K.sparsify_u8(input, scale, offset, self.prev_in, self._delta, self.mask, DCThreshold.get(self))

@@ -203,16 +203,29 @@ def max_pool(x, mask, prev_in, kernel, stride, padding, dilation=(1, 1)):
     """Delta max-pool: out = max(prev + x*mask) - max(prev) over in-bounds window
     elements, fp32 math; out-mask = OR over the window. Does NOT update prev_in (the
     module does that with add_to_dense afterwards, sparse_layers.py:1466-1468).
-    src/cuda/other_nn_layers.cu:2390-2459. Symmetric padding only."""
-    assert len(padding) == 2
+    src/cuda/other_nn_layers.cu:2390-2459.
+
+    Padding is a 2-tuple or (top, bottom, left, right). Out-of-bounds window elements are
+    ignored, with the reference's one exception (:2402-2422, "same behaviour as when first
+    applying padding and then pooling"): a literal 0 joins the window for rows inside the
+    bottom padding when top != bottom padding, and for columns inside the right padding
+    (of rows inside the image) when left != right padding."""
+    pt, pb, pl, pr = _pad4(padding)
     xm = x.float() * (mask != 0).float()
     p = prev_in.float()
     neg = -1e30
-    pad = (padding[1], padding[1], padding[0], padding[0])
-    acc = F.pad(p + xm, pad, value=neg)
-    prv = F.pad(p, pad, value=neg)
-    o = F.max_pool2d(acc, tuple(kernel), tuple(stride), 0, tuple(dilation)) - \
-        F.max_pool2d(prv, tuple(kernel), tuple(stride), 0, tuple(dilation))
+    h, w = x.shape[2], x.shape[3]
+
+    def padded(t):
+        t = F.pad(t, (pl, pr, pt, pb), value=neg)
+        if pl != pr and pr > 0:
+            t[:, :, pt:pt + h, pl + w:] = 0.0
+        if pt != pb and pb > 0:
+            t[:, :, pt + h:, :] = 0.0
+        return t
+
+    o = F.max_pool2d(padded(p + xm), tuple(kernel), tuple(stride), 0, tuple(dilation)) - \
+        F.max_pool2d(padded(p), tuple(kernel), tuple(stride), 0, tuple(dilation))
     om = dilate_mask(mask, kernel, stride, padding, dilation)
     return o.to(x.dtype).contiguous(memory_format=torch.channels_last), om
 
