@@ -63,6 +63,10 @@ _SIGNATURES = {
     "dc_concat": (c_int, [_P, _P, _P, _P, _P, _P, c_i64, c_int, c_int, c_int, _P]),
     "dc_densify": (c_int, [_P, _P, _P, _P, c_i64, c_int, c_int, c_int, _P]),
     "dc_compact_mask": (c_int, [_P, c_i64, _P, _P, _P]),
+    "dc_sparsify_dilated": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P]),
+    "dc_linear_delta": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
+    "dc_heatmap_argmax": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
+    "dc_centernet_decode": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, _P]),
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 

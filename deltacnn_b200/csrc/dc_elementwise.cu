@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(256) k_sparsify_c3(const T* __restrict__ x, T*
     }
 }
 
-// 8-bit frame: value = u8 * scale[c] + offset[c], rounded to T before the compare.
+// 8-bit frame: value = u8 * scale[c] + offset[c] (a rounded product, then a rounded sum: the arithmetic of
+// frame.float() * scale + offset in torch), rounded to T before the compare.
 template <typename T>
 __global__ void __launch_bounds__(256) k_sparsify_u8(const uint8_t* __restrict__ x, const float* __restrict__ scale,
                                                      const float* __restrict__ offset, T* __restrict__ prev,
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(256) k_sparsify_u8(const uint8_t* __restrict__
         bool hit = false;
         if (inb) {
             for (int c = lig; c < C; c += g) {
-                float v = rnd<T>(fmaf((float)x[off + c], scale[c], offset[c]));
+                float v = rnd<T>(__fadd_rn(__fmul_rn((float)x[off + c], scale[c]), offset[c]));
                 hit |= fabsf(rnd<T>(v - to_f<T>(prev[off + c]))) > thr;
             }
         }
@@ -129,13 +130,69 @@ __global__ void __launch_bounds__(256) k_sparsify_u8(const uint8_t* __restrict__
             if (lig == 0) mask[px] = active ? 1 : 0;
             if (active) {
                 for (int c = lig; c < C; c += g) {
-                    float v = rnd<T>(fmaf((float)x[off + c], scale[c], offset[c]));
+                    float v = rnd<T>(__fadd_rn(__fmul_rn((float)x[off + c], scale[c]), offset[c]));
                     delta[off + c] = from_f<T>(v - to_f<T>(prev[off + c]));
                     prev[off + c] = from_f<T>(v);
                 }
             }
         }
     }
+}
+
+// Noise-robust input mask, DCSparsify(dilation = k) (reference: src/deltacnn/sparse_layers.py:1233-1248, torch ops
+// there): delta = x - prev at EVERY pixel, mask = max-pool_{k x k, stride 1}(max_c |delta|) > threshold, and the cache
+// takes the new frame where the mask is set. max-pool(v) > t holds exactly when some element of the window has
+// v > t, so step 1 writes one hit flag per pixel and step 2 ORs the flags over the window (rows, then columns, in
+// shared memory) and updates the cache. Two kernels, because step 2 of a pixel needs step 1 of its neighbours
+// against the OLD cache.
+template <typename T>
+__global__ void __launch_bounds__(256) k_sparsify_hit(const T* __restrict__ x, const T* __restrict__ prev, T* __restrict__ delta,
+                                                      uint8_t* __restrict__ hit, int64_t npix, int C, float thr) {
+    grid_dep_launch();
+    grid_dep_wait();
+    for (int64_t px = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; px < npix; px += (int64_t)gridDim.x * blockDim.x) {
+        bool h = false;
+        for (int c = 0; c < C; ++c) {
+            const float d = rnd<T>(to_f<T>(x[px * C + c]) - to_f<T>(prev[px * C + c]));
+            delta[px * C + c] = from_f<T>(d);
+            h |= fabsf(d) > thr;
+        }
+        hit[px] = h ? 1 : 0;
+    }
+}
+
+constexpr int kDilTileW = 32, kDilTileH = 8, kDilMaxR = 16;
+template <typename T>
+__global__ void __launch_bounds__(256) k_sparsify_dilate(const T* __restrict__ x, T* __restrict__ prev, const uint8_t* __restrict__ hit,
+                                                         int32_t* __restrict__ mask, int h, int w, int C, int r) {
+    __shared__ uint8_t s_hit[(kDilTileH + 2 * kDilMaxR) * (kDilTileW + 2 * kDilMaxR)];
+    __shared__ uint8_t s_row[(kDilTileH + 2 * kDilMaxR) * kDilTileW];
+    grid_dep_launch();
+    grid_dep_wait();
+    const int x0 = blockIdx.x * kDilTileW, y0 = blockIdx.y * kDilTileH;
+    const int64_t b = blockIdx.z;
+    const int rw = kDilTileW + 2 * r, rh = kDilTileH + 2 * r;
+    for (int i = threadIdx.x; i < rw * rh; i += 256) {
+        const int yy = y0 - r + i / rw, xx = x0 - r + i % rw;
+        s_hit[i] = (yy >= 0 && yy < h && xx >= 0 && xx < w) ? hit[(b * h + yy) * w + xx] : 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rh * kDilTileW; i += 256) {      // OR along the row
+        const int ry = i / kDilTileW, cx = i % kDilTileW;
+        uint8_t v = 0;
+        for (int d = 0; d <= 2 * r; ++d) v |= s_hit[ry * rw + cx + d];
+        s_row[i] = v;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x % kDilTileW, ty = threadIdx.x / kDilTileW;
+    const int ox = x0 + tx, oy = y0 + ty;
+    if (ox >= w || oy >= h) return;
+    uint8_t v = 0;
+    for (int d = 0; d <= 2 * r; ++d) v |= s_row[(ty + d) * kDilTileW + tx];
+    const int64_t px = (b * h + oy) * w + ox;
+    mask[px] = v ? 1 : 0;
+    if (v)
+        for (int c = 0; c < C; ++c) prev[px * C + c] = x[px * C + c];
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -583,6 +640,33 @@ int dc_sparsify_u8(const uint8_t* x_u8, const float* scale, const float* offset,
         launch_pdl(k_sparsify_u8<__half>, pixel_grid(npix, g), dim3(256), 0, st, x_u8, scale, offset, (__half*)prev_in, (__half*)delta, mask, npix, channels, g, host_round_threshold<__half>(threshold));
     else return DC_ERR_DTYPE;
     return check_launch();
+}
+
+int dc_sparsify_dilated(const void* x, void* prev_in, void* delta, int32_t* mask, uint8_t* hit_scratch, int32_t n, int32_t h,
+                        int32_t w, int32_t channels, int32_t dtype, float threshold, int32_t dilation, void* stream) {
+    if (n < 0 || h <= 0 || w <= 0 || channels <= 0) return DC_ERR_SHAPE;
+    if (dilation < 1 || dilation % 2 == 0 || (dilation - 1) / 2 > kDilMaxR) return DC_ERR_UNSUPPORTED;   // odd windows up to 33
+    if (n == 0) return DC_OK;
+    DC_REQUIRE(x); DC_REQUIRE(prev_in); DC_REQUIRE(delta); DC_REQUIRE(mask); DC_REQUIRE(hit_scratch);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t npix = (int64_t)n * h * w;
+    int64_t blocks = divup64(npix, 256);
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    const dim3 tiles((unsigned)divup(w, kDilTileW), (unsigned)divup(h, kDilTileH), (unsigned)n);
+    const int r = (dilation - 1) / 2;
+    int rc;
+    if (dtype == DC_F32) {
+        rc = launch_pdl(k_sparsify_hit<float>, dim3((unsigned)blocks), dim3(256), 0, st, (const float*)x, (const float*)prev_in, (float*)delta, hit_scratch, npix, channels, threshold);
+        if (rc != DC_OK) return rc;
+        return launch_pdl(k_sparsify_dilate<float>, tiles, dim3(256), 0, st, (const float*)x, (float*)prev_in, (const uint8_t*)hit_scratch, mask, h, w, channels, r);
+    }
+    if (dtype == DC_F16) {
+        rc = launch_pdl(k_sparsify_hit<__half>, dim3((unsigned)blocks), dim3(256), 0, st, (const __half*)x, (const __half*)prev_in, (__half*)delta, hit_scratch, npix, channels, host_round_threshold<__half>(threshold));
+        if (rc != DC_OK) return rc;
+        return launch_pdl(k_sparsify_dilate<__half>, tiles, dim3(256), 0, st, (const __half*)x, (__half*)prev_in, (const uint8_t*)hit_scratch, mask, h, w, channels, r);
+    }
+    return DC_ERR_DTYPE;
 }
 
 int dc_activate_truncate(void* delta, void* prev_out, void* truncated, int32_t* mask, int64_t npix, int32_t channels,

@@ -365,6 +365,81 @@ def sparse_densify(delta, mask, prev_out, out=None, activation=0):
     return out
 
 
+def sparsify_dilated(input, prev_in, delta, mask, hit_scratch, threshold, dilation):
+    """``DCSparsify(dilation=k)``: dense difference, k x k window OR of the per-pixel threshold test, cache update
+    where the mask is set (reference: sparse_layers.py:1233-1248, torch ops there). ``hit_scratch``: uint8, one
+    byte per pixel."""
+    _check_feature(input, "input")
+    _check_mask(mask, input, "mask")
+    _check_like(prev_in, input, "prev_in")
+    _check_like(delta, input, "delta")
+    if hit_scratch.dtype != torch.uint8 or hit_scratch.numel() < _npix(input) or hit_scratch.device != input.device:
+        raise RuntimeError("deltacnn_b200.sparsify_dilated: hit_scratch must hold one byte per pixel on the input's device")
+    n, c, h, w = input.shape
+    check(lib.dc_sparsify_dilated(input.data_ptr(), prev_in.data_ptr(), delta.data_ptr(), mask.data_ptr(), hit_scratch.data_ptr(),
+                                  n, h, w, c, _dtype(input), float(threshold), int(dilation), _stream()), "sparsify_dilated")
+
+
+def linear_delta(delta, mask, weight, bias, acc, out, first_frame):
+    """Fully connected layer in delta form: ``acc += delta @ weight.T`` (+ bias on the first frame) for the streams
+    whose mask is set, ``out = acc`` in the feature dtype. ``delta``: (N, C) or (N, C, 1, 1); ``mask``: one int32 per
+    stream; ``acc``: (N, out) float32 state. No reference counterpart (it replaces densify + nn.Linear,
+    example/mobilenet_deltacnn.py:216-227)."""
+    if not delta.is_cuda:
+        raise RuntimeError("deltacnn_b200: delta must be a CUDA tensor (there is no CPU path)")
+    n, c_in = delta.shape[0], delta.shape[1]
+    c_out = weight.shape[0]
+    if delta.numel() != n * c_in or tuple(weight.shape) != (c_out, c_in) or not weight.is_contiguous() or weight.dtype != delta.dtype:
+        raise RuntimeError("deltacnn_b200.linear_delta: delta must be (N, C[, 1, 1]) and weight a contiguous (out, C) tensor of the same dtype")
+    if acc.dtype != torch.float32 or tuple(acc.shape) != (n, c_out) or tuple(out.shape) != (n, c_out) or out.dtype != delta.dtype:
+        raise RuntimeError("deltacnn_b200.linear_delta: acc must be float32 (N, out) and out (N, out) in the feature dtype")
+    if mask is not None and (mask.dtype != torch.int32 or mask.numel() != n):
+        raise RuntimeError("deltacnn_b200.linear_delta: mask must hold one int32 per stream")
+    check(lib.dc_linear_delta(delta.data_ptr(), _ptr(mask), weight.data_ptr(), _ptr(bias), acc.data_ptr(), out.data_ptr(),
+                              n, c_in, c_out, _dtype(delta), 1 if first_frame else 0, _stream()), "linear_delta")
+    return out
+
+
+def heatmap_argmax(heat, mask, out=None):
+    """(x, y, value) of the largest element of every heat map of a dense (N, J, H, W) channels-last tensor; streams
+    whose mask is empty keep their rows of ``out``. Returns a float32 (N, J, 3) tensor."""
+    _check_feature(heat, "heat")
+    _check_mask(mask, heat, "mask")
+    n, j, h, w = heat.shape
+    if out is None:
+        if mask is not None:
+            raise RuntimeError("deltacnn_b200.heatmap_argmax: the first call (no previous result) must not pass a mask")
+        out = torch.empty((n, j, 3), dtype=torch.float32, device=heat.device)
+    check(lib.dc_heatmap_argmax(heat.data_ptr(), _ptr(mask), out.data_ptr(), n, h, w, j, _dtype(heat), _stream()), "heatmap_argmax")
+    return out
+
+
+def centernet_decode(heat, wh, offset, mask, state=None, topk=100, min_score=0.0, stride=4.0, apply_sigmoid=False):
+    """CenterNet decode of dense head outputs on the device: 3x3 peak test, top-k, boxes. ``state`` is the tuple
+    (peaks, det, count) returned by the previous call (None on the first frame, where ``mask`` must be None);
+    returns (det (N, topk, 6) float32, count (N,) int32, state)."""
+    _check_feature(heat, "heat")
+    _check_feature(wh, "wh")
+    _check_feature(offset, "offset")
+    _check_mask(mask, heat, "mask")
+    n, classes, h, w = heat.shape
+    if tuple(wh.shape) != (n, 2, h, w) or tuple(offset.shape) != (n, 2, h, w) or wh.dtype != heat.dtype or offset.dtype != heat.dtype:
+        raise RuntimeError("deltacnn_b200.centernet_decode: wh and offset must be (N, 2, H, W) tensors of the heat map's dtype")
+    if state is None:
+        if mask is not None:
+            raise RuntimeError("deltacnn_b200.centernet_decode: the first call (no state) must not pass a mask")
+        state = (torch.empty((n, h, w, classes), dtype=torch.float32, device=heat.device),
+                 torch.empty((n, topk, 6), dtype=torch.float32, device=heat.device),
+                 torch.empty((n,), dtype=torch.int32, device=heat.device))
+    peaks, det, count = state
+    if tuple(det.shape) != (n, topk, 6) or peaks.numel() != n * h * w * classes:
+        raise RuntimeError("deltacnn_b200.centernet_decode: state does not match the input (call reset_layers())")
+    check(lib.dc_centernet_decode(heat.data_ptr(), wh.data_ptr(), offset.data_ptr(), _ptr(mask), peaks.data_ptr(), det.data_ptr(),
+                                  count.data_ptr(), n, h, w, classes, int(topk), float(min_score), float(stride),
+                                  1 if apply_sigmoid else 0, _dtype(heat), _stream()), "centernet_decode")
+    return det, count, state
+
+
 def compact_mask(mask, indices=None, count=None):
     """Indices of the active pixels of ``mask`` (order unspecified) and their number, on the device."""
     n = mask.numel()
@@ -377,22 +452,31 @@ def compact_mask(mask, indices=None, count=None):
 
 
 class DCPerformanceMetrics:
-    """Host-side accounting of one frame (reference: cuda_kernels.py:188-245 reads device counters
-    that are compiled out by default, src/cuda/common.cuh:37). Filled by ``DCPerformanceMetricsManager``
-    from the masks the layers produced."""
+    """Work accounting of the delta path over one or more frames, with the fields and ratios of the reference's
+    class (src/deltacnn/cuda_kernels.py:188-245). The reference fills it from device counters that its kernels
+    increment with atomics when built with ENABLE_METRICS (src/cuda/common.cuh:37-65, off by default); here the
+    same quantities are computed from the layers' masks by ``DCPerformanceMetricsManager`` (no atomics in the
+    kernels). Counts are per frame (totals divided by ``n_frames``); "flops" count multiply-accumulates, "mem" counts
+    tensor elements, as in the reference."""
 
-    def __init__(self, tiles, inputs, flops, memtransfer, n_frames=1):
+    def __init__(self, tiles, inputs, mode, flops, memtransfer, histogram, n_frames=1):
         n_frames = max(n_frames, 1)
-        self.tiles_active, self.tiles_total = tiles[0] // n_frames, tiles[1] // n_frames
+        val = lambda v: int(v) // n_frames
+        self.tiles_active, self.tiles_total = val(tiles[0]), val(tiles[1])
         self.tiles_ratio = self.tiles_active / max(self.tiles_total, 1)
-        self.inputs_active, self.inputs_total = inputs[0] // n_frames, inputs[1] // n_frames
+        self.inputs_active, self.inputs_total = val(inputs[0]), val(inputs[1])
         self.inputs_ratio = self.inputs_active / max(self.inputs_total, 1)
-        self.flops_actual, self.flops_theoretical, self.flops_dense = (f // n_frames for f in flops)
+        self.mode_sparse, self.mode_dense = val(mode[0]), val(mode[1])
+        self.mode_ratio = self.mode_sparse / max(self.mode_sparse + self.mode_dense, 1)
+        self.flops_actual, self.flops_theoretical, self.flops_dense = (val(f) for f in flops)
         self.flops_ratio_actual = self.flops_actual / max(self.flops_dense, 1)
         self.flops_ratio_theoretical = self.flops_theoretical / max(self.flops_dense, 1)
-        self.mem_read_actual, self.mem_read_dense, self.mem_write_actual, self.mem_write_dense = (m // n_frames for m in memtransfer)
+        self.mem_read_actual, self.mem_read_dense, self.mem_write_actual, self.mem_write_dense = (val(m) for m in memtransfer)
         self.mem_read_ratio = self.mem_read_actual / max(self.mem_read_dense, 1)
         self.mem_write_ratio = self.mem_write_actual / max(self.mem_write_dense, 1)
+        self.histogram = [int(h) // n_frames for h in histogram]
+        active = max(sum(int(h) for h in histogram[1:]), 1)
+        self.histogram_ratio = [int(h) / active for h in histogram]
 
     def to_dict(self):
         return dict(self.__dict__)
@@ -404,9 +488,27 @@ class DCPerformanceMetrics:
 
 
 class DCPerformanceMetricsManager:
-    """Collects per-layer work records appended by the layers while ``enabled`` is True."""
+    """Collects the counters of ``DCPerformanceMetrics`` while ``enabled`` is True (the reference's switch is the
+    compile-time ENABLE_METRICS). Every delta convolution and every truncation layer adds its frame's work through
+    ``add_conv`` / ``add_activation``; the sums stay on the device as int64 until ``get_metrics()`` reads them, so
+    collecting does not synchronise the stream.
+
+    Definitions, restated from the reference's counters (src/cuda/conv_kernel.cu:90-107, 196-217, 319-332;
+    src/cuda/other_nn_layers.cu:808-813), with an 8x8 output tile for every layer (the reference's tile size varies
+    with its kernel heuristics):
+      tiles     every tile / tiles with an active input pixel in their receptive field
+      inputs    receptive-field pixels of every tile / the active ones among them
+      histogram tiles by number of active input pixels (128 bins, the last holds 127 and more)
+      flops     actual: kernel MACs of every output pixel of an active tile (depthwise: of its active taps);
+                theoretical: active taps x Cin x Cout / groups of every updated output pixel; dense: all pixels
+      mem       read: active inputs x Cin + the filter, per active tile; written: Cout per updated output pixel;
+                dense: all inputs / outputs; truncation layers add 2 C read and 2 C written per masked pixel
+      mode      tiles handled with / without sub-tile sparsity (the reference's 3x3 kernel switches per tile; every
+                tile of this library's kernels gathers only active pixels, so all active tiles count as sparse)."""
     enabled = False
-    records = []
+    tile = 8
+    _acc = None            # int64 device tensor: 13 counters followed by the 128 histogram bins
+    N_BINS = 128
 
     @classmethod
     def init(cls):
@@ -414,17 +516,78 @@ class DCPerformanceMetricsManager:
 
     @classmethod
     def reset(cls):
-        cls.records = []
+        cls._acc = None
 
     @classmethod
-    def add(cls, record):
-        cls.records.append(record)
+    def _accumulate(cls, device, scalars, hist=None):
+        if cls._acc is None or cls._acc.device != device:
+            cls._acc = torch.zeros(13 + cls.N_BINS, dtype=torch.int64, device=device)
+        cls._acc[:13] += torch.stack([torch.as_tensor(v, dtype=torch.int64, device=device) for v in scalars])
+        if hist is not None:
+            cls._acc[13:] += hist
+
+    @classmethod
+    def add_conv(cls, mask_in, c_in, c_out, kernel, stride, padding, dilation, groups, out_hw, transposed=False):
+        """Account one delta convolution call from its in-mask (N,1,H,W int32) and geometry."""
+        if not cls.enabled or transposed:
+            return
+        import torch.nn.functional as F
+        t = cls.tile
+        n, _, h, w = mask_in.shape
+        ho, wo = out_hw
+        kh, kw = kernel
+        pt, pb, pl, pr = _pad4(padding)
+        m = (mask_in != 0).float()
+        # receptive field of a t x t tile of outputs; pad so that every (also partial) tile has a full window
+        rh, rw = (t - 1) * stride[0] + (kh - 1) * dilation[0] + 1, (t - 1) * stride[1] + (kw - 1) * dilation[1] + 1
+        ty, tx = -(-ho // t), -(-wo // t)
+        need_h, need_w = (ty - 1) * t * stride[0] + rh, (tx - 1) * t * stride[1] + rw
+        mp = F.pad(m, (pl, max(need_w - w - pl, 0), pt, max(need_h - h - pt, 0)))[:, :, :need_h, :need_w]
+        dens = F.avg_pool2d(mp, (rh, rw), stride=(t * stride[0], t * stride[1]), divisor_override=1)
+        dens = dens.round().long()                                   # (N,1,ty,tx) active inputs per tile
+        active_tile = dens > 0
+        # per output pixel: number of active taps (in-bounds) and the updated flag
+        ones = torch.ones(1, 1, kh, kw, device=m.device)
+        taps = F.conv2d(F.pad(m, (pl, pr, pt, pb)), ones, None, stride, 0, dilation).round().long()[:, :, :ho, :wo]
+        updated = taps > 0
+        tile_of = active_tile.repeat_interleave(t, 2).repeat_interleave(t, 3)[:, :, :ho, :wo]
+        per_px = kh * kw * c_in * c_out // groups
+        cig = c_in * c_out // groups                                 # MACs per active tap
+        n_tiles = n * ty * tx
+        if groups == 1:
+            flops_actual = tile_of.sum() * per_px
+        else:
+            flops_actual = (taps * tile_of).sum() * cig
+        filt = kh * kw * c_in * c_out // groups
+        scalars = [
+            active_tile.sum(), n_tiles, dens.sum(), n_tiles * rh * rw,
+            active_tile.sum(), 0,
+            flops_actual, taps.sum() * cig, n * ho * wo * per_px,
+            dens.sum() * c_in + active_tile.sum() * filt, n_tiles * (rh * rw * c_in + filt),
+            updated.sum() * c_out, n * ho * wo * c_out,
+        ]
+        hist = torch.bincount(dens.clamp(max=cls.N_BINS - 1).flatten(), minlength=cls.N_BINS)
+        cls._accumulate(mask_in.device, scalars, hist)
+
+    @classmethod
+    def add_activation(cls, mask_in, channels, truncation_mode=0, mask_kept=None):
+        """Account one truncation layer call: 2 C (3 C for norm/rms) elements read per masked pixel; 2 C written
+        (3 C where a norm/rms pixel stays active)."""
+        if not cls.enabled:
+            return
+        m_in = (mask_in != 0).sum()
+        read = (2 if truncation_mode == 0 else 3) * channels * m_in
+        if truncation_mode == 0 or mask_kept is None:
+            written = 2 * channels * m_in
+        else:
+            written = channels * (2 * m_in + (mask_kept != 0).sum())
+        zero = 0
+        cls._accumulate(mask_in.device, [zero, zero, zero, zero, zero, zero, zero, zero, zero, read, read, written, written])
 
     @classmethod
     def get_metrics(cls, n_frames=1):
-        tiles, inputs, flops, mem = [0, 0], [0, 0], [0, 0, 0], [0, 0, 0, 0]
-        for r in cls.records:
-            for acc, key in ((tiles, "tiles"), (inputs, "inputs"), (flops, "flops"), (mem, "mem")):
-                for i, v in enumerate(r.get(key, ())):
-                    acc[i] += int(v)
-        return DCPerformanceMetrics(tiles, inputs, flops, mem, n_frames=n_frames)
+        if cls._acc is None:
+            vals = [0] * (13 + cls.N_BINS)
+        else:
+            vals = cls._acc.cpu().tolist()
+        return DCPerformanceMetrics(vals[0:2], vals[2:4], vals[4:6], vals[6:9], vals[9:13], vals[13:], n_frames=n_frames)

@@ -305,6 +305,12 @@ class _DeltaConvMixin:
         act = self.activation_layer
         fuse = act is not None and self.fuse_activation and not act.first_iter and act.inplace and \
             act.truncation_mode == DCTruncation.max and self.frame_idx > 0
+        if K.DCPerformanceMetricsManager.enabled:
+            # work accounting: the truncation layer runs (and counts) on its own; same results as the fused epilogue
+            fuse = False
+            K.DCPerformanceMetricsManager.add_conv(mask, self.in_channels, self.out_channels, tuple(self.kernel_size), tuple(self.stride),
+                                                   self.padding, tuple(self.dilation), self.groups, tuple(self.out_shape),
+                                                   transposed=self._transposed)
         if fuse:
             check_cache(act.prev_out, "the activation cache")
             check_cache(act.out_truncated, "the truncation cache")
@@ -542,6 +548,7 @@ class DCSparsify(DCModule):
         self.frame_idx = -1
         self.mask = None
         self._delta = None
+        self._hit = None
         self._u8 = None
 
     def set_u8_input(self, scale=1.0 / 255.0, offset=0.0, dtype=torch.float16, channels=3):
@@ -594,15 +601,18 @@ class DCSparsify(DCModule):
             return input, mask
 
         threshold = DCThreshold.get(self)
+        if self.mask is not None and (self.mask.shape[0] != input.shape[0] or self.mask.shape[2:] != input.shape[2:]):
+            self.mask = None
         if self.dilation > 1:
-            # noise-robust variant: the mask is the max-pooled |delta| (reference :1233-1244), torch ops
-            x = input - self.prev_in
-            mask = torch.max(torch.abs(x), dim=1, keepdim=True)[0]
-            k = self.dilation
-            mask = torch.max_pool2d(mask, (k, k), stride=(1, 1), padding=((k - 1) // 2, (k - 1) // 2)) > threshold
-            tiled = mask.expand_as(x)
-            self.prev_in[tiled] = input[tiled]
-            return x, mask.int()
+            # noise-robust variant: the mask is the max-pooled |delta| > threshold (reference :1233-1248), two kernels here
+            if self.mask is None:
+                self.mask = torch.empty_like(input[:, :1], dtype=torch.int)
+            if self._delta is None or self._delta.shape != input.shape or not DCConv2d.reuse_buffers:
+                self._delta = torch.empty_like(input)
+            if self._hit is None or self._hit.numel() != self.mask.numel():
+                self._hit = torch.empty(self.mask.numel(), dtype=torch.uint8, device=input.device)
+            K.sparsify_dilated(input, self.prev_in, self._delta, self.mask, self._hit, threshold, self.dilation)
+            return self._delta, self.mask
 
         if self.mask is None or self.mask.shape[0] != input.shape[0] or self.mask.shape[2:] != input.shape[2:]:
             self.mask = torch.empty_like(input[:, :1], dtype=torch.int)
@@ -619,6 +629,7 @@ class DCSparsify(DCModule):
         self.prev_out = None
         self.mask = None
         self._delta = None
+        self._hit = None
         DCSparsify.idx = -1
 
 
@@ -724,7 +735,10 @@ class DCActivation(DCModule):
         if not self.inplace:
             val = val.clone()
             mask = mask.clone()
+        mask_before = mask.clone() if K.DCPerformanceMetricsManager.enabled else None
         K.sparse_activation(val, self.prev_out, self.out_truncated, mask, threshold, self.activation_int, self.truncation_mode.value)
+        if mask_before is not None:
+            K.DCPerformanceMetricsManager.add_activation(mask_before, val.shape[1], self.truncation_mode.value, mask)
         return val, mask
 
     def reset(self):
@@ -851,3 +865,110 @@ class DCBatchNorm2d(nn.BatchNorm2d, DCModule):
     def reset(self):
         DCModule.reset(self)
         self.first_iter = True
+
+
+class DCLinear(nn.Linear, DCModule):
+    """Fully connected head that consumes the (delta, mask) of a pooled 1x1 feature directly: the logits are a
+    running fp32 sum updated by ``weight @ delta`` for the streams whose mask is set, so the dense feature vector
+    is never formed. No reference counterpart: it replaces ``DCDensify`` + ``nn.Linear`` at the end of the
+    reference's example network (example/mobilenet_deltacnn.py:216-227), which is valid because a linear layer
+    commutes with the accumulation over frames. A dense tensor input goes through ``nn.Linear`` unchanged."""
+
+    def __init__(self, in_features, out_features, bias=True):
+        super().__init__(in_features, out_features, bias)
+        self.acc = None
+        self._out = None
+
+    def forward(self, input):
+        if type(input) == Tensor:
+            return super().forward(input.reshape(input.shape[0], -1))
+        delta, mask = input
+        n = delta.shape[0]
+        if delta.shape[2] != 1 or delta.shape[3] != 1:
+            raise RuntimeError("DCLinear takes the (delta, mask) of a 1x1 feature (put it behind DCAdaptiveAveragePooling)")
+        first = self.acc is None
+        if first:
+            self.acc = torch.zeros((n, self.out_features), dtype=torch.float32, device=delta.device)
+            DCModule.temp_buffers.append(self.acc)
+        elif self.acc.shape[0] != n:
+            raise RuntimeError("DCLinear: the batch size changed (call reset_layers())")
+        if self._out is None or self._out.shape[0] != n or self._out.dtype != delta.dtype or not DCConv2d.reuse_buffers:
+            self._out = torch.empty((n, self.out_features), dtype=delta.dtype, device=delta.device)
+        return K.linear_delta(delta, mask, self.weight, self.bias, self.acc, self._out, first)
+
+    def reset(self):
+        DCModule.reset(self)
+        self.acc = None
+        self._out = None
+
+
+class DCHeatmapArgmax(DCModule):
+    """Pose head tail on the device: accumulates the heat-map delta (as ``DCDensify``) and returns, per stream and
+    joint, (x, y, value) of the largest heat-map element as a float32 (N, J, 3) tensor; streams without an updated
+    pixel keep their previous result. ``heatmaps`` holds the dense accumulated maps. No reference counterpart (the
+    reference returns the densified maps to torch code, src/deltacnn/sparse_layers.py:1322-1329)."""
+
+    def __init__(self, activation=None, name=""):
+        super().__init__()
+        self.name = name
+        self.densify = DCDensify(activation=activation)
+        self.heatmaps = None
+        self._out = None
+
+    def forward(self, input):
+        if type(input) == Tensor:
+            self.heatmaps = input
+            return K.heatmap_argmax(input.contiguous(memory_format=torch.channels_last), None)
+        _, mask = input
+        first = self._out is None
+        self.heatmaps = self.densify(input)
+        self._out = K.heatmap_argmax(self.heatmaps, None if first else mask, self._out)
+        return self._out
+
+    def reset(self):
+        super().reset()
+        self.heatmaps = None
+        self._out = None
+
+
+class DCCenterNetDecode(DCModule):
+    """Detector tail on the device: accumulates the three head deltas (heat map, size, offset; as ``DCDensify``)
+    and decodes boxes there: a peak is an element equal to the maximum of its 3x3 neighbourhood, the ``topk`` best
+    peaks above ``min_score`` become rows (x1, y1, x2, y2, score, class). Only pixels next to an updated pixel of any
+    head are re-examined; streams without an update keep their boxes. Returns (det (N, topk, 6) float32,
+    count (N,) int32). No reference counterpart (src/deltacnn/sparse_layers.py:1322-1329 returns dense maps)."""
+
+    def __init__(self, topk=100, min_score=0.0, stride=4.0, apply_sigmoid=True, name=""):
+        super().__init__()
+        self.name = name
+        self.topk, self.min_score, self.stride, self.apply_sigmoid = topk, min_score, stride, apply_sigmoid
+        self.densify = nn.ModuleList([DCDensify(), DCDensify(), DCDensify()])
+        self.dense = None
+        self._state = None
+        self._union = None
+
+    def forward(self, heat, wh, offset):
+        ins = (heat, wh, offset)
+        if type(heat) == Tensor:
+            self.dense = tuple(t.contiguous(memory_format=torch.channels_last) for t in ins)
+            det, count, _ = K.centernet_decode(*self.dense, None, None, self.topk, self.min_score, self.stride, self.apply_sigmoid)
+            return det, count
+        first = self._state is None
+        masks = [m for _, m in ins]
+        self.dense = tuple(d(x) for d, x in zip(self.densify, ins))
+        mask = None
+        if not first:
+            if self._union is None or self._union.shape != masks[0].shape:
+                self._union = torch.empty_like(masks[0])
+            torch.bitwise_or(masks[0], masks[1], out=self._union)
+            torch.bitwise_or(self._union, masks[2], out=self._union)
+            mask = self._union
+        det, count, self._state = K.centernet_decode(*self.dense, mask, self._state, self.topk, self.min_score, self.stride,
+                                                     self.apply_sigmoid)
+        return det, count
+
+    def reset(self):
+        super().reset()
+        self.dense = None
+        self._state = None
+        self._union = None

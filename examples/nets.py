@@ -12,14 +12,15 @@ statistics from frames of the synthetic video (so that randomly initialised netw
 unit-scale activations at every depth) and folds them into the convolution weights and a bias.
 The delta network is then built with folded convolutions (bias=True, fused activation) and loads
 the folded state dict.
+
+This module itself never imports the CUDA library: the delta factory lives in ``nets_delta`` and is imported
+by ``build_pair`` only when a delta model is asked for, so dense baselines can be built without loading it.
 """
 import torch
 import torch.nn as nn
 
-from deltacnn_b200 import (DCActivation, DCAdaptiveAveragePooling, DCAdd, DCConv2d, DCConvTranspose2d, DCDensify,
-                           DCMaxPooling, DCModule, DCSparsify, DCUpsamplingNearest2d)
-
 _ACTS = {None: nn.Identity, "relu": nn.ReLU, "relu6": nn.ReLU6}
+DELTA_HEADS = True      # delta networks end in DCLinear on the pooled delta instead of DCDensify + a dense linear layer
 
 
 class DenseConv(nn.Module):
@@ -51,20 +52,6 @@ class DenseConv(nn.Module):
         self.bn = None
 
 
-class DeltaConv(DCModule):
-    """Folded delta convolution with fused activation; parameter names match DenseConv."""
-
-    def __init__(self, cin, cout, k, stride=1, padding=0, groups=1, act=None, transposed=False):
-        super().__init__()
-        if transposed:
-            self.conv = DCConvTranspose2d(cin, cout, k, stride, padding, bias=True, activation=act)
-        else:
-            self.conv = DCConv2d(cin, cout, k, stride, padding, groups=groups, bias=True, activation=act)
-
-    def forward(self, x):
-        return self.conv(x)
-
-
 class _DenseAdd(nn.Module):
     def __init__(self, act=None):
         super().__init__()
@@ -76,6 +63,7 @@ class _DenseAdd(nn.Module):
 
 class DenseOps:
     delta = False
+    base = nn.Module
     conv = DenseConv
     add = _DenseAdd
 
@@ -97,34 +85,39 @@ class DenseOps:
 
     sparsify = nn.Identity
     densify = nn.Identity
+    linear = nn.Linear
 
+    class keypoints(nn.Module):
+        """(x, y, value) of the largest element of every heat map: the dense anchor of DCHeatmapArgmax."""
 
-class DeltaOps:
-    delta = True
-    conv = DeltaConv
+        def forward(self, heat):
+            n, j, h, w = heat.shape
+            val, idx = heat.float().reshape(n, j, h * w).max(dim=2)
+            return torch.stack(((idx % w).float(), (idx // w).float(), val), dim=2)
 
-    @staticmethod
-    def add(act=None):
-        return DCAdd(activation=act)
+    class boxes(nn.Module):
+        """CenterNet decode with torch operators: the dense anchor of DCCenterNetDecode (same tie order)."""
 
-    @staticmethod
-    def deconv(cin, cout, k, stride, padding, act=None):
-        return DeltaConv(cin, cout, k, stride, padding, act=act, transposed=True)
+        def __init__(self, topk=100, min_score=0.0, stride=4.0):
+            super().__init__()
+            self.topk, self.min_score, self.stride = topk, min_score, stride
 
-    @staticmethod
-    def maxpool(k, stride, padding):
-        return DCMaxPooling(k, stride, padding)
-
-    @staticmethod
-    def avgpool():
-        return DCAdaptiveAveragePooling((1, 1))
-
-    @staticmethod
-    def upsample(scale):
-        return DCUpsamplingNearest2d(scale_factor=scale)
-
-    sparsify = DCSparsify
-    densify = DCDensify
+        def forward(self, heat, wh, off):
+            n, c, h, w = heat.shape
+            hf = heat.float()
+            peak = (torch.nn.functional.max_pool2d(hf, 3, 1, 1) == hf) & (hf > self.min_score)
+            score = torch.where(peak, hf, torch.full_like(hf, float("-inf"))).permute(0, 2, 3, 1).reshape(n, -1)
+            val, idx = torch.sort(score, dim=1, descending=True, stable=True)
+            val, idx = val[:, :self.topk], idx[:, :self.topk]
+            ok = torch.isfinite(val)
+            cls, pix = idx % c, idx // c
+            x, y = (pix % w).float(), (pix // w).float()
+            g = lambda t, ch: t.float()[:, ch].reshape(n, -1).gather(1, pix)
+            cx, cy, bw, bh = x + g(off, 0), y + g(off, 1), g(wh, 0), g(wh, 1)
+            det = torch.stack(((cx - bw / 2) * self.stride, (cy - bh / 2) * self.stride, (cx + bw / 2) * self.stride,
+                               (cy + bh / 2) * self.stride, torch.sigmoid(val), cls.float()), dim=2)
+            det = torch.where(ok[..., None], det, torch.tensor([0., 0., 0., 0., 0., -1.], device=det.device).expand_as(det))
+            return det, ok.sum(dim=1).to(torch.int32)
 
 
 def _conv_then_add(ops, conv, h, idt, add):
@@ -138,7 +131,7 @@ def _conv_then_add(ops, conv, h, idt, add):
 
 
 def _base(ops):
-    return DCModule if ops.delta else nn.Module
+    return ops.base
 
 
 # ------------------------------------------------------------------------------------------------
@@ -160,6 +153,7 @@ def make_mobilenet_v2(ops, num_classes=1000):
             self.conv = nn.Sequential(*layers)
             if self.use_res:
                 self.add = ops.add()
+                layers[-1].residual_last = True
 
         def forward(self, x):
             if not self.use_res:
@@ -190,11 +184,13 @@ def make_mobilenet_v2(ops, num_classes=1000):
             self.sparsify = ops.sparsify()
             self.pool = ops.avgpool()
             self.densify = ops.densify()
-            self.classifier = nn.Linear(1280, num_classes)
+            self.classifier = ops.linear(1280, num_classes)
 
         def forward(self, x):
-            x = self.features(self.sparsify(x))
-            x = self.densify(self.pool(x))
+            x = self.pool(self.features(self.sparsify(x)))
+            if ops.delta and DELTA_HEADS:
+                return self.classifier(x)           # the classifier consumes the pooled delta: no dense feature vector
+            x = self.densify(x)
             return self.classifier(x.reshape(x.shape[0], -1))
 
     return MobileNetV2()
@@ -215,6 +211,7 @@ def _make_resnet_parts(ops):
             self.c3 = ops.conv(width, cout, 1)
             self.down = ops.conv(cin, cout, 1, stride) if (stride != 1 or cin != cout) else None
             self.add = ops.add("relu")
+            self.c3.residual_last = True
 
         def forward(self, x):
             idt = x if self.down is None else self.down(x)
@@ -227,6 +224,7 @@ def _make_resnet_parts(ops):
             self.c2 = ops.conv(cout, cout, 3, 1, 1)
             self.down = ops.conv(cin, cout, 1, stride) if (stride != 1 or cin != cout) else None
             self.add = ops.add("relu")
+            self.c2.residual_last = True
 
         def forward(self, x):
             idt = x if self.down is None else self.down(x)
@@ -252,19 +250,22 @@ def make_resnet50(ops, num_classes=1000, widths=(64, 128, 256, 512), blocks=(3, 
             self.layers = nn.Sequential(*layers)
             self.pool = ops.avgpool()
             self.densify = ops.densify()
-            self.fc = nn.Linear(cin, num_classes)
+            self.fc = ops.linear(cin, num_classes)
 
         def forward(self, x):
-            x = self.layers(self.maxpool(self.stem(self.sparsify(x))))
-            x = self.densify(self.pool(x))
+            x = self.pool(self.layers(self.maxpool(self.stem(self.sparsify(x)))))
+            if ops.delta and DELTA_HEADS:
+                return self.fc(x)
+            x = self.densify(x)
             return self.fc(x.reshape(x.shape[0], -1))
 
     return ResNet50()
 
 
-def make_centernet(ops, head_channels=64):
+def make_centernet(ops, head_channels=64, decode=False):
     """ResNet-18 trunk, three 4x4 stride-2 transposed convolutions (256 channels, BN, ReLU) and
-    three heads (3x3 conv + ReLU + 1x1 conv): heat map (1), size (2), offset (2)."""
+    three heads (3x3 conv + ReLU + 1x1 conv): heat map (1), size (2), offset (2). With ``decode`` the network
+    returns boxes (det (N, 100, 6), count) instead of the three dense maps."""
     Base, _, Basic = _make_resnet_parts(ops)
 
     class Head(Base):
@@ -274,8 +275,9 @@ def make_centernet(ops, head_channels=64):
             self.c2 = ops.conv(head_channels, cout, 1)
             self.densify = ops.densify()
 
-        def forward(self, x):
-            return self.densify(self.c2(self.c1(x)))
+        def forward(self, x, dense=True):
+            x = self.c2(self.c1(x))
+            return self.densify(x) if dense else x
 
     class CenterNet(Base):
         def __init__(self):
@@ -295,10 +297,14 @@ def make_centernet(ops, head_channels=64):
                 cin = 256
             self.ups = nn.Sequential(*ups)
             self.hm, self.wh, self.off = Head(256, 1), Head(256, 2), Head(256, 2)
+            self.boxes = ops.boxes() if decode else None
 
         def forward(self, x):
             x = self.ups(self.layers(self.maxpool(self.stem(self.sparsify(x)))))
-            return self.hm(x), self.wh(x), self.off(x)
+            if self.boxes is None:
+                return self.hm(x), self.wh(x), self.off(x)
+            dense = not ops.delta                   # the delta decode accumulates the three head deltas itself
+            return self.boxes(self.hm(x, dense), self.wh(x, dense), self.off(x, dense))
 
     return CenterNet()
 
@@ -306,7 +312,7 @@ def make_centernet(ops, head_channels=64):
 # ------------------------------------------------------------------------------------------------
 # HRNet-W32 style pose network
 # ------------------------------------------------------------------------------------------------
-def make_hrnet_w32(ops, n_joints=17, width=32, blocks_per_branch=4, modules=(1, 4, 3)):
+def make_hrnet_w32(ops, n_joints=17, width=32, blocks_per_branch=4, modules=(1, 4, 3), decode=False):
     """Stem of two 3x3 stride-2 convolutions to 1/4 resolution; stage 1 of four bottlenecks;
     stages 2-4 with 2/3/4 parallel branches (widths w, 2w, 4w, 8w at 1/4 ... 1/32 resolution) of
     basic 3x3 blocks; every module ends with a full fusion (1x1 conv + nearest upsampling toward
@@ -369,6 +375,7 @@ def make_hrnet_w32(ops, n_joints=17, width=32, blocks_per_branch=4, modules=(1, 
             self.stage4 = nn.ModuleList([HRModule(chans[:4], 4 if m < modules[2] - 1 else 1) for m in range(modules[2])])
             self.final = ops.conv(chans[0], n_joints, 1)
             self.densify = ops.densify()
+            self.keypoints = ops.keypoints() if decode else None     # (x, y, value) per joint instead of the heat maps
 
         def forward(self, x):
             x = self.stage1(self.stem(self.sparsify(x)))
@@ -381,7 +388,10 @@ def make_hrnet_w32(ops, n_joints=17, width=32, blocks_per_branch=4, modules=(1, 
             xs = xs + [self.trans[3](xs[-1])]
             for m in self.stage4:
                 xs = m(xs)
-            return self.densify(self.final(xs[0]))
+            x = self.final(xs[0])
+            if self.keypoints is not None:
+                return self.keypoints(x)
+            return self.densify(x)
 
     return HRNet()
 
@@ -389,9 +399,12 @@ def make_hrnet_w32(ops, n_joints=17, width=32, blocks_per_branch=4, modules=(1, 
 BUILDERS = {"mobilenet": make_mobilenet_v2, "resnet50": make_resnet50, "hrnet": make_hrnet_w32, "centernet": make_centernet}
 
 
-def init_weights(model, seed=0):
+def init_weights(model, seed=0, residual_gain=1.0):
     """Kaiming-normal (fan_out) convolutions, unit BatchNorm, N(0, 0.01) classifier -- the
-    initialisation of the reference's example constructors (example/mobilenet_original.py:190-200)."""
+    initialisation of the reference's example constructors (example/mobilenet_original.py:190-200).
+    ``residual_gain`` < 1 sets the BatchNorm scale of the last convolution of every residual branch (the usual
+    "small last gamma" initialisation): the blocks stay close to the identity, which keeps a randomly initialised
+    network from amplifying rounding errors layer by layer."""
     torch.manual_seed(seed)
     for m in model.modules():
         if isinstance(m, (nn.Conv2d, nn.ConvTranspose2d)):
@@ -404,6 +417,10 @@ def init_weights(model, seed=0):
         elif isinstance(m, nn.Linear):
             nn.init.normal_(m.weight, 0, 0.01)
             nn.init.zeros_(m.bias)
+    if residual_gain != 1.0:
+        for m in model.modules():
+            if getattr(m, "residual_last", False) and getattr(m, "bn", None) is not None:
+                nn.init.constant_(m.bn.weight, residual_gain)
 
 
 @torch.no_grad()
@@ -419,16 +436,17 @@ def calibrate_and_fold(dense_model, frames):
     return dense_model
 
 
-def build_pair(name, calib_frames, seed=0, device="cpu", dtype=torch.float32, **kwargs):
+def build_pair(name, calib_frames, seed=0, device="cpu", dtype=torch.float32, residual_gain=1.0, **kwargs):
     """(dense folded model, delta model) with identical weights on ``device``/``dtype``; the delta
     model is ready to run (``process_filters()`` done). ``device`` must be a CUDA device for the
     delta model; with device='cpu' only the dense model is returned (delta is None)."""
     dense = BUILDERS[name](DenseOps, **kwargs)
-    init_weights(dense, seed)
+    init_weights(dense, seed, residual_gain)
     calibrate_and_fold(dense, calib_frames)
     state = dense.state_dict()
     delta = None
     if torch.device(device).type == "cuda":
+        from .nets_delta import DeltaOps        # the only place this module touches the CUDA library
         delta = BUILDERS[name](DeltaOps, **kwargs)
         delta.load_state_dict(state)
         delta.eval()

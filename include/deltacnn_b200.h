@@ -105,6 +105,14 @@ int dc_sparsify(const void* x, void* prev_in, void* delta, int32_t* mask,
 int dc_sparsify_u8(const uint8_t* x_u8, const float* scale, const float* offset, void* prev_in, void* delta,
                    int32_t* mask, int64_t npix, int32_t channels, int32_t dtype, float threshold, void* stream);
 
+/* DCSparsify(dilation = k), the noise-robust input mask (src/deltacnn/sparse_layers.py:1233-1248, where it is four
+ * torch operators and a boolean-index copy per frame): delta = x - prev_in at EVERY pixel, mask = 1 where the
+ * k x k window centred on the pixel (stride 1, in-bounds elements) holds a pixel with any |delta| > threshold, and
+ * prev_in = x where the mask is set. k must be odd, at most 33. hit_scratch: n*h*w bytes of device memory, only
+ * meaningful during the call. */
+int dc_sparsify_dilated(const void* x, void* prev_in, void* delta, int32_t* mask, uint8_t* hit_scratch, int32_t n, int32_t h,
+                        int32_t w, int32_t channels, int32_t dtype, float threshold, int32_t dilation, void* stream);
+
 /* Delta convolution. Replaces sparse_conv_bias_wrapper_masked
  * (src/cuda/conv_torch_wrapper.cpp:62-134 -> deltacnn / deltacnn_hp, src/cuda/conv_kernel.cu:3443,3947).
  * mask_out[q] = OR of mask_in over the in-bounds taps of q; out[q] = sum_taps W^T (in * mask_in) (+ bias).
@@ -240,6 +248,38 @@ int dc_densify(const void* delta, const int32_t* mask, void* prev_out, void* den
  * counterpart (the reference re-derives activity inside every kernel,
  * src/cuda/conv_kernel.cu:46-108). */
 int dc_compact_mask(const int32_t* mask, int64_t npix, int32_t* indices, int32_t* count, void* stream);
+
+/* ---- task heads behind the delta path -------------------------------------------------------------------
+ * No counterpart among the reference's kernels: its networks end with DCDensify and dense torch code
+ * (example/mobilenet_deltacnn.py:216-227: adaptive_avg_pooling -> densify -> reshape -> nn.Linear;
+ * src/deltacnn/sparse_layers.py:1322-1329). These entry points keep that tail on the device and in delta form;
+ * a stream (image of the batch) whose update mask is empty keeps its previous result. */
+
+/* Fully connected layer on the delta of a pooled feature: for every stream n with mask[n] != 0 (all streams when
+ * first_frame != 0 or mask is NULL), acc[n][o] += sum_c weight[o][c] * delta[n][c] (+ bias[o] on the first frame,
+ * where acc starts from zero), and out[n][o] = acc[n][o] rounded to the feature dtype. delta: n x c_in; weight:
+ * c_out x c_in (torch nn.Linear layout) and bias in the feature dtype; acc: n x c_out float32 state owned by the
+ * caller. Replaces densify + nn.Linear of example/mobilenet_deltacnn.py:216-227 (a linear layer commutes with the
+ * accumulation over frames). */
+int dc_linear_delta(const void* delta, const int32_t* mask, const void* weight, const void* bias, float* acc, void* out,
+                    int32_t n, int32_t c_in, int32_t c_out, int32_t dtype, int32_t first_frame, void* stream);
+
+/* Arg-max of dense heat maps (n, h, w, joints channels last; the output of dc_densify): out[n][j] = (x, y, value)
+ * of the largest element of joint j, the first in row-major order on ties. mask (n*h*w, may be NULL): streams
+ * without an active pixel are skipped and out keeps their previous rows. */
+int dc_heatmap_argmax(const void* heat, const int32_t* mask, float* out, int32_t n, int32_t h, int32_t w, int32_t joints,
+                      int32_t dtype, void* stream);
+
+/* CenterNet decode of dense head outputs (heat n,h,w,classes; wh and offset n,h,w,2; channels last): a peak is an
+ * element equal to the maximum of its 3x3 neighbourhood; det[n][k] = (x1, y1, x2, y2, score, class) of the topk
+ * best peaks with score > min_score, best first (ties: ascending pixel, class), centre (x + offset_x, y + offset_y),
+ * size wh, all multiplied by stride; rows beyond count[n] are zero with class -1. peaks (n*h*w*classes float32) is
+ * state owned by the caller: with a mask only pixels next to an updated pixel are re-examined, and streams without
+ * an updated pixel keep their rows; mask NULL (first frame) examines everything. topk <= 1024. apply_sigmoid != 0
+ * reports sigmoid(score). */
+int dc_centernet_decode(const void* heat, const void* wh, const void* offset, const int32_t* mask, float* peaks, float* det,
+                        int32_t* count, int32_t n, int32_t h, int32_t w, int32_t classes, int32_t topk, float min_score,
+                        float stride, int32_t apply_sigmoid, int32_t dtype, void* stream);
 
 #ifdef __cplusplus
 }

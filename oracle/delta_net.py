@@ -172,6 +172,8 @@ class OracleDensify(nn.Module):
 
 class OracleOps:
     delta = False          # plain nn.Module containers
+    base = nn.Module
+    linear = nn.Linear     # the reference's tail: densify, then a dense linear layer (example/mobilenet_deltacnn.py:216-227)
     conv = OracleConv
     add = OracleAdd
     sparsify = OracleSparsify
@@ -192,6 +194,16 @@ class OracleOps:
     @staticmethod
     def upsample(scale):
         return OracleUpsample(scale)
+
+    @staticmethod
+    def keypoints():
+        from examples.nets import DenseOps
+        return nn.Sequential(OracleDensify(), DenseOps.keypoints())
+
+    @staticmethod
+    def boxes(**kw):
+        from examples.nets import DenseOps
+        return DenseOps.boxes(**kw)
 
 
 def build_oracle_net(name, folded_state_dict, **kwargs):

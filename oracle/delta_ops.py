@@ -272,3 +272,71 @@ def densify(delta, mask, prev_out, activation=0):
     s = (prev_out.float() + delta.float()).to(prev_out.dtype)
     prev_out[sel] = s[sel]
     return activation_fn(prev_out.float(), activation).to(prev_out.dtype)
+
+
+def sparsify_dilated(x, prev_in, threshold, dilation):
+    """DCSparsify(dilation=k): src/deltacnn/sparse_layers.py:1233-1248. Returns (delta, mask); the delta is dense
+    (x - prev_in everywhere), the mask is the k x k max-pool (stride 1, padding (k-1)//2) of max_c |delta| compared
+    with the threshold, and prev_in takes x where the mask is set."""
+    d = (x.float() - prev_in.float()).to(x.dtype)
+    thr = _round_threshold(threshold, x.dtype)
+    a = d.float().abs().amax(dim=1, keepdim=True)
+    k = int(dilation)
+    m = F.max_pool2d(a, (k, k), stride=(1, 1), padding=((k - 1) // 2, (k - 1) // 2)) > thr
+    sel = m.expand_as(x)
+    prev_in[sel] = x[sel]
+    return d, m.to(torch.int32)
+
+
+def linear_delta(delta, mask, weight, bias, acc, first_frame):
+    """Classifier on the pooled delta. The reference's tail is DCDensify (prev_out += delta, sparse_layers.py:1322-1329)
+    followed by nn.Linear on the dense vector (example/mobilenet_deltacnn.py:216-227); a linear layer commutes with
+    that accumulation, so acc (float32, N x out) += delta @ W^T on masked streams (+ bias on the first frame) holds the
+    same logits. Returns acc rounded to the feature dtype."""
+    n = delta.shape[0]
+    d = delta.reshape(n, -1).float()
+    on = torch.ones(n, dtype=torch.bool) if (first_frame or mask is None) else (mask.reshape(n) != 0)
+    upd = d @ weight.float().t()
+    if first_frame:
+        acc.zero_()
+        if bias is not None:
+            upd = upd + bias.float()
+    acc[on] += upd[on]
+    return acc.to(delta.dtype)
+
+
+def heatmap_argmax(heat):
+    """(x, y, value) of the first maximum of every map of a dense (N, J, H, W) tensor (torch.argmax semantics)."""
+    n, j, h, w = heat.shape
+    flat = heat.float().reshape(n, j, h * w)
+    val, idx = flat.max(dim=2)
+    idx = torch.argmax(flat, dim=2)
+    return torch.stack(((idx % w).float(), (idx // w).float(), val), dim=2)
+
+
+def centernet_decode(heat, wh, offset, topk=100, min_score=0.0, stride=4.0, apply_sigmoid=False):
+    """CenterNet-style decode of dense head outputs (N,C,H,W / N,2,H,W): peaks = elements equal to the 3x3 max-pool
+    of the heat map, the topk best above min_score (ties by ascending (pixel, class) index), boxes from centre
+    (x + off_x, y + off_y) and size wh, times stride. Returns (det (N, topk, 6), count (N,))."""
+    n, c, h, w = heat.shape
+    hf = heat.float()
+    peak = F.max_pool2d(hf, 3, 1, 1) == hf
+    score = torch.where(peak & (hf > min_score), hf, torch.full_like(hf, float("-inf")))
+    det = torch.zeros(n, topk, 6)
+    det[:, :, 5] = -1
+    count = torch.zeros(n, dtype=torch.int32)
+    for b in range(n):
+        s = score[b].permute(1, 2, 0).reshape(-1)                      # index = pixel * classes + class
+        order = torch.sort(s, descending=True, stable=True)[1]
+        order = order[torch.isfinite(s[order])][:topk]
+        count[b] = len(order)
+        for k, i in enumerate(order.tolist()):
+            cl, p = i % c, i // c
+            y, x = p // w, p % w
+            cx, cy = x + float(offset[b, 0, y, x]), y + float(offset[b, 1, y, x])
+            bw, bh = float(wh[b, 0, y, x]), float(wh[b, 1, y, x])
+            sc = float(s[i])
+            if apply_sigmoid:
+                sc = 1.0 / (1.0 + float(torch.exp(torch.tensor(-sc))))
+            det[b, k] = torch.tensor([(cx - bw / 2) * stride, (cy - bh / 2) * stride, (cx + bw / 2) * stride, (cy + bh / 2) * stride, sc, cl])
+    return det, count

@@ -92,3 +92,83 @@ def test_filter_layout():
     wt = torch.arange(2 * 3 * 4 * 4, dtype=torch.float32).view(2, 3, 4, 4)      # [ci, co, kh, kw]
     ft = convert_filter_out_channels_last(wt, transposed=True)
     assert ft.shape == (4, 4, 2, 3) and ft[3, 1, 1, 2] == wt[1, 2, 3, 1]
+
+
+def test_threshold_tuning_front_to_back():
+    """The front-to-back search of the reference's readme (3.5): each layer's threshold doubles until the loss
+    leaves its budget, and the last accepted value is kept; earlier layers' choices are inputs to later ones."""
+    from deltacnn_b200 import DCThreshold
+    from deltacnn_b200.tuning import tune_thresholds
+    DCThreshold.reset()
+    keys = ["a", "b", "c"]
+    for k in keys:
+        DCThreshold.set(k, 0.0)
+    sens = {"a": 10.0, "b": 1.0, "c": 0.0}                 # loss = 1 + sum sens * t^2 : "c" does not matter at all
+    calls = []
+
+    def loss():
+        calls.append(dict(DCThreshold.t))
+        return 1.0 + sum(sens[k] * DCThreshold.t[k] ** 2 for k in keys)
+
+    table = tune_thresholds(loss, start=0.01, step=2.0, max_loss_increase=1.05, max_threshold=1.0)
+    a, b, c = table
+    assert a == 0.04 and 1.0 + 10 * 0.08 ** 2 > 1.05 >= 1.0 + 10 * a ** 2        # 0.08 would exceed the budget of layer a
+    base_b = 1.0 + 10 * a ** 2
+    assert base_b + b ** 2 <= base_b * 1.05 < base_b + (2 * b) ** 2
+    assert c == 0.64                                        # insensitive layer: runs to the largest value <= max_threshold
+    assert list(DCThreshold.t.values()) == table
+    DCThreshold.reset()
+
+
+def test_threshold_tuning_with_zero_start_loss_uses_the_absolute_slack():
+    from deltacnn_b200 import DCThreshold
+    from deltacnn_b200.tuning import tune_thresholds
+    DCThreshold.reset()
+    DCThreshold.set("x", 0.0)
+    table = tune_thresholds(lambda: DCThreshold.t["x"], start=0.001, step=2.0, max_loss_increase=1.001, abs_slack=0.01)
+    assert table == [0.008]
+    DCThreshold.reset()
+
+
+def test_performance_metrics_follow_the_reference_counter_definitions():
+    """DCPerformanceMetricsManager computes the reference's DCMetrics counters (src/cuda/common.cuh:41-65) from masks.
+    Checked on a hand-countable case and against the oracle's mask dilation on a random one."""
+    from deltacnn_b200.cuda_kernels import DCPerformanceMetricsManager as M
+    from oracle import delta_ops as O
+    M.reset()
+    M.enabled = True
+    try:
+        m = torch.zeros(1, 1, 16, 16, dtype=torch.int32)
+        m[0, 0, 3, 4] = 1
+        M.add_conv(m, 8, 16, (3, 3), (1, 1), (1, 1), (1, 1), 1, (16, 16))
+        r = M.get_metrics()
+        assert (r.tiles_active, r.tiles_total) == (1, 4)
+        assert (r.inputs_active, r.inputs_total) == (1, 4 * 10 * 10)
+        assert r.flops_theoretical == 9 * 8 * 16                       # nine output pixels see the one active tap
+        assert r.flops_actual == 64 * 9 * 8 * 16                       # every pixel of the active 8x8 tile, all taps
+        assert r.flops_dense == 256 * 9 * 8 * 16
+        assert r.mem_write_actual == 9 * 16 and r.mem_write_dense == 256 * 16
+        assert r.mem_read_actual == 1 * 8 + 9 * 8 * 16
+        assert r.histogram[0] == 3 and r.histogram[1] == 1 and sum(r.histogram) == 4
+        assert r.mode_sparse == 1 and r.mode_dense == 0
+        # a random stride-2 case: updated pixels must be the oracle's out-mask
+        M.reset()
+        g = torch.Generator().manual_seed(0)
+        m = (torch.rand(2, 1, 30, 34, generator=g) < 0.1).to(torch.int32)
+        ho, wo = O.conv_out_size(30, 34, (3, 3), (2, 2), (1, 1), (1, 1))
+        M.add_conv(m, 4, 6, (3, 3), (2, 2), (1, 1), (1, 1), 1, (ho, wo))
+        om = O.dilate_mask(m, (3, 3), (2, 2), (1, 1), (1, 1))
+        r = M.get_metrics()
+        assert r.mem_write_actual == int(om.sum()) * 6
+        assert r.tiles_total == 2 * 2 * 3 and r.inputs_total == r.tiles_total * 17 * 17
+        # truncation layer: 2C read and written per masked pixel; two frames averaged
+        M.reset()
+        M.add_activation(m, 10, 0)
+        M.add_activation(m, 10, 0)
+        r = M.get_metrics(n_frames=2)
+        assert r.mem_read_actual == 2 * 10 * int(m.sum()) and r.mem_write_actual == r.mem_read_actual
+        d = r.to_dict()
+        assert len(d["histogram"]) == 128 and "flops_ratio_actual" in d
+    finally:
+        M.enabled = False
+        M.reset()
