@@ -4,14 +4,18 @@ frames/sec, beside dense cuDNN inference of the same network on the same GPU and
 baseline. One step = one frame of every stream on this GPU (streams stacked on the batch axis,
 one CUDA-graph replay). Prints ONE JSON line (rank 0).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--streams S] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--streams S] [--total-streams T] [--impl reference]
 
 N > 1 is launched with torch.distributed.run, one rank per GPU; streams are independent, so the
-ranks share nothing on the data path (weak scaling: S streams per GPU).
+ranks share nothing on the data path. Default: S streams per GPU (weak scaling). With --total-streams T
+the T streams of the job are dealt to the ranks round-robin (stream s runs on rank s mod N; strong scaling).
+The timed block of K steps is repeated (--repeats) and the median is reported.
 """
 import argparse
+import hashlib
 import json
 import os
+import struct
 import subprocess
 import sys
 import threading
@@ -33,9 +37,12 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--streams", type=int, default=64, help="streams per GPU")
+    ap.add_argument("--total-streams", type=int, default=0, help="streams of the whole job, dealt round-robin to the GPUs (0: --streams per GPU)")
     ap.add_argument("--branches", type=int, default=2, help="groups of streams stepped concurrently inside one CUDA graph")
+    ap.add_argument("--repeats", type=int, default=5, help="repetitions of the timed block of --steps steps (median reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-extras", action="store_true", help="skip the dense-cuDNN / CPU / reference-kernel side measurements")
+    ap.add_argument("--no-extras", action="store_true", help="skip the dense-cuDNN / CPU / reference-kernel / roofline side measurements")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the ResNet-50 / HRNet / CenterNet side measurements")
     return ap.parse_args()
 
 
@@ -46,13 +53,35 @@ def pingpong(t, n):
     return r if r < n else period - r
 
 
+def stream_ids(rank, world, streams_per_gpu, total_streams=0):
+    """Global ids (= video seeds) of the streams of ``rank``: a contiguous block of ``streams_per_gpu``, or with
+    ``total_streams`` the ids s < total_streams with s mod world == rank."""
+    if total_streams > 0:
+        return [s for s in range(total_streams) if s % world == rank]
+    return list(range(rank * streams_per_gpu, (rank + 1) * streams_per_gpu))
+
+
+def stream_checksums(outputs):
+    """One float64 number per stream (row) of a step's output: the sum of its elements."""
+    return outputs.detach().double().reshape(outputs.shape[0], -1).sum(dim=1).cpu().tolist()
+
+
+def combine_checksums(ids, sums):
+    """Digest of per-stream checksums that does not depend on how the streams were dealt to ranks: sorted by
+    stream id, packed as (id, float64) pairs, SHA-256."""
+    h = hashlib.sha256()
+    for i, v in sorted(zip(ids, sums)):
+        h.update(struct.pack("<qd", int(i), float(v)))
+    return h.hexdigest()
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return float(p["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -65,7 +94,7 @@ class ClockSampler:
         q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -89,15 +118,19 @@ class ClockSampler:
         mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({names[i] for s in self.samples if len(s) >= 6 for i in range(4) if s[2 + i].lower().startswith("active")})
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons}
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
 
 
-def make_streams(n_streams, first_seed):
-    """(n_distinct, n_streams, 3, 224, 224) float32 frames of ``n_streams`` seeded videos."""
+def make_streams(n_streams, first_seed=0, seeds=None):
+    """(n_distinct, n_streams, 3, 224, 224) float32 frames of seeded videos, quantised to the 256 levels of 8-bit
+    video (the end-to-end leg uploads them as bytes); ``seeds`` lists the stream ids, default first_seed ..."""
     import torch
     from examples.synthetic_video import make_video
-    vids = [make_video("mobilenet", first_seed + s).frames(N_DISTINCT_FRAMES) for s in range(n_streams)]
-    return torch.stack(vids, dim=1)
+    seeds = list(range(first_seed, first_seed + n_streams)) if seeds is None else list(seeds)
+    vids = [make_video("mobilenet", s).frames(N_DISTINCT_FRAMES) for s in seeds]
+    frames = torch.stack(vids, dim=1)
+    return torch.round(frames * 255.0) * (1.0 / 255.0)     # level * float32(1/255): the arithmetic of the 8-bit sparsify kernel
 
 
 def cpu_delta_baseline(state_dict, frames32, seconds=15.0):
@@ -121,7 +154,8 @@ def cpu_delta_baseline(state_dict, frames32, seconds=15.0):
 
 def run_reference_arm(args, rank, world):
     """--impl reference: the reference's path has no CPU implementation of its own (its delta kernels
-    are CUDA only), so this arm times the CPU port of it (oracle/) on the host cores."""
+    are CUDA only), so this arm times the CPU port of it (oracle/) on the host cores. Nothing of the
+    product is imported here: the dense network comes from examples.nets, which does not load the CUDA library."""
     if rank != 0:
         return
     import torch
@@ -143,6 +177,7 @@ def run_reference_arm(args, rank, world):
             net(frames[pingpong(t, n), :1])
         dt = time.perf_counter() - t0
     fps = steps / dt
+    assert "deltacnn_b200" not in sys.modules, "the reference arm must not load the product"
     line = {"impl": "reference", "metric": METRIC, "value": fps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
             "warmup": args.warmup, "ms_per_step": 1000 * dt / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -164,7 +199,6 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from deltacnn_b200 import DCThreshold
     from examples.nets import build_pair
     from examples.runner import MultiBranchStep, PipelinedStep, set_depth_thresholds
 
@@ -172,13 +206,18 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    S, K_steps, W = args.streams, args.steps, max(args.warmup, 3)
+    ids = stream_ids(rank, world, args.streams, args.total_streams)
+    S, K_steps, W = len(ids), args.steps, max(args.warmup, 3)
+    total_streams = args.total_streams if args.total_streams > 0 else world * args.streams
 
-    frames32 = make_streams(S, first_seed=rank * S)                     # (F, S, 3, H, W) fp32 on the host
-    dense, delta = build_pair("mobilenet", frames32[:8, 0], device=dev, dtype=torch.float16)
+    frames32 = make_streams(S, seeds=ids)                               # (F, S, 3, H, W) fp32 on the host, 8-bit levels
+    calib = make_streams(1, 0)[:8, 0]                                   # BatchNorm is calibrated on stream 0 on every rank
+    dense, delta = build_pair("mobilenet", calib, device=dev, dtype=torch.float16)
     frames_dev = torch.stack([frames32[i].to(dev, torch.float16).contiguous(memory_format=torch.channels_last)
                               for i in range(frames32.shape[0])])
-    host_frames = [frames_dev[i].cpu().pin_memory() for i in range(frames_dev.shape[0])]   # channels-last bytes, pinned
+    # the same frames as bytes, N,H,W,C, in pinned host memory: what the end-to-end leg uploads
+    host_frames = [torch.round(frames32[i] * 255.0).to(torch.uint8).permute(0, 2, 3, 1).contiguous().pin_memory()
+                   for i in range(frames32.shape[0])]
     F = frames_dev.shape[0]
 
     stream = torch.cuda.Stream()
@@ -190,7 +229,9 @@ def main():
     bounds = [(g * S) // G for g in range(G + 1)]
     deltas = [delta]
     for _ in range(1, G):
-        deltas.append(build_pair("mobilenet", frames32[:8, 0], device=dev, dtype=torch.float16)[1])
+        deltas.append(build_pair("mobilenet", calib, device=dev, dtype=torch.float16)[1])
+    for m in deltas:
+        m.sparsify.set_u8_input(1.0 / 255.0, 0.0, torch.float16)      # 8-bit frames go straight into the sparsify kernel
     with torch.no_grad():
         for g, m in enumerate(deltas):
             sl = slice(bounds[g], bounds[g + 1])
@@ -216,11 +257,11 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(n, **kw):
+    def timed(fn, n):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        run_steps(n, **kw)
+        fn(n)
         e1.record(stream)
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -232,12 +273,31 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = timed(K_steps)
-    clocks = sampler.stop() if rank == 0 else None
+    reps = sorted(timed(run_steps, K_steps) for _ in range(max(1, args.repeats)))
+    ms = reps[len(reps) // 2]
 
-    # end to end through the module API: frames start in pinned host memory, logits end there; the upload
+    # checksum of the outputs after the same number of steps on every run: comparable between runs that deal the
+    # same streams differently to GPUs
+    with torch.no_grad():
+        out_now = torch.cat([o.float() for o in step.static_out], dim=0)
+    sums = stream_checksums(out_now)
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (ids, sums))
+        all_ids = [i for part in gathered for i in part[0]]
+        all_sums = [v for part in gathered for v in part[1]]
+    else:
+        all_ids, all_sums = ids, sums
+    checksum = {"sha256_over_streams": combine_checksums(all_ids, all_sums), "streams": len(all_ids),
+                "rank0_sum": float(sum(sums)), "steps_run": t_next[0] - 2}
+
+    # end to end through the module API: 8-bit frames start in pinned host memory, logits end there; the upload
     # of the next frame overlaps the current step (two input buffers, two graphs of the same model)
-    pipe = PipelinedStep(deltas, [frames_dev[1][bounds[g]:bounds[g + 1]] for g in range(G)], bounds, stream)
+    u8_example = [host_frames[1][bounds[g]:bounds[g + 1]].to(dev) for g in range(G)]
+    with torch.no_grad():
+        for g, m in enumerate(deltas):
+            m(u8_example[g])                                            # one eager 8-bit frame before capture
+    pipe = PipelinedStep(deltas, u8_example, bounds, stream)
 
     def next_host_frame():
         f = host_frames[pingpong(t_next[0], F)]
@@ -251,20 +311,10 @@ def main():
             pipe.upload(next_host_frame())      # frame t+1 goes up ...
             pipe.step()                         # ... while frame t is processed
 
-    def timed_e2e(n):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        run_e2e(n)
-        e1.record(stream)
-        barrier()
-        ms_ = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms_, op=dist.ReduceOp.MAX)
-        return float(ms_.item())
-
     run_e2e(3)
-    ms_e2e = timed_e2e(K_steps)
+    reps_e2e = sorted(timed(run_e2e, K_steps) for _ in range(max(1, args.repeats)))
+    ms_e2e = reps_e2e[len(reps_e2e) // 2]
+    clocks = sampler.stop() if rank == 0 else None
     d2h_bytes = sum(int(o.numel() * o.element_size()) for o in pipe.host_out[0])
 
     # measured fraction of updated input pixels over the frames used
@@ -276,22 +326,33 @@ def main():
     launches_per_step = count_launches(deltas, bounds, frames_dev, t_next, F)
 
     line = {
-        "metric": METRIC, "value": world * S * K_steps / (ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K_steps,
-        "warmup": W, "ms_per_step": ms / K_steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": METRIC, "value": total_streams * K_steps / (ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K_steps,
+        "warmup": W, "ms_per_step": ms / K_steps, "higher_is_better": True,
+        "scaling": "strong" if args.total_streams > 0 else "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "configs[1]: MobileNetV2 224x224 fp16 delta inference, synthetic videos (3 moving 40x40 rectangles, sigma 0.005)",
-                   "streams_per_gpu": S, "thresholds": THRESHOLDS, "updated_input_pixels": sum(dens) / len(dens),
+        "config": {"workload": "configs[1]: MobileNetV2 224x224 fp16 delta inference, synthetic videos (3 moving 40x40 rectangles, sigma 0.005, 8-bit levels)",
+                   "streams_per_gpu": S, "total_streams": total_streams,
+                   "partition": "stream s on rank s mod N" if args.total_streams > 0 else "rank r runs streams r*S .. r*S+S-1",
+                   "thresholds": THRESHOLDS, "updated_input_pixels": sum(dens) / len(dens),
                    "l2": "inputs larger than L2: a step touches a different frame (19 MB) and >1 GB of per-stream caches",
-                   "bn": "BatchNorm calibrated on 8 frames of stream 0 and folded", "step": "one frame of every stream, one CUDA-graph replay", "concurrent_stream_groups": G},
-        "e2e": {"value": world * S * K_steps / (ms_e2e / 1000.0), "unit": UNIT,
+                   "bn": "BatchNorm calibrated on 8 frames of stream 0 and folded", "step": "one frame of every stream, one CUDA-graph replay",
+                   "head": "classifier on the pooled delta (DCLinear), logits per stream", "concurrent_stream_groups": G},
+        "repeats": {"n": len(reps), "ms_per_step_min": reps[0] / K_steps, "ms_per_step_median": ms / K_steps,
+                    "ms_per_step_max": reps[-1] / K_steps, "timed_region_ms_total": sum(reps)},
+        "e2e": {"value": total_streams * K_steps / (ms_e2e / 1000.0), "unit": UNIT,
                 "h2d_bytes_per_step": int(host_frames[0].numel() * host_frames[0].element_size()),
-                "d2h_bytes_per_step": d2h_bytes},
+                "d2h_bytes_per_step": d2h_bytes, "input": "uint8 N,H,W,C frames from pinned host memory, normalised inside the sparsify kernel",
+                "ms_per_step_min": reps_e2e[0] / K_steps, "ms_per_step_max": reps_e2e[-1] / K_steps},
         "gpu_launches": launches_per_step * K_steps,
+        "output_checksum": checksum,
         "clocks": clocks,
     }
 
     if rank == 0 and not args.no_extras and world == 1:
-        line.update(side_measurements(args, dev, dense, deltas[0], frames_dev[:, bounds[0]:bounds[1]], frames_dev, frames32, stream, S, table, ms / K_steps))
+        line.update(side_measurements(args, dev, dense, deltas[0], frames_dev[:, bounds[0]:bounds[1]], frames_dev, frames32, stream, S,
+                                      ms / K_steps, (bounds[1] - bounds[0]) / S))
+        if "layer_density" in line:
+            line["config"]["layer_density"] = line.pop("layer_density")
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -304,7 +365,9 @@ def count_launches(deltas, bounds, frames_dev, t_next, F):
     import torch
     from deltacnn_b200 import _lib
     counts = [0]
-    names = [n for n in _lib.EXPORTED_SYMBOLS if n not in ("dc_version", "dc_status_string", "dc_last_cuda_error", "dc_filter_umma_bytes", "dc_umma_error", "dc_conv_workspace_bytes", "dc_deconv_workspace_bytes", "dc_static_workspace_max_pixels")]
+    skip = ("dc_version", "dc_status_string", "dc_last_cuda_error", "dc_filter_umma_bytes", "dc_umma_error", "dc_conv_workspace_bytes",
+            "dc_deconv_workspace_bytes", "dc_static_workspace_max_pixels")
+    names = [n for n in _lib.EXPORTED_SYMBOLS if n not in skip]
     originals = {}
 
     def wrap(name, fn):
@@ -328,8 +391,188 @@ def count_launches(deltas, bounds, frames_dev, t_next, F):
     return counts[0]
 
 
-def side_measurements(args, dev, dense, delta, frames_group0, frames_dev, frames32, stream, S, table, ms_per_step):
-    """Dense cuDNN baseline on the same GPU, CPU baselines, and the roofline of the dominant kernel."""
+def reference_kernels_gpu(delta, frames_group0, stream):
+    """The reference's own CUDA kernels (built for this GPU by oracle/Makefile, test infrastructure) timed beside
+    this library's on the same tensors and masks of one eager frame: one representative layer per kernel family.
+    Per launch: L2 flushed, CUDA events on the stream the kernel runs on (the reference launches on the legacy
+    default stream). The reference has no fused convolution epilogue, so its side of a fused layer is convolution
+    plus activate_truncate."""
+    import ctypes
+    import torch
+    import deltacnn_b200.cuda_kernels as K
+    from oracle import ref_kernels as R
+    if not R.available():
+        return {"unavailable": "oracle/_ref/libdeltacnn_ref.so is not built"}
+    lib = R.lib()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    legacy = torch.cuda.default_stream()
+    captured = {}
+    orig_conv, orig_sparsify = K.sparse_conv, K.sparsify
+    want = {"stem 3x3/2 3->32 @224": (3, 32, 3), "depthwise 3x3 96 @112 s2": (96, 96, 3), "1x1 16->96 @112 (+act)": (16, 96, 1),
+            "1x1 96->576 @14 (+act)": (96, 576, 1), "depthwise 3x3 576 @14": (576, 576, 3), "1x1 576->96 @14": (576, 96, 1)}
+
+    def conv_hook(*a, **kw):
+        x, filt = kw["x"], kw["filter"]
+        for name, (ci, co, k) in want.items():
+            if name not in captured and x.shape[1] == ci and filt.shape[3] == co and filt.shape[0] == k and \
+                    ((name.endswith("@14") or "@14 " in name) == (x.shape[2] == 14)):
+                ep = kw.get("epilogue")
+                captured[name] = dict(kw, x=x.clone(), mask=kw["mask"].clone(), epilogue=ep)
+        return orig_conv(*a, **kw)
+
+    def sparsify_hook(inp, prev, d, m, thr):
+        captured.setdefault("sparsify 3 @224", (inp.clone(), prev.clone(), thr))
+        return orig_sparsify(inp, prev, d, m, thr)
+
+    K.sparse_conv, K.sparsify = conv_hook, sparsify_hook
+    try:
+        with torch.no_grad():
+            delta(frames_group0[5])
+    finally:
+        K.sparse_conv, K.sparsify = orig_conv, orig_sparsify
+
+    def time_on(st, fn, reps=5):
+        best = []
+        for _ in range(reps):
+            with torch.cuda.stream(st):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(st)
+                fn()
+                e1.record(st)
+            torch.cuda.synchronize()
+            best.append(e0.elapsed_time(e1) * 1000.0)
+        best.sort()
+        return best[len(best) // 2]
+
+    out = {}
+    layers = {id(m): m for m in delta.modules()}
+    convs = [m for m in delta.modules() if hasattr(m, "orig_weights") and m.orig_weights is not None]
+    for name, c in captured.items():
+        if name.startswith("sparsify"):
+            x, prev, thr = c
+            n, ch, h, w = x.shape
+            d, m = torch.empty_like(x), torch.empty((n, 1, h, w), dtype=torch.int32, device=x.device)
+            p1, p2 = prev.clone(), prev.clone()
+            ours = time_on(stream, lambda: orig_sparsify(x, p1, d, m, thr))
+            ref = time_on(legacy, lambda: lib.ref_sparsify(1, R._p(x), R._p(p2), R._p(d), R._p(m), ctypes.c_float(thr), n, h, w, ch, 0))
+            out[name] = {"ours_us": round(ours, 2), "ref_us": round(ref, 2), "ref_kernel": "deltacnn_prepare_diff_mask_hp_kernel"}
+            continue
+        x, mask, filt = c["x"], c["mask"], c["filter"]
+        conv = next(m for m in convs if m.weight.data_ptr() == filt.data_ptr())
+        wt = conv.orig_weights                                        # torch layout
+        n, ci, h, w = x.shape
+        co = filt.shape[3]
+        k = filt.shape[0]
+        ho, wo = c["out"].shape[2], c["out"].shape[3]
+        ep = c.get("epilogue")
+        act = conv.activation_layer
+        prev_o, trunc_o = (act.prev_out.clone(), act.out_truncated.clone()) if (ep is not None and act is not None) else (None, None)
+        kw = dict(c)
+        if ep is not None and act is not None:
+            from deltacnn_b200 import DCThreshold
+            kw["epilogue"] = K.make_epilogue(prev_o, trunc_o, DCThreshold.get(act), act.activation_int, 0)
+        out_t, om_t = torch.empty_like(c["out"]), torch.empty_like(c["out_mask"])
+        kw.update(out=out_t, out_mask=om_t)
+        ours = time_on(stream, lambda: orig_conv(**kw))
+        rf = R.ref_filter(wt)
+        shape = R._ints(n, h, w, ci, ho, wo, co)
+        pt, pb, pl, pr = K._pad4(c["padding"])
+        geom = R._ints(k, k, c["stride"][0], c["stride"][1], pt, pl, pb, pr, 1, 1, c["groups"])
+        ro = torch.empty_like(c["out"])
+        rm = torch.empty_like(c["out_mask"])
+        ref_conv = time_on(legacy, lambda: lib.ref_conv(1, R._p(x), R._p(ro), R._p(rf), R._p(None), R._p(mask), R._p(rm), shape, geom, 0))
+        row = {"ours_us": round(ours, 2), "ref_conv_us": round(ref_conv, 2)}
+        if ep is not None and act is not None:
+            from deltacnn_b200 import DCThreshold
+            p2, t2 = act.prev_out.clone(), act.out_truncated.clone()
+            thr = float(DCThreshold.get(act))
+
+            def ref_act():
+                lib.ref_activate_truncate(1, R._p(ro), R._p(p2), R._p(t2), R._p(rm), ctypes.c_float(thr), n, ho, wo, co, act.activation_int, 0, 0)
+            ref_conv_only = ref_conv
+            lib.ref_conv(1, R._p(x), R._p(ro), R._p(rf), R._p(None), R._p(mask), R._p(rm), shape, geom, 1)
+            row["ref_act_us"] = round(time_on(legacy, ref_act, reps=1), 2)      # once: the call consumes its mask
+            row["ref_us"] = round(ref_conv_only + row["ref_act_us"], 2)
+        else:
+            row["ref_us"] = row["ref_conv_us"]
+        if ep is not None and getattr(ep, "residual", None):
+            row["ours_includes"] = "the residual add of the block (DCAdd) in the same kernel"
+        row["active_input_pixels"] = round(float((mask != 0).float().mean().item()), 4)
+        out[name] = row
+    out["how"] = "one layer per kernel family, 32 streams, per-launch CUDA events with L2 flushed (cold, serialised); the reference's side of a fused layer is its convolution plus its activate_truncate kernel"
+    return out
+
+
+def other_configs():
+    """Frames/sec of the other three configurations (fp16, CUDA graph on both sides) beside dense cuDNN."""
+    import torch
+    from examples import bench_configs
+    from deltacnn_b200 import DCConv2d, DCThreshold
+    out = {}
+    for name, streams in (("resnet50", 16), ("hrnet", 32), ("centernet", 32)):
+        try:
+            DCThreshold.reset()
+            r = bench_configs.run(name, streams, 6)
+            out[name] = {k: r[k] for k in ("streams", "resolution", "updated_input_pixels", "delta_fps", "dense_cudnn_fps", "patch_tiles")}
+            out[name]["speedup_vs_dense_cudnn"] = r["delta_fps"] / r["dense_cudnn_fps"]
+        except Exception as e:
+            out[name] = {"error": repr(e)}
+        finally:
+            DCConv2d.patch_tiles = False
+            torch.cuda.empty_cache()
+    return out
+
+
+def config1_fp32(frames32, dev):
+    """Configuration 1: MobileNetV2 fp32, batch 1, CUDA graph (the generic CUDA-core kernels), frames/sec at threshold 0.05."""
+    import torch
+    from deltacnn_b200 import DCThreshold
+    from examples.nets import build_pair
+    from examples.runner import GraphedStep
+    DCThreshold.reset()
+    DCThreshold.t_default = 0.05
+    try:
+        dense, delta = build_pair("mobilenet", frames32[:8, 0], device=dev)
+        fd = [frames32[i, :1].to(dev).contiguous(memory_format=torch.channels_last) for i in range(frames32.shape[0])]
+        with torch.no_grad():
+            delta(fd[0])
+            step = GraphedStep(delta, fd[1], warmup_frames=[fd[1]])
+            for t in range(2, 6):
+                step(fd[t])
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n = 64
+            e0.record()
+            for t in range(n):
+                step(fd[pingpong(6 + t, len(fd))])
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / n
+            g = torch.cuda.CUDAGraph()
+            static = fd[0].clone()
+            for _ in range(3):
+                dense(static)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g):
+                dense(static)
+            e0.record()
+            for t in range(n):
+                static.copy_(fd[pingpong(6 + t, len(fd))])
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms_dense = e0.elapsed_time(e1) / n
+        return {"value": 1000.0 / ms, "unit": UNIT, "ms_per_frame": ms, "dense_cudnn_fp32_fps": 1000.0 / ms_dense,
+                "how": "MobileNetV2 224x224 fp32, 1 stream, every threshold 0.05, CUDA graph, 64 frames"}
+    finally:
+        DCThreshold.t_default = 0.0
+        DCThreshold.reset()
+
+
+def side_measurements(args, dev, dense, delta, frames_group0, frames_dev, frames32, stream, S, ms_per_step, group_fraction):
+    """Dense cuDNN baseline on the same GPU, CPU baselines, the reference's kernels on the same layers, the roofline
+    of the dominant kernel and of the whole step, the other configurations."""
     import torch
     extra = {}
     F = frames_dev.shape[0]
@@ -373,7 +616,7 @@ def side_measurements(args, dev, dense, delta, frames_group0, frames_dev, frames
     # CPU baselines on a bounded sample
     torch.set_num_threads(os.cpu_count() or 1)
     from examples.nets import build_pair
-    dense_cpu, _ = build_pair("mobilenet", frames32[:8, 0], device="cpu")
+    dense_cpu, _ = build_pair("mobilenet", make_streams(1, 0)[:8, 0], device="cpu")
     fps_port, n_port = cpu_delta_baseline(dense_cpu.state_dict(), frames32, seconds=12.0)
     extra["cpu_baseline"] = {"value": fps_port, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                              "sample": f"{n_port} frames of one stream through the CPU restatement of the delta path (oracle/)"}
@@ -385,11 +628,23 @@ def side_measurements(args, dev, dense, delta, frames_group0, frames_dev, frames
             dense_cpu(frames32[k % F, :1]); k += 1
         extra["dense_cpu"] = {"value": k / (time.perf_counter() - t0), "unit": UNIT, "cores": torch.get_num_threads(),
                               "how": "dense PyTorch fp32 network, batch 1"}
-    try:
-        from examples.profile import roofline_of_dominant_kernel
-        extra["roofline"] = roofline_of_dominant_kernel(delta, frames_group0, stream, peaks())
-    except Exception as e:          # the roofline is reporting, never a reason to lose the bench line
-        extra["roofline"] = {"error": repr(e)}
+    hbm, tensor, kind = peaks()
+    for key, fn in (("roofline", lambda: None), ("ref_kernels_gpu", lambda: reference_kernels_gpu(delta, frames_group0, stream)),
+                    ("config1_fp32", lambda: config1_fp32(frames32, dev))):
+        try:                        # side measurements are reporting, never a reason to lose the bench line
+            if key == "roofline":
+                from examples.profile import roofline_report
+                extra["roofline"], extra["layer_density"] = roofline_report(delta, frames_group0, stream, (hbm, kind), tensor, ms_per_step,
+                                                                            group_fraction)
+            else:
+                extra[key] = fn()
+        except Exception as e:
+            extra[key] = {"error": repr(e)}
+    if not args.no_other_configs:
+        try:
+            extra["other_configs"] = other_configs()
+        except Exception as e:
+            extra["other_configs"] = {"error": repr(e)}
     return extra
 
 

@@ -25,7 +25,8 @@ def run(name, streams, frames, input_threshold=0.03, patches=None):
     dev = torch.device("cuda")
     DCConv2d.patch_tiles = (name != "resnet50") if patches is None else bool(patches)
     vids = torch.stack([make_video(name, s).frames(frames + 3) for s in range(streams)], dim=1)     # (F, S, 3, H, W)
-    dense, delta = build_pair(name, vids[:4, 0], device=dev, dtype=torch.float16)
+    heads = {"decode": True} if name in ("hrnet", "centernet") else {}      # key points / boxes decoded on the device
+    dense, delta = build_pair(name, vids[:4, 0], device=dev, dtype=torch.float16, **heads)
     fd = [vids[i].to(dev, torch.float16).contiguous(memory_format=torch.channels_last) for i in range(vids.shape[0])]
     DCThreshold.reset()
     with torch.no_grad():

@@ -4,6 +4,12 @@ small case that profiler captures are taken on (inputs larger than L2, well unde
     python examples/kernel_case.py pw     # tcgen05 pointwise 16->96 @112x112, fused ReLU6 + truncation, 32 streams (persistent CTAs over strided spans)
     python examples/kernel_case.py dw     # depthwise 3x3 96 ch @112x112 stride 2, fused ReLU6 + truncation, 32 streams
     python examples/kernel_case.py act    # stand-alone activation/truncation, 96 ch @112x112, 32 streams
+    python examples/kernel_case.py c3x3   # tcgen05 3x3 256->256 @64x64, fused ReLU + truncation, 32 streams, work list
+    python examples/kernel_case.py c3x3p  # the same layer on patch tiles (tiled TMA loads), no scratch
+    python examples/kernel_case.py stem   # tcgen05 RGB stem 3x3/2 3->32 @224x224, fused ReLU6 + truncation, 32 streams
+    python examples/kernel_case.py deconv # tcgen05 transposed 4x4/2 256->256 @34x60, fused ReLU + truncation, 16 streams, per-phase work lists
+    python examples/kernel_case.py dw576  # depthwise 3x3 576 ch @14x14 (a warp per channel slice), fully active, 64 streams
+    python examples/kernel_case.py sparsify  # RGB input delta + mask @224x224, 64 streams
 Prints the CUDA-event time per launch (L2 flushed between launches) and the algorithmic GB/s.
 """
 import os
@@ -74,6 +80,63 @@ def main():
                                     workspace=ws)
         run()
         nbytes = 2 * c * (int(mask.sum()) + 5 * int((torch.nn.functional.max_pool2d(mask.float(), 3, s, 1) > 0).sum())) + 4 * (mask.numel() + om.numel())
+    elif which in ("c3x3", "c3x3p", "stem", "deconv", "dw576"):
+        geo = {"c3x3": (32, 256, 256, 64, 64, 3, 1, 1, 1, 0.12, 1), "c3x3p": (32, 256, 256, 64, 64, 3, 1, 1, 1, 0.6, 1),
+               "stem": (32, 3, 32, 224, 224, 3, 2, 1, 1, 0.12, 2), "deconv": (16, 256, 256, 34, 60, 4, 2, 1, 1, 0.3, 1),
+               "dw576": (64, 576, 576, 14, 14, 3, 1, 1, 576, 1.0, 2)}[which]
+        n, cin, cout, h, w, k, s, pad, groups, density, act = geo
+        transposed = which == "deconv"
+        x = cl((torch.randn(n, cin, h, w, generator=g) * 0.3).to(dtype)).cuda()
+        mask = (torch.ones(n, 1, h, w, dtype=torch.int32) if density >= 1.0 else blob_mask(g, n, h, w, density)).cuda()
+        if transposed:
+            wt = (torch.randn(cin, cout, k, k, generator=g) * 0.05).to(dtype)
+            ho, wo = K.deconv_out_hw(h, w, (k, k), (s, s), (pad, pad), (1, 1))
+        else:
+            wt = (torch.randn(cout, cin // groups, k, k, generator=g) * (k * k * cin // groups) ** -0.5).to(dtype)
+            ho, wo = K.conv_out_hw(h, w, (k, k), (s, s), (pad, pad), (1, 1))
+        f = convert_filter_out_channels_last(wt, transposed=transposed).cuda()
+        desc = K.make_conv_desc(tuple(x.shape), cout, (ho, wo), (k, k), (s, s), (pad, pad), (1, 1), groups, 1)
+        packed = None
+        nb = _lib.lib.dc_filter_umma_bytes(desc, 1 if transposed else 0)
+        if nb > 0:
+            packed = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+            _lib.check(_lib.lib.dc_pack_filter_umma(desc, 1 if transposed else 0, f.data_ptr(), packed.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+        prev = cl(torch.randn(n, cout, ho, wo, generator=g).to(dtype)).cuda()
+        trunc = torch.zeros_like(prev)
+        out = torch.empty_like(prev)
+        om = torch.empty(n, 1, ho, wo, dtype=torch.int32, device="cuda")
+        ep = K.make_epilogue(prev, trunc, 0.02, act, 0)
+        if transposed:
+            ws = torch.zeros(K.deconv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
+            run = lambda: K.sparse_deconv(x, f, mask, None, (s, s), (pad, pad), (1, 1), 1, create_out_mask=True, out=out, out_mask=om,
+                                          epilogue=ep, desc=desc, filter_umma=packed, workspace=ws)
+            u = torch.nn.functional.conv_transpose2d(mask.float(), torch.ones(1, 1, k, k, device="cuda"), None, s, pad) > 0
+            taps = (k // s) ** 2
+        else:
+            ws = None if which == "c3x3p" else torch.zeros(K.conv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
+            run = lambda: K.sparse_conv(x, f, mask, None, (s, s), (pad, pad), (1, 1), groups, create_out_mask=True, out=out, out_mask=om,
+                                        filter_umma=packed, epilogue=ep, desc=desc, workspace=ws)
+            u = torch.nn.functional.max_pool2d(mask.float(), k, s, pad) > 0
+            taps = k * k
+        u_out = int(u.sum())
+        nbytes = 2 * (int(mask.sum()) * cin + taps * (cin // groups) * cout) + 2 * cout * 5 * u_out + 4 * (mask.numel() + om.numel())
+        print(f"{which}: {int(mask.sum())} active input pixels, {u_out} updated output pixels, {2.0 * u_out * taps * (cin // groups) * cout / 1e9:.2f} GFLOP")
+    elif which == "sparsify":
+        n, h, w = 64, 224, 224
+        prev = cl(torch.rand(n, 3, h, w, generator=g).to(dtype)).cuda()
+        x = prev.clone()
+        m0 = blob_mask(g, n, h, w, 0.1).cuda().bool().expand(n, 3, h, w)
+        x[m0] = 0.5 * x[m0] + 0.25
+        x = cl(x)
+        p = prev.clone()
+        delta = torch.empty_like(x)
+        mask = torch.empty(n, 1, h, w, dtype=torch.int32, device="cuda")
+
+        def run():
+            p.copy_(prev)
+            K.sparsify(x, p, delta, mask, 0.05)
+        run()
+        nbytes = 2 * 3 * (2 * mask.numel() + 2 * int(mask.sum())) + 4 * mask.numel()
     else:
         c, h, w = 96, 112, 112
         delta = cl((torch.randn(n, c, h, w, generator=g) * 0.3).to(dtype)).cuda()
@@ -95,6 +158,8 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1))
+    if _lib.lib.dc_umma_error() != 0:
+        raise SystemExit("a bounded wait of a tensor-core kernel gave up")
     t = sorted(times)[len(times) // 2]
     print(f"{which}: median {t * 1000:.1f} us per launch, algorithmic {nbytes / 1e6:.1f} MB, {nbytes / t / 1e6:.0f} GB/s")
 

@@ -114,9 +114,9 @@ class DenseOps:
             x, y = (pix % w).float(), (pix // w).float()
             g = lambda t, ch: t.float()[:, ch].reshape(n, -1).gather(1, pix)
             cx, cy, bw, bh = x + g(off, 0), y + g(off, 1), g(wh, 0), g(wh, 1)
-            det = torch.stack(((cx - bw / 2) * self.stride, (cy - bh / 2) * self.stride, (cx + bw / 2) * self.stride,
-                               (cy + bh / 2) * self.stride, torch.sigmoid(val), cls.float()), dim=2)
-            det = torch.where(ok[..., None], det, torch.tensor([0., 0., 0., 0., 0., -1.], device=det.device).expand_as(det))
+            okf = ok.float()
+            det = torch.stack(((cx - bw / 2) * self.stride * okf, (cy - bh / 2) * self.stride * okf, (cx + bw / 2) * self.stride * okf,
+                               (cy + bh / 2) * self.stride * okf, torch.sigmoid(val) * okf, cls.float() * okf - (1.0 - okf)), dim=2)
             return det, ok.sum(dim=1).to(torch.int32)
 
 

@@ -17,6 +17,12 @@ src/cuda/conv_kernel.cu:90-107,196-209 and src/cuda/other_nn_layers.cu:810-813):
   densify        esize*C*(2*M + 2*HW) + 4*HW ; upsample esize*C*(M_in + M_out) + 4*(HW_in + HW_out)
 
 with A_in = active input pixels, U_out = output pixels whose out-mask is 1, M = masked pixels.
+
+Roofline of a whole frame step: per layer t = max(flops_tile / P, bytes / BW) with flops_tile =
+2 * T_active * 64 * kh*kw*Cin*Cout/groups (T_active = 8x8 output tiles holding an updated pixel; transposed
+convolutions count kh*kw / stride^2 taps per output pixel), P the tensor-core peak for layers on the tcgen05 path
+and the fp32 CUDA-core peak for depthwise / thin / RGB layers, BW the HBM copy bandwidth; the layers of a step
+depend on each other, so the step's roofline time is the sum.
 """
 import collections
 
@@ -42,6 +48,8 @@ class OpProfiler:
     def __init__(self, stream):
         self.stream = stream
         self.records = []          # (class key, site description, ms, algorithmic bytes, flops)
+        self.details = []          # per record: mask densities (in, dilated out, kept out) and whether it runs on tensor cores
+        self.last_density, self.last_tensor = None, False
         self.flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
         self._orig = {}
 
@@ -62,7 +70,9 @@ class OpProfiler:
             groups = kwargs.get("groups", 1)
             b = es * (a_in * ci + u_out * co + kh * kw * cig * co) + 4 * (n * hi * wi + om.numel())
             taps = kh * kw / (kwargs["stride"][0] * kwargs["stride"][1]) if name == "sparse_deconv" else kh * kw
-            flops = 2.0 * u_out * taps * cig * co
+            flops = 2.0 * pre["tiles_active"] * 64 * taps * cig * co          # active 8x8 tiles, every pixel and tap of them
+            self.last_density = (a_in / max(mask.numel(), 1), u_out / max(om.numel(), 1), _count(om) / max(om.numel(), 1))
+            self.last_tensor = groups == 1 and ci >= 16 and co >= 16 and x.dtype == torch.float16
             kind = "dwconv" if groups > 1 else ("deconv" if name == "sparse_deconv" else "conv")
             key = f"{kind}{kh}x{kw}"
             ep = kwargs.get("epilogue")
@@ -125,7 +135,8 @@ class OpProfiler:
             else:
                 u = torch.nn.functional.conv_transpose2d(m, torch.ones(1, 1, kh, kw, device=m.device), None,
                                                          kwargs["stride"], kwargs["padding"])
-            return {"u_out": int((u > 0).sum().item())}
+            tiles = torch.nn.functional.max_pool2d((u > 0).float(), 8, 8, ceil_mode=True)
+            return {"u_out": int((u > 0).sum().item()), "tiles_active": int(tiles.sum().item())}
         return {}
 
     # ---- wrapping ---------------------------------------------------------------------------
@@ -139,8 +150,10 @@ class OpProfiler:
             e1.record(self.stream)
             e1.synchronize()
             ms = e0.elapsed_time(e1)
+            self.last_density, self.last_tensor = None, False
             key, site, nbytes, flops = self._account(name, args, kwargs, res, pre)
             self.records.append((key, site, ms, nbytes, flops))
+            self.details.append({"density": self.last_density, "tensor": self.last_tensor})
             return res
         return inner
 
@@ -166,19 +179,29 @@ class OpProfiler:
 
 
 def profile_frames(delta, frames, stream):
-    """Run ``frames`` (steady-state inputs) eagerly under the profiler; returns per-class totals."""
+    """Run ``frames`` (steady-state inputs) eagerly under the profiler; returns per-class totals, the records
+    and the per-record details."""
     with OpProfiler(stream) as prof, torch.no_grad():
         for f in frames:
             delta(f)
-    return prof.summary(), prof.records
+    return prof.summary(), prof.records, prof.details
 
 
-def roofline_of_dominant_kernel(delta, frames_dev, stream, peak):
-    """The kernel class with the largest share of a frame step, its algorithmic bytes per launch over
-    its measured (cold-L2) launch time, against the HBM copy bandwidth."""
+# DRAM bytes (read + written) of one profiler capture of a kernel class beside the algorithmic bytes of the captured
+# launch (profiles/*.md): traffic of a bench launch = its algorithmic bytes times this ratio. Classes without a
+# capture report no traffic.
+NCU_TRAFFIC_RATIO = {"conv1x1+act": 20.8 / 47.1}
+CUDA_CORE_PEAK_TFLOPS = 74.4      # fp32 FMA peak of the CUDA cores: 148 SMs x 128 lanes x 2 flops x 1.965 GHz
+
+
+def roofline_report(delta, frames_dev, stream, peak, tensor_peak_tflops, ms_per_step, group_fraction):
+    """Per-class table, the dominant class (algorithmic bytes per launch over its cold-L2 launch time against the HBM
+    copy bandwidth), the roofline of the whole step and of its convolution layers, and the per-layer mask
+    densities. ``group_fraction`` = streams profiled / streams of a step (the profile runs one stream group)."""
     peak_gbs, peak_kind = peak
     n = frames_dev.shape[0]
-    summary, _ = profile_frames(delta, [frames_dev[i % n] for i in range(3, 7)], stream)
+    n_frames = 4
+    summary, records, details = profile_frames(delta, [frames_dev[i % n] for i in range(3, 3 + n_frames)], stream)
     total_ms = sum(a["ms"] for a in summary.values())
     key, top = max(summary.items(), key=lambda kv: kv[1]["ms"])
     per_launch_bytes = top["bytes"] / top["launches"]
@@ -186,12 +209,34 @@ def roofline_of_dominant_kernel(delta, frames_dev, stream, peak):
     achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9
     table = {k: {"launches": a["launches"], "ms": round(a["ms"], 4), "share": round(a["ms"] / total_ms, 4),
                  "GBps": round(a["bytes"] / max(a["ms"], 1e-9) / 1e6, 1)} for k, a in summary.items()}
-    # DRAM traffic of the class's kernel from a profiler capture of one of its layers (16->96 @112x112, 32 streams:
-    # 20.8 MB read + written for 47.1 MB of algorithmic bytes: the writes and part of the caches stay in L2), scaled to
-    # this launch's algorithmic bytes; None for classes without such a capture.
-    traffic = per_launch_bytes * (20.8 / 47.1) if key == "conv1x1+act" else None
+    ratio = NCU_TRAFFIC_RATIO.get(key)
+    # whole-step roofline: every layer at the slower of its two bounds, summed (layers depend on each other)
+    scale = 1.0 / (n_frames * group_fraction)             # profiled totals -> one step of all streams
+    t_all = t_conv = ms_conv = bytes_all = flops_all = 0.0
+    for (k, _site, ms, nbytes, flops), det in zip(records, details):
+        p_flops = (tensor_peak_tflops if det["tensor"] else CUDA_CORE_PEAK_TFLOPS) * 1e12
+        t = max(flops / p_flops, nbytes / (peak_gbs * 1e9))
+        t_all += t
+        bytes_all += nbytes
+        flops_all += flops
+        if "conv" in k:
+            t_conv += t
+            ms_conv += ms
+    per_layer = len(records) // n_frames
+    density = [{"layer": f"{k} {site}", "in": round(d["density"][0], 4), "out_dilated": round(d["density"][1], 4),
+                "out_kept": round(d["density"][2], 4)}
+               for (k, site, *_), d in list(zip(records, details))[-per_layer:] if d["density"] is not None]
+    frame = {"algorithmic_bytes_per_step": bytes_all * scale, "flops_tile_per_step": flops_all * scale,
+             "t_roofline_ms": t_all * scale * 1e3, "achieved": t_all * scale * 1e3 / ms_per_step,
+             "how": "sum over layers of max(flops_tile / peak flops, bytes / HBM bandwidth) over the measured step time (CUDA graph)",
+             "conv_layers": {"t_roofline_ms": t_conv * scale * 1e3, "cold_serialised_ms": ms_conv * scale,
+                             "achieved": t_conv * 1e3 / max(ms_conv, 1e-9),
+                             "how": "convolution layers only, against the sum of their per-launch times (cold L2, launches serialised)"},
+             "peaks": {"hbm_gbs": peak_gbs, "tensor_tflops": tensor_peak_tflops, "cuda_core_tflops": CUDA_CORE_PEAK_TFLOPS}}
     return {"bound": "hbm", "kernel": key, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-            "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}", "traffic": traffic,
-            "traffic_how": "scaled from an ncu capture of one layer of the class (profiles/k_pw_umma_16to96_112x112_32streams.md)",
+            "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}",
+            "traffic": per_launch_bytes * ratio if ratio is not None else None,
+            "traffic_how": "algorithmic bytes of the launch times the DRAM/algorithmic ratio of an ncu capture of one layer of the class (profiles/)" if ratio is not None else "no ncu capture of this class",
+            "timing": "per-launch CUDA events with L2 flushed before every launch, launches serialised (not the in-graph time)",
             "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms, "launches_timed": top["launches"],
-            "share_of_step": top["ms"] / total_ms, "kernels": table}
+            "share_of_step": top["ms"] / total_ms, "kernels": table, "frame": frame}, density

@@ -122,16 +122,59 @@ def add(a, ma, b, mb, prev_out, wa, wb, activation, dense_out):
 
 
 def max_pool(x, mask, prev_in, kernel, stride, padding):
-    from .delta_ops import conv_out_size
+    """``padding``: (h, w) or (top, bottom, left, right) as in the Python API; the kernel config takes
+    (top, left, bottom, right) (src/deltacnn/cuda_kernels.py:43-47)."""
+    from .delta_ops import conv_out_size, _pad4
     n, c, h, w = x.shape
     ho, wo = conv_out_size(h, w, kernel, stride, padding, (1, 1))
+    pt, pb, pl, pr = _pad4(padding)
     out = torch.zeros((n, c, ho, wo), dtype=x.dtype, device=x.device).contiguous(memory_format=torch.channels_last)
     om = torch.zeros((n, 1, ho, wo), dtype=torch.int32, device=x.device)
     shape = _ints(n, h, w, c, ho, wo, c)
-    geom = _ints(kernel[0], kernel[1], stride[0], stride[1], padding[0], padding[1], padding[0], padding[1], 1, 1, 1)
+    geom = _ints(kernel[0], kernel[1], stride[0], stride[1], pt, pl, pb, pr, 1, 1, 1)
     torch.cuda.synchronize()
     _check(lib().ref_pool(_f16(x), _p(x), _p(prev_in), _p(out), _p(mask), _p(om), shape, geom, 0, 1), "pool")
     return out, om
+
+
+def global_avg_pool(x, mask):
+    """Average pool to 1x1 as the reference's Python wrapper sets it up (src/deltacnn/cuda_kernels.py:101-124):
+    a pre-zeroed float32 output (the fp16 kernel accumulates into fp32 with atomics), a pre-zeroed out-mask, window =
+    the whole image; the result is cast back to the input dtype."""
+    n, c, h, w = x.shape
+    out = torch.zeros((n, c, 1, 1), dtype=torch.float32, device=x.device).contiguous(memory_format=torch.channels_last)
+    om = torch.zeros((n, 1, 1, 1), dtype=torch.int32, device=x.device)
+    shape = _ints(n, h, w, c, 1, 1, c)
+    geom = _ints(h, w, 1, 1, 0, 0, 0, 0, 1, 1, 1)
+    torch.cuda.synchronize()
+    _check(lib().ref_pool(_f16(x), _p(x), _p(None), _p(out), _p(mask), _p(om), shape, geom, 1, 1), "global_avg_pool")
+    return out.to(x.dtype), om
+
+
+def add_to_dense(a, b, mask_a):
+    n, c, h, w = a.shape
+    torch.cuda.synchronize()
+    _check(lib().ref_add_to_dense(_f16(a), _p(a), _p(b), _p(mask_a), n, h, w, c, 0, 1), "add_to_dense")
+    return b
+
+
+def concatenate(a, ma, b, mb):
+    n, ca, h, w = a.shape
+    cb = b.shape[1]
+    out = torch.zeros((n, ca + cb, h, w), dtype=a.dtype, device=a.device).contiguous(memory_format=torch.channels_last)
+    mo = torch.zeros((n, 1, h, w), dtype=torch.int32, device=a.device)
+    torch.cuda.synchronize()
+    _check(lib().ref_concat(_f16(a), _p(a), _p(b), _p(out), _p(ma), _p(mb), _p(mo), n, h, w, ca, cb, 1), "concat")
+    return out, mo
+
+
+def mul_add(x, mask, scale, bias):
+    n, c, h, w = x.shape
+    out = torch.zeros_like(x)
+    mo = torch.zeros((n, 1, h, w), dtype=torch.int32, device=x.device)
+    torch.cuda.synchronize()
+    _check(lib().ref_mul_add(_f16(x), _p(x), _p(mask), _p(out), _p(mo), _p(scale), _p(bias), n, h, w, c, 1), "mul_add")
+    return out, mo
 
 
 def upsample(x, mask, scale):

@@ -57,3 +57,45 @@ def test_pingpong_indexing():
     idx = [bench.pingpong(t, n) for t in range(12)]
     assert idx == [0, 1, 2, 3, 4, 3, 2, 1, 0, 1, 2, 3]
     assert all(abs(a - b) == 1 for a, b in zip(idx, idx[1:]))   # consecutive frames are neighbours in time
+
+
+def _checksum_worker(rank, world, port, total, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import bench
+    ids = bench.stream_ids(rank, world, 0, total)
+    outputs = torch.stack([_fake_logits(s) for s in ids])          # what this rank's streams produced
+    sums = bench.stream_checksums(outputs)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (ids, sums))
+    all_ids = [i for part in gathered for i in part[0]]
+    all_sums = [v for part in gathered for v in part[1]]
+    out[rank] = (ids, bench.combine_checksums(all_ids, all_sums))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _fake_logits(stream_id):
+    g = torch.Generator().manual_seed(1000 + stream_id)
+    return torch.randn(10, generator=g)
+
+
+def test_round_robin_partition_gives_the_one_gpu_checksum():
+    """Streams dealt round-robin to two ranks (stream s on rank s mod 2): the digest over all streams' outputs equals
+    the digest of a single process running every stream, and changes when any stream's output changes."""
+    sys.path.insert(0, ROOT)
+    import bench
+    world, total = 2, 6
+    port = _free_port()
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_checksum_worker, args=(world, port, total, out), nprocs=world, join=True)
+    assert out[0][0] == [0, 2, 4] and out[1][0] == [1, 3, 5]
+    single_ids = bench.stream_ids(0, 1, 0, total)
+    single = bench.combine_checksums(single_ids, bench.stream_checksums(torch.stack([_fake_logits(s) for s in single_ids])))
+    assert out[0][1] == out[1][1] == single
+    changed = [_fake_logits(s) for s in single_ids]
+    changed[3] = changed[3] + 1e-6
+    assert bench.combine_checksums(single_ids, bench.stream_checksums(torch.stack(changed))) != single
+    assert bench.stream_ids(1, 4, 16) == list(range(16, 32))
