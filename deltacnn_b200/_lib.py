@@ -22,6 +22,12 @@ class ConvDesc(ctypes.Structure):
         "pad_top", "pad_left", "pad_bottom", "pad_right", "dil_h", "dil_w", "groups", "dtype")]
 
 
+class IrbDesc(ctypes.Structure):
+    """dc_irb_desc."""
+    _fields_ = [(n, c_int) for n in ("n", "h", "w", "c_in", "c_hidden", "c_out", "stride", "residual", "act_expand", "act_dw", "dtype")] + \
+               [("thr_expand", c_float), ("thr_dw", c_float)]
+
+
 class Epilogue(ctypes.Structure):
     """dc_epilogue."""
     _fields_ = [("prev_out", c_void_p), ("truncated", c_void_p), ("threshold", c_float),
@@ -63,6 +69,8 @@ _SIGNATURES = {
     "dc_concat": (c_int, [_P, _P, _P, _P, _P, _P, c_i64, c_int, c_int, c_int, _P]),
     "dc_densify": (c_int, [_P, _P, _P, _P, c_i64, c_int, c_int, c_int, _P]),
     "dc_compact_mask": (c_int, [_P, c_i64, _P, _P, _P]),
+    "dc_irb_supported": (c_int, [ctypes.POINTER(IrbDesc)]),
+    "dc_irb_fused": (c_int, [ctypes.POINTER(IrbDesc), _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "dc_sparsify_dilated": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P]),
     "dc_linear_delta": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "dc_heatmap_argmax": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),

@@ -47,6 +47,7 @@ size_t filter_umma_bytes(const dc_conv_desc* d, int transposed);
 int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, void* packed, cudaStream_t st);
 int umma_error_code();
 int stem_umma_error_code();
+int irb_error_code();
 int conv_stem_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
                    int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 int conv_thin(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
@@ -93,7 +94,9 @@ int dc_last_cuda_error(void) { return t_last_cuda_error; }
 
 int dc_umma_error(void) {
     const int a = umma_error_code();
-    return a != 0 ? a : stem_umma_error_code();
+    if (a != 0) return a;
+    const int b = stem_umma_error_code();
+    return b != 0 ? b : irb_error_code();
 }
 
 int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,

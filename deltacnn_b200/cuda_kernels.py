@@ -277,6 +277,11 @@ def sparsify_u8(frame_u8, scale, offset, prev_in, delta, mask, threshold):
     _check_feature(delta, "delta")
     _check_like(prev_in, delta, "prev_in")
     _check_mask(mask, delta, "mask")
+    for t, name in ((frame_u8, "frame"), (scale, "scale"), (offset, "offset"), (prev_in, "prev_in"), (mask, "mask")):
+        if t.device != delta.device:
+            raise RuntimeError(f"deltacnn_b200.sparsify_u8: {name} is on {t.device}, the delta tensor on {delta.device}")
+    if scale.dtype != torch.float32 or offset.dtype != torch.float32 or scale.numel() != delta.shape[1] or offset.numel() != delta.shape[1]:
+        raise RuntimeError("deltacnn_b200.sparsify_u8: scale and offset must be float32 with one entry per channel")
     if frame_u8.dtype != torch.uint8 or not frame_u8.is_contiguous() or \
             tuple(frame_u8.shape) != (delta.shape[0], delta.shape[2], delta.shape[3], delta.shape[1]):
         raise RuntimeError("deltacnn_b200.sparsify_u8: the frame must be a contiguous uint8 tensor of shape (N, H, W, C) matching delta")

@@ -581,7 +581,10 @@ class DCSparsify(DCModule):
                 self.mask = torch.empty((n, 1, h, w), dtype=torch.int, device=input.device)
             if self._delta is None or self._delta.shape != self.prev_in.shape or not DCConv2d.reuse_buffers:
                 self._delta = torch.empty_like(self.prev_in)
-            scale, offset, _ = self._u8
+            scale, offset, dtype = self._u8
+            if scale.device != input.device:              # the tables go to the kernel as device pointers
+                scale, offset = scale.to(input.device), offset.to(input.device)
+                self._u8 = (scale, offset, dtype)
             K.sparsify_u8(input, scale, offset, self.prev_in, self._delta, self.mask, DCThreshold.get(self))
             return self._delta, self.mask
         if DCConv2d.backend == DCBackend.cudnn:

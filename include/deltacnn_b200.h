@@ -249,6 +249,32 @@ int dc_densify(const void* delta, const int32_t* mask, void* prev_out, void* den
  * src/cuda/conv_kernel.cu:46-108). */
 int dc_compact_mask(const int32_t* mask, int64_t npix, int32_t* indices, int32_t* count, void* stream);
 
+/* Fused inverted-residual block (MobileNetV2): expansion 1x1 + activation/truncation, depthwise 3x3 (padding 1,
+ * stride 1 or 2) + activation/truncation, projection 1x1, optional residual add of the block input, in ONE launch for
+ * steady-state frames (no bias: the reference adds biases on the first frame only, src/deltacnn/sparse_layers.py:616).
+ * No reference counterpart: it replaces the three sparse_conv_bias_wrapper_masked calls, two deltacnn_activate_truncate
+ * calls and the sparse_add_tensors_wrapper call of a block (example/mobilenet_deltacnn.py:87-128), with the same
+ * results and cache updates bit for bit as dc_conv2d with fused epilogues. For small maps: the input rows of a band of
+ * output rows, halo included, must fit 128 pixels and at most 8 bands cover the map (14x14 and 7x7 maps); fp16;
+ * c_hidden a multiple of 64 (<= 1024), c_in a multiple of 8, c_out a multiple of 16; activations none / ReLU / ReLU6.
+ * Other shapes return DC_ERR_UNSUPPORTED (dc_irb_supported tells in advance) and the caller runs the three layers. */
+typedef struct dc_irb_desc {
+    int32_t n, h, w;                 /* block input: n streams of h x w pixels */
+    int32_t c_in, c_hidden, c_out;
+    int32_t stride;                  /* of the depthwise convolution */
+    int32_t residual;                /* != 0: out = projection + x where x is active (stride 1, c_in == c_out) */
+    int32_t act_expand, act_dw;      /* dc_activation of the two truncation layers */
+    int32_t dtype;                   /* DC_F16 */
+    float thr_expand, thr_dw;        /* their thresholds */
+} dc_irb_desc;
+int dc_irb_supported(const dc_irb_desc* desc);
+/* x, mask_in: block input (delta, mask). w_expand_umma / w_project_umma: DC_FILTER_UMMA images of the two 1x1 filters;
+ * w_dw_hwio: depthwise filter [3][3][1][c_hidden]. prev_* / trunc_*: the caches of the two truncation layers (n, h, w,
+ * c_hidden and n, h_out, w_out, c_hidden). out, mask_out: block output (n, h_out, w_out, c_out). */
+int dc_irb_fused(const dc_irb_desc* desc, const void* x, const int32_t* mask_in, const void* w_expand_umma, const void* w_dw_hwio,
+                 const void* w_project_umma, void* prev_expand, void* trunc_expand, void* prev_dw, void* trunc_dw, void* out,
+                 int32_t* mask_out, void* stream);
+
 /* ---- task heads behind the delta path -------------------------------------------------------------------
  * No counterpart among the reference's kernels: its networks end with DCDensify and dense torch code
  * (example/mobilenet_deltacnn.py:216-227: adaptive_avg_pooling -> densify -> reshape -> nn.Linear;

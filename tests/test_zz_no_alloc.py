@@ -57,7 +57,7 @@ def _case(seed, density, n, cin, cout, h, w, ksz, stride, pad, depthwise):
                 geom=(n, cout, ho, wo), conv=((stride, stride), (pad, pad)), keep=f)
 
 
-THRESHOLD, ACTIVATION = 0.7, 2
+THRESHOLD, ACTIVATION = 0.3, 2
 
 
 def _run(entry, c):
