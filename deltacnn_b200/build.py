@@ -35,7 +35,8 @@ def _newest_header():
 
 def _compile(src, verbose):
     obj = os.path.join(OBJ_DIR, src[:-3] + ".o")
-    cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
+    extra = os.environ.get("DC_NVCC_EXTRA", "").split()          # e.g. -DDC_IRB_STAMPS for a development build
+    cmd = ["nvcc"] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{res.stdout}\n{res.stderr}")

@@ -69,8 +69,11 @@ __global__ void __launch_bounds__(256) k_sparsify(const T* __restrict__ x, T* __
 }
 
 // RGB frames (3 channels): a thread owns the run of pixels that fills three 16-byte vectors (8 fp16
-// pixels or 4 fp32 pixels), so the two full reads of the frame are 16-byte accesses; the mask words
-// go out as vectors too and only the (few) active pixels are written back element-wise.
+// pixels or 4 fp32 pixels), so the two full reads of the frame are 16-byte accesses and the mask words go out as
+// vectors. A run with at least one active pixel writes its delta and cache vectors whole (the cache keeps its old
+// value at the run's inactive pixels; their delta, which the contract leaves undefined, receives the sub-threshold
+// difference): element-wise stores of the active pixels alone kept the load/store queue full (ncu: lg_throttle 16
+// stalled warps per issue). Runs without an active pixel write nothing but the mask.
 template <typename T>
 __global__ void __launch_bounds__(256) k_sparsify_c3(const T* __restrict__ x, T* __restrict__ prev, T* __restrict__ delta,
                                                      int32_t* __restrict__ mask, int64_t npix, float thr) {
@@ -82,25 +85,34 @@ __global__ void __launch_bounds__(256) k_sparsify_c3(const T* __restrict__ x, T*
     for (int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gi < ngroups; gi += (int64_t)gridDim.x * blockDim.x) {
         alignas(16) T xa[NE];
         alignas(16) T pa[NE];
+        alignas(16) T da[NE];
         const uint4* xs = reinterpret_cast<const uint4*>(x + gi * NE);
         const uint4* ps = reinterpret_cast<const uint4*>(prev + gi * NE);
 #pragma unroll
         for (int i = 0; i < 3; ++i) { reinterpret_cast<uint4*>(xa)[i] = xs[i]; reinterpret_cast<uint4*>(pa)[i] = ps[i]; }
         alignas(16) int32_t m[PPT];
+        bool any = false;
 #pragma unroll
         for (int px = 0; px < PPT; ++px) {
             bool hit = false;
 #pragma unroll
-            for (int c = 0; c < 3; ++c) hit |= fabsf(rnd<T>(to_f<T>(xa[px * 3 + c]) - to_f<T>(pa[px * 3 + c]))) > thr;
-            m[px] = hit ? 1 : 0;
-            if (hit) {
-                const int64_t o = (gi * PPT + px) * 3;
-#pragma unroll
-                for (int c = 0; c < 3; ++c) {
-                    delta[o + c] = from_f<T>(to_f<T>(xa[px * 3 + c]) - to_f<T>(pa[px * 3 + c]));
-                    prev[o + c] = xa[px * 3 + c];
-                }
+            for (int c = 0; c < 3; ++c) {
+                const float d = rnd<T>(to_f<T>(xa[px * 3 + c]) - to_f<T>(pa[px * 3 + c]));
+                da[px * 3 + c] = from_f<T>(d);
+                hit |= fabsf(d) > thr;
             }
+            m[px] = hit ? 1 : 0;
+            any |= hit;
+            if (hit) {
+#pragma unroll
+                for (int c = 0; c < 3; ++c) pa[px * 3 + c] = xa[px * 3 + c];
+            }
+        }
+        if (any) {
+            uint4* dd = reinterpret_cast<uint4*>(delta + gi * NE);
+            uint4* pd = reinterpret_cast<uint4*>(prev + gi * NE);
+#pragma unroll
+            for (int i = 0; i < 3; ++i) { dd[i] = reinterpret_cast<const uint4*>(da)[i]; pd[i] = reinterpret_cast<const uint4*>(pa)[i]; }
         }
 #pragma unroll
         for (int i = 0; i < PPT / 4; ++i) reinterpret_cast<int4*>(mask + gi * PPT)[i] = reinterpret_cast<const int4*>(m)[i];
@@ -538,7 +550,7 @@ static int sparsify_t(const T* x, T* prev, T* delta, int32_t* mask, int64_t npix
     constexpr int V = VecTraits<T>::kVec;
     const int W = pick_w<T>(C, {x, prev, delta});
     const float t = host_round_threshold<T>(thr);
-    if (C == 3 && aligned16(x) && aligned16(prev) && aligned16(mask)) {
+    if (C == 3 && aligned16(x) && aligned16(prev) && aligned16(delta) && aligned16(mask)) {
         constexpr int PPT = sizeof(T) == 2 ? 8 : 4;
         const int64_t ngroups = npix / PPT;
         if (ngroups > 0) {

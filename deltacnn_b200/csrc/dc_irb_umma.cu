@@ -27,6 +27,12 @@
 namespace dc {
 
 __device__ int g_irb_error = 0;       // sticky: the bounded wait that gave up (2 filter copy, 3 accumulator)
+#ifdef DC_IRB_STAMPS                  // development build: phase time stamps of CTA (0, 0)
+__device__ long long g_irb_stamps[16];
+#define IRB_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_irb_stamps[i] = clock64(); } while (0)
+#else
+#define IRB_STAMP(i) do { } while (0)
+#endif
 
 constexpr int kIrbThreads = 512;
 constexpr int kIrbWarps = kIrbThreads / 32;
@@ -116,6 +122,7 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
     grid_dep_launch();                 // only after the tensor memory is held (a dependent CTA allocates before it waits)
     const uint32_t tmem_base = s_u32[0];
     volatile uint32_t* ok_flag = &s_u32[1];
+    IRB_STAMP(0);
     const uint32_t w1_chunk_bytes = (uint32_t)p.nc * 128u;                          // one K block of a chunk
     auto load_w1 = [&](int j, int buf) {                                            // thread 0 only
         mbar_expect_tx(bar_w1(buf), (uint32_t)p.nkb1 * w1_chunk_bytes);
@@ -130,6 +137,7 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
     grid_dep_wait();
 
     // ---- A: slot table and input gather ----
+    IRB_STAMP(1);
     if (tid < 128) {
         const int slot = tid;
         const int ry = slot / p.w, ix = slot - ry * p.w;
@@ -163,6 +171,8 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
         fence_proxy_async();
     }
     __syncthreads();
+
+    IRB_STAMP(2);
 
     // ---- B: expansion GEMM, chunk by chunk; chunk j+1 runs on the tensor core while chunk j is converted ----
     const uint32_t idesc1 = make_idesc(p.nc);
@@ -221,16 +231,20 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
         tc_fence_before();
         __syncthreads();
     }
+    IRB_STAMP(3);
     const bool ok_b = *ok_flag != 0;      // uniform (written before the last barrier of the loop, or read after a barrier)
 
     // the projection filter's first K blocks can come in while the truncation and depthwise phases run
-    auto load_w2 = [&](int kb) {                                                    // thread 0 only
-        const int st = kb % p.w2_stages;
+    auto load_w2 = [&](int item) {                                                  // thread 0 only; item = K block * N tiles + N tile
+        const int st = item % p.w2_stages;
+        const int kb = item / p.ntile2, nt = item - kb * p.ntile2;
         mbar_expect_tx(bar_w2_full(st), p.w2_stage_bytes);
-        bulk_g2s(smem_u32(sW2 + (size_t)st * p.w2_stage_bytes), p.w2 + (size_t)kb * p.w2_kb_stride, p.w2_stage_bytes, bar_w2_full(st));
+        bulk_g2s(smem_u32(sW2 + (size_t)st * p.w2_stage_bytes), p.w2 + (size_t)kb * p.w2_kb_stride + (size_t)nt * p.w2_stage_bytes,
+                 p.w2_stage_bytes, bar_w2_full(st));
     };
+    const int w2_items = p.nkb2 * p.ntile2;
     if (ok_b && tid == 0)
-        for (int kb = 0; kb < p.w2_stages && kb < p.nkb2; ++kb) load_w2(kb);
+        for (int it = 0; it < p.w2_stages && it < w2_items; ++it) load_w2(it);
 
     // ---- C: truncation step of the expansion, a warp per pixel slot ----
     const __half2 thr1 = __float2half2_rn(p.thr1), thr2 = __float2half2_rn(p.thr2);
@@ -282,10 +296,13 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
         }
     };
     if (ok_b) truncate_slots(false);      // halo pixels: read-only here, the neighbouring band owns their caches
+    IRB_STAMP(4);
     if (gridDim.y > 1) cluster_sync_all();        // every band has read its halo before any band updates a cache
+    IRB_STAMP(5);
     if (ok_b) truncate_slots(true);
     __syncthreads();
 
+    IRB_STAMP(6);
     // ---- D: depthwise 3x3 + its truncation step, a warp per output pixel; results replace E in place ----
     if (ok_b) {
         const int rounds = (o1 - o0 + p.rows_per_round - 1) / p.rows_per_round;
@@ -391,27 +408,27 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
     __syncthreads();
     tc_fence_after();
 
+    IRB_STAMP(7);
     // ---- E: projection GEMM, K = hidden channels in blocks of 64, filter blocks through the ring ----
     if (ok_b && tid == 0) {
         const uint32_t idesc2 = make_idesc(p.bn2);
         const uint64_t ad0 = make_smem_desc(smem_u32(sE));
         const uint64_t bd0 = make_smem_desc(smem_u32(sW2));
         bool fine = true;
-        for (int kb = 0; kb < p.nkb2 && fine; ++kb) {
-            const int st = kb % p.w2_stages;
-            const uint32_t par = (uint32_t)((kb / p.w2_stages) & 1);
+        for (int it = 0; it < w2_items && fine; ++it) {
+            const int st = it % p.w2_stages;
+            const uint32_t par = (uint32_t)((it / p.w2_stages) & 1);
+            const int kb = it / p.ntile2, nt = it - kb * p.ntile2;
             if (!mbar_wait(bar_w2_full(st), par, ok_flag)) { fine = false; break; }
             tc_fence_after();
             const uint64_t ad = ad0 + (uint64_t)((uint32_t)kb * (p.e_kb_bytes >> 4));
-            for (int nt = 0; nt < p.ntile2; ++nt) {
-                const uint64_t bd = bd0 + (uint64_t)(((uint32_t)st * p.w2_stage_bytes + (uint32_t)nt * (uint32_t)p.bn2 * 128u) >> 4);
-                for (int ks = 0; ks < kKBlock / 16; ++ks)
-                    umma_f16(tmem_base + (uint32_t)(nt * p.bn2), ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc2, (kb > 0 || ks > 0) ? 1u : 0u);
-            }
+            const uint64_t bd = bd0 + (uint64_t)(((uint32_t)st * p.w2_stage_bytes) >> 4);
+            for (int ks = 0; ks < kKBlock / 16; ++ks)
+                umma_f16(tmem_base + (uint32_t)(nt * p.bn2), ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc2, (kb > 0 || ks > 0) ? 1u : 0u);
             umma_commit(bar_w2_free(st));
-            if (kb + p.w2_stages < p.nkb2) {
+            if (it + p.w2_stages < w2_items) {
                 if (!mbar_wait(bar_w2_free(st), par, ok_flag)) { fine = false; break; }
-                load_w2(kb + p.w2_stages);
+                load_w2(it + p.w2_stages);
             }
         }
         if (fine) umma_commit(bar_fin);
@@ -422,6 +439,7 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
     const bool ok_e = ok_b && *ok_flag != 0;
     tc_fence_after();
 
+    IRB_STAMP(8);
     // ---- F: tensor memory -> fp16 staging tile (over E) -> coalesced rows, residual, out-mask ----
     if (ok_e) {
         {
@@ -472,6 +490,7 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
         }
     }
 
+    IRB_STAMP(9);
     // ---- drain: every issued MMA and copy has completed on the success path; release tensor memory ----
     tc_fence_before();
     __syncthreads();
@@ -520,9 +539,12 @@ static IrbPlan plan_irb(const dc_irb_desc* d) {
     if (p.bn2 * p.ntile2 != d->c_out) return pl;        // equal N tiles only
     pl.nv = divup(d->c_hidden / 8, 32);
     p.stage_pitch = (uint32_t)d->c_out * 2u + 16u;
-    const uint32_t e_bytes = (uint32_t)p.nkb2 * p.e_kb_bytes + (16u * 1024u - p.e_kb_bytes);     // + what an MMA reads past the last K block
+    // An MMA reads 128 rows of every K block, i.e. up to 16 KB - e_kb_bytes past a block that holds fewer pixel slots: into
+    // the next K block or the buffer behind it (its rows beyond the slots are never used). Only the end of the whole
+    // layout needs room for that, which the depthwise filter, the tables and the alignment slack provide.
+    const uint32_t e_bytes = (uint32_t)p.nkb2 * p.e_kb_bytes;
     if ((uint32_t)(p.rows_per_band * p.wo) * p.stage_pitch > e_bytes) return pl;
-    const uint32_t x_bytes = (uint32_t)p.nkb1 * p.e_kb_bytes + (16u * 1024u - p.e_kb_bytes);
+    const uint32_t x_bytes = (uint32_t)p.nkb1 * p.e_kb_bytes;
     const uint32_t wd_bytes = ((uint32_t)9 * d->c_hidden * 2u + 1023u) & ~1023u;
     const uint32_t misc_bytes = 24 * 8 + 128 * 4 + 5 * 128 + 64;
     const uint32_t budget = 227u * 1024u - 1024u /* alignment slack */;
@@ -533,8 +555,8 @@ static IrbPlan plan_irb(const dc_irb_desc* d) {
         if (d->c_hidden % nc != 0) continue;
         const uint32_t w1b = (uint32_t)p.nkb1 * nc * 128u;
         const uint32_t total = e_bytes + x_bytes + 2u * w1b + wd_bytes + misc_bytes;
-        // the projection ring lives in the input + expansion-filter area: at least two stages must fit
-        if (total <= budget && x_bytes + 2u * w1b >= 2u * (uint32_t)d->c_out * 128u) { p.nc = nc; break; }
+        // the projection ring (stages of one N tile of one K block) lives in the input + expansion-filter area: at least two must fit
+        if (total <= budget && x_bytes + 2u * w1b >= 2u * (uint32_t)p.bn2 * 128u) { p.nc = nc; break; }
     }
     if (p.nc == 0) return pl;
     p.nchunks = d->c_hidden / p.nc;
@@ -544,19 +566,28 @@ static IrbPlan plan_irb(const dc_irb_desc* d) {
     p.off_wd = p.off_w1 + 2u * p.w1_buf_bytes;
     p.off_misc = p.off_wd + wd_bytes;
     p.off_w2 = p.off_x;
-    p.w2_stage_bytes = (uint32_t)d->c_out * 128u;
+    p.w2_stage_bytes = (uint32_t)p.bn2 * 128u;
     p.w2_stages = (int)((x_bytes + 2u * p.w1_buf_bytes) / p.w2_stage_bytes);
     if (p.w2_stages > 8) p.w2_stages = 8;
-    if (p.w2_stages > p.nkb2) p.w2_stages = p.nkb2;
+    if (p.w2_stages > p.nkb2 * p.ntile2) p.w2_stages = p.nkb2 * p.ntile2;
+
     p.acc_stride = (p.nc + 31) & ~31;
     int need = 2 * p.acc_stride > d->c_out ? 2 * p.acc_stride : d->c_out;
     p.tmem_cols = 32;
     while (p.tmem_cols < need) p.tmem_cols <<= 1;
     if (p.tmem_cols > 512) return pl;
     pl.smem = (size_t)p.off_misc + misc_bytes + 1024;
+    const size_t reach = (size_t)p.off_x + x_bytes - p.e_kb_bytes + 16u * 1024u + 1024u;      // what the last input K block's MMA reads
+    if (pl.smem < reach) pl.smem = reach;
     pl.ok = pl.smem <= 227 * 1024;
     return pl;
 }
+
+#ifdef DC_IRB_STAMPS
+extern "C" int dc_irb_debug_stamps(long long* out16) {
+    return cudaMemcpyFromSymbol(out16, g_irb_stamps, 16 * sizeof(long long)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int irb_error_code() {
     int v = 0;

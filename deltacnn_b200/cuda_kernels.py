@@ -445,6 +445,43 @@ def centernet_decode(heat, wh, offset, mask, state=None, topk=100, min_score=0.0
     return det, count, state
 
 
+def make_irb_desc(x_shape, c_hidden, c_out, stride, residual, act_expand, act_dw, thr_expand, thr_dw):
+    d = _lib.IrbDesc()
+    d.n, d.c_in, d.h, d.w = x_shape
+    d.c_hidden, d.c_out, d.stride, d.residual = int(c_hidden), int(c_out), int(stride), 1 if residual else 0
+    d.act_expand, d.act_dw, d.dtype = max(int(act_expand), 0), max(int(act_dw), 0), _lib.DC_F16
+    d.thr_expand, d.thr_dw = float(thr_expand), float(thr_dw)
+    return d
+
+
+def irb_supported(desc):
+    """True when ``fused_inverted_residual`` has a kernel for this block shape (small maps, fp16)."""
+    return bool(lib.dc_irb_supported(desc))
+
+
+def fused_inverted_residual(x, mask, w_expand_umma, w_dw, w_project_umma, prev_expand, trunc_expand, prev_dw, trunc_dw, out, mask_out, desc):
+    """One launch for a whole inverted-residual block on a steady-state frame: expansion 1x1 + activation/truncation,
+    depthwise 3x3 + activation/truncation, projection 1x1 and the residual add, with the results and cache updates of
+    the separate calls bit for bit. No reference counterpart (the reference issues six launches per block,
+    example/mobilenet_deltacnn.py:87-128). ``desc`` from ``make_irb_desc``; returns (out, mask_out)."""
+    _check_feature(x, "x")
+    _check_mask(mask, x, "mask")
+    n, _, h, w = x.shape
+    ho, wo = (h - 1) // desc.stride + 1, (w - 1) // desc.stride + 1
+    for t, shape, name in ((prev_expand, (n, desc.c_hidden, h, w), "prev_expand"), (trunc_expand, (n, desc.c_hidden, h, w), "trunc_expand"),
+                           (prev_dw, (n, desc.c_hidden, ho, wo), "prev_dw"), (trunc_dw, (n, desc.c_hidden, ho, wo), "trunc_dw"),
+                           (out, (n, desc.c_out, ho, wo), "out")):
+        if tuple(t.shape) != shape or t.dtype != x.dtype or t.device != x.device or not t.is_contiguous(memory_format=torch.channels_last):
+            raise RuntimeError(f"deltacnn_b200.fused_inverted_residual: {name} must be a channels_last {shape} tensor like x "
+                               "(call reset_layers() after a batch or resolution change)")
+    if mask_out.dtype != torch.int32 or mask_out.numel() != n * ho * wo:
+        raise RuntimeError("deltacnn_b200.fused_inverted_residual: mask_out must hold one int32 per output pixel")
+    check(lib.dc_irb_fused(desc, x.data_ptr(), mask.data_ptr(), w_expand_umma.data_ptr(), w_dw.data_ptr(), w_project_umma.data_ptr(),
+                           prev_expand.data_ptr(), trunc_expand.data_ptr(), prev_dw.data_ptr(), trunc_dw.data_ptr(), out.data_ptr(),
+                           mask_out.data_ptr(), _stream()), "fused_inverted_residual")
+    return out, mask_out
+
+
 def compact_mask(mask, indices=None, count=None):
     """Indices of the active pixels of ``mask`` (order unspecified) and their number, on the device."""
     n = mask.numel()

@@ -433,6 +433,7 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
     fuse_residual = True      # forward(input, residual=...) adds the residual inside the convolution kernel where it can
     fuse_residual_activation = False   # ... also when the add layer has an activation (its accumulated sum is updated by the convolution)
     patch_tiles = False       # stride-1 KxK layers: patch tiles loaded by tiled TMA (mostly active maps) instead of work lists
+    fuse_blocks = True        # DCFusedInvertedResidual runs whole inverted-residual blocks of small maps in one kernel
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1, groups: int = 1,
                  bias: bool = True, padding_mode: str = "zeros", delta_threshold: float = None, name: str = None,
@@ -975,3 +976,65 @@ class DCCenterNetDecode(DCModule):
         self.dense = None
         self._state = None
         self._union = None
+
+
+class DCFusedInvertedResidual:
+    """Runs an inverted-residual block -- expansion ``DCConv2d`` 1x1 with activation, depthwise ``DCConv2d`` 3x3 with
+    activation, projection ``DCConv2d`` 1x1, optionally followed by the residual ``DCAdd`` of the block input -- as ONE
+    kernel on steady-state frames of small feature maps (``cuda_kernels.fused_inverted_residual``). It owns no state:
+    the caches and thresholds are those of the three layers' activation layers, so a stream may switch between this
+    call and the layers' own forwards from frame to frame, with identical results. No reference counterpart (the
+    reference runs six kernels per block, example/mobilenet_deltacnn.py:87-128)."""
+
+    def __init__(self, expand, depthwise, project):
+        self.expand, self.depthwise, self.project = expand, depthwise, project
+        self._desc = None
+        self._key = None
+        self._out = None
+        self._mask_out = None
+
+    def ready(self, input, residual=False):
+        """True when this frame of this block can take the fused kernel."""
+        e, d, p = self.expand, self.depthwise, self.project
+        if not DCConv2d.fuse_blocks or K.DCPerformanceMetricsManager.enabled or type(input) == Tensor:
+            return False
+        x = input[0]
+        if x.dtype != torch.float16 or any(c.backend != DCBackend.deltacnn for c in (e, d, p)):
+            return False
+        if e.weight_umma is None or p.weight_umma is None or d.orig_weights is None or tuple(d.kernel_size) != (3, 3) or \
+                tuple(d.padding) != (1, 1) or d.groups != d.in_channels or tuple(e.kernel_size) != (1, 1) or tuple(p.kernel_size) != (1, 1) or \
+                tuple(e.stride) != (1, 1) or tuple(p.stride) != (1, 1) or d.stride[0] != d.stride[1] or tuple(d.dilation) != (1, 1):
+            return False
+        if p.activation_layer is not None or p.dense_out or e.dense_out or d.dense_out:
+            return False
+        for c in (e, d):
+            a = c.activation_layer
+            if a is None or a.first_iter or not a.inplace or a.truncation_mode != DCTruncation.max or c.frame_idx < 0 or not c.fuse_activation:
+                return False
+        if p.frame_idx < 0:
+            return False
+        key = (tuple(x.shape), bool(residual))
+        if self._key != key:
+            ae, ad = e.activation_layer, d.activation_layer
+            desc = K.make_irb_desc(tuple(x.shape), e.out_channels, p.out_channels, d.stride[0], residual, ae.activation_int,
+                                   ad.activation_int, 0.0, 0.0)
+            self._key, self._desc = key, (desc if K.irb_supported(desc) else None)
+            self._out = self._mask_out = None
+        return self._desc is not None
+
+    def __call__(self, input, residual=False):
+        x, mask = input
+        e, d, p = self.expand, self.depthwise, self.project
+        ae, ad = e.activation_layer, d.activation_layer
+        desc = self._desc
+        desc.thr_expand, desc.thr_dw = float(DCThreshold.get(ae)), float(DCThreshold.get(ad))
+        n, _, h, w = x.shape
+        ho, wo = (h - 1) // desc.stride + 1, (w - 1) // desc.stride + 1
+        if self._out is None or not DCConv2d.reuse_buffers:
+            self._out = torch.empty((n, p.out_channels, ho, wo), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+            self._mask_out = torch.empty((n, 1, ho, wo), dtype=torch.int32, device=x.device)
+        for c in (e, d, p):                       # what the three forwards would have counted
+            DCConv2d.conv_idx += 1
+            c.frame_idx += 1
+        return K.fused_inverted_residual(x, mask, e.weight_umma, d.weight, p.weight_umma, ae.prev_out, ae.out_truncated, ad.prev_out,
+                                         ad.out_truncated, self._out, self._mask_out, desc)

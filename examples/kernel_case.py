@@ -10,6 +10,8 @@ small case that profiler captures are taken on (inputs larger than L2, well unde
     python examples/kernel_case.py deconv # tcgen05 transposed 4x4/2 256->256 @34x60, fused ReLU + truncation, 16 streams, per-phase work lists
     python examples/kernel_case.py dw576  # depthwise 3x3 576 ch @14x14 (a warp per channel slice), fully active, 64 streams
     python examples/kernel_case.py sparsify  # RGB input delta + mask @224x224, 64 streams
+    python examples/kernel_case.py irb576 [reps] [streams]   # fused inverted-residual block 96->576->96 @14x14 with residual, fully active
+    python examples/kernel_case.py irb960 [reps] [streams]   # fused block 160->960->160 @7x7; "sep576" / "sep960": the same blocks as three calls
 Prints the CUDA-event time per launch (L2 flushed between launches) and the algorithmic GB/s.
 """
 import os
@@ -121,6 +123,42 @@ def main():
         u_out = int(u.sum())
         nbytes = 2 * (int(mask.sum()) * cin + taps * (cin // groups) * cout) + 2 * cout * 5 * u_out + 4 * (mask.numel() + om.numel())
         print(f"{which}: {int(mask.sum())} active input pixels, {u_out} updated output pixels, {2.0 * u_out * taps * (cin // groups) * cout / 1e9:.2f} GFLOP")
+    elif which in ("irb576", "irb960", "sep576", "sep960", "irb384", "sep384"):
+        n = int(sys.argv[3]) if len(sys.argv) > 3 else 64
+        cin, chid, cout, h, w = {"576": (96, 576, 96, 14, 14), "960": (160, 960, 160, 7, 7), "384": (64, 384, 64, 14, 14)}[which[3:]]
+        x = cl((torch.randn(n, cin, h, w, generator=g) * 0.3).to(dtype)).cuda()
+        mask = torch.ones(n, 1, h, w, dtype=torch.int32, device="cuda")
+        hw = lambda wt: convert_filter_out_channels_last(wt).cuda()
+        f1 = hw((torch.randn(chid, cin, 1, 1, generator=g) * cin ** -0.5).to(dtype))
+        fd = hw((torch.randn(chid, 1, 3, 3, generator=g) * 0.4).to(dtype))
+        f2 = hw((torch.randn(cout, chid, 1, 1, generator=g) * chid ** -0.5).to(dtype))
+
+        def pack(f, ci, co):
+            d_ = K.make_conv_desc((1, ci, 8, 8), co, (8, 8), (1, 1), (1, 1), (0, 0), (1, 1), 1, 1)
+            pk = torch.zeros(_lib.lib.dc_filter_umma_bytes(d_, 0), dtype=torch.uint8, device="cuda")
+            _lib.check(_lib.lib.dc_pack_filter_umma(d_, 0, f.data_ptr(), pk.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+            return pk
+        p1, p2 = pack(f1, cin, chid), pack(f2, chid, cout)
+        caches = [cl(torch.randn(n, chid, h, w, generator=g).to(dtype)).cuda(), torch.zeros(n, chid, h, w, dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last),
+                  cl(torch.randn(n, chid, h, w, generator=g).to(dtype)).cuda(), torch.zeros(n, chid, h, w, dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last)]
+        out = torch.empty(n, cout, h, w, dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last)
+        om = torch.empty(n, 1, h, w, dtype=torch.int32, device="cuda")
+        if which.startswith("irb"):
+            desc = K.make_irb_desc(tuple(x.shape), chid, cout, 1, True, 2, 2, 0.02, 0.02)
+            run = lambda: K.fused_inverted_residual(x, mask, p1, fd, p2, *caches, out, om, desc)
+        else:
+            a, ma = torch.empty_like(caches[0]), torch.empty_like(om)
+            b_, mb = torch.empty_like(caches[0]), torch.empty_like(om)
+
+            def run():
+                K.sparse_conv(x, f1, mask, None, (1, 1), (0, 0), (1, 1), 1, create_out_mask=True, out=a, out_mask=ma, filter_umma=p1,
+                              epilogue=K.make_epilogue(caches[0], caches[1], 0.02, 2, 0))
+                K.sparse_conv(a, fd, ma, None, (1, 1), (1, 1), (1, 1), chid, create_out_mask=True, out=b_, out_mask=mb,
+                              epilogue=K.make_epilogue(caches[2], caches[3], 0.02, 2, 0))
+                K.sparse_conv(b_, f2, mb, None, (1, 1), (0, 0), (1, 1), 1, create_out_mask=True, out=out, out_mask=om, filter_umma=p2,
+                              epilogue=K.make_residual_epilogue(x, mask))
+        npx = n * h * w
+        nbytes = 2 * npx * (2 * cin + cout + 8 * chid) + 8 * npx          # block input (twice: residual), output, four caches read and written
     elif which == "sparsify":
         n, h, w = 64, 224, 224
         prev = cl(torch.rand(n, 3, h, w, generator=g).to(dtype)).cuda()

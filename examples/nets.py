@@ -154,8 +154,12 @@ def make_mobilenet_v2(ops, num_classes=1000):
             if self.use_res:
                 self.add = ops.add()
                 layers[-1].residual_last = True
+            # delta networks: the whole block as one kernel where the library has one (small maps, steady-state frames)
+            self.fused = ops.fused_block(*layers) if (ops.delta and expand != 1) else None
 
         def forward(self, x):
+            if self.fused is not None and self.fused.ready(x, self.use_res):
+                return self.fused(x, self.use_res)
             if not self.use_res:
                 return self.conv(x)
             if ops.delta:

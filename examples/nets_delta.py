@@ -1,7 +1,7 @@
 """The "ops" factory that builds the networks of ``nets`` out of the DC* modules of deltacnn_b200 (the delta
 twin of ``nets.DenseOps``): folded delta convolutions with fused activation, DCAdd, delta pooling, and the
 device-side heads."""
-from deltacnn_b200 import (DCAdaptiveAveragePooling, DCAdd, DCCenterNetDecode, DCConv2d, DCConvTranspose2d, DCDensify,
+from deltacnn_b200 import (DCAdaptiveAveragePooling, DCAdd, DCCenterNetDecode, DCConv2d, DCConvTranspose2d, DCDensify, DCFusedInvertedResidual,
                            DCHeatmapArgmax, DCLinear, DCMaxPooling, DCModule, DCSparsify, DCUpsamplingNearest2d)
 
 
@@ -52,3 +52,8 @@ class DeltaOps:
     @staticmethod
     def boxes(topk=100, min_score=0.0, stride=4.0):
         return DCCenterNetDecode(topk=topk, min_score=min_score, stride=stride, apply_sigmoid=True)
+
+    @staticmethod
+    def fused_block(expand, depthwise, project):
+        """One-kernel form of an inverted-residual block built from its three DeltaConv layers."""
+        return DCFusedInvertedResidual(expand.conv, depthwise.conv, project.conv)
