@@ -50,25 +50,24 @@ __device__ __forceinline__ void dw_pixel(const DwStripParams& p, const float* s_
             pu[j].load(p.prev + off + i * 8);
             pr[j].load(p.trunc + off + i * 8);
         }
-        float acc[8];
+        float2 acc[4];                    // fp32 accumulators, two channels per packed FMA (fma.rn.f32x2)
         const int ci = mine ? i * 8 : 0;
         {
             const float4 b0 = *reinterpret_cast<const float4*>(s_b + ci), b1 = *reinterpret_cast<const float4*>(s_b + ci + 4);
-            acc[0] = b0.x; acc[1] = b0.y; acc[2] = b0.z; acc[3] = b0.w; acc[4] = b1.x; acc[5] = b1.y; acc[6] = b1.z; acc[7] = b1.w;
+            acc[0] = make_float2(b0.x, b0.y); acc[1] = make_float2(b0.z, b0.w); acc[2] = make_float2(b1.x, b1.y); acc[3] = make_float2(b1.z, b1.w);
         }
 #pragma unroll
         for (int t9 = 0; t9 < 9; ++t9) {
             const float4 w0 = *reinterpret_cast<const float4*>(s_w + t9 * p.c + ci), w1 = *reinterpret_cast<const float4*>(s_w + t9 * p.c + ci + 4);
             const __half2* h = reinterpret_cast<const __half2*>(&v[t9]);
-            const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
-            acc[0] = fmaf(f0.x, w0.x, acc[0]); acc[1] = fmaf(f0.y, w0.y, acc[1]);
-            acc[2] = fmaf(f1.x, w0.z, acc[2]); acc[3] = fmaf(f1.y, w0.w, acc[3]);
-            acc[4] = fmaf(f2.x, w1.x, acc[4]); acc[5] = fmaf(f2.y, w1.y, acc[5]);
-            acc[6] = fmaf(f3.x, w1.z, acc[6]); acc[7] = fmaf(f3.y, w1.w, acc[7]);
+            acc[0] = __ffma2_rn(__half22float2(h[0]), make_float2(w0.x, w0.y), acc[0]);
+            acc[1] = __ffma2_rn(__half22float2(h[1]), make_float2(w0.z, w0.w), acc[1]);
+            acc[2] = __ffma2_rn(__half22float2(h[2]), make_float2(w1.x, w1.y), acc[2]);
+            acc[3] = __ffma2_rn(__half22float2(h[3]), make_float2(w1.z, w1.w), acc[3]);
         }
         __half2* dh = reinterpret_cast<__half2*>(pd[j].s);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) dh[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+        for (int k = 0; k < 4; ++k) dh[k] = __float22half2_rn(acc[k]);
         if ((kEpi == 0)) {
             if (mine) pd[j].store(p.out + off + i * 8);
         } else if (mine) {
@@ -353,25 +352,24 @@ __global__ void __launch_bounds__(256) k_dw3x3_sliced(DwStripParams p, int S) {
             pu.load(p.prev + off);
             pr.load(p.trunc + off);
         }
-        float acc[8];
+        float2 acc[4];                    // fp32 accumulators, two channels per packed FMA (fma.rn.f32x2)
         const int ci = mine ? i * 8 : 0;
         {
             const float4 b0 = *reinterpret_cast<const float4*>(s_b + ci), b1 = *reinterpret_cast<const float4*>(s_b + ci + 4);
-            acc[0] = b0.x; acc[1] = b0.y; acc[2] = b0.z; acc[3] = b0.w; acc[4] = b1.x; acc[5] = b1.y; acc[6] = b1.z; acc[7] = b1.w;
+            acc[0] = make_float2(b0.x, b0.y); acc[1] = make_float2(b0.z, b0.w); acc[2] = make_float2(b1.x, b1.y); acc[3] = make_float2(b1.z, b1.w);
         }
 #pragma unroll
         for (int t9 = 0; t9 < 9; ++t9) {
             const float4 w0 = *reinterpret_cast<const float4*>(s_w + t9 * p.c + ci), w1 = *reinterpret_cast<const float4*>(s_w + t9 * p.c + ci + 4);
             const __half2* h = reinterpret_cast<const __half2*>(&v[t9]);
-            const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
-            acc[0] = fmaf(f0.x, w0.x, acc[0]); acc[1] = fmaf(f0.y, w0.y, acc[1]);
-            acc[2] = fmaf(f1.x, w0.z, acc[2]); acc[3] = fmaf(f1.y, w0.w, acc[3]);
-            acc[4] = fmaf(f2.x, w1.x, acc[4]); acc[5] = fmaf(f2.y, w1.y, acc[5]);
-            acc[6] = fmaf(f3.x, w1.z, acc[6]); acc[7] = fmaf(f3.y, w1.w, acc[7]);
+            acc[0] = __ffma2_rn(__half22float2(h[0]), make_float2(w0.x, w0.y), acc[0]);
+            acc[1] = __ffma2_rn(__half22float2(h[1]), make_float2(w0.z, w0.w), acc[1]);
+            acc[2] = __ffma2_rn(__half22float2(h[2]), make_float2(w1.x, w1.y), acc[2]);
+            acc[3] = __ffma2_rn(__half22float2(h[3]), make_float2(w1.z, w1.w), acc[3]);
         }
         __half2* dh = reinterpret_cast<__half2*>(pd.s);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) dh[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+        for (int k = 0; k < 4; ++k) dh[k] = __float22half2_rn(acc[k]);
         if ((kEpi == 0)) {                                               // uniform over the CTA
             if (mine) pd.store(p.out + off);
             continue;

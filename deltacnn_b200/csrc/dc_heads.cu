@@ -12,55 +12,74 @@ namespace dc {
 // out[n][o] = acc[n][o] in the feature dtype. A fully connected layer is linear, so it can consume the delta of
 // the pooled feature directly: the dense feature vector is never formed. acc is the fp32 state of the layer
 // (bias on the first frame, then the running sum), which keeps the rounding of many frames out of the logits.
-// A warp owns one output o and walks the streams four at a time; lanes stride over the 16-byte packs of the
-// weight row, partial sums are reduced with shuffles in a fixed order (reproducible).
+// A CTA owns eight outputs (a warp each) and walks the streams eight at a time: the eight delta rows are staged in
+// shared memory once per CTA, every warp reads its weight row once per group of streams (16-byte packs, lanes stride
+// over the row) and keeps eight partial sums, reduced with shuffles in a fixed order (reproducible).
 // ---------------------------------------------------------------------------------------------
+constexpr int kLinStreams = 8;
+
 template <typename T, int W>
 __global__ void __launch_bounds__(256) k_linear_delta(const T* __restrict__ delta, const int32_t* __restrict__ mask,
                                                       const T* __restrict__ weight, const T* __restrict__ bias,
                                                       float* __restrict__ acc, T* __restrict__ out, int n, int cin, int cout,
                                                       int first) {
+    extern __shared__ __align__(16) uint8_t lin_smem[];
+    T* s_d = reinterpret_cast<T*>(lin_smem);                 // [kLinStreams][cin]
+    __shared__ int s_on[kLinStreams];
     grid_dep_launch();
     grid_dep_wait();
-    const int lane = threadIdx.x & 31;
-    const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (o >= cout) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int o = blockIdx.x * 8 + warp;
     const int nvec = cin / W;
-    const T* wrow = weight + (int64_t)o * cin;
-    const float b = (first && bias != nullptr) ? to_f<T>(bias[o]) : 0.f;
-    for (int n0 = 0; n0 < n; n0 += 4) {
-        bool on[4];
+    const T* wrow = weight + (int64_t)(o < cout ? o : 0) * cin;
+    const float b = (first && bias != nullptr && o < cout) ? to_f<T>(bias[o]) : 0.f;
+    for (int n0 = 0; n0 < n; n0 += kLinStreams) {
+        if (tid < kLinStreams) s_on[tid] = (n0 + tid < n && (first || mask == nullptr || mask[n0 + tid] != 0)) ? 1 : 0;
+        __syncthreads();
         bool any = false;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            on[j] = n0 + j < n && (first || mask == nullptr || mask[n0 + j] != 0);
-            any |= on[j];
-        }
-        if (!any) continue;
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int i = lane; i < nvec; i += 32) {
-            Pack<T, W> wv;
-            wv.load(wrow + i * W);
+        for (int j = 0; j < kLinStreams; ++j) any |= s_on[j] != 0;
+        if (any) {                                           // uniform over the CTA
+            for (int idx = tid; idx < kLinStreams * nvec; idx += 256) {
+                const int j = idx / nvec, i = idx - j * nvec;
+                if (s_on[j]) {
+                    Pack<T, W> v;
+                    v.load(delta + (int64_t)(n0 + j) * cin + i * W);
+                    v.store(s_d + (size_t)j * cin + i * W);
+                }
+            }
+            __syncthreads();
+            if (o < cout) {
+                float sum[kLinStreams];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (!on[j]) continue;
-                Pack<T, W> dv;
-                dv.load(delta + (int64_t)(n0 + j) * cin + i * W);
+                for (int j = 0; j < kLinStreams; ++j) sum[j] = 0.f;
+                for (int i = lane; i < nvec; i += 32) {
+                    Pack<T, W> wv;
+                    wv.load(wrow + i * W);
 #pragma unroll
-                for (int k = 0; k < W; ++k) s[j] = fmaf(wv.get(k), dv.get(k), s[j]);
+                    for (int j = 0; j < kLinStreams; ++j) {
+                        if (s_on[j]) {                       // uniform
+                            Pack<T, W> dv;
+                            dv.load(s_d + (size_t)j * cin + i * W);
+#pragma unroll
+                            for (int k = 0; k < W; ++k) sum[j] = fmaf(wv.get(k), dv.get(k), sum[j]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < kLinStreams; ++j) {
+                    if (!s_on[j]) continue;
+                    const float tot = group_sum(sum[j], 32);
+                    if (lane == 0) {
+                        const int64_t idx = (int64_t)(n0 + j) * cout + o;
+                        const float a = (first ? 0.f : acc[idx]) + tot + b;
+                        acc[idx] = a;
+                        out[idx] = from_f<T>(a);
+                    }
+                }
             }
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (!on[j]) continue;               // uniform over the warp
-            const float tot = group_sum(s[j], 32);
-            if (lane == 0) {
-                const int64_t idx = (int64_t)(n0 + j) * cout + o;
-                const float a = (first ? 0.f : acc[idx]) + tot + b;
-                acc[idx] = a;
-                out[idx] = from_f<T>(a);
-            }
-        }
+        __syncthreads();                                     // s_on and the staged rows are rewritten by the next group
     }
 }
 
@@ -294,15 +313,32 @@ int dc_linear_delta(const void* delta, const int32_t* mask, const void* weight, 
     if (delta == nullptr || weight == nullptr || acc == nullptr || out == nullptr) return DC_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;
     const dim3 grid((unsigned)divup(c_out, 8));
+    const size_t esz = dtype == DC_F16 ? 2 : 4;
+    const size_t smem = (size_t)kLinStreams * c_in * esz;
+    if (dtype != DC_F16 && dtype != DC_F32) return DC_ERR_DTYPE;
+    if (smem > 200 * 1024) return DC_ERR_UNSUPPORTED;
+    const bool vec = c_in % (int)(16 / esz) == 0 && aligned16(delta) && aligned16(weight);
+#define DC_LIN(T, W_)                                                                                                                         \
+    do {                                                                                                                                      \
+        if (smem > 48 * 1024) {                                                                                                               \
+            static PerDeviceOnce once;                                                                                                        \
+            bool* done = once.slot();                                                                                                         \
+            if (done == nullptr) return DC_ERR_LAUNCH;                                                                                        \
+            if (!*done) {                                                                                                                     \
+                if (cudaFuncSetAttribute(k_linear_delta<T, W_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)      \
+                    return check_launch();                                                                                                    \
+                *done = true;                                                                                                                 \
+            }                                                                                                                                 \
+        }                                                                                                                                     \
+        launch_pdl(k_linear_delta<T, W_>, grid, dim3(256), smem, st, (const T*)delta, mask, (const T*)weight, (const T*)bias, acc, (T*)out,  \
+                   n, c_in, c_out, first_frame);                                                                                              \
+    } while (0)
     if (dtype == DC_F16) {
-        const bool vec = c_in % 8 == 0 && aligned16(delta) && aligned16(weight);
-        if (vec) launch_pdl(k_linear_delta<__half, 8>, grid, dim3(256), 0, st, (const __half*)delta, mask, (const __half*)weight, (const __half*)bias, acc, (__half*)out, n, c_in, c_out, first_frame);
-        else launch_pdl(k_linear_delta<__half, 1>, grid, dim3(256), 0, st, (const __half*)delta, mask, (const __half*)weight, (const __half*)bias, acc, (__half*)out, n, c_in, c_out, first_frame);
-    } else if (dtype == DC_F32) {
-        const bool vec = c_in % 4 == 0 && aligned16(delta) && aligned16(weight);
-        if (vec) launch_pdl(k_linear_delta<float, 4>, grid, dim3(256), 0, st, (const float*)delta, mask, (const float*)weight, (const float*)bias, acc, (float*)out, n, c_in, c_out, first_frame);
-        else launch_pdl(k_linear_delta<float, 1>, grid, dim3(256), 0, st, (const float*)delta, mask, (const float*)weight, (const float*)bias, acc, (float*)out, n, c_in, c_out, first_frame);
-    } else return DC_ERR_DTYPE;
+        if (vec) DC_LIN(__half, 8); else DC_LIN(__half, 1);
+    } else {
+        if (vec) DC_LIN(float, 4); else DC_LIN(float, 1);
+    }
+#undef DC_LIN
     return check_launch();
 }
 

@@ -86,7 +86,9 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
     uint8_t* s_f1 = s_min + 128;                          // [128] slot active after the expansion's truncation
     uint8_t* s_f2 = s_f1 + 128;                           // [128] output pixel active after the depthwise truncation
     uint8_t* s_own = s_f2 + 128;                          // [128] slot belongs to this band (its caches are written here)
-    uint32_t* s_u32 = reinterpret_cast<uint32_t*>(s_own + 128);     // [0] tmem base, [1] ok flag
+    uint8_t* s_lown = s_own + 128;                        // [128] active slots of this band, in slot order
+    uint8_t* s_lhalo = s_lown + 128;                      // [128] active halo slots (owned by a neighbouring band)
+    uint32_t* s_u32 = reinterpret_cast<uint32_t*>(s_lhalo + 128);   // [0] tmem base, [1] ok flag, [2] halo slots, [3] own slots
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x, band = blockIdx.y;
@@ -151,6 +153,21 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
         s_f2[slot] = 0;
     }
     __syncthreads();
+    if (warp == kIrbWarps - 1) {          // compact the active slots (own / halo) in slot order: ballots and running counts
+        int n_own = 0, n_halo = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int slot = c * 32 + lane;
+            const bool a = s_min[slot] != 0, o = s_own[slot] != 0;
+            const unsigned bo = __ballot_sync(DC_FULL, a && o), bh = __ballot_sync(DC_FULL, a && !o);
+            const unsigned lt = (1u << lane) - 1u;
+            if (a && o) s_lown[n_own + __popc(bo & lt)] = (uint8_t)slot;
+            if (a && !o) s_lhalo[n_halo + __popc(bh & lt)] = (uint8_t)slot;
+            n_own += __popc(bo);
+            n_halo += __popc(bh);
+        }
+        if (lane == 0) { s_u32[2] = (uint32_t)n_halo; s_u32[3] = (uint32_t)n_own; }
+    }
     {
         const int chunk = tid & 7, row0 = tid >> 3;                                 // 64 rows per pass
         const uint32_t sX_u32 = smem_u32(sX);
@@ -248,75 +265,108 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
 
     // ---- C: truncation step of the expansion, a warp per pixel slot ----
     const __half2 thr1 = __float2half2_rn(p.thr1), thr2 = __float2half2_rn(p.thr2);
-    auto truncate_slots = [&](bool own_pass) {
-        for (int r = warp; r < r_in; r += kIrbWarps) {
-            if (s_min[r] == 0 || (s_own[r] != 0) != own_pass) continue;             // warp-uniform
-            const int64_t off = (int64_t)s_pix[r] * p.chid;
-            Pack<__half, 8> d[NV], y[NV], t[NV];
-            bool tz[NV];
+    constexpr int kU = NV >= 4 ? 1 : 2;          // pixel slots a warp has in flight at once (registers: 3 * NV packs each)
+    auto truncate_slots = [&](const uint8_t* list, int count, bool own_pass) {
+        for (int i = warp * kU; i < count; i += kIrbWarps * kU) {
+            int r[kU];
+            int64_t off[kU];
+            bool val[kU];                                                           // warp-uniform
+            Pack<__half, 8> d[kU][NV], y[kU][NV], t[kU][NV];
+            bool tz[kU][NV];
 #pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int pk = lane + 32 * j;
-                if (pk < npk) {
-                    d[j].load(reinterpret_cast<const __half*>(sE + (size_t)(pk >> 3) * p.e_kb_bytes + swz(r, pk & 7)));
-                    y[j].load(p.prev1 + off + pk * 8);
-                    t[j].load(p.trunc1 + off + pk * 8);
-                }
-            }
-            bool hit = false;
+            for (int u = 0; u < kU; ++u) {
+                val[u] = i + u < count;
+                r[u] = list[val[u] ? i + u : i];
+                off[u] = (int64_t)s_pix[r[u]] * p.chid;
 #pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int pk = lane + 32 * j;
-                if (pk < npk) {
-                    const uint4 tv = *reinterpret_cast<const uint4*>(t[j].s);
-                    tz[j] = ((tv.x | tv.y | tv.z | tv.w) & 0x7fff7fffu) == 0u;      // the carried residual is already zero
-                    hit |= truncate_pack_h2(d[j], y[j], t[j], p.act1, thr1);
-                }
-            }
-            const bool active = __any_sync(DC_FULL, hit);
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int pk = lane + 32 * j;
-                if (pk < npk) {
-                    __half* e = reinterpret_cast<__half*>(sE + (size_t)(pk >> 3) * p.e_kb_bytes + swz(r, pk & 7));
-                    Pack<__half, 8> z; z.zero();
-                    if (active) {
-                        d[j].store(e);
-                        if (own_pass) {
-                            y[j].store(p.prev1 + off + pk * 8);
-                            if (!tz[j]) z.store(p.trunc1 + off + pk * 8);           // zero is what it holds already otherwise
-                        }
-                    } else {
-                        z.store(e);
-                        if (own_pass) t[j].store(p.trunc1 + off + pk * 8);
+                for (int j = 0; j < NV; ++j) {
+                    const int pk = lane + 32 * j;
+                    if (val[u] && pk < npk) {
+                        y[u][j].load(p.prev1 + off[u] + pk * 8);
+                        t[u][j].load(p.trunc1 + off[u] + pk * 8);
+                        d[u][j].load(reinterpret_cast<const __half*>(sE + (size_t)(pk >> 3) * p.e_kb_bytes + swz(r[u], pk & 7)));
                     }
                 }
             }
-            if (lane == 0) s_f1[r] = active ? 1 : 0;
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                if (!val[u]) continue;
+                bool hit = false;
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const int pk = lane + 32 * j;
+                    if (pk < npk) {
+                        const uint4 tv = *reinterpret_cast<const uint4*>(t[u][j].s);
+                        tz[u][j] = ((tv.x | tv.y | tv.z | tv.w) & 0x7fff7fffu) == 0u;    // the carried residual is already zero
+                        hit |= truncate_pack_h2(d[u][j], y[u][j], t[u][j], p.act1, thr1);
+                    }
+                }
+                const bool active = __any_sync(DC_FULL, hit);
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const int pk = lane + 32 * j;
+                    if (pk < npk) {
+                        __half* e = reinterpret_cast<__half*>(sE + (size_t)(pk >> 3) * p.e_kb_bytes + swz(r[u], pk & 7));
+                        Pack<__half, 8> z; z.zero();
+                        if (active) {
+                            d[u][j].store(e);
+                            if (own_pass) {
+                                y[u][j].store(p.prev1 + off[u] + pk * 8);
+                                if (!tz[u][j]) z.store(p.trunc1 + off[u] + pk * 8);      // zero is what it holds already otherwise
+                            }
+                        } else {
+                            z.store(e);
+                            if (own_pass) t[u][j].store(p.trunc1 + off[u] + pk * 8);
+                        }
+                    }
+                }
+                if (lane == 0) s_f1[r[u]] = active ? 1 : 0;
+            }
         }
     };
-    if (ok_b) truncate_slots(false);      // halo pixels: read-only here, the neighbouring band owns their caches
+    if (ok_b) truncate_slots(s_lhalo, (int)s_u32[2], false);      // halo pixels: read-only here, the neighbouring band owns their caches
     IRB_STAMP(4);
     if (gridDim.y > 1) cluster_sync_all();        // every band has read its halo before any band updates a cache
     IRB_STAMP(5);
-    if (ok_b) truncate_slots(true);
+    if (ok_b) truncate_slots(s_lown, (int)s_u32[3], true);
     __syncthreads();
 
     IRB_STAMP(6);
     // ---- D: depthwise 3x3 + its truncation step, a warp per output pixel; results replace E in place ----
     if (ok_b) {
         const int rounds = (o1 - o0 + p.rows_per_round - 1) / p.rows_per_round;
-        for (int rd = 0; rd < rounds; ++rd) {
-            const int row_first = rd * p.rows_per_round;                            // relative to o0
+        Pack<__half, 8> y[NV], t[NV];
+        // pixel of round `rd` handled by this warp
+        auto pixel_of = [&](int rd, int& orow, int& ox) -> bool {
+            const int row_first = rd * p.rows_per_round;
             const int rows_here = min(p.rows_per_round, o1 - o0 - row_first);
-            const int px = warp;                                                    // pixel of the round handled by this warp
-            const bool have = px < rows_here * p.wo;
-            const int orow = row_first + (have ? px / p.wo : 0), ox = have ? px % p.wo : 0;
+            if (warp >= rows_here * p.wo) { orow = 0; ox = 0; return false; }
+            orow = row_first + warp / p.wo;
+            ox = warp - (warp / p.wo) * p.wo;
+            return true;
+        };
+        // the two cache rows of a pixel are asked for one round ahead, so their latency hides behind the arithmetic
+        auto load_caches = [&](int rd) {
+            int orow, ox;
+            if (!pixel_of(rd, orow, ox)) return;
+            const int64_t off = (((int64_t)b * p.ho + o0 + orow) * p.wo + ox) * p.chid;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int pk = lane + 32 * j;
+                if (pk < npk) {
+                    y[j].load(p.prev2 + off + pk * 8);
+                    t[j].load(p.trunc2 + off + pk * 8);
+                }
+            }
+        };
+        load_caches(0);
+        for (int rd = 0; rd < rounds; ++rd) {
+            int orow, ox;
+            const bool have = pixel_of(rd, orow, ox);
             const int pout = orow * p.wo + ox;                                      // own output pixel index = slot of the result
             Pack<__half, 8> e2[NV];
-            bool write_rows = false;
             if (have) {
-                // active taps: slot of tap (ky, kx) = ((orow * s + ky) * w) + ox * s - 1 + kx  (slot rows start at input row i0 = o0*s - 1)
+                // active taps: slot of tap (ky, kx) = (orow * s + ky) * w + ox * s - 1 + kx  (slot rows start at input row o0 * s - 1)
                 unsigned tb = 0;
                 const int sx0 = ox * p.s - 1, srow0 = orow * p.s;
 #pragma unroll
@@ -324,32 +374,21 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
                     const int ix = sx0 + t9 % 3;
                     if (ix >= 0 && ix < p.w && s_f1[(srow0 + t9 / 3) * p.w + ix] != 0) tb |= 1u << t9;
                 }
-                write_rows = true;
-                const int64_t gq = ((int64_t)b * p.ho + o0 + orow) * p.wo + ox;     // global output pixel
-                const int64_t off = gq * p.chid;
+                const int64_t off = (((int64_t)b * p.ho + o0 + orow) * p.wo + ox) * p.chid;
                 if (tb == 0u) {
 #pragma unroll
                     for (int j = 0; j < NV; ++j) e2[j].zero();
                     if (lane == 0) s_f2[pout] = 0;
                 } else {
-                    Pack<__half, 8> y[NV], t[NV];
                     bool tz[NV];
-#pragma unroll
-                    for (int j = 0; j < NV; ++j) {
-                        const int pk = lane + 32 * j;
-                        if (pk < npk) {
-                            y[j].load(p.prev2 + off + pk * 8);
-                            t[j].load(p.trunc2 + off + pk * 8);
-                        }
-                    }
                     bool hit = false;
 #pragma unroll
                     for (int j = 0; j < NV; ++j) {
                         const int pk = lane + 32 * j;
                         if (pk < npk) {
-                            float acc[8];
+                            float2 acc[4];                  // fp32 accumulators, two channels per packed FMA (fma.rn.f32x2)
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+                            for (int q = 0; q < 4; ++q) acc[q] = make_float2(0.f, 0.f);
 #pragma unroll
                             for (int t9 = 0; t9 < 9; ++t9) {
                                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -361,15 +400,11 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
                                 const __half2* hv = reinterpret_cast<const __half2*>(&v);
                                 const __half2* hw = reinterpret_cast<const __half2*>(&wv);
 #pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    const float2 f = __half22float2(hv[q]), g = __half22float2(hw[q]);
-                                    acc[2 * q] = fmaf(f.x, g.x, acc[2 * q]);
-                                    acc[2 * q + 1] = fmaf(f.y, g.y, acc[2 * q + 1]);
-                                }
+                                for (int q = 0; q < 4; ++q) acc[q] = __ffma2_rn(__half22float2(hv[q]), __half22float2(hw[q]), acc[q]);
                             }
                             __half2* dh = reinterpret_cast<__half2*>(e2[j].s);
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) dh[q] = __floats2half2_rn(acc[2 * q], acc[2 * q + 1]);
+                            for (int q = 0; q < 4; ++q) dh[q] = __float22half2_rn(acc[q]);
                             const uint4 tv = *reinterpret_cast<const uint4*>(t[j].s);
                             tz[j] = ((tv.x | tv.y | tv.z | tv.w) & 0x7fff7fffu) == 0u;
                             hit |= truncate_pack_h2(e2[j], y[j], t[j], p.act2, thr2);
@@ -392,8 +427,9 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
                     if (lane == 0) s_f2[pout] = active ? 1 : 0;
                 }
             }
+            if (rd + 1 < rounds) load_caches(rd + 1);
             __syncthreads();              // every read of E for the round's output rows is done
-            if (write_rows) {
+            if (have) {
 #pragma unroll
                 for (int j = 0; j < NV; ++j) {
                     const int pk = lane + 32 * j;
@@ -469,8 +505,10 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
             const int orow = pr / p.wo, ox = pr - orow * p.wo;
             const int64_t gq = ((int64_t)b * p.ho + o0 + orow) * p.wo + ox;
             const bool on = s_f2[pr] != 0;
-            // residual: the block input at the same pixel (stride 1, same shape), where its mask is set
-            const bool ron = p.residual != 0 && p.mask_in[gq] != 0;
+            // residual: the block input at the same pixel (stride 1, same shape), where its mask is set; its row is
+            // still in the gathered input tile (the projection filter's ring leaves that tile alone in this case)
+            const int slot_in = (orow + 1) * p.w + ox;
+            const bool ron = p.residual != 0 && s_min[slot_in] != 0;
             if (lane == 0) p.mask_out[gq] = (on || ron) ? 1 : 0;
             if (!(on || ron)) continue;
             for (int pk = lane; pk < npo; pk += 32) {
@@ -479,7 +517,7 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
                 else d.zero();
                 if (ron) {
                     Pack<__half, 8> rr;
-                    rr.load(p.x + gq * p.cin + pk * 8);
+                    rr.load(reinterpret_cast<const __half*>(sX + (size_t)(pk >> 3) * p.e_kb_bytes + swz(slot_in, pk & 7)));
                     __half2* dh = reinterpret_cast<__half2*>(d.s);
                     const __half2* rh = reinterpret_cast<const __half2*>(rr.s);
 #pragma unroll
@@ -490,7 +528,6 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
         }
     }
 
-    IRB_STAMP(9);
     // ---- drain: every issued MMA and copy has completed on the success path; release tensor memory ----
     tc_fence_before();
     __syncthreads();
@@ -546,7 +583,7 @@ static IrbPlan plan_irb(const dc_irb_desc* d) {
     if ((uint32_t)(p.rows_per_band * p.wo) * p.stage_pitch > e_bytes) return pl;
     const uint32_t x_bytes = (uint32_t)p.nkb1 * p.e_kb_bytes;
     const uint32_t wd_bytes = ((uint32_t)9 * d->c_hidden * 2u + 1023u) & ~1023u;
-    const uint32_t misc_bytes = 24 * 8 + 128 * 4 + 5 * 128 + 64;
+    const uint32_t misc_bytes = 24 * 8 + 128 * 4 + 7 * 128 + 64;
     const uint32_t budget = 227u * 1024u - 1024u /* alignment slack */;
     // expansion chunk: the widest that fits shared memory (two buffers) and tensor memory (two accumulators)
     static const int kChunks[] = {256, 192, 160, 128, 96, 64, 48, 32, 16};
@@ -555,8 +592,10 @@ static IrbPlan plan_irb(const dc_irb_desc* d) {
         if (d->c_hidden % nc != 0) continue;
         const uint32_t w1b = (uint32_t)p.nkb1 * nc * 128u;
         const uint32_t total = e_bytes + x_bytes + 2u * w1b + wd_bytes + misc_bytes;
-        // the projection ring (stages of one N tile of one K block) lives in the input + expansion-filter area: at least two must fit
-        if (total <= budget && x_bytes + 2u * w1b >= 2u * (uint32_t)p.bn2 * 128u) { p.nc = nc; break; }
+        // the projection ring (stages of one N tile of one K block) lives in the expansion-filter area, plus the input tile
+        // when no residual needs that tile at the end: at least two stages must fit
+        const uint32_t ring = 2u * w1b + (d->residual ? 0u : x_bytes);
+        if (total <= budget && ring >= 2u * (uint32_t)p.bn2 * 128u) { p.nc = nc; break; }
     }
     if (p.nc == 0) return pl;
     p.nchunks = d->c_hidden / p.nc;
@@ -565,9 +604,9 @@ static IrbPlan plan_irb(const dc_irb_desc* d) {
     p.off_w1 = p.off_x + x_bytes;
     p.off_wd = p.off_w1 + 2u * p.w1_buf_bytes;
     p.off_misc = p.off_wd + wd_bytes;
-    p.off_w2 = p.off_x;
+    p.off_w2 = d->residual ? p.off_w1 : p.off_x;
     p.w2_stage_bytes = (uint32_t)p.bn2 * 128u;
-    p.w2_stages = (int)((x_bytes + 2u * p.w1_buf_bytes) / p.w2_stage_bytes);
+    p.w2_stages = (int)((2u * p.w1_buf_bytes + (d->residual ? 0u : x_bytes)) / p.w2_stage_bytes);
     if (p.w2_stages > 8) p.w2_stages = 8;
     if (p.w2_stages > p.nkb2 * p.ntile2) p.w2_stages = p.nkb2 * p.ntile2;
 

@@ -433,7 +433,7 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
     fuse_residual = True      # forward(input, residual=...) adds the residual inside the convolution kernel where it can
     fuse_residual_activation = False   # ... also when the add layer has an activation (its accumulated sum is updated by the convolution)
     patch_tiles = False       # stride-1 KxK layers: patch tiles loaded by tiled TMA (mostly active maps) instead of work lists
-    fuse_blocks = True        # DCFusedInvertedResidual runs whole inverted-residual blocks of small maps in one kernel
+    fuse_blocks = False       # DCFusedInvertedResidual: whole inverted-residual blocks of small maps in one kernel (opt-in)
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1, groups: int = 1,
                  bias: bool = True, padding_mode: str = "zeros", delta_threshold: float = None, name: str = None,

@@ -23,6 +23,7 @@ def _reset_dc_state():
         DCThreshold.t_default = 0.0
         DCConv2d.backend = DCBackend.deltacnn
         DCConv2d.conv_idx = -1
+        DCConv2d.fuse_blocks = False
         DCAdd.idx = DCSparsify.idx = DCActivation.idx = DCDensify.idx = -1
         DCModule.temp_buffers = []
     except Exception:

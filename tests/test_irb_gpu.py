@@ -169,7 +169,7 @@ def test_mobilenet_with_fused_blocks_equals_unfused():
                 outs[fused] = [delta(x).clone() for x in xs[1:]]
             used[fused] = sum(1 for b in delta.features if getattr(b, "fused", None) is not None and b.fused._desc is not None)
     finally:
-        DCConv2d.fuse_blocks = True
+        DCConv2d.fuse_blocks = False
     assert used[True] == 10 and used[False] == 0
     for t, (a, b) in enumerate(zip(outs[True], outs[False])):
         assert torch.equal(a, b), f"frame {t + 1}"
