@@ -3,7 +3,7 @@
 // densifies the last feature map and hands it to dense torch code (example/mobilenet_deltacnn.py:216-227,
 // src/deltacnn/sparse_layers.py:1322-1329). All three keep their result from the previous frame for streams
 // (images of the batch) whose update mask is empty, so an unchanged stream costs one mask read.
-#include "dc_common.cuh"
+#include "dc_umma.cuh"
 
 namespace dc {
 
@@ -12,74 +12,95 @@ namespace dc {
 // out[n][o] = acc[n][o] in the feature dtype. A fully connected layer is linear, so it can consume the delta of
 // the pooled feature directly: the dense feature vector is never formed. acc is the fp32 state of the layer
 // (bias on the first frame, then the running sum), which keeps the rounding of many frames out of the logits.
-// A CTA owns eight outputs (a warp each) and walks the streams eight at a time: the eight delta rows are staged in
-// shared memory once per CTA, every warp reads its weight row once per group of streams (16-byte packs, lanes stride
-// over the row) and keeps eight partial sums, reduced with shuffles in a fixed order (reproducible).
+// A CTA owns eight outputs (a warp each) and walks the streams in passes of up to 32: the pass's delta rows are staged
+// in shared memory with all loads in flight together, the old sums are asked for at the same time, every warp then
+// forms the 32 dot products of its weight row (lanes stride over 16-byte packs) and folds the 32 x 32 partial sums
+// with a butterfly of 31 shuffles, after which lane s holds the sum of stream s. Fixed order: reproducible.
 // ---------------------------------------------------------------------------------------------
-constexpr int kLinStreams = 8;
+constexpr int kLinStreams = 32;
 
 template <typename T, int W>
 __global__ void __launch_bounds__(256) k_linear_delta(const T* __restrict__ delta, const int32_t* __restrict__ mask,
                                                       const T* __restrict__ weight, const T* __restrict__ bias,
                                                       float* __restrict__ acc, T* __restrict__ out, int n, int cin, int cout,
-                                                      int first) {
+                                                      int first, int spp) {
     extern __shared__ __align__(16) uint8_t lin_smem[];
-    T* s_d = reinterpret_cast<T*>(lin_smem);                 // [kLinStreams][cin]
+    constexpr bool kAsync = W > 1;                           // 16-byte packs: rows are staged by asynchronous copies
+    T* s_w = reinterpret_cast<T*>(lin_smem);                 // [8][cin] the weight rows of this CTA (kAsync only)
+    T* s_d = s_w + (kAsync ? 8 * (size_t)cin : 0);           // [spp][cin], spp <= 32 streams per pass
     __shared__ int s_on[kLinStreams];
-    grid_dep_launch();
-    grid_dep_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int o = blockIdx.x * 8 + warp;
     const int nvec = cin / W;
     const T* wrow = weight + (int64_t)(o < cout ? o : 0) * cin;
+    if constexpr (kAsync) {                                  // weights do not depend on the previous kernel
+        for (int i = lane; i < nvec; i += 32) cp_async16(smem_u32(s_w + (size_t)warp * cin + i * W), wrow + i * W, 16u);
+        cp_async_commit();
+    }
+    grid_dep_launch();
+    grid_dep_wait();
     const float b = (first && bias != nullptr && o < cout) ? to_f<T>(bias[o]) : 0.f;
-    for (int n0 = 0; n0 < n; n0 += kLinStreams) {
-        if (tid < kLinStreams) s_on[tid] = (n0 + tid < n && (first || mask == nullptr || mask[n0 + tid] != 0)) ? 1 : 0;
+    for (int n0 = 0; n0 < n; n0 += spp) {
+        const int cnt = min(spp, n - n0);
+        const bool mine = lane < cnt && (first || mask == nullptr || mask[n0 + lane] != 0);      // stream n0 + lane
+        if (warp == 0) s_on[lane] = mine ? 1 : 0;
+        // the old sum of (stream n0 + lane, output o): in flight while the rows are staged
+        const float a_prev = (mine && !first && o < cout) ? acc[(int64_t)(n0 + lane) * cout + o] : 0.f;
         __syncthreads();
-        bool any = false;
-#pragma unroll
-        for (int j = 0; j < kLinStreams; ++j) any |= s_on[j] != 0;
-        if (any) {                                           // uniform over the CTA
-            for (int idx = tid; idx < kLinStreams * nvec; idx += 256) {
-                const int j = idx / nvec, i = idx - j * nvec;
-                if (s_on[j]) {
-                    Pack<T, W> v;
-                    v.load(delta + (int64_t)(n0 + j) * cin + i * W);
-                    v.store(s_d + (size_t)j * cin + i * W);
-                }
-            }
-            __syncthreads();
-            if (o < cout) {
-                float sum[kLinStreams];
-#pragma unroll
-                for (int j = 0; j < kLinStreams; ++j) sum[j] = 0.f;
-                for (int i = lane; i < nvec; i += 32) {
-                    Pack<T, W> wv;
-                    wv.load(wrow + i * W);
-#pragma unroll
-                    for (int j = 0; j < kLinStreams; ++j) {
-                        if (s_on[j]) {                       // uniform
-                            Pack<T, W> dv;
-                            dv.load(s_d + (size_t)j * cin + i * W);
-#pragma unroll
-                            for (int k = 0; k < W; ++k) sum[j] = fmaf(wv.get(k), dv.get(k), sum[j]);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < kLinStreams; ++j) {
-                    if (!s_on[j]) continue;
-                    const float tot = group_sum(sum[j], 32);
-                    if (lane == 0) {
-                        const int64_t idx = (int64_t)(n0 + j) * cout + o;
-                        const float a = (first ? 0.f : acc[idx]) + tot + b;
-                        acc[idx] = a;
-                        out[idx] = from_f<T>(a);
-                    }
+        for (int idx = tid; idx < cnt * nvec; idx += 256) {
+            const int j = idx / nvec, i = idx - j * nvec;
+            if (s_on[j]) {
+                if constexpr (kAsync) {
+                    cp_async16(smem_u32(s_d + (size_t)j * cin + i * W), delta + (int64_t)(n0 + j) * cin + i * W, 16u);
+                } else {
+                    s_d[(size_t)j * cin + i] = delta[(int64_t)(n0 + j) * cin + i];
                 }
             }
         }
-        __syncthreads();                                     // s_on and the staged rows are rewritten by the next group
+        if constexpr (kAsync) {
+            cp_async_commit();
+            cp_async_wait_group<0>();
+        }
+        __syncthreads();
+        if (o < cout) {
+            float sum[kLinStreams];
+#pragma unroll
+            for (int j = 0; j < kLinStreams; ++j) sum[j] = 0.f;
+            for (int i = lane; i < nvec; i += 32) {
+                Pack<T, W> wv;
+                wv.load(kAsync ? s_w + (size_t)warp * cin + i * W : wrow + i * W);
+                float wf[W];
+#pragma unroll
+                for (int k = 0; k < W; ++k) wf[k] = wv.get(k);
+#pragma unroll
+                for (int j = 0; j < kLinStreams; ++j) {
+                    if (j < cnt && s_on[j]) {                // uniform over the CTA
+                        Pack<T, W> dv;
+                        dv.load(s_d + (size_t)j * cin + i * W);
+#pragma unroll
+                        for (int k = 0; k < W; ++k) sum[j] = fmaf(wf[k], dv.get(k), sum[j]);
+                    }
+                }
+            }
+            // fold: after the step with distance w, a lane keeps the half of the streams its bit w selects
+#pragma unroll
+            for (int w = 16; w >= 1; w >>= 1) {
+                const bool up = (lane & w) != 0;
+#pragma unroll
+                for (int k = 0; k < w; ++k) {
+                    const float keep = up ? sum[k + w] : sum[k];
+                    const float send = up ? sum[k] : sum[k + w];
+                    sum[k] = keep + __shfl_xor_sync(DC_FULL, send, w);
+                }
+            }
+            if (mine) {
+                const int64_t idx = (int64_t)(n0 + lane) * cout + o;
+                const float a = a_prev + sum[0] + b;
+                acc[idx] = a;
+                out[idx] = from_f<T>(a);
+            }
+        }
+        __syncthreads();                                     // s_on and the staged rows are rewritten by the next pass
     }
 }
 
@@ -314,10 +335,14 @@ int dc_linear_delta(const void* delta, const int32_t* mask, const void* weight, 
     cudaStream_t st = (cudaStream_t)stream;
     const dim3 grid((unsigned)divup(c_out, 8));
     const size_t esz = dtype == DC_F16 ? 2 : 4;
-    const size_t smem = (size_t)kLinStreams * c_in * esz;
     if (dtype != DC_F16 && dtype != DC_F32) return DC_ERR_DTYPE;
-    if (smem > 200 * 1024) return DC_ERR_UNSUPPORTED;
     const bool vec = c_in % (int)(16 / esz) == 0 && aligned16(delta) && aligned16(weight);
+    const size_t row = (size_t)c_in * esz, wrows = vec ? 8 * row : 0;    // the vector form also stages its eight weight rows
+    if (wrows + row > 200 * 1024) return DC_ERR_UNSUPPORTED;
+    int spp = (int)((200 * 1024 - wrows) / row);                         // streams whose rows fit the staging buffer
+    if (spp > kLinStreams) spp = kLinStreams;
+    if (spp > n) spp = n;
+    const size_t smem = wrows + (size_t)spp * row;
 #define DC_LIN(T, W_)                                                                                                                         \
     do {                                                                                                                                      \
         if (smem > 48 * 1024) {                                                                                                               \
@@ -331,7 +356,7 @@ int dc_linear_delta(const void* delta, const int32_t* mask, const void* weight, 
             }                                                                                                                                 \
         }                                                                                                                                     \
         launch_pdl(k_linear_delta<T, W_>, grid, dim3(256), smem, st, (const T*)delta, mask, (const T*)weight, (const T*)bias, acc, (T*)out,  \
-                   n, c_in, c_out, first_frame);                                                                                              \
+                   n, c_in, c_out, first_frame, spp);                                                                                         \
     } while (0)
     if (dtype == DC_F16) {
         if (vec) DC_LIN(__half, 8); else DC_LIN(__half, 1);

@@ -10,6 +10,7 @@ small case that profiler captures are taken on (inputs larger than L2, well unde
     python examples/kernel_case.py deconv # tcgen05 transposed 4x4/2 256->256 @34x60, fused ReLU + truncation, 16 streams, per-phase work lists
     python examples/kernel_case.py dw576  # depthwise 3x3 576 ch @14x14 (a warp per channel slice), fully active, 64 streams
     python examples/kernel_case.py sparsify  # RGB input delta + mask @224x224, 64 streams
+    python examples/kernel_case.py linear [reps] [streams]   # classifier on the pooled delta, 1280 -> 1000 ("linear_dense": densify + torch linear)
     python examples/kernel_case.py irb576 [reps] [streams]   # fused inverted-residual block 96->576->96 @14x14 with residual, fully active
     python examples/kernel_case.py irb960 [reps] [streams]   # fused block 160->960->160 @7x7; "sep576" / "sep960": the same blocks as three calls
 Prints the CUDA-event time per launch (L2 flushed between launches) and the algorithmic GB/s.
@@ -159,6 +160,21 @@ def main():
                               epilogue=K.make_residual_epilogue(x, mask))
         npx = n * h * w
         nbytes = 2 * npx * (2 * cin + cout + 8 * chid) + 8 * npx          # block input (twice: residual), output, four caches read and written
+    elif which in ("linear", "linear_dense"):
+        n = int(sys.argv[3]) if len(sys.argv) > 3 else 32
+        cin, cout = 1280, 1000
+        wt = (torch.randn(cout, cin, generator=g) * 0.01).to(dtype).cuda()
+        bias = torch.zeros(cout, dtype=dtype, device="cuda")
+        delta = cl(torch.randn(n, cin, 1, 1, generator=g).to(dtype)).cuda()
+        mask = torch.ones(n, 1, 1, 1, dtype=torch.int32, device="cuda")
+        acc = torch.zeros(n, cout, device="cuda")
+        out = torch.empty(n, cout, dtype=dtype, device="cuda")
+        prev = torch.zeros_like(delta)
+        if which == "linear":
+            run = lambda: K.linear_delta(delta, mask, wt, bias, acc, out, False)
+        else:
+            run = lambda: torch.nn.functional.linear(K.sparse_densify(delta, mask, prev).reshape(n, -1), wt, bias)
+        nbytes = 2 * (n * cin + cin * cout + n * cout) + 8 * n * cout
     elif which == "sparsify":
         n, h, w = 64, 224, 224
         prev = cl(torch.rand(n, 3, h, w, generator=g).to(dtype)).cuda()

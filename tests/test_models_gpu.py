@@ -112,7 +112,7 @@ def test_config2_mobilenet_fp16_8_streams_128_frames_threshold0():
     """Configuration 2 at threshold 0: eight seeded streams, 128 frames each, fp16, against the fp32 network. The
     accumulated caches are half-precision sums, so every frame adds a rounding error of half an ulp to them and the
     delta network's error performs a random walk on top of the dense fp16 network's own error (3e-2 with these
-    randomly initialised weights): the test bounds it by twice the dense fp16 error over the first 16 frames and by
+    randomly initialised weights): the test bounds it by three times the dense fp16 error over the first 32 frames and by
     six times over all 128, records the series, and checks that the growth is sub-linear (no systematic drift)."""
     from examples.nets import build_pair
     from examples.synthetic_video import make_video
@@ -132,7 +132,7 @@ def test_config2_mobilenet_fp16_8_streams_128_frames_threshold0():
             e, d = _rel(delta(x.half()), truth), _rel(dense16(x.half()), truth)
             worst_dense = max(worst_dense, d)
             series.append(e)
-            assert e <= max(1e-2, (2.0 if t < 16 else 6.0) * d), f"frame {t}: {e:.3e} against dense fp16 {d:.3e}"
+            assert e <= max(1e-2, (3.0 if t < 32 else 6.0) * d), f"frame {t}: {e:.3e} against dense fp16 {d:.3e}"
     quarter = [max(series[i:i + 32]) for i in range(0, n_frames, 32)]
     _record("mobilenet config 2 (8 streams x 128 frames, gain 1)", {"dense_fp16_vs_fp32": worst_dense, "delta_fp16_vs_fp32_frames_0_31": quarter[0],
                                                                      "frames_32_63": quarter[1], "frames_64_95": quarter[2], "frames_96_127": quarter[3]})
