@@ -846,7 +846,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         pl.taps = (d->kh / 2) * (d->kw / 2);
         pl.nkb = pl.taps * pl.ncb;
     }
-    finish_plan(pl, d, npix_out, want_fused, ws != nullptr, multi_span);
+    finish_plan(pl, d, npix_out, want_fused, ws != nullptr || patch_mode, multi_span);
     const bool fused = want_fused && pl.ntiles == 1;
     PwParams p{};
     p.in = (const __half*)in; p.mi = mi; p.wimg = (const uint8_t*)filt; p.bias = (const __half*)bias;

@@ -12,12 +12,14 @@ namespace dc {
 // out[n][o] = acc[n][o] in the feature dtype. A fully connected layer is linear, so it can consume the delta of
 // the pooled feature directly: the dense feature vector is never formed. acc is the fp32 state of the layer
 // (bias on the first frame, then the running sum), which keeps the rounding of many frames out of the logits.
-// A CTA owns eight outputs (a warp each) and walks the streams in passes of up to 32: the pass's delta rows are staged
-// in shared memory with all loads in flight together, the old sums are asked for at the same time, every warp then
-// forms the 32 dot products of its weight row (lanes stride over 16-byte packs) and folds the 32 x 32 partial sums
-// with a butterfly of 31 shuffles, after which lane s holds the sum of stream s. Fixed order: reproducible.
+// A CTA owns eight outputs (a warp each) and a pass of up to 16 streams (blockIdx.y; further passes in strides of
+// gridDim.y): the pass's delta rows and the CTA's weight rows are staged in shared memory by asynchronous copies, all
+// in flight together, and the old sums are asked for at the same time; every warp then forms the 16 dot products of
+// its weight row without a branch (lanes stride over 16-byte packs; rows of streams without an update hold stale
+// data and their sums are dropped) and folds the 32 x 16 partial sums with a butterfly of 31 shuffles, after which
+// lane s holds the sum of stream s. Fixed order: reproducible.
 // ---------------------------------------------------------------------------------------------
-constexpr int kLinStreams = 32;
+constexpr int kLinStreams = 16;
 
 template <typename T, int W>
 __global__ void __launch_bounds__(256) k_linear_delta(const T* __restrict__ delta, const int32_t* __restrict__ mask,
@@ -27,7 +29,7 @@ __global__ void __launch_bounds__(256) k_linear_delta(const T* __restrict__ delt
     extern __shared__ __align__(16) uint8_t lin_smem[];
     constexpr bool kAsync = W > 1;                           // 16-byte packs: rows are staged by asynchronous copies
     T* s_w = reinterpret_cast<T*>(lin_smem);                 // [8][cin] the weight rows of this CTA (kAsync only)
-    T* s_d = s_w + (kAsync ? 8 * (size_t)cin : 0);           // [spp][cin], spp <= 32 streams per pass
+    T* s_d = s_w + (kAsync ? 8 * (size_t)cin : 0);           // [spp][cin], spp <= 16 streams per pass
     __shared__ int s_on[kLinStreams];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int o = blockIdx.x * 8 + warp;
@@ -40,10 +42,10 @@ __global__ void __launch_bounds__(256) k_linear_delta(const T* __restrict__ delt
     grid_dep_launch();
     grid_dep_wait();
     const float b = (first && bias != nullptr && o < cout) ? to_f<T>(bias[o]) : 0.f;
-    for (int n0 = 0; n0 < n; n0 += spp) {
+    for (int n0 = (int)blockIdx.y * spp; n0 < n; n0 += (int)gridDim.y * spp) {
         const int cnt = min(spp, n - n0);
         const bool mine = lane < cnt && (first || mask == nullptr || mask[n0 + lane] != 0);      // stream n0 + lane
-        if (warp == 0) s_on[lane] = mine ? 1 : 0;
+        if (warp == 0 && lane < kLinStreams) s_on[lane] = mine ? 1 : 0;
         // the old sum of (stream n0 + lane, output o): in flight while the rows are staged
         const float a_prev = (mine && !first && o < cout) ? acc[(int64_t)(n0 + lane) * cout + o] : 0.f;
         __syncthreads();
@@ -74,17 +76,19 @@ __global__ void __launch_bounds__(256) k_linear_delta(const T* __restrict__ delt
                 for (int k = 0; k < W; ++k) wf[k] = wv.get(k);
 #pragma unroll
                 for (int j = 0; j < kLinStreams; ++j) {
-                    if (j < cnt && s_on[j]) {                // uniform over the CTA
-                        Pack<T, W> dv;
-                        dv.load(s_d + (size_t)j * cin + i * W);
+                    const int jj = j < cnt ? j : cnt - 1;     // beyond the pass: a valid row, the sum is not used
+                    Pack<T, W> dv;
+                    dv.load(s_d + (size_t)jj * cin + i * W);
 #pragma unroll
-                        for (int k = 0; k < W; ++k) sum[j] = fmaf(wf[k], dv.get(k), sum[j]);
-                    }
+                    for (int k = 0; k < W; ++k) sum[j] = fmaf(wf[k], dv.get(k), sum[j]);
                 }
             }
-            // fold: after the step with distance w, a lane keeps the half of the streams its bit w selects
+            // fold: lanes L and L ^ 16 first, then after the step with distance w a lane keeps the half of the streams
+            // its bit w selects; lane L ends with the sum of stream L & 15
 #pragma unroll
-            for (int w = 16; w >= 1; w >>= 1) {
+            for (int k = 0; k < kLinStreams; ++k) sum[k] += __shfl_xor_sync(DC_FULL, sum[k], 16);
+#pragma unroll
+            for (int w = kLinStreams / 2; w >= 1; w >>= 1) {
                 const bool up = (lane & w) != 0;
 #pragma unroll
                 for (int k = 0; k < w; ++k) {
@@ -93,7 +97,7 @@ __global__ void __launch_bounds__(256) k_linear_delta(const T* __restrict__ delt
                     sum[k] = keep + __shfl_xor_sync(DC_FULL, send, w);
                 }
             }
-            if (mine) {
+            if (mine) {                                      // lane < cnt <= 16
                 const int64_t idx = (int64_t)(n0 + lane) * cout + o;
                 const float a = a_prev + sum[0] + b;
                 acc[idx] = a;
@@ -333,7 +337,6 @@ int dc_linear_delta(const void* delta, const int32_t* mask, const void* weight, 
     if (n == 0) return DC_OK;
     if (delta == nullptr || weight == nullptr || acc == nullptr || out == nullptr) return DC_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;
-    const dim3 grid((unsigned)divup(c_out, 8));
     const size_t esz = dtype == DC_F16 ? 2 : 4;
     if (dtype != DC_F16 && dtype != DC_F32) return DC_ERR_DTYPE;
     const bool vec = c_in % (int)(16 / esz) == 0 && aligned16(delta) && aligned16(weight);
@@ -343,6 +346,9 @@ int dc_linear_delta(const void* delta, const int32_t* mask, const void* weight, 
     if (spp > kLinStreams) spp = kLinStreams;
     if (spp > n) spp = n;
     const size_t smem = wrows + (size_t)spp * row;
+    int passes = divup(n, spp);
+    if (passes > 8) passes = 8;
+    const dim3 grid((unsigned)divup(c_out, 8), (unsigned)passes);
 #define DC_LIN(T, W_)                                                                                                                         \
     do {                                                                                                                                      \
         if (smem > 48 * 1024) {                                                                                                               \
