@@ -206,6 +206,7 @@ def main():
     times = []
     for _ in range(reps):
         flush.fill_(1)
+        torch.cuda._sleep(600000)         # the device stays busy while the host prepares the call: no idle time between the events
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         run()

@@ -144,6 +144,9 @@ class OpProfiler:
         def inner(*args, **kwargs):
             pre = self._pre(name, args, kwargs)
             self.flush.fill_(1)
+            # keep the device busy while the host prepares the call (argument checks, descriptors): the interval between
+            # the two events must hold the kernels of the call and no idle time
+            torch.cuda._sleep(600000)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(self.stream)
             res = fn(*args, **kwargs)
