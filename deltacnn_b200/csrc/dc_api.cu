@@ -48,6 +48,7 @@ int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, vo
 int umma_error_code();
 int stem_umma_error_code();
 int irb_error_code();
+int halo_error_code();
 int conv_stem_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
                    int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 int conv_thin(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
@@ -96,7 +97,9 @@ int dc_umma_error(void) {
     const int a = umma_error_code();
     if (a != 0) return a;
     const int b = stem_umma_error_code();
-    return b != 0 ? b : irb_error_code();
+    if (b != 0) return b;
+    const int c = irb_error_code();
+    return c != 0 ? c : halo_error_code();
 }
 
 int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter, int32_t filter_layout,

@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(kSuThreads, 3) k_stem_umma(const StemUParams p
             }
             fence_proxy_async();
             __syncthreads();
-            if (tid == 0) {
+            if (warp == 0 && elect_one()) {            // an elected lane of a converged warp: MMA operands in uniform registers
                 tc_fence_after();
                 const uint64_t ad0 = make_smem_desc(smem_u32(sA));
                 const uint64_t bd0 = make_smem_desc(smem_u32(sB));

@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                     *ok_flag = 0; atomicExch(&g_umma_error, 1);
                     break;
                 }
-                if (tid == 0) {
+                if (warp == 0 && elect_one()) {        // (elected lane of a converged warp: TMA operands in uniform registers)
                     mbar_expect_tx(bar_full(pslot), (uint32_t)kABytes);
                     if (patch) {
                         const int tap_ = kb / p.ncb, cb_ = kb - tap_ * p.ncb;
@@ -461,7 +461,7 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                     }
                 }
                 cp_async_commit();
-                if (tid == 0 && !p.b_resident) {
+                if (warp == 0 && !p.b_resident && elect_one()) {
                     mbar_expect_tx(bar_bfull(pslot), b_block_bytes);
                     bulk_g2s(smem_u32(sB + (size_t)pslot * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(pslot));
                 }
@@ -479,37 +479,44 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
             cp_async_wait_group<0>();
             signal_block();
         } else {
-            // ---- one thread feeds the tensor core ----
-            if (lane == 0) {
-                if (tile == 0 && p.b_resident) {       // the whole filter slab of this CTA: one bulk copy per K block, one barrier
-                    mbar_expect_tx(bar_bfull(0), (uint32_t)p.nkb * b_block_bytes);
-                    for (int kb = 0; kb < p.nkb; ++kb)
-                        bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(0));
-                }
+            // ---- the tensor core's warp: warp-uniform control flow, one elected lane issues the MMAs and the commits
+            //      (tcgen05.mma takes its operands from uniform registers; issued from a divergent single-lane loop every
+            //      MMA cost ~200 cycles of issue time, under elect.sync ~35) ----
+            if (tile == 0 && p.b_resident && elect_one()) {       // the whole filter slab of this CTA: one bulk copy per K block, one barrier
+                mbar_expect_tx(bar_bfull(0), (uint32_t)p.nkb * b_block_bytes);
+                for (int kb = 0; kb < p.nkb; ++kb)
+                    bulk_g2s(smem_u32(sB + (size_t)kb * b_block_bytes), wimg + filter_block(kb) * p.b_kb_stride, b_block_bytes, bar_bfull(0));
+            }
+            __syncwarp();
+            {
                 const uint64_t ad0 = make_smem_desc(sA_u32);
                 const uint64_t bd0 = make_smem_desc(smem_u32(sB));
                 const uint32_t b_step = b_block_bytes >> 4;
                 int cb = 0;
+                bool got = true;
                 for (int kb = 0; kb < p.nkb; ++kb) {
-                    bool got = mbar_wait(bar_full(mslot), (uint32_t)(mwrap & 1), ok_flag);
+                    got = mbar_wait_warp(bar_full(mslot), (uint32_t)(mwrap & 1), ok_flag);
                     if (got) {
-                        if (!p.b_resident) got = mbar_wait(bar_bfull(mslot), (uint32_t)(mwrap & 1), ok_flag);
-                        else if (tile == 0 && kb == 0) got = mbar_wait(bar_bfull(0), 0u, ok_flag);
+                        if (!p.b_resident) got = mbar_wait_warp(bar_bfull(mslot), (uint32_t)(mwrap & 1), ok_flag);
+                        else if (tile == 0 && kb == 0) got = mbar_wait_warp(bar_bfull(0), 0u, ok_flag);
                     }
                     if (!got) { *ok_flag = 0; atomicExch(&g_umma_error, 2); break; }
                     tc_fence_after();
                     const int ksteps = cb == p.ncb - 1 ? last_ksteps : kKBlock / 16;
-                    const uint64_t ad = ad0 + (uint64_t)((uint32_t)mslot * (kABytes >> 4));
-                    const uint64_t bd = bd0 + (uint64_t)((uint32_t)(p.b_resident ? kb : mslot) * b_step);
-                    for (int ks = 0; ks < ksteps; ++ks)
-                        umma_f16(tmem_base, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(bar_empty(mslot));
+                    if (elect_one()) {
+                        const uint64_t ad = ad0 + (uint64_t)((uint32_t)mslot * (kABytes >> 4));
+                        const uint64_t bd = bd0 + (uint64_t)((uint32_t)(p.b_resident ? kb : mslot) * b_step);
+                        for (int ks = 0; ks < ksteps; ++ks)
+                            umma_f16(tmem_base, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit(bar_empty(mslot));
+                    }
+                    __syncwarp();
                     if (++mslot == nse) { mslot = 0; ++mwrap; }
                     if (++cb == p.ncb) cb = 0;
                 }
-                if (*ok_flag != 0) umma_commit(bar_accum);
+                if (got && *ok_flag != 0 && elect_one()) umma_commit(bar_accum);
+                __syncwarp();
             }
-            __syncwarp();
         }
         // every MMA of the tile has completed: the accumulator is final and the stage ring is free
         if (!mbar_wait_warp(bar_accum, (uint32_t)(tile & 1), ok_flag)) { *ok_flag = 0; atomicExch(&g_umma_error, 3); }
@@ -751,6 +758,8 @@ int pack_filter_umma(const dc_conv_desc* d, int transposed, const void* hwio, vo
 }
 
 int scan_conv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
+int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out, int32_t* mo,
+                 const dc_epilogue* ep, uint32_t b_kb_stride, int* fused_out, cudaStream_t st);
 
 int scan_deconv_mask(const dc_conv_desc* d, const int32_t* mi, int32_t* mo, void* ws, size_t ws_bytes, int defer_active, cudaStream_t st);
 
@@ -783,7 +792,7 @@ static bool encode_rows_map(CUtensorMap* map, const void* in, int64_t npix_in, i
 }
 
 // Tensor map of the input as [n][h][w][c] (fp16), box {64 channels, tw, th, 1}, 128-byte swizzle: what tma_load_patch reads.
-static bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_desc* d, int tw, int th) {
+bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_desc* d, int tw, int th) {
     CUtensorMap rows_probe;
     if (!encode_rows_map(&rows_probe, in, (int64_t)d->n * d->h_in * d->w_in, d->c_in)) return false;   // looks the encoder up
     void* ptr = nullptr;
@@ -842,6 +851,18 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
     if (pointwise && has_res) ws = nullptr;
     const bool multi_span = ws == nullptr && pointwise && unit_stride && npix_out >= kListMinPixels;
     const bool patch_mode = kxk_patch && ws == nullptr;
+    if (patch_mode && !transposed) {
+        // 3x3 layers: halo tiles (one load of the patch's halo per channel block instead of one per tap)
+        int fused_there = 0;
+        const int rc = conv3x3_halo(d, in, mi, filt, bias, out, mo, ep, (uint32_t)pl.rows * 128u, &fused_there, st);
+        if (rc != DC_ERR_UNSUPPORTED) {
+            if (rc != DC_OK) return rc;
+            if (ep != nullptr && !fused_there)
+                return dc_activate_truncate(out, ep->prev_out, ep->truncated, mo, npix_out, d->c_out, d->dtype, ep->threshold,
+                                            ep->activation, ep->truncation, (void*)st);
+            return DC_OK;
+        }
+    }
     if (transposed) {                 // the kernel sees one phase: m x m taps
         pl.taps = (d->kh / 2) * (d->kw / 2);
         pl.nkb = pl.taps * pl.ncb;

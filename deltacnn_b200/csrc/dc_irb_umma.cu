@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
 
     // ---- B: expansion GEMM, chunk by chunk; chunk j+1 runs on the tensor core while chunk j is converted ----
     const uint32_t idesc1 = make_idesc(p.nc);
-    auto issue_expand = [&](int j) {                                                // thread 0 only
+    auto issue_expand = [&](int j) {                                                // the elected lane of warp 0 only
         const int buf = j & 1;
         const uint64_t ad0 = make_smem_desc(smem_u32(sX));
         const uint64_t bd0 = make_smem_desc(smem_u32(sW1 + (size_t)buf * p.w1_buf_bytes));
@@ -206,14 +206,15 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
         }
         umma_commit(bar_acc(buf));
     };
-    if (tid == 0) {
+    // (MMAs are issued by an elected lane of converged warp 0: their operands sit in uniform registers)
+    if (warp == 0 && elect_one()) {
         if (mbar_wait(bar_w1(0), 0u, ok_flag)) { tc_fence_after(); issue_expand(0); }
         else { *ok_flag = 0; atomicExch(&g_irb_error, 2); }
     }
     for (int j = 0; j < p.nchunks; ++j) {
         const int buf = j & 1;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
-        if (tid == 0 && j + 1 < p.nchunks && *ok_flag != 0) {
+        if (warp == 0 && j + 1 < p.nchunks && *ok_flag != 0 && elect_one()) {
             if (mbar_wait(bar_w1(buf ^ 1), (uint32_t)(((j + 1) >> 1) & 1), ok_flag)) { tc_fence_after(); issue_expand(j + 1); }
             else { *ok_flag = 0; atomicExch(&g_irb_error, 2); }
         }
@@ -446,7 +447,7 @@ __global__ void __launch_bounds__(kIrbThreads, 1) k_irb_umma(const IrbParams p) 
 
     IRB_STAMP(7);
     // ---- E: projection GEMM, K = hidden channels in blocks of 64, filter blocks through the ring ----
-    if (ok_b && tid == 0) {
+    if (ok_b && warp == 0 && elect_one()) {
         const uint32_t idesc2 = make_idesc(p.bn2);
         const uint64_t ad0 = make_smem_desc(smem_u32(sE));
         const uint64_t bd0 = make_smem_desc(smem_u32(sW2));

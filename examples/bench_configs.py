@@ -16,49 +16,70 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from examples.nets import build_pair  # noqa: E402
-from examples.runner import GraphedStep, set_depth_thresholds  # noqa: E402
+from examples.runner import MultiBranchStep, capture_groups, set_depth_thresholds  # noqa: E402
 from examples.synthetic_video import make_video  # noqa: E402
 from deltacnn_b200 import DCConv2d, DCThreshold  # noqa: E402
 
 
-def run(name, streams, frames, input_threshold=0.03, patches=None):
+def run(name, streams, frames, input_threshold=0.03, patches=None, groups=1):
+    """``groups`` > 1: the streams are split into that many groups, each with its own model instance (own caches, same
+    weights) and its own CUDA stream inside ONE captured graph, so kernels of different groups overlap (what bench.py
+    does for MobileNetV2). The dense network is timed as one batch and as two concurrent half batches; the better
+    one is reported."""
     dev = torch.device("cuda")
     DCConv2d.patch_tiles = (name != "resnet50") if patches is None else bool(patches)
     vids = torch.stack([make_video(name, s).frames(frames + 3) for s in range(streams)], dim=1)     # (F, S, 3, H, W)
     heads = {"decode": True} if name in ("hrnet", "centernet") else {}      # key points / boxes decoded on the device
-    dense, delta = build_pair(name, vids[:4, 0], device=dev, dtype=torch.float16, **heads)
+    G = max(1, min(groups, streams))
+    bounds = [(g * streams) // G for g in range(G + 1)]
     fd = [vids[i].to(dev, torch.float16).contiguous(memory_format=torch.channels_last) for i in range(vids.shape[0])]
     DCThreshold.reset()
+    dense, deltas = None, []
+    for g in range(G):
+        dense, delta = build_pair(name, vids[:4, 0], device=dev, dtype=torch.float16, **heads)
+        deltas.append(delta)
     with torch.no_grad():
-        delta(fd[0])
-        set_depth_thresholds(input_threshold, 0.01, 0.05)
-        step = GraphedStep(delta, fd[1], warmup_frames=[fd[1]])
-        step(fd[2])
+        for g, m in enumerate(deltas):
+            sl = slice(bounds[g], bounds[g + 1])
+            m(fd[0][sl])
+            set_depth_thresholds(input_threshold, 0.01, 0.05, model=m)
+            m(fd[1][sl])
+        step = MultiBranchStep(deltas, [fd[1][bounds[g]:bounds[g + 1]] for g in range(G)])
+
+        def load(frame):
+            for g in range(G):
+                step.static_in[g].copy_(frame[bounds[g]:bounds[g + 1]], non_blocking=True)
+        load(fd[2]); step.graph.replay()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for t in range(3, 3 + frames):
-            step(fd[t])
+            load(fd[t]); step.graph.replay()
         e1.record()
         torch.cuda.synchronize()
         ms_delta = e0.elapsed_time(e1) / frames
-        density = float(delta.sparsify.mask.float().mean().item())
+        density = float(deltas[0].sparsify.mask.float().mean().item())
         torch.backends.cudnn.benchmark = True
-        static = fd[0].clone()
-        for _ in range(3):
-            dense(static)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            dense(static)
-        e0.record()
-        for t in range(3, 3 + frames):
-            static.copy_(fd[t]); g.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        ms_dense = e0.elapsed_time(e1) / frames
-    return {"config": name, "streams": streams, "patch_tiles": DCConv2d.patch_tiles, "resolution": list(vids.shape[-2:]), "updated_input_pixels": density,
-            "delta_fps": streams / ms_delta * 1000, "dense_cudnn_fps": streams / ms_dense * 1000,
+
+        def dense_ms(parts):
+            bnd = [(g * streams) // parts for g in range(parts + 1)]
+            ins = [fd[0][bnd[g]:bnd[g + 1]].clone() for g in range(parts)]
+            for x in ins:
+                for _ in range(3):
+                    dense(x)
+            graph, _ = capture_groups([dense] * parts, ins)
+            torch.cuda.synchronize()
+            e0.record()
+            for t in range(3, 3 + frames):
+                for g in range(parts):
+                    ins[g].copy_(fd[t][bnd[g]:bnd[g + 1]], non_blocking=True)
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / frames
+        ms_dense = min(dense_ms(1), dense_ms(2) if streams >= 2 else float("inf"))
+    return {"config": name, "streams": streams, "groups": G, "patch_tiles": DCConv2d.patch_tiles, "resolution": list(vids.shape[-2:]),
+            "updated_input_pixels": density, "delta_fps": streams / ms_delta * 1000, "dense_cudnn_fps": streams / ms_dense * 1000,
             "ms_per_step_delta": ms_delta, "ms_per_step_dense": ms_dense}
 
 
@@ -69,7 +90,8 @@ if __name__ == "__main__":
     ap.add_argument("--frames", type=int, default=8)
     ap.add_argument("--patches", type=int, default=None)
     ap.add_argument("--fuse-add-act", type=int, default=0, help="1: residual adds with activation run in the convolution epilogue")
+    ap.add_argument("--groups", type=int, default=1, help="stream groups stepped concurrently inside one CUDA graph")
     a = ap.parse_args()
     DCConv2d.fuse_residual_activation = bool(a.fuse_add_act)
     for c in a.configs:
-        print(json.dumps(run(c, a.streams, a.frames, patches=a.patches)), flush=True)
+        print(json.dumps(run(c, a.streams, a.frames, patches=a.patches, groups=a.groups)), flush=True)

@@ -6,6 +6,7 @@ small case that profiler captures are taken on (inputs larger than L2, well unde
     python examples/kernel_case.py act    # stand-alone activation/truncation, 96 ch @112x112, 32 streams
     python examples/kernel_case.py c3x3   # tcgen05 3x3 256->256 @64x64, fused ReLU + truncation, 32 streams, work list
     python examples/kernel_case.py c3x3p  # the same layer on patch tiles (tiled TMA loads), no scratch
+    python examples/kernel_case.py h32    # 3x3 32->32 @64x64 fully active, 32 streams (halo tiles; DC_HALO=0: patch tiles); also h64, h128, h256to64
     python examples/kernel_case.py stem   # tcgen05 RGB stem 3x3/2 3->32 @224x224, fused ReLU6 + truncation, 32 streams
     python examples/kernel_case.py deconv # tcgen05 transposed 4x4/2 256->256 @34x60, fused ReLU + truncation, 16 streams, per-phase work lists
     python examples/kernel_case.py dw576  # depthwise 3x3 576 ch @14x14 (a warp per channel slice), fully active, 64 streams
@@ -83,8 +84,11 @@ def main():
                                     workspace=ws)
         run()
         nbytes = 2 * c * (int(mask.sum()) + 5 * int((torch.nn.functional.max_pool2d(mask.float(), 3, s, 1) > 0).sum())) + 4 * (mask.numel() + om.numel())
-    elif which in ("c3x3", "c3x3p", "stem", "deconv", "dw576"):
+    elif which in ("c3x3", "c3x3p", "h32", "h64", "h128", "h256to64", "h32n", "h64n", "stem", "deconv", "dw576"):
         geo = {"c3x3": (32, 256, 256, 64, 64, 3, 1, 1, 1, 0.12, 1), "c3x3p": (32, 256, 256, 64, 64, 3, 1, 1, 1, 0.6, 1),
+               "h32": (32, 32, 32, 64, 64, 3, 1, 1, 1, 1.0, 1), "h64": (32, 64, 64, 136, 240, 3, 1, 1, 1, 0.9, 1),
+               "h32n": (32, 32, 32, 64, 64, 3, 1, 1, 1, 1.0, 1), "h64n": (32, 64, 64, 136, 240, 3, 1, 1, 1, 0.9, 1),
+               "h128": (32, 128, 128, 68, 120, 3, 1, 1, 1, 0.9, 1), "h256to64": (32, 256, 64, 136, 240, 3, 1, 1, 1, 0.9, 1),
                "stem": (32, 3, 32, 224, 224, 3, 2, 1, 1, 0.12, 2), "deconv": (16, 256, 256, 34, 60, 4, 2, 1, 1, 0.3, 1),
                "dw576": (64, 576, 576, 14, 14, 3, 1, 1, 576, 1.0, 2)}[which]
         n, cin, cout, h, w, k, s, pad, groups, density, act = geo
@@ -108,7 +112,7 @@ def main():
         trunc = torch.zeros_like(prev)
         out = torch.empty_like(prev)
         om = torch.empty(n, 1, ho, wo, dtype=torch.int32, device="cuda")
-        ep = K.make_epilogue(prev, trunc, 0.02, act, 0)
+        ep = None if which in ("h32n", "h64n") else K.make_epilogue(prev, trunc, 0.02, act, 0)      # ...n: plain store, no truncation
         if transposed:
             ws = torch.zeros(K.deconv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
             run = lambda: K.sparse_deconv(x, f, mask, None, (s, s), (pad, pad), (1, 1), 1, create_out_mask=True, out=out, out_mask=om,
@@ -116,7 +120,7 @@ def main():
             u = torch.nn.functional.conv_transpose2d(mask.float(), torch.ones(1, 1, k, k, device="cuda"), None, s, pad) > 0
             taps = (k // s) ** 2
         else:
-            ws = None if which == "c3x3p" else torch.zeros(K.conv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
+            ws = None if which == "c3x3p" or which[0] == "h" else torch.zeros(K.conv_workspace_bytes(desc), dtype=torch.uint8, device="cuda")
             run = lambda: K.sparse_conv(x, f, mask, None, (s, s), (pad, pad), (1, 1), groups, create_out_mask=True, out=out, out_mask=om,
                                         filter_umma=packed, epilogue=ep, desc=desc, workspace=ws)
             u = torch.nn.functional.max_pool2d(mask.float(), k, s, pad) > 0
