@@ -34,7 +34,10 @@ namespace dc {
 __device__ int g_umma_error = 0;
 
 constexpr int kStages = 4;           // shared-memory ring depth
-constexpr int kDelay = 1;            // a producer signals a K block after issuing kDelay more (copies in flight per thread)
+#ifndef DC_KDELAY
+#define DC_KDELAY 1
+#endif
+constexpr int kDelay = DC_KDELAY;    // a producer signals a K block after issuing kDelay more (copies in flight per thread)
 constexpr int kPwThreads = 256;
 constexpr int kPwWarps = kPwThreads / 32;
 constexpr int kProducerWarps = kPwWarps - 1;                  // the last warp feeds the tensor core

@@ -78,6 +78,9 @@ def run(name, streams, frames, input_threshold=0.03, patches=None, groups=1):
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) / frames
         ms_dense = min(dense_ms(1), dense_ms(2) if streams >= 2 else float("inf"))
+    from deltacnn_b200 import _lib
+    if _lib.lib.dc_umma_error() != 0:
+        raise RuntimeError(f"a bounded wait of a tensor-core kernel gave up (code {_lib.lib.dc_umma_error()})")
     return {"config": name, "streams": streams, "groups": G, "patch_tiles": DCConv2d.patch_tiles, "resolution": list(vids.shape[-2:]),
             "updated_input_pixels": density, "delta_fps": streams / ms_delta * 1000, "dense_cudnn_fps": streams / ms_dense * 1000,
             "ms_per_step_delta": ms_delta, "ms_per_step_dense": ms_dense}

@@ -47,6 +47,9 @@ CASES = [
     (48, 80, 2, 24, 40, 1),        # channel counts that are no multiple of 64 / 16
     (64, 64, 2, 26, 19, 0),        # no padding: the output is smaller than the input
     (32, 32, 24, 96, 80, 1),       # ~10 tiles per CTA: the rings of tile records, stages and accumulators wrap around
+    (256, 64, 2, 33, 40, 1),       # narrow N with a filter too large to stay: the patch-tile kernel takes these
+    (128, 32, 3, 48, 24, 1),
+    (128, 64, 16, 64, 64, 1),
 ]
 
 
