@@ -48,6 +48,18 @@ def _compile(src, verbose):
 def build(force=False, verbose=False):
     """Compile what is out of date and link the shared library; returns its path."""
     os.makedirs(OBJ_DIR, exist_ok=True)
+    # objects compiled with other extra flags are stale whatever their age
+    flags_file = os.path.join(OBJ_DIR, "flags.txt")
+    flags = os.environ.get("DC_NVCC_EXTRA", "")
+    try:
+        with open(flags_file) as f:
+            same = f.read() == flags
+    except OSError:
+        same = flags == ""
+    if not same:
+        force = True
+    with open(flags_file, "w") as f:
+        f.write(flags)
     hdr_time = _newest_header()
     todo, objs = [], []
     for src in _sources():

@@ -96,8 +96,10 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" 
 
 // kEpi: 0 plain store, 1 fused truncation step, 2 residual added (the DCAdd behind a linear layer), 3 residual and the add
 // layer's activation with its accumulated sum. kExactAct: the fused activation is exact in packed half arithmetic.
-template <int kEpi, bool kExactAct>
-__global__ void __launch_bounds__(kHaloThreads, 2) k_conv3x3_halo(const HaloParams p, const __grid_constant__ CUtensorMap tmap_in) {
+// kU: groups of rows a warp of the epilogue keeps in flight (4 when the CTA has its SM to itself and the tile needs more
+// than one round of cache reads otherwise: then all of a tile's cache rows are asked for in one round trip).
+template <int kEpi, bool kExactAct, int kU>
+__global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(const HaloParams p, const __grid_constant__ CUtensorMap tmap_in) {
     constexpr bool kFused = kEpi == 1;
     constexpr bool kRes = kEpi >= 2;
     extern __shared__ uint8_t smem_raw[];
@@ -374,8 +376,14 @@ __global__ void __launch_bounds__(kHaloThreads, 2) k_conv3x3_halo(const HaloPara
                                 if (t == 1 && cb == 0) HALO_STAMP(44 + tap);
                                 if (p.dbg & 1) continue;
 #endif
-                                for (int ks = 0; ks < ksteps; ++ks)
-                                    umma_f16(tacc, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (cb > 0 || tap > 0 || ks > 0) ? 1u : 0u);
+                                if (ksteps == kKBlock / 16) {      // a full channel block: constant offsets, no loop
+#pragma unroll
+                                    for (int ks = 0; ks < kKBlock / 16; ++ks)
+                                        umma_f16(tacc, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (cb > 0 || tap > 0 || ks > 0) ? 1u : 0u);
+                                } else {
+                                    for (int ks = 0; ks < ksteps; ++ks)
+                                        umma_f16(tacc, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (cb > 0 || tap > 0 || ks > 0) ? 1u : 0u);
+                                }
                             }
                             umma_commit(bar(kAEmpty + stage));
                         }
@@ -389,8 +397,14 @@ __global__ void __launch_bounds__(kHaloThreads, 2) k_conv3x3_halo(const HaloPara
                             if (elect_one()) {
                                 const uint64_t ad = ad0 + (uint64_t)((ky * kHaloPitch + kx) * 8);
                                 const uint64_t bd = make_smem_desc(sB_u32 + (uint32_t)bs * b_block_bytes);
-                                for (int ks = 0; ks < ksteps; ++ks)
-                                    umma_f16(tacc, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (cb > 0 || tap > 0 || ks > 0) ? 1u : 0u);
+                                if (ksteps == kKBlock / 16) {
+#pragma unroll
+                                    for (int ks = 0; ks < kKBlock / 16; ++ks)
+                                        umma_f16(tacc, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (cb > 0 || tap > 0 || ks > 0) ? 1u : 0u);
+                                } else {
+                                    for (int ks = 0; ks < ksteps; ++ks)
+                                        umma_f16(tacc, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (cb > 0 || tap > 0 || ks > 0) ? 1u : 0u);
+                                }
                                 umma_commit(bar(kBEmpty + bs));
                                 if (tap == 8) umma_commit(bar(kAEmpty + stage));
                             }
@@ -418,7 +432,6 @@ __global__ void __launch_bounds__(kHaloThreads, 2) k_conv3x3_halo(const HaloPara
         while (g < nch && g < 32) g <<= 1;
         const int lig = lane & (g - 1), ppw = 32 / g;
         const __half2 thr2 = __float2half2_rn(p.thr);
-        constexpr int kU = 2;
         const int rb_first = ew * ppw * kU, rb_step = kHaloEpiWarps * ppw * kU;
         int nt = 0;
         for (int t = 0; t < tiles_mine; ++t) {
@@ -698,11 +711,11 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
     if (attr_set == nullptr) return DC_ERR_LAUNCH;
     if (!*attr_set) {
         bool ok_attr = true;
-        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
-        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+#define DC_HALO_ATTR(E, X) \
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<E, X, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess; \
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<E, X, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess
+        DC_HALO_ATTR(0, true); DC_HALO_ATTR(1, true); DC_HALO_ATTR(1, false); DC_HALO_ATTR(2, true); DC_HALO_ATTR(3, true);
+#undef DC_HALO_ATTR
         if (!ok_attr) return check_launch();
         *attr_set = true;
     }
@@ -710,11 +723,19 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
     const dim3 grid((unsigned)(p.npatches < persistent ? p.npatches : persistent));
     const bool exact_act = !fused || (p.act >= DC_ACT_NONE && p.act <= DC_ACT_RELU6);
     int rc;
-    if (has_res && res_act) rc = launch_pdl(k_conv3x3_halo<3, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);
-    else if (has_res) rc = launch_pdl(k_conv3x3_halo<2, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);
-    else if (!fused) rc = launch_pdl(k_conv3x3_halo<0, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);
-    else if (exact_act) rc = launch_pdl(k_conv3x3_halo<1, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);
-    else rc = launch_pdl(k_conv3x3_halo<1, false>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);
+    // rows per round of the epilogue's cache reads: 8 warps x (32 / lanes per row) x kU
+    int lanes_row = 1;
+    while (lanes_row < d->c_out / 8 && lanes_row < 32) lanes_row <<= 1;
+    const bool deep = pl.ctas_per_sm == 1 && 8 * (32 / lanes_row) * 2 < kRows;
+#define DC_HALO_LAUNCH(E, X)                                                                                              \
+    rc = deep ? launch_pdl(k_conv3x3_halo<E, X, 4>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap)                       \
+              : launch_pdl(k_conv3x3_halo<E, X, 2>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap)
+    if (has_res && res_act) DC_HALO_LAUNCH(3, true);
+    else if (has_res) DC_HALO_LAUNCH(2, true);
+    else if (!fused) DC_HALO_LAUNCH(0, true);
+    else if (exact_act) DC_HALO_LAUNCH(1, true);
+    else DC_HALO_LAUNCH(1, false);
+#undef DC_HALO_LAUNCH
     if (fused_out != nullptr) *fused_out = (fused || has_res) ? 1 : 0;
     return rc;
 }

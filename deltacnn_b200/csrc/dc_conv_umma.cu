@@ -509,8 +509,14 @@ __global__ void __launch_bounds__(kPwThreads, 3) k_pw_umma(const PwParams p, con
                     if (elect_one()) {
                         const uint64_t ad = ad0 + (uint64_t)((uint32_t)mslot * (kABytes >> 4));
                         const uint64_t bd = bd0 + (uint64_t)((uint32_t)(p.b_resident ? kb : mslot) * b_step);
-                        for (int ks = 0; ks < ksteps; ++ks)
-                            umma_f16(tmem_base, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                        if (ksteps == kKBlock / 16) {              // a full K block: constant offsets, no loop
+#pragma unroll
+                            for (int ks = 0; ks < kKBlock / 16; ++ks)
+                                umma_f16(tmem_base, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                        } else {
+                            for (int ks = 0; ks < ksteps; ++ks)
+                                umma_f16(tmem_base, ad + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                        }
                         umma_commit(bar_empty(mslot));
                     }
                     __syncwarp();

@@ -109,6 +109,78 @@ __global__ void __launch_bounds__(256) k_pool(const T* __restrict__ in, const T*
     }
 }
 
+// Max pooling with a 3x3 window (no dilation, the same padding on opposite sides): the same arithmetic as k_pool with the
+// window unrolled, so that the nine mask words are in flight together and every window row's six value reads as well
+// (the general kernel walks the window tap by tap, one dependent mask read before each value read).
+template <typename T, int W>
+__global__ void __launch_bounds__(256) k_maxpool3(const T* __restrict__ in, const T* __restrict__ prev,
+                                                  const int32_t* __restrict__ mi, T* __restrict__ out,
+                                                  int32_t* __restrict__ mo, PoolGeom p, int g) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int nvec = p.c / W;
+    const int64_t npix = (int64_t)p.n * p.ho * p.wo;
+    const int lane = threadIdx.x & 31;
+    const int lig = lane & (g - 1);
+    const int ppw = 32 / g;
+    const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t base = warp0 * ppw; base < npix; base += nwarps * ppw) {
+        const int64_t px = base + lane / g;
+        if (px >= npix) continue;
+        const uint32_t t = fast_div((uint32_t)px, p.wo_mul, p.wo_shift);
+        const int ox = (int)((uint32_t)px - t * (uint32_t)p.wo);
+        const int64_t b = (int64_t)fast_div(t, p.ho_mul, p.ho_shift);
+        const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
+        const int y0 = oy * p.sh - p.pt, x0 = ox * p.sw - p.pl;
+        bool inb[9], on[9];
+        int32_t mv[9];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) {
+            const int iy = y0 + k / 3, ix = x0 + k % 3;
+            inb[k] = iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi;
+            mv[k] = inb[k] ? mi[(b * p.hi + iy) * p.wi + ix] : 0;
+        }
+        bool any = false;
+#pragma unroll
+        for (int k = 0; k < 9; ++k) { on[k] = mv[k] != 0; any |= on[k]; }
+        if (mo != nullptr && lig == 0) mo[px] = any ? 1 : 0;
+        if (!any && mo != nullptr) continue;
+        const int64_t src0 = (b * p.hi + y0) * p.wi + x0;
+        for (int i = lig; i < nvec; i += g) {
+            float acc[W], pre[W];
+#pragma unroll
+            for (int k = 0; k < W; ++k) { acc[k] = -1e30f; pre[k] = -1e30f; }
+#pragma unroll
+            for (int ky = 0; ky < 3; ++ky) {
+                Pack<T, W> q[3], v[3];
+#pragma unroll
+                for (int kx = 0; kx < 3; ++kx) {
+                    const int k = ky * 3 + kx;
+                    const int64_t src = src0 + (int64_t)ky * p.wi + kx;
+                    if (inb[k]) q[kx].load(prev + src * p.c + i * W);
+                    if (on[k]) v[kx].load(in + src * p.c + i * W);
+                }
+#pragma unroll
+                for (int kx = 0; kx < 3; ++kx) {
+                    const int k = ky * 3 + kx;
+                    if (!inb[k]) continue;
+#pragma unroll
+                    for (int e = 0; e < W; ++e) {
+                        const float qe = q[kx].get(e);
+                        acc[e] = fmaxf(acc[e], on[k] ? rnd<T>(qe + v[kx].get(e)) : qe);
+                        pre[e] = fmaxf(pre[e], qe);
+                    }
+                }
+            }
+            Pack<T, W> o;
+#pragma unroll
+            for (int k = 0; k < W; ++k) o.set(k, acc[k] - pre[k]);
+            o.store(out + px * p.c + i * W);
+        }
+    }
+}
+
 // Global average pool: one CTA per (image, slab of 32 channel packs). The 256 threads are 8 pixel lanes x 32
 // packs: lane j sums the active pixels j, j+8, ... of its pack in fp32, then the eight partial sums are
 // added in a fixed order through shared memory, so the result is reproducible (the reference uses float
@@ -198,7 +270,10 @@ static int pool_t(const dc_conv_desc* d, const T* in, T* prev, const int32_t* mi
     int64_t blocks = divup64(divup64(npix, 32 / g), 8);
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    if (vec_ok) launch_pdl(k_pool<T, V>, dim3((unsigned)blocks), dim3(256), 0, st, in, prev, mi, out, mo, p, mode, g);
+    const bool window3 = mode == 0 && vec_ok && mi != nullptr && d->kh == 3 && d->kw == 3 && d->dil_h == 1 && d->dil_w == 1 &&
+                         d->pad_top == d->pad_bottom && d->pad_left == d->pad_right;
+    if (window3) launch_pdl(k_maxpool3<T, V>, dim3((unsigned)blocks), dim3(256), 0, st, in, prev, mi, out, mo, p, g);
+    else if (vec_ok) launch_pdl(k_pool<T, V>, dim3((unsigned)blocks), dim3(256), 0, st, in, prev, mi, out, mo, p, mode, g);
     else launch_pdl(k_pool<T, 1>, dim3((unsigned)blocks), dim3(256), 0, st, in, prev, mi, out, mo, p, mode, g);
     return check_launch();
 }

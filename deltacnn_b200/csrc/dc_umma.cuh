@@ -24,7 +24,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-#ifdef DC_WAIT_HINT
+#if defined(DC_WAIT_TEST)
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#elif defined(DC_WAIT_HINT)
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
 #else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
