@@ -25,6 +25,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# The launcher gives every rank of a multi-GPU run a host thread pool of size one (OMP_NUM_THREADS=1). The CPU libraries
+# then take other kernels for the BatchNorm calibration than in a single-GPU run, the folded weights differ in their last
+# bits, and the output checksums of the same streams could not be compared between partitions. A small pool (set before
+# torch is imported) keeps the calibration identical; the hot path does not use host threads.
+if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
+    os.environ["OMP_NUM_THREADS"] = "4"
+
 METRIC = "frames/sec (MobileNetV2 224x224 fp16 delta inference, ~10% updated pixels)"
 UNIT = "frames/s"
 THRESHOLDS = dict(input_threshold=0.05, first=0.01, last=0.05)
@@ -289,7 +296,8 @@ def main():
     else:
         all_ids, all_sums = ids, sums
     checksum = {"sha256_over_streams": combine_checksums(all_ids, all_sums), "streams": len(all_ids),
-                "rank0_sum": float(sum(sums)), "steps_run": t_next[0] - 2}
+                "rank0_sum": float(sum(sums)), "steps_run": t_next[0] - 2,
+                "first_streams": {str(i): v for i, v in sorted(zip(all_ids, all_sums))[:8]}}
 
     # end to end through the module API: 8-bit frames start in pinned host memory, logits end there; the upload
     # of the next frame overlaps the current step (two input buffers, two graphs of the same model)

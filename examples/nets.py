@@ -431,9 +431,17 @@ def init_weights(model, seed=0, residual_gain=1.0):
 def calibrate_and_fold(dense_model, frames):
     """One training-mode forward over ``frames`` sets every BatchNorm's running statistics to the
     batch statistics (momentum=None: cumulative average), then every BatchNorm is folded."""
-    dense_model.train()
-    dense_model(frames)
-    dense_model.eval()
+    # one host thread: the batch statistics are sums whose order would otherwise follow the thread count. (A process
+    # whose thread pool has size one from the start, OMP_NUM_THREADS=1, still takes other kernels of the CPU libraries and
+    # folds weights that differ in the last bits: callers that compare runs keep the pool larger than one.)
+    threads = torch.get_num_threads()
+    torch.set_num_threads(1)
+    try:
+        dense_model.train()
+        dense_model(frames)
+        dense_model.eval()
+    finally:
+        torch.set_num_threads(threads)
     for m in dense_model.modules():
         if isinstance(m, DenseConv):
             m.fold()
