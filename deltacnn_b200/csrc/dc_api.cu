@@ -53,6 +53,8 @@ int conv_stem_umma(const dc_conv_desc* d, const void* in, const int32_t* mi, con
                    int32_t* mo, const dc_epilogue* ep, cudaStream_t st);
 int conv_thin(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, cudaStream_t st);
+int conv_pw_simt(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
+                 int32_t* mo, cudaStream_t st);
 int conv_stem(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
               int32_t* mo, const dc_epilogue* ep, void* ws, size_t ws_bytes, cudaStream_t st);
 int dwconv3x3_strip(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, void* out,
@@ -122,6 +124,7 @@ int dc_conv2d_ws(const dc_conv_desc* desc, const void* in, const int32_t* mask_i
     rc = conv_stem(desc, in, mask_in, filter, bias, out, mask_out, epilogue, workspace, workspace_bytes, st);
     if (rc != DC_ERR_UNSUPPORTED) return rc;
     rc = conv_thin(desc, in, mask_in, filter, bias, out, mask_out, st);
+    if (rc == DC_ERR_UNSUPPORTED) rc = conv_pw_simt(desc, in, mask_in, filter, bias, out, mask_out, st);
     if (rc == DC_ERR_UNSUPPORTED) rc = conv2d_simt(desc, in, mask_in, filter, bias, out, mask_out, st);
     if (rc != DC_OK) return rc;
     return run_epilogue(desc, out, mask_out, epilogue, stream);
