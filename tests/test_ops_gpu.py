@@ -720,6 +720,36 @@ def test_pointwise_conv_with_fused_residual_equals_conv_then_add(cin, cout, n, h
     assert torch.isnan(o2[~sel]).all(), "pixels outside the union mask must not be written"
 
 
+def test_fused_residual_on_a_large_pointwise_layer_with_scratch():
+    """The residual form of a 1x1 layer whose map is large enough for the work-list front (more than eight 128-pixel
+    spans per persistent CTA) and whose caller passes scratch memory, as DCConv2d always does: the call must not be
+    refused, the scratch stays unused, and the result equals convolution + dc_add."""
+    import deltacnn_b200.cuda_kernels as k
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    cin, cout, n, h, w = 32, 16, 8, 256, 256                 # 524 288 output pixels
+    g = torch.Generator().manual_seed(7)
+    x = rand_feat(g, n, cin, h, w, torch.float16, 0.3).cuda()
+    mask = rand_mask(g, n, h, w, 0.3).cuda()
+    res = rand_feat(g, n, cout, h, w, torch.float16, 0.5).cuda()
+    rmask = rand_mask(g, n, h, w, 0.2).cuda()
+    f = convert_filter_out_channels_last((torch.randn(cout, cin, 1, 1, generator=g) / cin ** 0.5).half()).cuda()
+    packed = _pack_umma(f, cin, cout, 1)
+    desc = k.make_conv_desc(tuple(x.shape), cout, (h, w), (1, 1), (1, 1), (0, 0), (1, 1), 1, 1)
+    ws = torch.full((k.conv_workspace_bytes(desc),), 0x5A, dtype=torch.uint8, device="cuda")
+    o1, m1 = k.sparse_conv(x, f, mask, None, (1, 1), (0, 0), (1, 1), 1, create_out_mask=True, filter_umma=packed)
+    ref, mref = torch.zeros_like(o1), torch.empty_like(m1)
+    k.sparse_add_tensors(res, o1, None, ref, rmask, m1, mref, 1.0, 1.0, 0, False)
+    out = torch.zeros_like(o1)
+    o2, m2 = k.sparse_conv(x, f, mask, None, (1, 1), (0, 0), (1, 1), 1, create_out_mask=True, out=out, filter_umma=packed,
+                           epilogue=k.make_residual_epilogue(res, rmask), workspace=ws)
+    assert _lib.lib.dc_umma_error() == 0
+    assert torch.equal(m2, mref)
+    sel = (mref != 0).expand_as(ref)
+    assert torch.equal(o2[sel], ref[sel])
+    assert bool((ws == 0x5A).all()), "the residual form finds its own rows: the scratch must stay untouched"
+
+
 @pytest.mark.parametrize("cin,cout,k,n,h,w", [(64, 64, 3, 2, 40, 48), (32, 32, 3, 2, 64, 64), (128, 256, 1, 2, 20, 20), (256, 64, 3, 1, 17, 33)])
 @pytest.mark.parametrize("act", [0, 1])
 @pytest.mark.parametrize("density,res_density", [(0.1, 0.1), (1.0, 1.0), (0.97, 0.5), (0.0, 0.3)])
