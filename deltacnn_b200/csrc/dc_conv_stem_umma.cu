@@ -130,12 +130,46 @@ __global__ void __launch_bounds__(kSuThreads, 3) k_stem_umma(const StemUParams p
             const bool valid = sid < p.nspans && q64 < (int64_t)npix;
             const uint32_t q = valid ? (uint32_t)q64 : 0u;
             unsigned long long tapbits = 0ull;
+            int ox = 0, oy = 0, b = 0;
             if (valid) {
                 const uint32_t t = fast_div(q, p.wo_mul, p.wo_shift);
-                const int ox = (int)(q - t * (uint32_t)p.wo);
-                const int b = (int)fast_div(t, p.ho_mul, p.ho_shift);
-                const int oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
-                const int y0 = oy * p.sh - p.pt, x0 = ox * p.sw - p.pl;
+                ox = (int)(q - t * (uint32_t)p.wo);
+                b = (int)fast_div(t, p.ho_mul, p.ho_shift);
+                oy = (int)(t - (uint32_t)b * (uint32_t)p.ho);
+            }
+            const int y0 = oy * p.sh - p.pt, x0 = ox * p.sw - p.pl;
+            // The 32 output pixels of a warp are consecutive. When they lie in one image row (and the kernel is not dilated,
+            // at most 8 wide, stride <= 2) the warp reads the mask words of the input rows together, coalesced and once
+            // (31 * stride + kw <= 96 columns per row: three reads per lane and row instead of kw), turns every row into
+            // a bit mask with ballots, and each lane cuts its own kw bits out of it.
+            const int oy0 = __shfl_sync(DC_FULL, oy, 0), b0 = __shfl_sync(DC_FULL, b, 0), x00 = __shfl_sync(DC_FULL, x0, 0);
+            const bool coop = p.dh == 1 && p.dw == 1 && p.kw <= 8 && p.sw <= 2 &&
+                              __all_sync(DC_FULL, valid && oy == oy0 && b == b0) != 0;
+            if (coop) {
+                const int ncol = 31 * p.sw + p.kw;
+                const int shift = lane * p.sw;
+                for (int ky = 0; ky < p.kh; ++ky) {
+                    const int iy = y0 + ky;
+                    unsigned w0 = 0u, w1 = 0u, w2 = 0u;
+                    if (iy >= 0 && iy < p.hi) {                     // uniform over the warp
+                        const int32_t* mrow = p.mi + ((int64_t)b0 * p.hi + iy) * p.wi;
+                        int mv[3];
+#pragma unroll
+                        for (int m = 0; m < 3; ++m) {
+                            const int c = lane + 32 * m, ix = x00 + c;
+                            mv[m] = (c < ncol && ix >= 0 && ix < p.wi) ? mrow[ix] : 0;
+                        }
+                        w0 = __ballot_sync(DC_FULL, mv[0] != 0);
+                        w1 = __ballot_sync(DC_FULL, mv[1] != 0);
+                        w2 = __ballot_sync(DC_FULL, mv[2] != 0);
+                    }
+                    const unsigned long long lo = (unsigned long long)w0 | ((unsigned long long)w1 << 32);
+                    unsigned long long win = lo >> shift;
+                    if (shift > 0) win |= (unsigned long long)w2 << (64 - shift);
+                    tapbits |= (win & ((1ull << p.kw) - 1ull)) << (ky * p.kw);
+                }
+                if (kEpi == 0 || tapbits == 0ull) p.mo[q] = tapbits != 0ull ? 1 : 0;
+            } else if (valid) {
                 const int in0 = (b * p.hi + y0) * p.wi + x0;
                 for (int ky = 0; ky < p.kh; ++ky) {
                     const int iy = y0 + ky * p.dh;

@@ -54,11 +54,11 @@ def _run_equivalence(name, frames, dtype, n_streams=1, **kw):
 
 
 def _record(name, row):
-    """Measured errors go to gpurun_out/fp16_gate_table.json (when that folder exists) for the design notes."""
+    """Measured errors go to fp16_gate_table.json in the folder DC_TEST_OUTPUT_DIR names (nothing is written without it)."""
     import json
     import os
-    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if not os.path.isdir(root):
+    root = os.environ.get("DC_TEST_OUTPUT_DIR", "")
+    if not root or not os.path.isdir(root):
         return
     path = os.path.join(root, "fp16_gate_table.json")
     table = {}
