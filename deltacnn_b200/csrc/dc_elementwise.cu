@@ -346,28 +346,26 @@ __global__ void __launch_bounds__(256) k_add(const T* __restrict__ a, const T* _
         if (!dense_out && lig == 0) mo[px] = any ? 1 : 0;
         if (!any && !dense_out) continue;
         const int64_t off = px * C;
+        const bool with_prev = dense_out || act > 0;
         for (int i = lig; i < nvec; i += g) {
-            Pack<T, W> o;
+            // the three reads of a pack are issued together (none of them waits for another one's data)
+            Pack<T, W> o, va, vb, y;
+            if (aa) va.load(a + off + i * W); else va.zero();
+            if (ab) vb.load(b + off + i * W); else vb.zero();
+            if (with_prev) y.load(prev + off + i * W);
             float s[W];
 #pragma unroll
-            for (int k = 0; k < W; ++k) s[k] = 0.f;
-            if (aa) {
-                Pack<T, W> v; v.load(a + off + i * W);
-#pragma unroll
-                for (int k = 0; k < W; ++k) s[k] = v.get(k) * wa;
-            }
+            for (int k = 0; k < W; ++k) s[k] = aa ? va.get(k) * wa : 0.f;
             if (ab) {
-                Pack<T, W> v; v.load(b + off + i * W);
 #pragma unroll
-                for (int k = 0; k < W; ++k) s[k] = fmaf(v.get(k), wb, s[k]);
+                for (int k = 0; k < W; ++k) s[k] = fmaf(vb.get(k), wb, s[k]);
             }
-            if (!dense_out && act <= 0) {
+            if (!with_prev) {
 #pragma unroll
                 for (int k = 0; k < W; ++k) o.set(k, s[k]);
                 o.store(out + off + i * W);
                 continue;
             }
-            Pack<T, W> y; y.load(prev + off + i * W);
 #pragma unroll
             for (int k = 0; k < W; ++k) {
                 float yo = y.get(k);
