@@ -9,6 +9,10 @@
 // other change). Compared with one request per tap this reads the input from L2 once instead of nine times and
 // turns nine dependent load/wait rounds per channel block into one.
 //
+// Layers with at most 32 input channels keep their halo as rows of 64 bytes (32-channel boxes, 64-byte swizzle on both the
+// TMA and the MMA side; the filter keeps its 128-byte rows, every operand has its own descriptor): half the stage, which
+// lets two CTAs share an SM (3x3 32->32 @64x64: 32.8 -> 24.6 us).
+//
 // The delta tensor is only defined at active pixels, so halo pixels inside the image whose in-mask is clear are
 // overwritten with zeros in shared memory before the tensor core reads them; every patch with at least one active
 // output pixel takes this path, inactive output rows are computed and dropped.
@@ -42,7 +46,6 @@ __device__ long long g_halo_stamps[64];
 constexpr int kHaloTh = 16, kHaloTw = 8;                  // output patch
 constexpr int kHaloRows = kHaloTh + 2, kHaloCols = kHaloTw + 2, kHaloPitch = 16;
 constexpr int kHaloPix = kHaloRows * kHaloCols;           // 180 halo pixels that are read
-constexpr int kHaloABytes = kHaloRows * kHaloPitch * 128; // one halo stage: 36864 bytes
 constexpr int kHaloThreads = 384;
 constexpr int kHaloEpiWarps = 8, kHaloEpiThreads = kHaloEpiWarps * 32, kHaloFirstEpiWarp = 4;
 constexpr int kHaloInfo = 8;                              // ring of tile records
@@ -64,6 +67,8 @@ struct HaloParams {
     int64_t npatches;
     uint32_t ppx_mul, ppx_shift, ppi_mul, ppi_shift;
     uint32_t off_b, off_stage, off_misc, stage_pitch;
+    uint32_t a_row;                 // bytes of a halo pixel's row in shared memory: 128 (64 channels, 128-byte swizzle) or 64 (32 channels, 64-byte swizzle)
+    uint32_t a_stage;               // bytes of a halo stage: 18 x 16 pixels x a_row
     int dbg;
 };
 
@@ -71,13 +76,13 @@ struct HaloParams {
 // (bits 7-9 select the pattern row), so a start address that is a multiple of 128 bytes inside a 1024-byte pattern needs
 // nothing else: the descriptor's base-offset field stays 0 (measured: with the field set to the row position the
 // results are wrong).
-__device__ __forceinline__ uint64_t make_smem_desc_ex(uint32_t smem_addr, uint32_t sbo) {
+__device__ __forceinline__ uint64_t make_smem_desc_ex(uint32_t smem_addr, uint32_t sbo, uint32_t layout) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
     d |= (uint64_t)1 << 16;
     d |= (uint64_t)(sbo >> 4) << 32;
     d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
+    d |= (uint64_t)layout << 61;                              // 2: 128-byte swizzle, 4: 64-byte swizzle
     return d;
 }
 
@@ -240,8 +245,8 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                 const int stage = ia % p.nA, ause = ia / p.nA;
                 if (ause > 0 && !mbar_wait_warp(bar(kAEmpty + stage), (uint32_t)((ause - 1) & 1), ok_flag)) { fail(12); break; }
                 if (elect_one()) {
-                    mbar_expect_tx(bar(kAFull + stage), (uint32_t)kHaloABytes);
-                    tma_load_patch(sA_u32 + (uint32_t)stage * kHaloABytes, &tmap_in, cb * kKBlock, x0 - p.pl, y0 - p.pt, b, bar(kAFull + stage));
+                    mbar_expect_tx(bar(kAFull + stage), p.a_stage);
+                    tma_load_patch(sA_u32 + (uint32_t)stage * p.a_stage, &tmap_in, cb * kKBlock, x0 - p.pl, y0 - p.pt, b, bar(kAFull + stage));
                     if (t < 4 && cb == 0) HALO_STAMP(8 + t);
                 }
             }
@@ -285,12 +290,13 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                     const int stage = ia % p.nA, ause = ia / p.nA;
                     if (!mbar_wait_all(bar(kAFull + stage), (uint32_t)(ause & 1), ok_flag)) { fail(22); okw = false; break; }
                     if (need) {
-                        uint8_t* st = sA + (size_t)stage * kHaloABytes;
-                        for (int i = lane; i < kHaloPix * 8; i += 32) {
-                            const int px = i >> 3;
+                        uint8_t* st = sA + (size_t)stage * p.a_stage;
+                        const int cpr = (int)(p.a_row >> 4);                  // 16-byte chunks of a pixel's row: 8 or 4
+                        for (int i = lane; i < kHaloPix * cpr; i += 32) {
+                            const int px = i / cpr;
                             if (codes[px] == 2) {
                                 const int hy = px / kHaloCols, hx = px - hy * kHaloCols;
-                                *reinterpret_cast<uint4*>(st + (size_t)(hy * kHaloPitch + hx) * 128 + (i & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                                *reinterpret_cast<uint4*>(st + (size_t)(hy * kHaloPitch + hx) * p.a_row + (i - px * cpr) * 16) = make_uint4(0u, 0u, 0u, 0u);
                             }
                         }
                         fence_proxy_async();
@@ -362,7 +368,8 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                     if (p.b_resident && nt == 0 && cb == 0 && !mbar_wait_all(bar(kBFull), 0u, ok_flag)) { fail(44); okw = false; break; }
                     tc_fence_after();
                     const int ksteps = cb == p.ncb - 1 ? p.last_ksteps : kKBlock / 16;
-                    const uint64_t ad0 = make_smem_desc_ex(sA_u32 + (uint32_t)stage * kHaloABytes, kHaloPitch * 128u);
+                    const uint64_t ad0 = make_smem_desc_ex(sA_u32 + (uint32_t)stage * p.a_stage, kHaloPitch * p.a_row, p.a_row == 64u ? 4u : 2u);
+                    const uint32_t a_px = p.a_row >> 4;                       // a halo pixel in descriptor units of 16 bytes
                     if (p.b_resident) {
                         if (elect_one()) {
                             const uint64_t bd0 = make_smem_desc(sB_u32 + (uint32_t)cb * b_block_bytes);
@@ -370,7 +377,7 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
 #pragma unroll
                             for (int tap = 0; tap < 9; ++tap) {
                                 const int ky = tap / 3, kx = tap - ky * 3;
-                                const uint64_t ad = ad0 + (uint64_t)((ky * kHaloPitch + kx) * 8);
+                                const uint64_t ad = ad0 + (uint64_t)((uint32_t)(ky * kHaloPitch + kx) * a_px);
                                 const uint64_t bd = bd0 + (uint64_t)tap * b_tap;
 #ifdef DC_HALO_STAMPS
                                 if (t == 1 && cb == 0) HALO_STAMP(44 + tap);
@@ -395,7 +402,7 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                             if (!mbar_wait_all(bar(kBFull + bs), (uint32_t)((ib / p.nB) & 1), ok_flag)) { fail(45); okw = false; break; }
                             tc_fence_after();
                             if (elect_one()) {
-                                const uint64_t ad = ad0 + (uint64_t)((ky * kHaloPitch + kx) * 8);
+                                const uint64_t ad = ad0 + (uint64_t)((uint32_t)(ky * kHaloPitch + kx) * a_px);
                                 const uint64_t bd = make_smem_desc(sB_u32 + (uint32_t)bs * b_block_bytes);
                                 if (ksteps == kKBlock / 16) {
 #pragma unroll
@@ -603,7 +610,7 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
 
 // ---- host side ------------------------------------------------------------------------------------
 
-bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_desc* d, int tw, int th);
+bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_desc* d, int tw, int th, int box_c);
 
 struct HaloPlan {
     bool ok;
@@ -612,8 +619,10 @@ struct HaloPlan {
     size_t smem;
 };
 
-static HaloPlan plan_halo(const dc_conv_desc* d) {
+static HaloPlan plan_halo(const dc_conv_desc* d, bool a64_allowed) {
     HaloPlan pl{};
+    // at most 32 input channels: halo rows of 64 bytes (64-byte swizzle), half the stage
+    const size_t a_stage = (size_t)kHaloRows * kHaloPitch * ((d->c_in <= 32 && a64_allowed) ? 64 : 128);
     pl.ok = d->dtype == DC_F16 && d->groups == 1 && d->kh == 3 && d->kw == 3 && d->stride_h == 1 && d->stride_w == 1 &&
             d->dil_h == 1 && d->dil_w == 1 && d->c_in % 8 == 0 && d->c_in >= 16 && d->c_out % 8 == 0 && d->c_out >= 16 && d->c_out <= 256 &&
             d->pad_top <= 1 && d->pad_left <= 1 && d->h_out >= 8 && d->w_out >= 8;
@@ -630,7 +639,7 @@ static HaloPlan plan_halo(const dc_conv_desc* d) {
     const size_t resident = 9 * (size_t)pl.ncb * b_block;
     pl.ok = false;
     for (int nA = 3; nA >= 2 && !pl.ok; --nA) {
-        if (resident <= 96 * 1024 && nA * (size_t)kHaloABytes + resident + staging + misc <= budget) {
+        if (resident <= 96 * 1024 && nA * a_stage + resident + staging + misc <= budget) {
             pl.ok = true; pl.nA = nA; pl.b_resident = 1; pl.nB = 0;
         }
     }
@@ -638,22 +647,22 @@ static HaloPlan plan_halo(const dc_conv_desc* d) {
     if (!pl.ok && pl.bn >= 128) {
         for (int nA = 3; nA >= 2 && !pl.ok; --nA)
             for (int nB = kHaloMaxB; nB >= 4 && !pl.ok; --nB)
-                if (nA * (size_t)kHaloABytes + nB * b_block + staging + misc <= budget) {
+                if (nA * a_stage + nB * b_block + staging + misc <= budget) {
                     pl.ok = true; pl.nA = nA; pl.b_resident = 0; pl.nB = nB;
                 }
     }
     if (!pl.ok) return pl;
     const size_t b_bytes = pl.b_resident ? resident : pl.nB * b_block;
-    pl.off_b = (uint32_t)(pl.nA * (size_t)kHaloABytes);
+    pl.off_b = (uint32_t)((pl.nA * a_stage + 1023) & ~(size_t)1023);
     pl.off_stage = (uint32_t)((pl.off_b + b_bytes + 1023) & ~(size_t)1023);
     pl.off_misc = (uint32_t)(pl.off_stage + staging);
     pl.smem = pl.off_misc + misc + 1024 /* alignment slack */;
     // a smaller footprint (two stages) that lets two CTAs share an SM beats a third stage
     if (pl.b_resident && pl.nA == 3) {
-        const size_t two = 2 * (size_t)kHaloABytes + resident + staging + misc + 1024;
+        const size_t two = 2 * a_stage + resident + staging + misc + 2048;
         if (2 * (two + 1024) <= 227 * 1024 && 4 * pl.tmem_cols <= 512) {
             pl.nA = 2;
-            pl.off_b = (uint32_t)(2 * (size_t)kHaloABytes);
+            pl.off_b = (uint32_t)((2 * a_stage + 1023) & ~(size_t)1023);
             pl.off_stage = (uint32_t)((pl.off_b + b_bytes + 1023) & ~(size_t)1023);
             pl.off_misc = (uint32_t)(pl.off_stage + staging);
             pl.smem = pl.off_misc + misc + 1024;
@@ -670,7 +679,8 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
                  const dc_epilogue* ep, uint32_t b_kb_stride, int* fused_out, cudaStream_t st) {
     static const int mode = [] { const char* e = getenv("DC_HALO"); return e != nullptr ? atoi(e) : 1; }();   // DC_HALO=0 turns the halo-tile form off
     if (mode == 0) return DC_ERR_UNSUPPORTED;
-    HaloPlan pl = plan_halo(d);
+    static const bool a64_allowed = [] { const char* e = getenv("DC_HALO_A64"); return !(e != nullptr && e[0] == '0'); }();   // DC_HALO_A64=0: 128-byte rows for every layer
+    HaloPlan pl = plan_halo(d, a64_allowed);
     if (!pl.ok || mi == nullptr || mo == nullptr) return DC_ERR_UNSUPPORTED;
     const bool has_res = ep != nullptr && ep->residual != nullptr;
     const bool fused = ep != nullptr && !has_res && ep->truncation == DC_TRUNC_MAX;
@@ -681,7 +691,8 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
         return DC_ERR_UNSUPPORTED;
     alignas(64) CUtensorMap tmap;
     memset(&tmap, 0, sizeof(tmap));
-    if (!encode_patch_map(&tmap, in, d, kHaloPitch, kHaloRows)) return DC_ERR_UNSUPPORTED;
+    const bool a64 = d->c_in <= 32 && a64_allowed;
+    if (!encode_patch_map(&tmap, in, d, kHaloPitch, kHaloRows, a64 ? 32 : kKBlock)) return DC_ERR_UNSUPPORTED;
     HaloParams p{};
     p.mi = mi; p.wimg = (const uint8_t*)filt; p.bias = (const __half*)bias;
     p.out = (__half*)out; p.mo = mo;
@@ -705,6 +716,8 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
     fast_div_init((uint32_t)p.patch_px, &p.ppx_mul, &p.ppx_shift);
     fast_div_init((uint32_t)(p.patch_px * p.patch_py), &p.ppi_mul, &p.ppi_shift);
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
+    p.a_row = a64 ? 64u : 128u;
+    p.a_stage = (uint32_t)kHaloRows * kHaloPitch * p.a_row;
     { const char* e = getenv("DC_HALO_DBG"); p.dbg = e != nullptr ? atoi(e) : 0; }
     static PerDeviceOnce attr_once;
     bool* attr_set = attr_once.slot();

@@ -801,7 +801,8 @@ static bool encode_rows_map(CUtensorMap* map, const void* in, int64_t npix_in, i
 }
 
 // Tensor map of the input as [n][h][w][c] (fp16), box {64 channels, tw, th, 1}, 128-byte swizzle: what tma_load_patch reads.
-bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_desc* d, int tw, int th) {
+// ``box_c`` = channels per box: 64 (128-byte swizzle) or 32 (64-byte swizzle, rows of 64 bytes).
+bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_desc* d, int tw, int th, int box_c) {
     CUtensorMap rows_probe;
     if (!encode_rows_map(&rows_probe, in, (int64_t)d->n * d->h_in * d->w_in, d->c_in)) return false;   // looks the encoder up
     void* ptr = nullptr;
@@ -814,10 +815,10 @@ bool encode_patch_map(CUtensorMap* map, const void* in, const dc_conv_desc* d, i
     const cuuint64_t c2 = (cuuint64_t)d->c_in * 2u;
     const cuuint64_t gdim[4] = {(cuuint64_t)d->c_in, (cuuint64_t)d->w_in, (cuuint64_t)d->h_in, (cuuint64_t)d->n};
     const cuuint64_t gstride[3] = {c2, c2 * (cuuint64_t)d->w_in, c2 * (cuuint64_t)d->w_in * (cuuint64_t)d->h_in};
-    const cuuint32_t box[4] = {(cuuint32_t)kKBlock, (cuuint32_t)tw, (cuuint32_t)th, 1u};
+    const cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)tw, (cuuint32_t)th, 1u};
     const cuuint32_t estride[4] = {1u, 1u, 1u, 1u};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(in), gdim, gstride, box, estride,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, box_c == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -847,7 +848,10 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
                             (ep->activation == DC_ACT_NONE || (ep->prev_out != nullptr && aligned16(ep->prev_out)));
         if (!ok_res) return DC_ERR_UNSUPPORTED;
     }
-    const bool want_fused = !has_res && ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
+    bool want_fused = !has_res && ep != nullptr && ep->truncation == DC_TRUNC_MAX && d->c_out <= 256;
+    // a handful of tiles with a long K loop (3x3 256 -> 256 on an 8x8 map): one CTA per tile would walk the whole loop while
+    // most SMs idle; splitting the output channels over CTAs and truncating in a second pass is faster
+    if (want_fused && pl.nkb >= 16 && divup64(npix_out, 128) * 8 <= sm_count()) want_fused = false;
     // 1x1 layers without padding can do without a work list: each CTA compacts its own pixels. On small maps a CTA
     // owns one contiguous span; on large maps persistent CTAs own strided spans (multi-span mode). When the map is so
     // large that a CTA would need several rounds of spans and the caller gave scratch memory, the work list is
@@ -948,7 +952,7 @@ static int conv_umma_impl(const dc_conv_desc* d, int transposed, const void* in,
         p.npatches = (int64_t)d->n * p.patch_px * p.patch_py;
         fast_div_init((uint32_t)p.patch_px, &p.ppx_mul, &p.ppx_shift);
         fast_div_init((uint32_t)(p.patch_px * p.patch_py), &p.ppi_mul, &p.ppi_shift);
-        p.tma_rows = encode_patch_map(&tmap, in, d, tw, th) ? 2 : 0;
+        p.tma_rows = encode_patch_map(&tmap, in, d, tw, th, kKBlock) ? 2 : 0;
         int64_t per_sm = (int64_t)(227 * 1024) / (int64_t)(pl.smem + 1024);
         if (per_sm > 3) per_sm = 3;
         if (per_sm < 1) per_sm = 1;
