@@ -67,8 +67,6 @@ struct HaloParams {
     int64_t npatches;
     uint32_t ppx_mul, ppx_shift, ppi_mul, ppi_shift;
     uint32_t off_b, off_stage, off_misc, stage_pitch;
-    uint32_t a_row;                 // bytes of a halo pixel's row in shared memory: 128 (64 channels, 128-byte swizzle) or 64 (32 channels, 64-byte swizzle)
-    uint32_t a_stage;               // bytes of a halo stage: 18 x 16 pixels x a_row
     int dbg;
 };
 
@@ -103,10 +101,14 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" 
 // layer's activation with its accumulated sum. kExactAct: the fused activation is exact in packed half arithmetic.
 // kU: groups of rows a warp of the epilogue keeps in flight (4 when the CTA has its SM to itself and the tile needs more
 // than one round of cache reads otherwise: then all of a tile's cache rows are asked for in one round trip).
-template <int kEpi, bool kExactAct, int kU>
+// kA64: halo rows of 64 bytes (layers of at most 32 input channels) instead of 128: compile-time, so that the tap offsets
+// of the MMA loop stay constants.
+template <int kEpi, bool kExactAct, int kU, bool kA64>
 __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(const HaloParams p, const __grid_constant__ CUtensorMap tmap_in) {
     constexpr bool kFused = kEpi == 1;
     constexpr bool kRes = kEpi >= 2;
+    constexpr uint32_t kARow = kA64 ? 64u : 128u;              // bytes of a halo pixel's row in shared memory
+    constexpr uint32_t kAStage = (uint32_t)kHaloRows * kHaloPitch * kARow;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
@@ -245,8 +247,8 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                 const int stage = ia % p.nA, ause = ia / p.nA;
                 if (ause > 0 && !mbar_wait_warp(bar(kAEmpty + stage), (uint32_t)((ause - 1) & 1), ok_flag)) { fail(12); break; }
                 if (elect_one()) {
-                    mbar_expect_tx(bar(kAFull + stage), p.a_stage);
-                    tma_load_patch(sA_u32 + (uint32_t)stage * p.a_stage, &tmap_in, cb * kKBlock, x0 - p.pl, y0 - p.pt, b, bar(kAFull + stage));
+                    mbar_expect_tx(bar(kAFull + stage), kAStage);
+                    tma_load_patch(sA_u32 + (uint32_t)stage * kAStage, &tmap_in, cb * kKBlock, x0 - p.pl, y0 - p.pt, b, bar(kAFull + stage));
                     if (t < 4 && cb == 0) HALO_STAMP(8 + t);
                 }
             }
@@ -290,13 +292,13 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                     const int stage = ia % p.nA, ause = ia / p.nA;
                     if (!mbar_wait_all(bar(kAFull + stage), (uint32_t)(ause & 1), ok_flag)) { fail(22); okw = false; break; }
                     if (need) {
-                        uint8_t* st = sA + (size_t)stage * p.a_stage;
-                        const int cpr = (int)(p.a_row >> 4);                  // 16-byte chunks of a pixel's row: 8 or 4
+                        uint8_t* st = sA + (size_t)stage * kAStage;
+                        constexpr int cpr = (int)(kARow >> 4);                  // 16-byte chunks of a pixel's row: 8 or 4
                         for (int i = lane; i < kHaloPix * cpr; i += 32) {
                             const int px = i / cpr;
                             if (codes[px] == 2) {
                                 const int hy = px / kHaloCols, hx = px - hy * kHaloCols;
-                                *reinterpret_cast<uint4*>(st + (size_t)(hy * kHaloPitch + hx) * p.a_row + (i - px * cpr) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                                *reinterpret_cast<uint4*>(st + (size_t)(hy * kHaloPitch + hx) * kARow + (i - px * cpr) * 16) = make_uint4(0u, 0u, 0u, 0u);
                             }
                         }
                         fence_proxy_async();
@@ -368,8 +370,8 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                     if (p.b_resident && nt == 0 && cb == 0 && !mbar_wait_all(bar(kBFull), 0u, ok_flag)) { fail(44); okw = false; break; }
                     tc_fence_after();
                     const int ksteps = cb == p.ncb - 1 ? p.last_ksteps : kKBlock / 16;
-                    const uint64_t ad0 = make_smem_desc_ex(sA_u32 + (uint32_t)stage * p.a_stage, kHaloPitch * p.a_row, p.a_row == 64u ? 4u : 2u);
-                    const uint32_t a_px = p.a_row >> 4;                       // a halo pixel in descriptor units of 16 bytes
+                    const uint64_t ad0 = make_smem_desc_ex(sA_u32 + (uint32_t)stage * kAStage, kHaloPitch * kARow, kA64 ? 4u : 2u);
+                    constexpr uint32_t a_px = kARow >> 4;                       // a halo pixel in descriptor units of 16 bytes
                     if (p.b_resident) {
                         if (elect_one()) {
                             const uint64_t bd0 = make_smem_desc(sB_u32 + (uint32_t)cb * b_block_bytes);
@@ -716,8 +718,6 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
     fast_div_init((uint32_t)p.patch_px, &p.ppx_mul, &p.ppx_shift);
     fast_div_init((uint32_t)(p.patch_px * p.patch_py), &p.ppi_mul, &p.ppi_shift);
     p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
-    p.a_row = a64 ? 64u : 128u;
-    p.a_stage = (uint32_t)kHaloRows * kHaloPitch * p.a_row;
     { const char* e = getenv("DC_HALO_DBG"); p.dbg = e != nullptr ? atoi(e) : 0; }
     static PerDeviceOnce attr_once;
     bool* attr_set = attr_once.slot();
@@ -725,8 +725,10 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
     if (!*attr_set) {
         bool ok_attr = true;
 #define DC_HALO_ATTR(E, X) \
-        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<E, X, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess; \
-        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<E, X, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<E, X, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess; \
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<E, X, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess; \
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<E, X, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess; \
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<E, X, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess
         DC_HALO_ATTR(0, true); DC_HALO_ATTR(1, true); DC_HALO_ATTR(1, false); DC_HALO_ATTR(2, true); DC_HALO_ATTR(3, true);
 #undef DC_HALO_ATTR
         if (!ok_attr) return check_launch();
@@ -741,8 +743,12 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
     while (lanes_row < d->c_out / 8 && lanes_row < 32) lanes_row <<= 1;
     const bool deep = pl.ctas_per_sm == 1 && 8 * (32 / lanes_row) * 2 < kRows;
 #define DC_HALO_LAUNCH(E, X)                                                                                              \
-    rc = deep ? launch_pdl(k_conv3x3_halo<E, X, 4>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap)                       \
-              : launch_pdl(k_conv3x3_halo<E, X, 2>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap)
+    do {                                                                                                                  \
+        if (a64) rc = deep ? launch_pdl(k_conv3x3_halo<E, X, 4, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap)    \
+                           : launch_pdl(k_conv3x3_halo<E, X, 2, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);   \
+        else rc = deep ? launch_pdl(k_conv3x3_halo<E, X, 4, false>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap)       \
+                       : launch_pdl(k_conv3x3_halo<E, X, 2, false>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);      \
+    } while (0)
     if (has_res && res_act) DC_HALO_LAUNCH(3, true);
     else if (has_res) DC_HALO_LAUNCH(2, true);
     else if (!fused) DC_HALO_LAUNCH(0, true);
