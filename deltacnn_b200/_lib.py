@@ -69,6 +69,9 @@ _SIGNATURES = {
     "dc_concat": (c_int, [_P, _P, _P, _P, _P, _P, c_i64, c_int, c_int, c_int, _P]),
     "dc_densify": (c_int, [_P, _P, _P, _P, c_i64, c_int, c_int, c_int, _P]),
     "dc_compact_mask": (c_int, [_P, c_i64, _P, _P, _P]),
+    "dc_conv3x3_heads_supported": (c_int, [ctypes.POINTER(ConvDesc), c_int]),
+    "dc_conv3x3_heads": (c_int, [ctypes.POINTER(ConvDesc), _P, _P, _P, _P, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
+                                 ctypes.POINTER(Epilogue), _P]),
     "dc_irb_supported": (c_int, [ctypes.POINTER(IrbDesc)]),
     "dc_irb_fused": (c_int, [ctypes.POINTER(IrbDesc), _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "dc_sparsify_dilated": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P]),

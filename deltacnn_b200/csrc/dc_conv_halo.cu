@@ -59,6 +59,10 @@ struct HaloParams {
     __half* out; int32_t* mo; __half* prev; __half* trunc;
     float thr; int act;
     const __half* res; const int32_t* res_mask; __half* res_prev; int res_act;   // residual forms
+    // several layers on the same input in one launch (the 3x3 convolutions of detection heads): the output channels are
+    // nseg equal segments, each with its own output, out-mask, caches, threshold and activation
+    int nseg, seg_cout;
+    __half* seg_out[4]; int32_t* seg_mo[4]; __half* seg_prev[4]; __half* seg_trunc[4]; float seg_thr[4]; int seg_act[4];
     int h, w, ho, wo, pt, pl;
     int cin, cout, ncb, bn, tmem_cols, last_ksteps;
     int nA, nB, b_resident;
@@ -103,7 +107,8 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" 
 // than one round of cache reads otherwise: then all of a tile's cache rows are asked for in one round trip).
 // kA64: halo rows of 64 bytes (layers of at most 32 input channels) instead of 128: compile-time, so that the tap offsets
 // of the MMA loop stay constants.
-template <int kEpi, bool kExactAct, int kU, bool kA64>
+// kSeg: the output channels are p.nseg segments with their own outputs and caches (kEpi 0 or 1).
+template <int kEpi, bool kExactAct, int kU, bool kA64, bool kSeg = false>
 __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(const HaloParams p, const __grid_constant__ CUtensorMap tmap_in) {
     constexpr bool kFused = kEpi == 1;
     constexpr bool kRes = kEpi >= 2;
@@ -151,6 +156,14 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
     const uint32_t sA_u32 = smem_u32(sA), sB_u32 = smem_u32(sB);
     const int tiles_mine = (int)((p.npatches - blockIdx.x + gridDim.x - 1) / gridDim.x);
     auto fail = [&](int code) { *ok_flag = 0; atomicExch(&g_halo_error, code); };
+    auto write_mo = [&](int64_t idx, int v) {                 // the out-mask word of a pixel (of every segment)
+        if constexpr (kSeg) {
+#pragma unroll
+            for (int sg = 0; sg < 4; ++sg) if (sg < p.nseg) p.seg_mo[sg][idx] = v;
+        } else {
+            p.mo[idx] = v;
+        }
+    };
     auto patch_origin = [&](int t, int& b, int& y0, int& x0) {
         const uint32_t pid = (uint32_t)blockIdx.x + (uint32_t)t * gridDim.x;
         const uint32_t pb = fast_div(pid, p.ppi_mul, p.ppi_shift);
@@ -277,7 +290,7 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                             for (int kx = 0; kx < 3; ++kx) on |= codes[(y + ky) * kHaloCols + x + kx] == 1;
                         bool ron = false;
                         if constexpr (kRes) ron = ((s_info[slot * kHaloInfoWords + 5 + j] >> lane) & 1u) != 0u;
-                        if (!kFused || !on) p.mo[((int64_t)b * p.ho + oy) * p.wo + ox] = (on || ron) ? 1 : 0;
+                        if (!kFused || !on) write_mo(((int64_t)b * p.ho + oy) * p.wo + ox, (on || ron) ? 1 : 0);
                     }
                     const unsigned bal = __ballot_sync(DC_FULL, on);
                     if (lane == 0) s_info[slot * kHaloInfoWords + j] = bal;
@@ -316,7 +329,7 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
                 for (int j = 0; j < 4; ++j) {
                     const int r = lane + 32 * j;
                     const int oy = y0 + (r >> 3), ox = x0 + (r & 7);
-                    if (oy < p.ho && ox < p.wo) p.mo[((int64_t)b * p.ho + oy) * p.wo + ox] = 0;
+                    if (oy < p.ho && ox < p.wo) write_mo(((int64_t)b * p.ho + oy) * p.wo + ox, 0);
                 }
                 if (lane == 0) mbar_arrive(bar(kRowsFull + slot));
             }
@@ -496,7 +509,7 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
             };
             bool ok2 = true;
             if (any) {
-                if (rb_first < kRows) load_caches(rb_first);
+                if (!kSeg && rb_first < kRows) load_caches(rb_first);
                 ok2 = mbar_wait(bar(kAccFull + buf), (uint32_t)((nt >> 1) & 1), ok_flag);
             }
             if (!epi_bar_and(ok1 && ok2)) {
@@ -510,6 +523,94 @@ __global__ void __launch_bounds__(kHaloThreads, kU == 4 ? 1 : 2) k_conv3x3_halo(
             }
             if (etid == 0 && t < 4) HALO_STAMP(24 + t);
             tc_fence_after();
+            if constexpr (kSeg) {
+                // segment by segment: its columns of the accumulator -> staging tile -> rows against the segment's own caches
+                const int nch_s = p.seg_cout >> 3;
+                int gs = 1;
+                while (gs < nch_s && gs < 32) gs <<= 1;
+                const int ligs = lane & (gs - 1), ppws = 32 / gs;
+                for (int seg = 0; seg < p.nseg; ++seg) {
+                    const int c_base = seg * p.seg_cout;
+                    if (seg > 0) epi_bar_sync();                   // the previous segment's rows are done with the staging tile
+                    {
+                        const int quarter = warp & 3;
+                        const int r = quarter * 32 + lane;
+                        uint8_t* srow = sStage + (size_t)r * p.stage_pitch;
+#pragma unroll 1
+                        for (int c0 = (ew >> 2) * 16; c0 < p.seg_cout; c0 += 32) {
+                            uint32_t acc[16];
+                            tmem_ld16(tmem_base + (uint32_t)(buf * p.tmem_cols) + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c_base + c0), acc);
+                            tmem_ld_wait();
+                            uint4 o[2];
+                            __half2* h = reinterpret_cast<__half2*>(o);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                h[j] = __floats2half2_rn(__uint_as_float(acc[2 * j]) + s_bias[c_base + c0 + 2 * j],
+                                                         __uint_as_float(acc[2 * j + 1]) + s_bias[c_base + c0 + 2 * j + 1]);
+                            *reinterpret_cast<uint4*>(srow + c0 * 2) = o[0];
+                            *reinterpret_cast<uint4*>(srow + c0 * 2 + 16) = o[1];
+                        }
+                    }
+                    tc_fence_before();
+                    epi_bar_sync();
+                    if (etid == 0 && seg == p.nseg - 1) {          // the accumulator is staged or consumed: the next tile may use it
+                        mbar_arrive(bar(kAccEmpty + buf));
+                        mbar_arrive(bar(kInfoEmpty + slot));
+                    }
+                    __syncwarp();
+                    __half* out_s = seg == 0 ? p.seg_out[0] : seg == 1 ? p.seg_out[1] : seg == 2 ? p.seg_out[2] : p.seg_out[3];
+                    int32_t* mo_s = seg == 0 ? p.seg_mo[0] : seg == 1 ? p.seg_mo[1] : seg == 2 ? p.seg_mo[2] : p.seg_mo[3];
+                    __half* prev_s = seg == 0 ? p.seg_prev[0] : seg == 1 ? p.seg_prev[1] : seg == 2 ? p.seg_prev[2] : p.seg_prev[3];
+                    __half* trunc_s = seg == 0 ? p.seg_trunc[0] : seg == 1 ? p.seg_trunc[1] : seg == 2 ? p.seg_trunc[2] : p.seg_trunc[3];
+                    const float thr_s = seg == 0 ? p.seg_thr[0] : seg == 1 ? p.seg_thr[1] : seg == 2 ? p.seg_thr[2] : p.seg_thr[3];
+                    const int act_s = seg == 0 ? p.seg_act[0] : seg == 1 ? p.seg_act[1] : seg == 2 ? p.seg_act[2] : p.seg_act[3];
+                    const __half2 thr2_s = __float2half2_rn(thr_s);
+#pragma unroll 1
+                    for (int rb = ew * ppws * kU; rb < kRows; rb += kHaloEpiWarps * ppws * kU) {
+#pragma unroll
+                        for (int u = 0; u < kU; ++u) {
+                            const int r = rb + u * ppws + lane / gs;
+                            mine[u] = row_on(r) && ligs < nch_s;
+                            q[u] = ((int64_t)b * p.ho + y0 + (r >> 3)) * p.wo + x0 + (r & 7);
+                            off[u] = mine[u] ? q[u] * p.seg_cout + ligs * 8 : 0;
+                            if (mine[u]) {
+                                if (kFused) {
+                                    y[u].load(prev_s + off[u]);
+                                    tr[u].load(trunc_s + off[u]);
+                                }
+                                d[u].load(reinterpret_cast<const __half*>(sStage + (size_t)r * p.stage_pitch) + ligs * 8);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < kU; ++u) {
+                            if (!kFused) {
+                                if (mine[u]) d[u].store(out_s + off[u]);
+                                continue;
+                            }
+                            bool hit = false;
+                            if (mine[u]) {
+                                if constexpr (kExactAct) hit = truncate_pack_h2(d[u], y[u], tr[u], act_s, thr2_s);
+                                else hit = truncate_pack_f32(d[u], y[u], tr[u], act_s, thr_s);
+                            }
+                            const bool active = group_any(hit, gs, lane);
+                            if (mine[u]) {
+                                if (active) {
+                                    Pack<__half, 8> z; z.zero();
+                                    y[u].store(prev_s + off[u]);
+                                    d[u].store(out_s + off[u]);
+                                    z.store(trunc_s + off[u]);
+                                } else {
+                                    tr[u].store(trunc_s + off[u]);
+                                }
+                            }
+                            const int r = rb + u * ppws + lane / gs;
+                            if (ligs == 0 && row_on(r)) mo_s[q[u]] = active ? 1 : 0;
+                        }
+                    }
+                }
+                ++nt;
+                continue;
+            }
             // tensor memory -> fp16 staging tile (row = TMEM lane)
             {
                 const int quarter = warp & 3;
@@ -621,7 +722,7 @@ struct HaloPlan {
     size_t smem;
 };
 
-static HaloPlan plan_halo(const dc_conv_desc* d, bool a64_allowed) {
+static HaloPlan plan_halo(const dc_conv_desc* d, bool a64_allowed, int seg_cout = 0) {
     HaloPlan pl{};
     // at most 32 input channels: halo rows of 64 bytes (64-byte swizzle), half the stage
     const size_t a_stage = (size_t)kHaloRows * kHaloPitch * ((d->c_in <= 32 && a64_allowed) ? 64 : 128);
@@ -634,7 +735,8 @@ static HaloPlan plan_halo(const dc_conv_desc* d, bool a64_allowed) {
     pl.tmem_cols = 32;
     while (pl.tmem_cols < pl.bn) pl.tmem_cols <<= 1;
     const size_t b_block = (size_t)pl.bn * 128;
-    pl.stage_pitch = (uint32_t)pl.bn * 2 + 16;
+    // the staging tile holds one segment of the output channels at a time when the layer has several (else all of them)
+    pl.stage_pitch = (uint32_t)(seg_cout > 0 ? seg_cout : pl.bn) * 2 + 16;
     const size_t staging = ((size_t)kRows * pl.stage_pitch + 1023) & ~(size_t)1023;
     const size_t misc = 8 * 72 + 64 + kHaloInfo * kHaloInfoWords * 4 + kHaloInfo * kHaloCodesPitch + 4 * 256 + 4 * kHaloRawPitch * 4 + 64;
     const size_t budget = 227 * 1024 - 1024;
@@ -759,6 +861,70 @@ int conv3x3_halo(const dc_conv_desc* d, const void* in, const int32_t* mi, const
     return rc;
 }
 
+// Several 3x3 layers on the same input in one launch (see HaloParams::nseg): ``d`` describes the concatenated layer
+// (c_out = all output channels), the packed filter and the bias are the concatenation along the output channels.
+int conv3x3_halo_heads(const dc_conv_desc* d, const void* in, const int32_t* mi, const void* filt, const void* bias, int nseg,
+                       void* const* outs, int32_t* const* mos, const dc_epilogue* eps, uint32_t b_kb_stride, bool plan_only, cudaStream_t st) {
+    if (nseg < 2 || nseg > 4 || d->c_out % nseg != 0 || (d->c_out / nseg) % 16 != 0) return DC_ERR_UNSUPPORTED;
+    const int seg_cout = d->c_out / nseg;
+    HaloPlan pl = plan_halo(d, false, seg_cout);
+    if (!pl.ok) return DC_ERR_UNSUPPORTED;
+    if (plan_only) return DC_OK;
+    if (mi == nullptr || in == nullptr || filt == nullptr || outs == nullptr || mos == nullptr) return DC_ERR_NULL_POINTER;
+    const bool fused = eps != nullptr;
+    bool exact_act = true;
+    HaloParams p{};
+    for (int sg = 0; sg < nseg; ++sg) {
+        if (outs[sg] == nullptr || mos[sg] == nullptr || !aligned16(outs[sg])) return DC_ERR_NULL_POINTER;
+        p.seg_out[sg] = (__half*)outs[sg];
+        p.seg_mo[sg] = mos[sg];
+        if (fused) {
+            const dc_epilogue& e = eps[sg];
+            if (e.residual != nullptr || e.truncation != DC_TRUNC_MAX || e.prev_out == nullptr || e.truncated == nullptr ||
+                !aligned16(e.prev_out) || !aligned16(e.truncated))
+                return DC_ERR_UNSUPPORTED;
+            p.seg_prev[sg] = (__half*)e.prev_out;
+            p.seg_trunc[sg] = (__half*)e.truncated;
+            p.seg_thr[sg] = host_round_threshold<__half>(e.threshold);
+            p.seg_act[sg] = e.activation;
+            exact_act = exact_act && e.activation >= DC_ACT_NONE && e.activation <= DC_ACT_RELU6;
+        }
+    }
+    alignas(64) CUtensorMap tmap;
+    memset(&tmap, 0, sizeof(tmap));
+    if (!encode_patch_map(&tmap, in, d, kHaloPitch, kHaloRows, kKBlock)) return DC_ERR_UNSUPPORTED;
+    p.mi = mi; p.wimg = (const uint8_t*)filt; p.bias = (const __half*)bias;
+    p.nseg = nseg; p.seg_cout = seg_cout;
+    p.h = d->h_in; p.w = d->w_in; p.ho = d->h_out; p.wo = d->w_out; p.pt = d->pad_top; p.pl = d->pad_left;
+    p.cin = d->c_in; p.cout = d->c_out; p.ncb = pl.ncb; p.bn = pl.bn; p.tmem_cols = pl.tmem_cols;
+    p.last_ksteps = (d->c_in - (pl.ncb - 1) * kKBlock + 15) >> 4;
+    p.nA = pl.nA; p.nB = pl.nB; p.b_resident = pl.b_resident;
+    p.b_kb_stride = b_kb_stride;
+    p.patch_px = divup(d->w_out, kHaloTw);
+    p.patch_py = divup(d->h_out, kHaloTh);
+    p.npatches = (int64_t)d->n * p.patch_px * p.patch_py;
+    if (p.npatches > 0x7fffffffLL) return DC_ERR_UNSUPPORTED;
+    fast_div_init((uint32_t)p.patch_px, &p.ppx_mul, &p.ppx_shift);
+    fast_div_init((uint32_t)(p.patch_px * p.patch_py), &p.ppi_mul, &p.ppi_shift);
+    p.off_b = pl.off_b; p.off_stage = pl.off_stage; p.off_misc = pl.off_misc; p.stage_pitch = pl.stage_pitch;
+    static PerDeviceOnce attr_once;
+    bool* attr_set = attr_once.slot();
+    if (attr_set == nullptr) return DC_ERR_LAUNCH;
+    if (!*attr_set) {
+        bool ok_attr = true;
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<0, true, 4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<1, true, 4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        ok_attr &= cudaFuncSetAttribute(k_conv3x3_halo<1, false, 4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+        if (!ok_attr) return check_launch();
+        *attr_set = true;
+    }
+    const int64_t persistent = sm_count();                     // these variants keep an SM to themselves
+    const dim3 grid((unsigned)(p.npatches < persistent ? p.npatches : persistent));
+    if (!fused) return launch_pdl(k_conv3x3_halo<0, true, 4, false, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);
+    if (exact_act) return launch_pdl(k_conv3x3_halo<1, true, 4, false, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);
+    return launch_pdl(k_conv3x3_halo<1, false, 4, false, true>, grid, dim3(kHaloThreads), pl.smem, st, p, tmap);
+}
+
 #ifdef DC_HALO_STAMPS
 extern "C" int dc_halo_debug_stamps(long long* out64) {
     return cudaMemcpyFromSymbol(out64, g_halo_stamps, 64 * sizeof(long long)) == cudaSuccess ? 0 : 1;
@@ -772,3 +938,28 @@ int halo_error_code() {
 }
 
 }  // namespace dc
+
+using namespace dc;
+
+extern "C" {
+
+// rows of a K block of the packed tensor-core filter image (the layout of dc_pack_filter_umma): the output channels
+// rounded up to 256, plus room for a ragged last N tile
+static uint32_t umma_kb_stride(const dc_conv_desc* d) { return (uint32_t)(divup(d->c_out, 256) * 256 + 256) * 128u; }
+
+int dc_conv3x3_heads_supported(const dc_conv_desc* desc, int32_t n_heads) {
+    if (desc == nullptr) return 0;
+    return conv3x3_halo_heads(desc, nullptr, nullptr, nullptr, nullptr, n_heads, nullptr, nullptr, nullptr, 0u, true, nullptr) == DC_OK ? 1 : 0;
+}
+
+int dc_conv3x3_heads(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter_umma, const void* bias,
+                     int32_t n_heads, void* const* outs, int32_t* const* masks_out, const dc_epilogue* epilogues, void* stream) {
+    if (desc == nullptr) return DC_ERR_NULL_POINTER;
+    if (!aligned16(in) || !aligned16(filter_umma)) return DC_ERR_ALIGNMENT;
+    if ((int64_t)desc->n * desc->h_out * desc->w_out == 0) return DC_OK;
+    return conv3x3_halo_heads(desc, in, mask_in, filter_umma, bias, n_heads, outs, masks_out, epilogues, umma_kb_stride(desc), false,
+                              (cudaStream_t)stream);
+}
+
+}  // extern "C"
+

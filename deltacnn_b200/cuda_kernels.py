@@ -482,6 +482,42 @@ def fused_inverted_residual(x, mask, w_expand_umma, w_dw, w_project_umma, prev_e
     return out, mask_out
 
 
+def conv3x3_heads_supported(desc, n_heads):
+    """Whether ``conv3x3_heads`` has a kernel for the concatenated layer ``desc`` (c_out = all heads' output channels)."""
+    return bool(lib.dc_conv3x3_heads_supported(desc, int(n_heads)))
+
+
+def conv3x3_heads(x, mask, filter_umma, bias, outs, masks_out, desc, epilogues=None):
+    """Several stride-1 3x3 convolutions on the same input (delta, mask) in one launch; head h writes ``outs[h]`` /
+    ``masks_out[h]`` and, with ``epilogues`` (one ``make_epilogue`` per head), runs that head's activation/truncation
+    step in the same launch. ``desc`` is the descriptor of the concatenated layer, ``filter_umma`` / ``bias`` the packed
+    filter / bias of the filters concatenated along the output channels. Same results per head as ``sparse_conv`` with a
+    fused epilogue. No reference counterpart (the reference runs every head's convolution and truncation on its own,
+    src/cuda/conv_torch_wrapper.cpp:62-134, 295-344)."""
+    import ctypes
+    _check_feature(x, "x")
+    _check_mask(mask, x, "mask")
+    nh = len(outs)
+    if len(masks_out) != nh or (epilogues is not None and len(epilogues) != nh):
+        raise RuntimeError("deltacnn_b200.conv3x3_heads: outs, masks_out and epilogues must have one entry per head")
+    n = x.shape[0]
+    seg = desc.c_out // max(nh, 1)
+    for h, (o, m) in enumerate(zip(outs, masks_out)):
+        if tuple(o.shape) != (n, seg, desc.h_out, desc.w_out) or o.dtype != x.dtype or o.device != x.device or \
+                not o.is_contiguous(memory_format=torch.channels_last):
+            raise RuntimeError(f"deltacnn_b200.conv3x3_heads: outs[{h}] must be a channels_last {(n, seg, desc.h_out, desc.w_out)} tensor like x")
+        if m.dtype != torch.int32 or m.device != x.device or m.numel() != n * desc.h_out * desc.w_out:
+            raise RuntimeError(f"deltacnn_b200.conv3x3_heads: masks_out[{h}] must hold one int32 per output pixel")
+    out_ptrs = (ctypes.c_void_p * nh)(*[o.data_ptr() for o in outs])
+    mask_ptrs = (ctypes.c_void_p * nh)(*[m.data_ptr() for m in masks_out])
+    eps = None
+    if epilogues is not None:
+        eps = (Epilogue * nh)(*epilogues)
+    check(lib.dc_conv3x3_heads(desc, x.data_ptr(), mask.data_ptr(), filter_umma.data_ptr(), _ptr(bias), nh, out_ptrs, mask_ptrs, eps,
+                               _stream()), "conv3x3_heads")
+    return outs, masks_out
+
+
 def compact_mask(mask, indices=None, count=None):
     """Indices of the active pixels of ``mask`` (order unspecified) and their number, on the device."""
     n = mask.numel()

@@ -434,6 +434,7 @@ class DCConv2d(_DeltaConvMixin, nn.Conv2d, DCModule):
     fuse_residual_activation = False   # ... also when the add layer has an activation (its accumulated sum is updated by the convolution)
     patch_tiles = False       # stride-1 KxK layers: patch tiles loaded by tiled TMA (mostly active maps) instead of work lists
     fuse_blocks = False       # DCFusedInvertedResidual: whole inverted-residual blocks of small maps in one kernel (opt-in)
+    fuse_heads = True         # DCFusedHeads: the 3x3 layers of several heads on the same input in one kernel
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1, groups: int = 1,
                  bias: bool = True, padding_mode: str = "zeros", delta_threshold: float = None, name: str = None,
@@ -976,6 +977,77 @@ class DCCenterNetDecode(DCModule):
         self.dense = None
         self._state = None
         self._union = None
+
+
+class DCFusedHeads:
+    """Runs the first layers of several heads that read the SAME input -- stride-1 3x3 ``DCConv2d`` layers with a fused
+    activation, equal in shape -- as ONE kernel on steady-state frames (``cuda_kernels.conv3x3_heads``): the input tile
+    is loaded once for all heads, every head keeps its own output, out-mask, caches and threshold. It owns no state (the
+    caches are those of the layers' activation layers), so a stream may switch between this call and the layers' own
+    forwards from frame to frame. No reference counterpart (the reference runs every head's convolution and truncation
+    kernels on their own)."""
+
+    def __init__(self, convs):
+        self.convs = list(convs)
+        self._key = None
+        self._desc = None
+        self._packed = None
+
+    def ready(self, input):
+        """True when this frame can take the fused kernel."""
+        if not DCConv2d.fuse_heads or K.DCPerformanceMetricsManager.enabled or type(input) == Tensor or len(self.convs) < 2:
+            return False
+        x = input[0]
+        c0 = self.convs[0]
+        if x.dtype != torch.float16 or not x.is_cuda:
+            return False
+        for c in self.convs:
+            a = c.activation_layer
+            if c.backend != DCBackend.deltacnn or c._transposed or tuple(c.kernel_size) != (3, 3) or tuple(c.stride) != (1, 1) or \
+                    tuple(c.dilation) != (1, 1) or c.groups != 1 or tuple(c.padding) != tuple(c0.padding) or \
+                    c.in_channels != c0.in_channels or c.out_channels != c0.out_channels or c.orig_weights is None or c.dense_out:
+                return False
+            if a is None or a.first_iter or not a.inplace or a.truncation_mode != DCTruncation.max or not c.fuse_activation or c.frame_idx <= 0:
+                return False
+        key = tuple(x.shape)
+        if self._key != key:
+            self._key, self._desc = key, None
+            hw = K.conv_out_hw(x.shape[2], x.shape[3], c0.kernel_size, c0.stride, c0.padding, c0.dilation)
+            total = c0.out_channels * len(self.convs)
+            desc = K.make_conv_desc(key, total, hw, (3, 3), c0.stride, c0.padding, c0.dilation, 1, K._dtype(x))
+            if K.conv3x3_heads_supported(desc, len(self.convs)):
+                from ._lib import lib, check
+                w_cat = torch.cat([c.weight.data for c in self.convs], dim=3).contiguous()      # HWIO, concatenated outputs
+                nbytes = lib.dc_filter_umma_bytes(desc, 0)
+                if nbytes > 0:
+                    self._packed = torch.zeros(nbytes, dtype=torch.uint8, device=x.device)
+                    check(lib.dc_pack_filter_umma(desc, 0, w_cat.data_ptr(), self._packed.data_ptr(),
+                                                  torch.cuda.current_stream(x.device).cuda_stream), "pack_filter_umma")
+                    self._desc = desc
+        return self._desc is not None
+
+    def __call__(self, input):
+        x, mask = input
+        desc = self._desc
+        n = x.shape[0]
+        outs, masks, eps = [], [], []
+        for c in self.convs:
+            dims = (n, c.out_channels, desc.h_out, desc.w_out)
+            if c._out is None or tuple(c._out.shape) != dims or not DCModule_reuse_buffers():
+                c._out = torch.empty(dims, dtype=x.dtype, device=x.device).contiguous(memory_format=torch.channels_last)
+                c.out_mask = torch.empty((n, 1, desc.h_out, desc.w_out), dtype=torch.int32, device=x.device)
+            a = c.activation_layer
+            for t, what in ((a.prev_out, "the activation cache"), (a.out_truncated, "the truncation cache")):
+                if t is None or tuple(t.shape) != dims or t.dtype != x.dtype or t.device != x.device:
+                    raise RuntimeError(f"deltacnn_b200: {what} of {c!r} does not match the output {dims} "
+                                       "(call reset_layers() after a batch or resolution change)")
+            outs.append(c._out)
+            masks.append(c.out_mask)
+            eps.append(K.make_epilogue(a.prev_out, a.out_truncated, DCThreshold.get(a), a.activation_int, a.truncation_mode.value))
+            DCConv2d.conv_idx += 1                    # what the layer's own forward would have counted
+            c.frame_idx += 1
+        K.conv3x3_heads(x, mask, self._packed, None, outs, masks, desc, epilogues=eps)
+        return [(o, m) for o, m in zip(outs, masks)]
 
 
 class DCFusedInvertedResidual:

@@ -280,7 +280,10 @@ def make_centernet(ops, head_channels=64, decode=False):
             self.densify = ops.densify()
 
         def forward(self, x, dense=True):
-            x = self.c2(self.c1(x))
+            return self.tail(self.c1(x), dense)
+
+        def tail(self, x, dense=True):            # everything behind the 3x3 layer
+            x = self.c2(x)
             return self.densify(x) if dense else x
 
     class CenterNet(Base):
@@ -302,13 +305,18 @@ def make_centernet(ops, head_channels=64, decode=False):
             self.ups = nn.Sequential(*ups)
             self.hm, self.wh, self.off = Head(256, 1), Head(256, 2), Head(256, 2)
             self.boxes = ops.boxes() if decode else None
+            # the three heads' 3x3 layers read the same map: one kernel on steady-state frames of the delta network
+            self.fused_heads = ops.fused_heads([self.hm.c1, self.wh.c1, self.off.c1]) if ops.delta else None
 
         def forward(self, x):
             x = self.ups(self.layers(self.maxpool(self.stem(self.sparsify(x)))))
-            if self.boxes is None:
-                return self.hm(x), self.wh(x), self.off(x)
-            dense = not ops.delta                   # the delta decode accumulates the three head deltas itself
-            return self.boxes(self.hm(x, dense), self.wh(x, dense), self.off(x, dense))
+            dense = self.boxes is None or not ops.delta     # the delta decode accumulates the three head deltas itself
+            heads = (self.hm, self.wh, self.off)
+            if self.fused_heads is not None and self.fused_heads.ready(x):
+                outs = [h.tail(t, dense) for h, t in zip(heads, self.fused_heads(x))]
+            else:
+                outs = [h(x, dense) for h in heads]
+            return tuple(outs) if self.boxes is None else self.boxes(*outs)
 
     return CenterNet()
 

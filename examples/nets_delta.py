@@ -1,7 +1,8 @@
 """The "ops" factory that builds the networks of ``nets`` out of the DC* modules of deltacnn_b200 (the delta
 twin of ``nets.DenseOps``): folded delta convolutions with fused activation, DCAdd, delta pooling, and the
 device-side heads."""
-from deltacnn_b200 import (DCAdaptiveAveragePooling, DCAdd, DCCenterNetDecode, DCConv2d, DCConvTranspose2d, DCDensify, DCFusedInvertedResidual,
+from deltacnn_b200 import (DCAdaptiveAveragePooling, DCAdd, DCCenterNetDecode, DCConv2d, DCConvTranspose2d, DCDensify, DCFusedHeads,
+                           DCFusedInvertedResidual,
                            DCHeatmapArgmax, DCLinear, DCMaxPooling, DCModule, DCSparsify, DCUpsamplingNearest2d)
 
 
@@ -57,3 +58,9 @@ class DeltaOps:
     def fused_block(expand, depthwise, project):
         """One-kernel form of an inverted-residual block built from its three DeltaConv layers."""
         return DCFusedInvertedResidual(expand.conv, depthwise.conv, project.conv)
+
+    @staticmethod
+    def fused_heads(convs):
+        """One-kernel form of the 3x3 first layers of several heads that read the same feature map."""
+        return DCFusedHeads([c.conv for c in convs])
+

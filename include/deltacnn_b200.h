@@ -275,6 +275,20 @@ int dc_irb_fused(const dc_irb_desc* desc, const void* x, const int32_t* mask_in,
                  const void* w_project_umma, void* prev_expand, void* trunc_expand, void* prev_dw, void* trunc_dw, void* out,
                  int32_t* mask_out, void* stream);
 
+/* Several 3x3 convolutions on the SAME input in one launch (the first layers of detection heads: CenterNet's heat-map,
+ * size and offset heads each start with a 3x3 256 -> 64 convolution + ReLU on the same feature map). No reference
+ * counterpart: it replaces n_heads sparse_conv_bias_wrapper_masked + deltacnn_activate_truncate pairs
+ * (src/cuda/conv_torch_wrapper.cpp:62-134, 295-344) with the same results per head; the input tile is loaded once for
+ * all heads. desc describes the concatenated layer (c_out = sum of the heads' output channels, which must be equal per
+ * head, a multiple of 16, n_heads 2..4); filter_umma / bias are the DC_FILTER_UMMA image / bias of the filters
+ * concatenated along the output channels. outs[h], masks_out[h]: output (n, h_out, w_out, c_out / n_heads) and out-mask of
+ * head h. epilogues (array of n_heads, or NULL for plain stores): prev_out / truncated / threshold / activation of each
+ * head's truncation layer (truncation DC_TRUNC_MAX). fp16, stride 1, no dilation, padding <= 1. Shapes without this form
+ * return DC_ERR_UNSUPPORTED (dc_conv3x3_heads_supported tells in advance) and the caller runs the layers one by one. */
+int dc_conv3x3_heads_supported(const dc_conv_desc* desc, int32_t n_heads);
+int dc_conv3x3_heads(const dc_conv_desc* desc, const void* in, const int32_t* mask_in, const void* filter_umma, const void* bias,
+                     int32_t n_heads, void* const* outs, int32_t* const* masks_out, const dc_epilogue* epilogues, void* stream);
+
 /* ---- task heads behind the delta path -------------------------------------------------------------------
  * No counterpart among the reference's kernels: its networks end with DCDensify and dense torch code
  * (example/mobilenet_deltacnn.py:216-227: adaptive_avg_pooling -> densify -> reshape -> nn.Linear;

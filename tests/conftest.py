@@ -24,6 +24,7 @@ def _reset_dc_state():
         DCConv2d.backend = DCBackend.deltacnn
         DCConv2d.conv_idx = -1
         DCConv2d.fuse_blocks = False
+        DCConv2d.fuse_heads = True
         DCAdd.idx = DCSparsify.idx = DCActivation.idx = DCDensify.idx = -1
         DCModule.temp_buffers = []
     except Exception:

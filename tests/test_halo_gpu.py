@@ -118,3 +118,61 @@ def test_halo_tiles_repeat_calls_give_identical_results():
         o, m = kk.sparse_conv(x, f, mask, None, (1, 1), (1, 1), (1, 1), 1, create_out_mask=True, out=out, filter_umma=packed)
         outs.append((o.clone(), m.clone()))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.parametrize("cin,seg,nh,n,h,w", [(256, 64, 3, 2, 33, 40), (64, 32, 2, 3, 24, 16), (64, 32, 4, 1, 40, 24), (128, 64, 3, 1, 20, 17)])
+@pytest.mark.parametrize("kind", ["full", "half", "sparse"])
+def test_several_heads_in_one_launch(cin, seg, nh, n, h, w, kind):
+    """dc_conv3x3_heads: the 3x3 convolutions of several heads on the same input in one launch. Plain form against the
+    oracle per head; fused form (each head's own caches, threshold and activation) against the plain form followed by the
+    stand-alone truncation kernel per head: identical masks, caches and values."""
+    import deltacnn_b200.cuda_kernels as kk
+    from deltacnn_b200 import _lib
+    from deltacnn_b200.filter_conversion import convert_filter_out_channels_last
+    g = torch.Generator().manual_seed(3)
+    x = cl((torch.randn(n, cin, h, w, generator=g) * 0.5).half())
+    mask = _masks(g, n, h, w, kind)
+    wts = [(torch.randn(seg, cin, 3, 3, generator=g) / (3 * cin ** 0.5)).half() for _ in range(nh)]
+    biases = [torch.randn(seg, generator=g).half() for _ in range(nh)]
+    wcat, bcat = torch.cat(wts, dim=0), torch.cat(biases, dim=0)
+    f = convert_filter_out_channels_last(wcat).cuda()
+    packed = _packed(kk, f, cin, seg * nh, 1)
+    desc = kk.make_conv_desc((n, cin, h, w), seg * nh, (h, w), (3, 3), (1, 1), (1, 1), (1, 1), 1, 1)
+    assert kk.conv3x3_heads_supported(desc, nh)
+    xd, md = x.cuda(), mask.cuda()
+    xd[(mask == 0).expand_as(x)] = float("nan")
+    outs = [cl(torch.full((n, seg, h, w), float("nan"), dtype=torch.float16)).cuda() for _ in range(nh)]
+    mos = [torch.full((n, 1, h, w), -7, dtype=torch.int32, device="cuda") for _ in range(nh)]
+    kk.conv3x3_heads(xd, md, packed, bcat.cuda(), outs, mos, desc)
+    torch.cuda.synchronize()
+    assert _lib.lib.dc_umma_error() == 0
+    for hd in range(nh):
+        ref, m_ref = O.conv(x, mask, wts[hd], biases[hd], (1, 1), (1, 1), (1, 1), 1)
+        assert torch.equal(mos[hd].cpu(), m_ref), f"head {hd}: out-mask"
+        sel = (m_ref != 0).expand_as(ref)
+        if sel.any():
+            scale = max(ref.float()[sel].abs().max().item(), 1e-6)
+            assert (outs[hd].cpu().float()[sel] - ref.float()[sel]).abs().max().item() / scale <= 1e-2, f"head {hd}: values"
+        assert torch.isnan(outs[hd].cpu()[~sel]).all(), "pixels outside the out-mask must not be written"
+    # fused truncation, every head with its own threshold and activation
+    prevs = [cl(torch.randn(n, seg, h, w, generator=g).half()) for _ in range(nh)]
+    truncs = [cl((torch.randn(n, seg, h, w, generator=g) * 0.02).half()) for _ in range(nh)]
+    thr = [0.6 + 0.15 * hd for hd in range(nh)]
+    acts = [1, 2, 1, 0][:nh]
+    p1, t1 = [p.cuda() for p in prevs], [t.cuda() for t in truncs]
+    o1 = [cl(torch.zeros(n, seg, h, w, dtype=torch.float16)).cuda() for _ in range(nh)]
+    m1 = [torch.empty(n, 1, h, w, dtype=torch.int32, device="cuda") for _ in range(nh)]
+    kk.conv3x3_heads(xd, md, packed, None, o1, m1, desc)
+    for hd in range(nh):
+        kk.sparse_activation(o1[hd], p1[hd], t1[hd], m1[hd], thr[hd], acts[hd], 0)
+    p2, t2 = [p.cuda() for p in prevs], [t.cuda() for t in truncs]
+    o2 = [cl(torch.zeros(n, seg, h, w, dtype=torch.float16)).cuda() for _ in range(nh)]
+    m2 = [torch.empty(n, 1, h, w, dtype=torch.int32, device="cuda") for _ in range(nh)]
+    kk.conv3x3_heads(xd, md, packed, None, o2, m2, desc,
+                     epilogues=[kk.make_epilogue(p2[hd], t2[hd], thr[hd], acts[hd], 0) for hd in range(nh)])
+    torch.cuda.synchronize()
+    assert _lib.lib.dc_umma_error() == 0
+    for hd in range(nh):
+        assert torch.equal(m1[hd], m2[hd]) and torch.equal(p1[hd], p2[hd]) and torch.equal(t1[hd], t2[hd]), f"head {hd}"
+        sel = (m1[hd] != 0).expand_as(o1[hd])
+        assert torch.equal(o1[hd][sel], o2[hd][sel]), f"head {hd}"

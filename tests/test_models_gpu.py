@@ -177,6 +177,29 @@ def test_centernet_threshold0_matches_dense(dtype):
     _run_equivalence("centernet", frames, dtype)
 
 
+def test_centernet_heads_in_one_kernel_are_used_and_match_the_separate_layers():
+    """The three heads' 3x3 layers run as one kernel on steady-state fp16 frames (DCFusedHeads); with that form and
+    with the layers one by one the boxes' inputs agree to half-precision accuracy and both pass the dense gate."""
+    from deltacnn_b200 import DCConv2d, DCThreshold
+    from examples.nets import build_pair
+    frames = _frames("centernet", 0, 4, size=(272, 480))
+    outs = {}
+    try:
+        for fused in (True, False):
+            DCConv2d.fuse_heads = fused
+            DCThreshold.reset()
+            _, delta = build_pair("centernet", frames[:4], device="cuda", dtype=torch.float16)
+            with torch.no_grad():
+                outs[fused] = [[o.float().clone() for o in _outs(delta(frames[t:t + 1].cuda().half().contiguous(memory_format=torch.channels_last)))]
+                               for t in range(frames.shape[0])]
+            assert (delta.fused_heads._desc is not None) == fused
+    finally:
+        DCConv2d.fuse_heads = True
+    for t in range(frames.shape[0]):
+        for a, b in zip(outs[True][t], outs[False][t]):
+            assert _rel(a, b) <= 1e-2, f"frame {t}"
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_hrnet_threshold0_matches_dense(dtype):
     frames = _frames("hrnet", 0, 3)
