@@ -45,7 +45,10 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--streams", type=int, default=64, help="streams per GPU")
     ap.add_argument("--total-streams", type=int, default=0, help="streams of the whole job, dealt round-robin to the GPUs (0: --streams per GPU)")
-    ap.add_argument("--branches", type=int, default=2, help="groups of streams stepped concurrently inside one CUDA graph")
+    ap.add_argument("--branches", type=int, default=1, help="groups of streams stepped concurrently inside one CUDA graph")
+    ap.add_argument("--stages", default="6,10,14",
+                    help="frame pipeline over the depth of the network: indices into the network's feature blocks where a new "
+                         "stage starts (stage s of a step works on the frame of s steps ago); empty: no pipeline")
     ap.add_argument("--repeats", type=int, default=5, help="repetitions of the timed block of --steps steps (median reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the dense-cuDNN / CPU / reference-kernel / roofline side measurements")
@@ -207,7 +210,7 @@ def main():
     import torch
     import torch.distributed as dist
     from examples.nets import build_pair
-    from examples.runner import MultiBranchStep, PipelinedStep, set_depth_thresholds
+    from examples.runner import DepthPipeline, DepthPipelinedStep, MultiBranchStep, PipelinedStep, set_depth_thresholds
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -245,19 +248,36 @@ def main():
             m(frames_dev[0][sl])                                        # first frame: dense initialisation
             table = set_depth_thresholds(model=m, **THRESHOLDS)
             m(frames_dev[1][sl])                                        # one eager steady-state frame: buffers allocated
-        step = MultiBranchStep(deltas, [frames_dev[1][bounds[g]:bounds[g + 1]] for g in range(G)])
+        # With --stages every group's network is also cut into depth stages that work on consecutive frames at the
+        # same time (examples/runner.py, DepthPipeline): every step still runs every layer once for every stream, and
+        # the logits a step returns belong to the frame of len(cuts) steps earlier.
+        cuts = [int(v) for v in args.stages.split(",") if v.strip()]
+        if cuts:
+            step = DepthPipelinedStep([m.depth_stages(cuts) for m in deltas], [frames_dev[1][bounds[g]:bounds[g + 1]] for g in range(G)],
+                                      models=deltas)
+        else:
+            step = MultiBranchStep(deltas, [frames_dev[1][bounds[g]:bounds[g + 1]] for g in range(G)])
     t_next = [2]
+    last_frame = [frames_dev[1]]
 
     def load(frame):
+        bufs = step.static_in
         for g in range(G):
-            step.static_in[g].copy_(frame[bounds[g]:bounds[g + 1]], non_blocking=True)
+            bufs[g].copy_(frame[bounds[g]:bounds[g + 1]], non_blocking=True)
+        last_frame[0] = frame
 
     def run_steps(n):
         for _ in range(n):
             i = pingpong(t_next[0], F)
             t_next[0] += 1
             load(frames_dev[i])
-            step.graph.replay()
+            step()
+
+    def drained_outputs():
+        """Outputs that belong to the last loaded frame (the pipeline, if any, emptied by repeating that frame)."""
+        if cuts:
+            return step.drain([last_frame[0][bounds[g]:bounds[g + 1]] for g in range(G)])
+        return step.static_out
 
     def barrier():
         if world > 1:
@@ -286,7 +306,7 @@ def main():
     # checksum of the outputs after the same number of steps on every run: comparable between runs that deal the
     # same streams differently to GPUs
     with torch.no_grad():
-        out_now = torch.cat([o.float() for o in step.static_out], dim=0)
+        out_now = torch.cat([o.float() for o in drained_outputs()], dim=0)
     sums = stream_checksums(out_now)
     if world > 1:
         gathered = [None] * world
@@ -305,7 +325,11 @@ def main():
     with torch.no_grad():
         for g, m in enumerate(deltas):
             m(u8_example[g])                                            # one eager 8-bit frame before capture
-    pipe = PipelinedStep(deltas, u8_example, bounds, stream)
+    if cuts:
+        depth_pipe = DepthPipeline([m.depth_stages(cuts) for m in deltas], u8_example, models=deltas)
+        pipe = PipelinedStep(deltas, u8_example, bounds, stream, capture=depth_pipe.capture)
+    else:
+        pipe = PipelinedStep(deltas, u8_example, bounds, stream)
 
     def next_host_frame():
         f = host_frames[pingpong(t_next[0], F)]
@@ -331,7 +355,33 @@ def main():
         for _ in range(4):
             run_steps(1)
             dens.append(sum(float(m.sparsify.mask.float().mean().item()) for m in deltas) / G)
+        drained_outputs()
     launches_per_step = count_launches(deltas, bounds, frames_dev, t_next, F)
+
+    # the same streams without the depth pipeline (two stream groups side by side): what the pipeline buys
+    unpipelined = None
+    if cuts and rank == 0 and world == 1 and not args.no_extras:
+        with torch.no_grad():
+            plain_models = [build_pair("mobilenet", calib, device=dev, dtype=torch.float16)[1] for _ in range(2)]
+            half = [0, S // 2, S]
+            for g, m in enumerate(plain_models):
+                sl = slice(half[g], half[g + 1])
+                m(frames_dev[0][sl])
+                set_depth_thresholds(model=m, **THRESHOLDS)
+                m(frames_dev[1][sl])
+            plain = MultiBranchStep(plain_models, [frames_dev[1][half[g]:half[g + 1]] for g in range(2)])
+
+        def run_plain(n):
+            for k in range(n):
+                f = frames_dev[pingpong(2 + k, F)]
+                plain.load([f[half[g]:half[g + 1]] for g in range(2)])
+                plain.graph.replay()
+
+        run_plain(W)
+        reps_plain = sorted(timed(run_plain, K_steps) for _ in range(3))
+        unpipelined = {"value": total_streams * K_steps / (reps_plain[1] / 1000.0), "unit": UNIT, "ms_per_step": reps_plain[1] / K_steps,
+                       "concurrent_stream_groups": 2, "what": "every step runs one frame through the whole network before the next starts"}
+        del plain, plain_models
 
     line = {
         "metric": METRIC, "value": total_streams * K_steps / (ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": K_steps,
@@ -344,7 +394,11 @@ def main():
                    "thresholds": THRESHOLDS, "updated_input_pixels": sum(dens) / len(dens),
                    "l2": "inputs larger than L2: a step touches a different frame (19 MB) and >1 GB of per-stream caches",
                    "bn": "BatchNorm calibrated on 8 frames of stream 0 and folded", "step": "one frame of every stream, one CUDA-graph replay",
-                   "head": "classifier on the pooled delta (DCLinear), logits per stream", "concurrent_stream_groups": G},
+                   "head": "classifier on the pooled delta (DCLinear), logits per stream", "concurrent_stream_groups": G,
+                   "depth_pipeline": ({"stages": len(cuts) + 1, "cuts_in_feature_blocks": cuts, "latency_steps": len(cuts),
+                                       "what": "every step runs every layer once for all streams; stage s works on the frame of s steps "
+                                               "earlier, the stages are concurrent branches of the step's CUDA graph; the checksum is taken "
+                                               "after the pipeline has been emptied"} if cuts else None)},
         "repeats": {"n": len(reps), "ms_per_step_min": reps[0] / K_steps, "ms_per_step_median": ms / K_steps,
                     "ms_per_step_max": reps[-1] / K_steps, "timed_region_ms_total": sum(reps)},
         "e2e": {"value": total_streams * K_steps / (ms_e2e / 1000.0), "unit": UNIT,
@@ -355,6 +409,8 @@ def main():
         "output_checksum": checksum,
         "clocks": clocks,
     }
+    if unpipelined is not None:
+        line["unpipelined"] = unpipelined
 
     if rank == 0 and not args.no_extras and world == 1:
         line.update(side_measurements(args, dev, dense, deltas[0], frames_dev[:, bounds[0]:bounds[1]], frames_dev, frames32, stream, S,

@@ -197,6 +197,32 @@ def make_mobilenet_v2(ops, num_classes=1000):
             x = self.densify(x)
             return self.classifier(x.reshape(x.shape[0], -1))
 
+        def depth_stages(self, cuts):
+            """The network as consecutive stages for a frame pipeline: ``cuts`` are indices into ``features`` where a
+            new stage starts. Returns one callable per stage; the first takes the frame batch, the others the previous
+            stage's output, the last returns what ``forward`` returns. Run in order they equal ``forward``."""
+            edges = [0] + [int(c) for c in cuts] + [len(self.features)]
+            assert all(a < b for a, b in zip(edges, edges[1:])), "cuts must be increasing indices inside features"
+
+            def make(si):
+                lo, hi = edges[si], edges[si + 1]
+                first, last = si == 0, si == len(edges) - 2
+
+                def stage(x):
+                    if first:
+                        x = self.sparsify(x)
+                    for i in range(lo, hi):
+                        x = self.features[i](x)
+                    if last:
+                        x = self.pool(x)
+                        if ops.delta and DELTA_HEADS:
+                            return self.classifier(x)
+                        x = self.densify(x)
+                        return self.classifier(x.reshape(x.shape[0], -1))
+                    return x
+                return stage
+            return [make(si) for si in range(len(edges) - 1)]
+
     return MobileNetV2()
 
 

@@ -97,6 +97,120 @@ class MultiBranchStep:
         return self.static_out
 
 
+class DepthPipeline:
+    """A frame pipeline over the depth of a network, inside one CUDA graph: the network of every stream group is cut
+    into consecutive stages, and one step runs stage 0 on frame t, stage 1 on what stage 0 produced from frame t-1,
+    stage 2 on what stage 1 produced one step earlier, and so on, all as concurrent branches of the graph. Every step
+    still runs every layer once for every stream; the result a step returns belongs to the frame of
+    ``latency_steps`` = stages - 1 steps earlier. A step of a delta network is a chain of short dependent kernels;
+    the pipeline puts several such chains side by side without making the batch of any kernel smaller.
+
+    Between two stages lies a (delta, mask) pair. It is kept in two buffers used in turn (two graphs, for even and
+    odd steps): stage s writes the buffer of this step's parity while stage s+1 reads the other one. The buffers
+    start with all-zero masks, which every delta layer treats as "nothing changed", so the pipeline fills itself
+    during the first steps and ``drain`` (steps that repeat the last frame, whose delta is zero) empties it.
+
+    ``stages_per_group[g]`` are the stage callables of group g (first takes the frame batch, the others a (delta,
+    mask) pair); the models must have processed their first frame and one steady-state frame. Construction runs
+    every stage once eagerly on ``example_inputs`` to learn the shapes between the stages: pass the frame the models
+    saw last, so that this pass changes nothing. With ``models`` (the module of every group) the layer that ends a
+    stage writes straight into the buffer of the step's parity: the module attributes that hold its output tensors
+    are pointed at that buffer while the graph of a parity is captured. Without it, or where no such attribute is
+    found, the stage's output is copied into the buffer."""
+
+    def __init__(self, stages_per_group, example_inputs, models=None):
+        self.stages = stages_per_group
+        self.latency_steps = len(stages_per_group[0]) - 1
+        self.between = []                   # [group][stage boundary][parity] -> (delta, mask)
+        self.owners = []                    # [group][stage boundary] -> [(module, attribute, 0 delta / 1 mask)]
+        with torch.no_grad():
+            for g, (fns, x) in enumerate(zip(stages_per_group, example_inputs)):
+                row, own = [], []
+                for fn in fns[:-1]:
+                    x = fn(x)
+                    val, mask = x
+                    row.append([(torch.zeros_like(val), torch.zeros_like(mask)) for _ in range(2)])
+                    found = []
+                    if models is not None:
+                        for mod in models[g].modules():
+                            for attr, v in vars(mod).items():
+                                if v is val:
+                                    found.append((mod, attr, 0))
+                                elif v is mask:
+                                    found.append((mod, attr, 1))
+                    own.append(found if {w for _, _, w in found} == {0, 1} else [])
+                fns[-1](x)
+                self.between.append(row)
+                self.owners.append(own)
+        torch.cuda.synchronize()
+
+    def capture(self, inputs, parity, pool=None):
+        """Graph of one step for the steps of ``parity``, reading the frames from ``inputs`` (one tensor per group).
+        Returns (graph, outputs of the last stages)."""
+        fns, ins, last = [], [], []
+
+        def writer(fn, dst):
+            def run(x):
+                val, mask = fn(x)
+                if val.data_ptr() != dst[0].data_ptr():
+                    dst[0].copy_(val)
+                if mask.data_ptr() != dst[1].data_ptr():
+                    dst[1].copy_(mask)
+                return None
+            return run
+
+        for g, stage_fns in enumerate(self.stages):
+            n = len(stage_fns)
+            for s, fn in enumerate(stage_fns):
+                ins.append(inputs[g] if s == 0 else self.between[g][s - 1][1 - parity])
+                fns.append(fn if s == n - 1 else writer(fn, self.between[g][s][parity]))
+                last.append(s == n - 1)
+                if s < n - 1:
+                    for mod, attr, which in self.owners[g][s]:
+                        setattr(mod, attr, self.between[g][s][parity][which])
+        graph, outs = capture_groups(fns, ins, pool=pool)
+        return graph, [o for o, is_last in zip(outs, last) if is_last]
+
+
+class DepthPipelinedStep:
+    """Device-side stepping through a ``DepthPipeline``: two input buffers and two graphs used in turn."""
+
+    def __init__(self, stages_per_group, example_inputs, models=None):
+        self.pipe = DepthPipeline(stages_per_group, example_inputs, models)
+        self.latency_steps = self.pipe.latency_steps
+        self.inputs = [[x.clone() for x in example_inputs] for _ in range(2)]
+        self.graphs, self.outputs = [], []
+        pool = None
+        for parity in range(2):
+            g, outs = self.pipe.capture(self.inputs[parity], parity, pool)
+            pool = g.pool()
+            self.graphs.append(g)
+            self.outputs.append(outs)
+        self.t = 0
+
+    @property
+    def static_in(self):
+        """Input buffers of the next step."""
+        return self.inputs[self.t % 2]
+
+    def __call__(self, frames=None):
+        i = self.t % 2
+        if frames is not None:
+            for dst, src in zip(self.inputs[i], frames):
+                dst.copy_(src, non_blocking=True)
+        self.graphs[i].replay()
+        self.t += 1
+        return self.outputs[i]
+
+    def drain(self, last_frames):
+        """Steps that repeat the last frame (zero delta) until its result has left the pipeline and every buffer
+        between two stages holds an all-zero mask again; returns the outputs, which now belong to that frame."""
+        out = self.outputs[(self.t - 1) % 2]
+        for _ in range(self.latency_steps + 1):
+            out = self(last_frames)
+        return out
+
+
 class PipelinedStep:
     """End-to-end stepping from host memory: two sets of input buffers and two captured graphs of the
     same model group(s), so that the host->device copy of frame t+1 (on a copy stream) overlaps the delta
@@ -104,15 +218,17 @@ class PipelinedStep:
     must be warmed up (first frame and one steady-state frame done) before construction. ``bounds`` are
     the batch offsets of the groups inside a full frame batch."""
 
-    def __init__(self, models, example_inputs, bounds, compute_stream):
+    def __init__(self, models, example_inputs, bounds, compute_stream, capture=None):
         self.compute = compute_stream
         self.copy = torch.cuda.Stream()
         self.bounds = bounds
         self.inputs = [[x.clone() for x in example_inputs] for _ in range(2)]
         self.graphs, self.outputs = [], []
         pool = None
-        for bufs in self.inputs:
-            g, outs = capture_groups(models, bufs, pool=pool)
+        for i, bufs in enumerate(self.inputs):
+            # ``capture(bufs, i, pool)``: another way to build the graph of the steps that read input buffer i
+            # (``DepthPipeline.capture``: the buffer index is also the step's parity)
+            g, outs = capture(bufs, i, pool) if capture is not None else capture_groups(models, bufs, pool=pool)
             pool = g.pool()
             self.graphs.append(g)
             self.outputs.append(outs)
