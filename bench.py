@@ -590,11 +590,14 @@ def other_configs():
     from examples import bench_configs
     from deltacnn_b200 import DCConv2d, DCThreshold
     out = {}
-    for name, streams in (("resnet50", 16), ("hrnet", 32), ("centernet", 32)):
+    # every configuration runs as a frame pipeline over its depth, like the MobileNetV2 step (cut indices: see the
+    # network's depth_stages in examples/nets.py)
+    for name, streams, cuts in (("resnet50", 16, [3, 7, 11, 14]), ("hrnet", 32, [1, 3, 5, 7, 9]), ("centernet", 32, [3, 7, 9])):
         try:
             DCThreshold.reset()
-            r = bench_configs.run(name, streams, 6)
-            out[name] = {k: r[k] for k in ("streams", "resolution", "updated_input_pixels", "delta_fps", "dense_cudnn_fps", "patch_tiles")}
+            r = bench_configs.run(name, streams, 6, stages=cuts)
+            out[name] = {k: r[k] for k in ("streams", "resolution", "updated_input_pixels", "delta_fps", "dense_cudnn_fps", "patch_tiles",
+                                           "depth_stages")}
             out[name]["speedup_vs_dense_cudnn"] = r["delta_fps"] / r["dense_cudnn_fps"]
         except Exception as e:
             out[name] = {"error": repr(e)}

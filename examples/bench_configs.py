@@ -16,16 +16,18 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from examples.nets import build_pair  # noqa: E402
-from examples.runner import MultiBranchStep, capture_groups, set_depth_thresholds  # noqa: E402
+from examples.runner import DepthPipelinedStep, MultiBranchStep, capture_groups, set_depth_thresholds  # noqa: E402
 from examples.synthetic_video import make_video  # noqa: E402
 from deltacnn_b200 import DCConv2d, DCThreshold  # noqa: E402
 
 
-def run(name, streams, frames, input_threshold=0.03, patches=None, groups=1):
+def run(name, streams, frames, input_threshold=0.03, patches=None, groups=1, stages=None):
     """``groups`` > 1: the streams are split into that many groups, each with its own model instance (own caches, same
     weights) and its own CUDA stream inside ONE captured graph, so kernels of different groups overlap (what bench.py
     does for MobileNetV2). The dense network is timed as one batch and as two concurrent half batches; the better
-    one is reported."""
+    one is reported. ``stages``: cut indices of a frame pipeline over the depth of the network (examples/runner.py,
+    DepthPipeline; the network's ``depth_stages`` says what the indices count); the pipeline is filled before the timed
+    steps, and every timed step runs every layer once for every stream."""
     dev = torch.device("cuda")
     DCConv2d.patch_tiles = (name != "resnet50") if patches is None else bool(patches)
     vids = torch.stack([make_video(name, s).frames(frames + 3) for s in range(streams)], dim=1)     # (F, S, 3, H, W)
@@ -44,17 +46,24 @@ def run(name, streams, frames, input_threshold=0.03, patches=None, groups=1):
             m(fd[0][sl])
             set_depth_thresholds(input_threshold, 0.01, 0.05, model=m)
             m(fd[1][sl])
-        step = MultiBranchStep(deltas, [fd[1][bounds[g]:bounds[g + 1]] for g in range(G)])
+        parts = [fd[1][bounds[g]:bounds[g + 1]] for g in range(G)]
+        if stages:
+            step = DepthPipelinedStep([m.depth_stages(stages) for m in deltas], parts, models=deltas)
+        else:
+            step = MultiBranchStep(deltas, parts)
 
         def load(frame):
+            bufs = step.static_in
             for g in range(G):
-                step.static_in[g].copy_(frame[bounds[g]:bounds[g + 1]], non_blocking=True)
-        load(fd[2]); step.graph.replay()
+                bufs[g].copy_(frame[bounds[g]:bounds[g + 1]], non_blocking=True)
+        # frames 2, 1, 2, ... 2 before the timed ones: neighbouring frames, so every stage of a pipeline is busy
+        for t in [2] + [1, 2] * ((len(stages) + 1) // 2 if stages else 0):
+            load(fd[t]); step()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for t in range(3, 3 + frames):
-            load(fd[t]); step.graph.replay()
+            load(fd[t]); step()
         e1.record()
         torch.cuda.synchronize()
         ms_delta = e0.elapsed_time(e1) / frames
@@ -81,7 +90,8 @@ def run(name, streams, frames, input_threshold=0.03, patches=None, groups=1):
     from deltacnn_b200 import _lib
     if _lib.lib.dc_umma_error() != 0:
         raise RuntimeError(f"a bounded wait of a tensor-core kernel gave up (code {_lib.lib.dc_umma_error()})")
-    return {"config": name, "streams": streams, "groups": G, "patch_tiles": DCConv2d.patch_tiles, "resolution": list(vids.shape[-2:]),
+    return {"config": name, "streams": streams, "groups": G, "depth_stages": (len(stages) + 1) if stages else 1,
+            "patch_tiles": DCConv2d.patch_tiles, "resolution": list(vids.shape[-2:]),
             "updated_input_pixels": density, "delta_fps": streams / ms_delta * 1000, "dense_cudnn_fps": streams / ms_dense * 1000,
             "ms_per_step_delta": ms_delta, "ms_per_step_dense": ms_dense}
 
@@ -94,7 +104,10 @@ if __name__ == "__main__":
     ap.add_argument("--patches", type=int, default=None)
     ap.add_argument("--fuse-add-act", type=int, default=0, help="1: residual adds with activation run in the convolution epilogue")
     ap.add_argument("--groups", type=int, default=1, help="stream groups stepped concurrently inside one CUDA graph")
+    ap.add_argument("--stages", default="", help="cut indices of a frame pipeline over the depth of the network (resnet50: into its "
+                                                 "16 blocks; centernet: into 8 trunk blocks + 3 transposed convolutions)")
     a = ap.parse_args()
     DCConv2d.fuse_residual_activation = bool(a.fuse_add_act)
+    cuts = [int(v) for v in a.stages.split(",") if v.strip()]
     for c in a.configs:
-        print(json.dumps(run(c, a.streams, a.frames, patches=a.patches, groups=a.groups)), flush=True)
+        print(json.dumps(run(c, a.streams, a.frames, patches=a.patches, groups=a.groups, stages=cuts or None)), flush=True)

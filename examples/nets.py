@@ -134,6 +134,29 @@ def _base(ops):
     return ops.base
 
 
+def depth_stages_of(front, blocks, tail, cuts):
+    """A network ``tail(blocks[-1](... blocks[0](front(frame))))`` as consecutive stages for a frame pipeline
+    (examples/runner.py, DepthPipeline): ``cuts`` are the indices into ``blocks`` where a new stage starts. Returns one
+    callable per stage; the first takes the frame batch, the others the previous stage's output, the last returns what
+    the network returns. Called in order on one frame they are the network's forward pass."""
+    blocks = list(blocks)
+    edges = [0] + [int(c) for c in cuts] + [len(blocks)]
+    assert all(a < b for a, b in zip(edges, edges[1:])), "cuts must be increasing indices inside the block list"
+
+    def make(si):
+        lo, hi = edges[si], edges[si + 1]
+        first, last = si == 0, si == len(edges) - 2
+
+        def stage(x):
+            if first:
+                x = front(x)
+            for b in blocks[lo:hi]:
+                x = b(x)
+            return tail(x) if last else x
+        return stage
+    return [make(si) for si in range(len(edges) - 1)]
+
+
 # ------------------------------------------------------------------------------------------------
 # MobileNetV2
 # ------------------------------------------------------------------------------------------------
@@ -190,38 +213,19 @@ def make_mobilenet_v2(ops, num_classes=1000):
             self.densify = ops.densify()
             self.classifier = ops.linear(1280, num_classes)
 
-        def forward(self, x):
-            x = self.pool(self.features(self.sparsify(x)))
+        def tail(self, x):
+            x = self.pool(x)
             if ops.delta and DELTA_HEADS:
                 return self.classifier(x)           # the classifier consumes the pooled delta: no dense feature vector
             x = self.densify(x)
             return self.classifier(x.reshape(x.shape[0], -1))
 
+        def forward(self, x):
+            return self.tail(self.features(self.sparsify(x)))
+
         def depth_stages(self, cuts):
-            """The network as consecutive stages for a frame pipeline: ``cuts`` are indices into ``features`` where a
-            new stage starts. Returns one callable per stage; the first takes the frame batch, the others the previous
-            stage's output, the last returns what ``forward`` returns. Run in order they equal ``forward``."""
-            edges = [0] + [int(c) for c in cuts] + [len(self.features)]
-            assert all(a < b for a, b in zip(edges, edges[1:])), "cuts must be increasing indices inside features"
-
-            def make(si):
-                lo, hi = edges[si], edges[si + 1]
-                first, last = si == 0, si == len(edges) - 2
-
-                def stage(x):
-                    if first:
-                        x = self.sparsify(x)
-                    for i in range(lo, hi):
-                        x = self.features[i](x)
-                    if last:
-                        x = self.pool(x)
-                        if ops.delta and DELTA_HEADS:
-                            return self.classifier(x)
-                        x = self.densify(x)
-                        return self.classifier(x.reshape(x.shape[0], -1))
-                    return x
-                return stage
-            return [make(si) for si in range(len(edges) - 1)]
+            """Stages for a frame pipeline; ``cuts`` are indices into ``features`` where a new stage starts."""
+            return depth_stages_of(self.sparsify, self.features, self.tail, cuts)
 
     return MobileNetV2()
 
@@ -282,12 +286,22 @@ def make_resnet50(ops, num_classes=1000, widths=(64, 128, 256, 512), blocks=(3, 
             self.densify = ops.densify()
             self.fc = ops.linear(cin, num_classes)
 
-        def forward(self, x):
-            x = self.pool(self.layers(self.maxpool(self.stem(self.sparsify(x)))))
+        def front(self, x):
+            return self.maxpool(self.stem(self.sparsify(x)))
+
+        def tail(self, x):
+            x = self.pool(x)
             if ops.delta and DELTA_HEADS:
                 return self.fc(x)
             x = self.densify(x)
             return self.fc(x.reshape(x.shape[0], -1))
+
+        def forward(self, x):
+            return self.tail(self.layers(self.front(x)))
+
+        def depth_stages(self, cuts):
+            """Stages for a frame pipeline; ``cuts`` are indices into ``layers`` (16 blocks) where a new stage starts."""
+            return depth_stages_of(self.front, self.layers, self.tail, cuts)
 
     return ResNet50()
 
@@ -334,8 +348,10 @@ def make_centernet(ops, head_channels=64, decode=False):
             # the three heads' 3x3 layers read the same map: one kernel on steady-state frames of the delta network
             self.fused_heads = ops.fused_heads([self.hm.c1, self.wh.c1, self.off.c1]) if ops.delta else None
 
-        def forward(self, x):
-            x = self.ups(self.layers(self.maxpool(self.stem(self.sparsify(x)))))
+        def front(self, x):
+            return self.maxpool(self.stem(self.sparsify(x)))
+
+        def tail(self, x):
             dense = self.boxes is None or not ops.delta     # the delta decode accumulates the three head deltas itself
             heads = (self.hm, self.wh, self.off)
             if self.fused_heads is not None and self.fused_heads.ready(x):
@@ -343,6 +359,14 @@ def make_centernet(ops, head_channels=64, decode=False):
             else:
                 outs = [h(x, dense) for h in heads]
             return tuple(outs) if self.boxes is None else self.boxes(*outs)
+
+        def forward(self, x):
+            return self.tail(self.ups(self.layers(self.front(x))))
+
+        def depth_stages(self, cuts):
+            """Stages for a frame pipeline; ``cuts`` are indices into the eight trunk blocks followed by the three
+            transposed convolutions (0..10) where a new stage starts."""
+            return depth_stages_of(self.front, list(self.layers) + list(self.ups), self.tail, cuts)
 
     return CenterNet()
 
@@ -415,21 +439,31 @@ def make_hrnet_w32(ops, n_joints=17, width=32, blocks_per_branch=4, modules=(1, 
             self.densify = ops.densify()
             self.keypoints = ops.keypoints() if decode else None     # (x, y, value) per joint instead of the heat maps
 
-        def forward(self, x):
-            x = self.stage1(self.stem(self.sparsify(x)))
-            xs = [self.trans[0](x), self.trans[1](x)]
-            for m in self.stage2:
-                xs = m(xs)
-            xs = xs + [self.trans[2](xs[-1])]
-            for m in self.stage3:
-                xs = m(xs)
-            xs = xs + [self.trans[3](xs[-1])]
-            for m in self.stage4:
-                xs = m(xs)
+        def front(self, x):
+            return self.stage1(self.stem(self.sparsify(x)))
+
+        def blocks(self):
+            """The network between ``front`` and ``tail`` as a chain of callables on the list of branch tensors."""
+            split = lambda x: [self.trans[0](x), self.trans[1](x)]
+            grow = lambda k: (lambda xs: list(xs) + [self.trans[k](xs[-1])])
+            return [split, *self.stage2, grow(2), *self.stage3, grow(3), *self.stage4]
+
+        def tail(self, xs):
             x = self.final(xs[0])
             if self.keypoints is not None:
                 return self.keypoints(x)
             return self.densify(x)
+
+        def forward(self, x):
+            xs = self.front(x)
+            for b in self.blocks():
+                xs = b(xs)
+            return self.tail(xs)
+
+        def depth_stages(self, cuts):
+            """Stages for a frame pipeline; ``cuts`` are indices into ``blocks()`` (branch split, the modules of stage 2,
+            new branch, the modules of stage 3, new branch, the modules of stage 4) where a new stage starts."""
+            return depth_stages_of(self.front, self.blocks(), self.tail, cuts)
 
     return HRNet()
 

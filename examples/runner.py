@@ -105,13 +105,14 @@ class DepthPipeline:
     ``latency_steps`` = stages - 1 steps earlier. A step of a delta network is a chain of short dependent kernels;
     the pipeline puts several such chains side by side without making the batch of any kernel smaller.
 
-    Between two stages lies a (delta, mask) pair. It is kept in two buffers used in turn (two graphs, for even and
+    Between two stages lie (delta, mask) pairs (one, or a list of them where the network has parallel branches). They
+    are kept in two sets of buffers used in turn (two graphs, for even and
     odd steps): stage s writes the buffer of this step's parity while stage s+1 reads the other one. The buffers
     start with all-zero masks, which every delta layer treats as "nothing changed", so the pipeline fills itself
     during the first steps and ``drain`` (steps that repeat the last frame, whose delta is zero) empties it.
 
-    ``stages_per_group[g]`` are the stage callables of group g (first takes the frame batch, the others a (delta,
-    mask) pair); the models must have processed their first frame and one steady-state frame. Construction runs
+    ``stages_per_group[g]`` are the stage callables of group g (first takes the frame batch, the others what the
+    stage before returned); the models must have processed their first frame and one steady-state frame. Construction runs
     every stage once eagerly on ``example_inputs`` to learn the shapes between the stages: pass the frame the models
     saw last, so that this pass changes nothing. With ``models`` (the module of every group) the layer that ends a
     stage writes straight into the buffer of the step's parity: the module attributes that hold its output tensors
@@ -121,25 +122,27 @@ class DepthPipeline:
     def __init__(self, stages_per_group, example_inputs, models=None):
         self.stages = stages_per_group
         self.latency_steps = len(stages_per_group[0]) - 1
-        self.between = []                   # [group][stage boundary][parity] -> (delta, mask)
-        self.owners = []                    # [group][stage boundary] -> [(module, attribute, 0 delta / 1 mask)]
+        self.shape = []                     # [group][stage boundary] -> what the stage returned (nested lists / tuples of tensors)
+        self.between = []                   # [group][stage boundary][parity] -> the tensors of that structure, flattened
+        self.owners = []                    # [group][stage boundary][tensor] -> [(module, attribute)] holding that tensor
         with torch.no_grad():
             for g, (fns, x) in enumerate(zip(stages_per_group, example_inputs)):
-                row, own = [], []
+                shapes, row, own = [], [], []
                 for fn in fns[:-1]:
                     x = fn(x)
-                    val, mask = x
-                    row.append([(torch.zeros_like(val), torch.zeros_like(mask)) for _ in range(2)])
-                    found = []
+                    leaves = _leaves(x)
+                    shapes.append(x)
+                    row.append([[torch.zeros_like(v) for v in leaves] for _ in range(2)])
+                    found = [[] for _ in leaves]
                     if models is not None:
                         for mod in models[g].modules():
                             for attr, v in vars(mod).items():
-                                if v is val:
-                                    found.append((mod, attr, 0))
-                                elif v is mask:
-                                    found.append((mod, attr, 1))
-                    own.append(found if {w for _, _, w in found} == {0, 1} else [])
+                                for i, leaf in enumerate(leaves):
+                                    if v is leaf:
+                                        found[i].append((mod, attr))
+                    own.append(found)
                 fns[-1](x)
+                self.shape.append(shapes)
                 self.between.append(row)
                 self.owners.append(own)
         torch.cuda.synchronize()
@@ -151,25 +154,41 @@ class DepthPipeline:
 
         def writer(fn, dst):
             def run(x):
-                val, mask = fn(x)
-                if val.data_ptr() != dst[0].data_ptr():
-                    dst[0].copy_(val)
-                if mask.data_ptr() != dst[1].data_ptr():
-                    dst[1].copy_(mask)
+                for v, d in zip(_leaves(fn(x)), dst):
+                    if v.data_ptr() != d.data_ptr():      # a tensor no layer of this stage could be pointed at the buffer for
+                        d.copy_(v)
                 return None
             return run
 
         for g, stage_fns in enumerate(self.stages):
             n = len(stage_fns)
             for s, fn in enumerate(stage_fns):
-                ins.append(inputs[g] if s == 0 else self.between[g][s - 1][1 - parity])
+                ins.append(inputs[g] if s == 0 else _like(self.shape[g][s - 1], iter(self.between[g][s - 1][1 - parity])))
                 fns.append(fn if s == n - 1 else writer(fn, self.between[g][s][parity]))
                 last.append(s == n - 1)
                 if s < n - 1:
-                    for mod, attr, which in self.owners[g][s]:
-                        setattr(mod, attr, self.between[g][s][parity][which])
+                    for found, buf in zip(self.owners[g][s], self.between[g][s][parity]):
+                        for mod, attr in found:
+                            setattr(mod, attr, buf)
         graph, outs = capture_groups(fns, ins, pool=pool)
         return graph, [o for o, is_last in zip(outs, last) if is_last]
+
+
+def _leaves(x):
+    """The tensors of a nested list / tuple structure, in order."""
+    if torch.is_tensor(x):
+        return [x]
+    out = []
+    for v in x:
+        out += _leaves(v)
+    return out
+
+
+def _like(x, tensors):
+    """The structure of ``x`` filled with the tensors the iterator ``tensors`` yields."""
+    if torch.is_tensor(x):
+        return next(tensors)
+    return type(x)(_like(v, tensors) for v in x)
 
 
 class DepthPipelinedStep:

@@ -245,25 +245,28 @@ def test_nonzero_thresholds_bounded_error_and_graph_replay():
         assert _rel(eager[2], ref) < 0.5, "thresholded output drifted far from the dense network"
 
 
-@pytest.mark.parametrize("cuts,groups,direct", [([5, 9, 13], 1, True), ([8], 2, True), ([2, 4, 7, 10, 14, 17], 1, True),
-                                                ([6, 10, 14], 1, False)])
-def test_depth_pipeline_returns_the_plain_networks_outputs_some_steps_later(cuts, groups, direct):
+@pytest.mark.parametrize("name,size,cuts,groups,direct", [
+    ("mobilenet", None, [5, 9, 13], 1, True), ("mobilenet", None, [8], 2, True), ("mobilenet", None, [2, 4, 7, 10, 14, 17], 1, True),
+    ("mobilenet", None, [6, 10, 14], 1, False), ("resnet50", (256, 256), [3, 7, 13], 1, True), ("centernet", (160, 224), [2, 4, 6, 8, 10], 1, True), ("hrnet", (128, 128), [2, 3, 5, 7, 8, 10], 1, False), ("hrnet", (128, 128), [3, 7], 1, True)])
+def test_depth_pipeline_returns_the_plain_networks_outputs_some_steps_later(name, size, cuts, groups, direct):
     """A frame pipeline over the depth of the network (stage s of a step works on the frame of s steps ago, all stages
     concurrent in one CUDA graph) must return, bit for bit, what the network returns when every frame runs through it
     alone: len(cuts) steps later, and after drain() for the last frame."""
     from examples.nets import build_pair
     from examples.runner import DepthPipelinedStep, set_depth_thresholds
     n_frames, streams = 12, 2 * groups
-    vids = torch.stack([_frames("mobilenet", 10 + s, n_frames) for s in range(streams)], dim=1)      # (F, S, 3, H, W)
+    vids = torch.stack([_frames(name, 10 + s, n_frames, size) for s in range(streams)], dim=1)      # (F, S, 3, H, W)
     xs = [vids[t].cuda().half().contiguous(memory_format=torch.channels_last) for t in range(n_frames)]
     bounds = [(g * streams) // groups for g in range(groups + 1)]
     part = lambda x: [x[bounds[g]:bounds[g + 1]] for g in range(groups)]
+    # outputs of all groups as one list of tensors: output k of every group, concatenated over the groups
+    joined = lambda per_group: [torch.cat([_outs(o)[k].float() for o in per_group], dim=0) for k in range(len(_outs(per_group[0])))]
     with torch.no_grad():
-        _, plain = build_pair("mobilenet", vids[:4, 0], device="cuda", dtype=torch.float16)
+        _, plain = build_pair(name, vids[:4, 0], device="cuda", dtype=torch.float16)
         plain(xs[0])
         set_depth_thresholds(0.05, 0.01, 0.05, model=plain)
-        want = [None] + [plain(x).float().clone() for x in xs[1:]]
-        models = [build_pair("mobilenet", vids[:4, 0], device="cuda", dtype=torch.float16)[1] for _ in range(groups)]
+        want = [None] + [[o.clone() for o in joined([plain(x)])] for x in xs[1:]]
+        models = [build_pair(name, vids[:4, 0], device="cuda", dtype=torch.float16)[1] for _ in range(groups)]
         for g, m in enumerate(models):
             m(part(xs[0])[g])
             set_depth_thresholds(0.05, 0.01, 0.05, model=m)
@@ -272,15 +275,18 @@ def test_depth_pipeline_returns_the_plain_networks_outputs_some_steps_later(cuts
         step = DepthPipelinedStep([m.depth_stages(cuts) for m in models], part(xs[1]), models=models if direct else None)
         assert step.latency_steps == len(cuts)
         if direct:
-            assert all(len(found) >= 2 for own in step.pipe.owners for found in own), "no layer took a buffer between stages"
+            assert all(len(found) >= 1 for own in step.pipe.owners for leaves in own for found in leaves), \
+                "a tensor between two stages has no layer that writes it in place"
         for t in range(2, n_frames):
-            got = torch.cat([o.float() for o in step(part(xs[t]))], dim=0)
+            got = joined(step(part(xs[t])))
             torch.cuda.synchronize()
-            assert torch.equal(got, want[max(t - len(cuts), 1)]), f"step of frame {t}"
-        got = torch.cat([o.float() for o in step.drain(part(xs[-1]))], dim=0)
+            for a_, b_ in zip(got, want[max(t - len(cuts), 1)]):
+                assert torch.equal(a_, b_), f"step of frame {t}"
+        got = joined(step.drain(part(xs[-1])))
         torch.cuda.synchronize()
-        assert torch.equal(got, want[-1])
-        assert float((want[-1] - want[1]).abs().max()) > 0, "the frames must differ for this test to mean anything"
+        for a_, b_ in zip(got, want[-1]):
+            assert torch.equal(a_, b_)
+        assert float((want[-1][0] - want[1][0]).abs().max()) > 0, "the frames must differ for this test to mean anything"
 
 
 def test_fused_residual_equals_separate_add():
