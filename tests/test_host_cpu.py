@@ -172,3 +172,26 @@ def test_performance_metrics_follow_the_reference_counter_definitions():
     finally:
         M.enabled = False
         M.reset()
+
+
+@pytest.mark.parametrize("name,size,cuts", [("mobilenet", 64, [5, 9, 13]), ("resnet50", 64, [3, 7, 11, 14]),
+                                            ("hrnet", 64, [1, 3, 5, 7, 9]), ("centernet", 64, [3, 7, 9])])
+def test_depth_stages_in_order_are_the_forward_pass(name, size, cuts):
+    """The stage callables a network hands to the frame pipeline, called one after the other on one frame, are its
+    forward pass (checked on the dense build of every example network, on the CPU)."""
+    import torch
+    from examples.nets import BUILDERS, DenseOps, init_weights
+    net = BUILDERS[name](DenseOps)
+    init_weights(net, 0)
+    net.eval()
+    x = torch.randn(1, 3, size, size)
+    with torch.no_grad():
+        want = net(x)
+        y = x
+        for stage in net.depth_stages(cuts):
+            y = stage(y)
+    want = list(want) if isinstance(want, (tuple, list)) else [want]
+    got = list(y) if isinstance(y, (tuple, list)) else [y]
+    assert len(want) == len(got) and all(torch.equal(a, b) for a, b in zip(want, got))
+    with pytest.raises(AssertionError):
+        net.depth_stages([4, 4])
