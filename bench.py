@@ -341,7 +341,8 @@ def main():
             pipe.upload(next_host_frame())
         for _ in range(n):
             pipe.upload(next_host_frame())      # frame t+1 goes up ...
-            pipe.step()                         # ... while frame t is processed
+            pipe.step()                         # ... while frame t is processed and the result of frame t-1 comes down
+        pipe.join()                             # the timed region ends when the last result has reached the host
 
     run_e2e(3)
     reps_e2e = sorted(timed(run_e2e, K_steps) for _ in range(max(1, args.repeats)))

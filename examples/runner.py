@@ -252,9 +252,15 @@ class PipelinedStep:
             self.graphs.append(g)
             self.outputs.append(outs)
         self.host_out = [[torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs] for outs in self.outputs]
+        # results leave on a stream of their own: a small device copy on the compute stream frees the model's output
+        # buffer for the next step, the copy to the host then runs beside that step
+        self.down = torch.cuda.Stream()
+        self.result = [[torch.empty_like(o) for o in outs] for outs in self.outputs]
         self.copied = [torch.cuda.Event(), torch.cuda.Event()]
         self.consumed = [torch.cuda.Event(), torch.cuda.Event()]
-        for e in self.consumed:
+        self.stepped_ev = [torch.cuda.Event(), torch.cuda.Event()]
+        self.downloaded = [torch.cuda.Event(), torch.cuda.Event()]
+        for e in self.consumed + self.downloaded:
             e.record(self.compute)
         self.uploaded = 0      # frames uploaded so far
         self.stepped = 0       # frames processed so far
@@ -271,15 +277,29 @@ class PipelinedStep:
         self.uploaded += 1
 
     def step(self):
-        """Run the delta step on the oldest uploaded frame batch; returns the pinned host tensors the results
-        are being copied to (valid once the compute stream has been synchronised)."""
+        """Run the delta step on the oldest uploaded frame batch; returns the pinned host tensors the results are being
+        copied to (valid once ``join()`` has been called and the compute stream synchronised, or after a device-wide
+        synchronisation; overwritten two steps later)."""
         assert self.stepped < self.uploaded
         i = self.stepped % 2
         self.compute.wait_event(self.copied[i])
+        self.compute.wait_event(self.downloaded[i])       # the results of two steps ago have left self.result[i]
         with torch.cuda.stream(self.compute):
             self.graphs[i].replay()
             self.consumed[i].record(self.compute)
-            for dst, src in zip(self.host_out[i], self.outputs[i]):
+            for dst, src in zip(self.result[i], self.outputs[i]):
                 dst.copy_(src, non_blocking=True)
+            self.stepped_ev[i].record(self.compute)
+        self.down.wait_event(self.stepped_ev[i])
+        with torch.cuda.stream(self.down):
+            for dst, src in zip(self.host_out[i], self.result[i]):
+                dst.copy_(src, non_blocking=True)
+            self.downloaded[i].record(self.down)
         self.stepped += 1
         return self.host_out[i]
+
+    def join(self):
+        """Make the compute stream wait for the result copies in flight (so that an event recorded on it afterwards,
+        or its synchronisation, covers them)."""
+        for e in self.downloaded:
+            self.compute.wait_event(e)

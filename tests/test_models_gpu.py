@@ -289,6 +289,42 @@ def test_depth_pipeline_returns_the_plain_networks_outputs_some_steps_later(name
         assert float((want[-1][0] - want[1][0]).abs().max()) > 0, "the frames must differ for this test to mean anything"
 
 
+@pytest.mark.parametrize("cuts", [None, [6, 10, 14]])
+def test_end_to_end_stepping_from_pinned_host_memory_returns_the_plain_outputs(cuts):
+    """PipelinedStep (uploads of frame t+1 beside the step of frame t, results copied to the host on a stream of their
+    own), with and without the depth pipeline underneath: what arrives in pinned host memory is what the plain network
+    returns for the same frames (len(cuts) steps later with the depth pipeline)."""
+    from examples.nets import build_pair
+    from examples.runner import DepthPipeline, PipelinedStep, set_depth_thresholds
+    n_frames, streams = 10, 2
+    vids = torch.stack([_frames("mobilenet", 20 + s, n_frames) for s in range(streams)], dim=1)
+    host = [vids[t].half().contiguous(memory_format=torch.channels_last).pin_memory() for t in range(n_frames)]
+    xs = [h.cuda() for h in host]
+    lag = len(cuts) if cuts else 0
+    with torch.no_grad():
+        _, plain = build_pair("mobilenet", vids[:4, 0], device="cuda", dtype=torch.float16)
+        plain(xs[0])
+        set_depth_thresholds(0.05, 0.01, 0.05, model=plain)
+        want = [None] + [plain(x).clone() for x in xs[1:]]
+        _, model = build_pair("mobilenet", vids[:4, 0], device="cuda", dtype=torch.float16)
+        model(xs[0])
+        set_depth_thresholds(0.05, 0.01, 0.05, model=model)
+        model(xs[1])
+        stream = torch.cuda.Stream()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            capture = DepthPipeline([model.depth_stages(cuts)], [xs[1]], models=[model]).capture if cuts else None
+            pipe = PipelinedStep([model], [xs[1]], [0, streams], stream, capture=capture)
+            pipe.upload(host[2])
+            for t in range(2, n_frames):
+                if t + 1 < n_frames:
+                    pipe.upload(host[t + 1])
+                out = pipe.step()
+                pipe.join()
+                stream.synchronize()
+                assert torch.equal(out[0].cuda(), want[max(t - lag, 1)]), f"step of frame {t}"
+
+
 def test_fused_residual_equals_separate_add():
     """MobileNetV2 fp16 with the residual added inside the projection convolutions against the same network with
     DCAdd layers: identical outputs on every frame at the benchmark's thresholds."""
