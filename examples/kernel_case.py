@@ -7,6 +7,7 @@ small case that profiler captures are taken on (inputs larger than L2, well unde
     python examples/kernel_case.py c3x3   # tcgen05 3x3 256->256 @64x64, fused ReLU + truncation, 32 streams, work list
     python examples/kernel_case.py c3x3p  # the same layer on patch tiles (tiled TMA loads), no scratch
     python examples/kernel_case.py h32    # 3x3 32->32 @64x64 fully active, 32 streams (halo tiles; DC_HALO=0: patch tiles); also h64, h128, h256to64
+    python examples/kernel_case.py heads3 [reps] [streams]   # three 3x3 256->64 head layers @136x240 in one segmented halo-tile launch, 16 streams
     python examples/kernel_case.py stem   # tcgen05 RGB stem 3x3/2 3->32 @224x224, fused ReLU6 + truncation, 32 streams
     python examples/kernel_case.py deconv # tcgen05 transposed 4x4/2 256->256 @34x60, fused ReLU + truncation, 16 streams, per-phase work lists
     python examples/kernel_case.py dw576  # depthwise 3x3 576 ch @14x14 (a warp per channel slice), fully active, 64 streams
@@ -179,6 +180,28 @@ def main():
         else:
             run = lambda: torch.nn.functional.linear(K.sparse_densify(delta, mask, prev).reshape(n, -1), wt, bias)
         nbytes = 2 * (n * cin + cin * cout + n * cout) + 8 * n * cout
+    elif which == "heads3":
+        # three 3x3 256 -> 64 head layers on the same 136x240 map (90 % active) as ONE launch, each with its own fused
+        # ReLU + truncation, caches, output and out-mask
+        n = int(sys.argv[3]) if len(sys.argv) > 3 else 16
+        cin, seg, nh, h, w = 256, 64, 3, 136, 240
+        x = cl((torch.randn(n, cin, h, w, generator=g) * 0.3).to(dtype)).cuda()
+        mask = blob_mask(g, n, h, w, 0.9).cuda()
+        wt = (torch.randn(nh * seg, cin, 3, 3, generator=g) * (9 * cin) ** -0.5).to(dtype)
+        f = convert_filter_out_channels_last(wt).cuda()
+        desc = K.make_conv_desc(tuple(x.shape), nh * seg, (h, w), (3, 3), (1, 1), (1, 1), (1, 1), 1, 1)
+        assert K.conv3x3_heads_supported(desc, nh)
+        packed = torch.zeros(_lib.lib.dc_filter_umma_bytes(desc, 0), dtype=torch.uint8, device="cuda")
+        _lib.check(_lib.lib.dc_pack_filter_umma(desc, 0, f.data_ptr(), packed.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+        outs = [torch.empty(n, seg, h, w, dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last) for _ in range(nh)]
+        oms = [torch.empty(n, 1, h, w, dtype=torch.int32, device="cuda") for _ in range(nh)]
+        prevs = [cl(torch.randn(n, seg, h, w, generator=g).to(dtype)).cuda() for _ in range(nh)]
+        truncs = [torch.zeros_like(p_) for p_ in prevs]
+        eps = [K.make_epilogue(prevs[i], truncs[i], 0.02, 1, 0) for i in range(nh)]
+        run = lambda: K.conv3x3_heads(x, mask, packed, None, outs, oms, desc, eps)
+        u_out = int((torch.nn.functional.max_pool2d(mask.float(), 3, 1, 1) > 0).sum())
+        nbytes = 2 * (int(mask.sum()) * cin + 9 * cin * nh * seg) + 2 * nh * seg * 5 * u_out + 4 * (mask.numel() + nh * mask.numel())
+        print(f"heads3: {int(mask.sum())} active input pixels, {u_out} updated output pixels, {2.0 * u_out * 9 * cin * nh * seg / 1e9:.2f} GFLOP")
     elif which == "sparsify":
         n, h, w = 64, 224, 224
         prev = cl(torch.rand(n, 3, h, w, generator=g).to(dtype)).cuda()
