@@ -210,7 +210,7 @@ def main():
     import torch
     import torch.distributed as dist
     from examples.nets import build_pair
-    from examples.runner import DepthPipeline, DepthPipelinedStep, MultiBranchStep, PipelinedStep, set_depth_thresholds
+    from deltacnn_b200.stepping import DepthPipeline, DepthPipelinedStep, MultiBranchStep, PipelinedStep, set_depth_thresholds
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -249,7 +249,7 @@ def main():
             table = set_depth_thresholds(model=m, **THRESHOLDS)
             m(frames_dev[1][sl])                                        # one eager steady-state frame: buffers allocated
         # With --stages every group's network is also cut into depth stages that work on consecutive frames at the
-        # same time (examples/runner.py, DepthPipeline): every step still runs every layer once for every stream, and
+        # same time (deltacnn_b200/stepping.py, DepthPipeline): every step still runs every layer once for every stream, and
         # the logits a step returns belong to the frame of len(cuts) steps earlier.
         cuts = [int(v) for v in args.stages.split(",") if v.strip()]
         if cuts:
@@ -613,7 +613,7 @@ def config1_fp32(frames32, dev):
     import torch
     from deltacnn_b200 import DCThreshold
     from examples.nets import build_pair
-    from examples.runner import GraphedStep
+    from deltacnn_b200.stepping import GraphedStep
     DCThreshold.reset()
     DCThreshold.t_default = 0.05
     try:
@@ -663,7 +663,7 @@ def side_measurements(args, dev, dense, delta, frames_group0, frames_dev, frames
     # dense cuDNN, same frames, CUDA graph; measured as one batch and as two concurrent half batches (the same
     # multi-stream treatment the delta path gets) -- the faster of the two is the baseline
     torch.backends.cudnn.benchmark = True
-    from examples.runner import capture_groups
+    from deltacnn_b200.stepping import capture_groups
 
     def dense_ms(groups):
         bnd = [(g * S) // groups for g in range(groups + 1)]

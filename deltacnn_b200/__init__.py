@@ -11,3 +11,4 @@ from .sparse_layers import DCConv2d, DCConvTranspose2d, DCMaxPooling, DCAdaptive
     DCActivation, DCUpsamplingNearest2d, DCSparsify, DCThreshold, DCBackend, DCModule, DCBatchNorm2d, DCConcatenate, \
     DCTruncation, DCLinear, DCHeatmapArgmax, DCCenterNetDecode, DCFusedInvertedResidual, DCFusedHeads
 from .cuda_kernels import DCPerformanceMetricsManager, DCPerformanceMetrics
+from .stepping import GraphedStep, MultiBranchStep, DepthPipeline, DepthPipelinedStep, PipelinedStep, set_depth_thresholds

@@ -1,8 +1,10 @@
-"""Frame-step driver for a batch of independent video streams: first (dense) frame, threshold
-table, and a CUDA-graph replay of the steady-state delta step."""
+"""Stepping many independent video streams through a delta network (host side; no reference counterpart: the
+reference's examples call the model once per frame, example/mobilenet_deltacnn.py): the threshold table by depth, the
+CUDA-graph replay of a steady-state frame step, several stream groups or several depth stages of the network as concurrent
+branches of one graph, and double-buffered stepping from pinned host memory. Nothing here changes a layer's results."""
 import torch
 
-from deltacnn_b200 import DCThreshold, DCSparsify
+from .sparse_layers import DCThreshold, DCSparsify
 
 
 def set_depth_thresholds(input_threshold=0.05, first=0.01, last=0.05, model=None):

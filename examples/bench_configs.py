@@ -16,7 +16,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from examples.nets import build_pair  # noqa: E402
-from examples.runner import DepthPipelinedStep, MultiBranchStep, capture_groups, set_depth_thresholds  # noqa: E402
+from deltacnn_b200.stepping import DepthPipelinedStep, MultiBranchStep, capture_groups, set_depth_thresholds  # noqa: E402
 from examples.synthetic_video import make_video  # noqa: E402
 from deltacnn_b200 import DCConv2d, DCThreshold  # noqa: E402
 
@@ -25,7 +25,7 @@ def run(name, streams, frames, input_threshold=0.03, patches=None, groups=1, sta
     """``groups`` > 1: the streams are split into that many groups, each with its own model instance (own caches, same
     weights) and its own CUDA stream inside ONE captured graph, so kernels of different groups overlap (what bench.py
     does for MobileNetV2). The dense network is timed as one batch and as two concurrent half batches; the better
-    one is reported. ``stages``: cut indices of a frame pipeline over the depth of the network (examples/runner.py,
+    one is reported. ``stages``: cut indices of a frame pipeline over the depth of the network (deltacnn_b200/stepping.py,
     DepthPipeline; the network's ``depth_stages`` says what the indices count); the pipeline is filled before the timed
     steps, and every timed step runs every layer once for every stream."""
     dev = torch.device("cuda")

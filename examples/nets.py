@@ -136,7 +136,7 @@ def _base(ops):
 
 def depth_stages_of(front, blocks, tail, cuts):
     """A network ``tail(blocks[-1](... blocks[0](front(frame))))`` as consecutive stages for a frame pipeline
-    (examples/runner.py, DepthPipeline): ``cuts`` are the indices into ``blocks`` where a new stage starts. Returns one
+    (deltacnn_b200/stepping.py, DepthPipeline): ``cuts`` are the indices into ``blocks`` where a new stage starts. Returns one
     callable per stage; the first takes the frame batch, the others the previous stage's output, the last returns what
     the network returns. Called in order on one frame they are the network's forward pass."""
     blocks = list(blocks)

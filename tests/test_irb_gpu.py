@@ -152,7 +152,7 @@ def test_mobilenet_with_fused_blocks_equals_unfused():
     kernel and the network with separate layer kernels give identical logits on every frame."""
     from deltacnn_b200 import DCConv2d, DCThreshold
     from examples.nets import build_pair
-    from examples.runner import set_depth_thresholds
+    from deltacnn_b200.stepping import set_depth_thresholds
     from examples.synthetic_video import make_video
     frames = make_video("mobilenet", 4).frames(7)
     xs = [frames[t:t + 1].cuda().half().repeat(2, 1, 1, 1).contiguous(memory_format=torch.channels_last) for t in range(7)]

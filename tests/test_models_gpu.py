@@ -222,7 +222,7 @@ def test_reset_layers_restarts_the_stream():
 def test_nonzero_thresholds_bounded_error_and_graph_replay():
     from deltacnn_b200 import DCThreshold
     from examples.nets import build_pair
-    from examples.runner import GraphedStep, set_depth_thresholds
+    from deltacnn_b200.stepping import GraphedStep, set_depth_thresholds
     frames = _frames("mobilenet", 1, 10)
     dense, delta = build_pair("mobilenet", frames[:4], device="cuda", dtype=torch.float16)
     xs = [frames[t:t + 1].cuda().half().contiguous(memory_format=torch.channels_last) for t in range(10)]
@@ -253,7 +253,7 @@ def test_depth_pipeline_returns_the_plain_networks_outputs_some_steps_later(name
     concurrent in one CUDA graph) must return, bit for bit, what the network returns when every frame runs through it
     alone: len(cuts) steps later, and after drain() for the last frame."""
     from examples.nets import build_pair
-    from examples.runner import DepthPipelinedStep, set_depth_thresholds
+    from deltacnn_b200.stepping import DepthPipelinedStep, set_depth_thresholds
     n_frames, streams = 12, 2 * groups
     vids = torch.stack([_frames(name, 10 + s, n_frames, size) for s in range(streams)], dim=1)      # (F, S, 3, H, W)
     xs = [vids[t].cuda().half().contiguous(memory_format=torch.channels_last) for t in range(n_frames)]
@@ -295,7 +295,7 @@ def test_end_to_end_stepping_from_pinned_host_memory_returns_the_plain_outputs(c
     own), with and without the depth pipeline underneath: what arrives in pinned host memory is what the plain network
     returns for the same frames (len(cuts) steps later with the depth pipeline)."""
     from examples.nets import build_pair
-    from examples.runner import DepthPipeline, PipelinedStep, set_depth_thresholds
+    from deltacnn_b200.stepping import DepthPipeline, PipelinedStep, set_depth_thresholds
     n_frames, streams = 10, 2
     vids = torch.stack([_frames("mobilenet", 20 + s, n_frames) for s in range(streams)], dim=1)
     host = [vids[t].half().contiguous(memory_format=torch.channels_last).pin_memory() for t in range(n_frames)]
@@ -330,7 +330,7 @@ def test_fused_residual_equals_separate_add():
     DCAdd layers: identical outputs on every frame at the benchmark's thresholds."""
     from deltacnn_b200 import DCThreshold, DCConv2d
     from examples.nets import build_pair
-    from examples.runner import set_depth_thresholds
+    from deltacnn_b200.stepping import set_depth_thresholds
     frames = _frames("mobilenet", 2, 6)
     xs = [frames[t:t + 1].cuda().half().repeat(2, 1, 1, 1).contiguous(memory_format=torch.channels_last) for t in range(6)]
     outs = {}
