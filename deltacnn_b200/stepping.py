@@ -108,15 +108,15 @@ class DepthPipeline:
     the pipeline puts several such chains side by side without making the batch of any kernel smaller.
 
     Between two stages lie (delta, mask) pairs (one, or a list of them where the network has parallel branches). They
-    are kept in two sets of buffers used in turn (two graphs, for even and
-    odd steps): stage s writes the buffer of this step's parity while stage s+1 reads the other one. The buffers
-    start with all-zero masks, which every delta layer treats as "nothing changed", so the pipeline fills itself
-    during the first steps and ``drain`` (steps that repeat the last frame, whose delta is zero) empties it.
+    are kept in two sets of buffers used in turn (two graphs, for even and odd steps): stage s writes the buffers of
+    this step's parity while stage s+1 reads the others. The buffers start with all-zero masks, which every delta
+    layer treats as "nothing changed", so the pipeline fills itself during the first steps and ``drain`` (steps that
+    repeat the last frame, whose delta is zero) empties it.
 
     ``stages_per_group[g]`` are the stage callables of group g (first takes the frame batch, the others what the
-    stage before returned); the models must have processed their first frame and one steady-state frame. Construction runs
-    every stage once eagerly on ``example_inputs`` to learn the shapes between the stages: pass the frame the models
-    saw last, so that this pass changes nothing. With ``models`` (the module of every group) the layer that ends a
+    stage before returned); the models must have processed their first frame and one steady-state frame.
+    Construction runs every stage once eagerly on ``example_inputs`` to learn the shapes between the stages: pass the
+    frame the models saw last, so that this pass changes nothing. With ``models`` (the module of every group) the layer that ends a
     stage writes straight into the buffer of the step's parity: the module attributes that hold its output tensors
     are pointed at that buffer while the graph of a parity is captured. Without it, or where no such attribute is
     found, the stage's output is copied into the buffer."""
