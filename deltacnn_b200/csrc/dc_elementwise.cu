@@ -151,6 +151,62 @@ __global__ void __launch_bounds__(256) k_sparsify_u8(const uint8_t* __restrict__
     }
 }
 
+// 8-bit RGB frames: the run-of-pixels form of k_sparsify_c3 (a thread owns 8 fp16 or 4 fp32 pixels: 24 or 12 bytes of the
+// frame, three 16-byte vectors of the cache and of the delta, the mask words as vectors), with the arithmetic of
+// k_sparsify_u8.
+template <typename T>
+__global__ void __launch_bounds__(256) k_sparsify_u8_c3(const uint8_t* __restrict__ x, const float* __restrict__ scale,
+                                                        const float* __restrict__ offset, T* __restrict__ prev,
+                                                        T* __restrict__ delta, int32_t* __restrict__ mask, int64_t npix, float thr) {
+    constexpr int PPT = sizeof(T) == 2 ? 8 : 4;                         // pixels per thread
+    constexpr int NE = PPT * 3;                                         // elements per thread
+    grid_dep_launch();
+    grid_dep_wait();
+    const float sc[3] = {scale[0], scale[1], scale[2]};
+    const float of[3] = {offset[0], offset[1], offset[2]};
+    const int64_t ngroups = npix / PPT;
+    for (int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gi < ngroups; gi += (int64_t)gridDim.x * blockDim.x) {
+        alignas(8) uint8_t xb[NE];
+        alignas(16) T pa[NE];
+        alignas(16) T da[NE];
+        const uint32_t* xs = reinterpret_cast<const uint32_t*>(x + gi * NE);     // NE is a multiple of 4, the frame 4-byte aligned
+        const uint4* ps = reinterpret_cast<const uint4*>(prev + gi * NE);
+#pragma unroll
+        for (int i = 0; i < NE / 4; ++i) reinterpret_cast<uint32_t*>(xb)[i] = xs[i];
+#pragma unroll
+        for (int i = 0; i < 3; ++i) reinterpret_cast<uint4*>(pa)[i] = ps[i];
+        alignas(16) int32_t m[PPT];
+        bool any = false;
+#pragma unroll
+        for (int px = 0; px < PPT; ++px) {
+            bool hit = false;
+            T v[3];
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const float vf = rnd<T>(__fadd_rn(__fmul_rn((float)xb[px * 3 + c], sc[c]), of[c]));
+                const float d = rnd<T>(vf - to_f<T>(pa[px * 3 + c]));
+                v[c] = from_f<T>(vf);
+                da[px * 3 + c] = from_f<T>(d);
+                hit |= fabsf(d) > thr;
+            }
+            m[px] = hit ? 1 : 0;
+            any |= hit;
+            if (hit) {
+#pragma unroll
+                for (int c = 0; c < 3; ++c) pa[px * 3 + c] = v[c];
+            }
+        }
+        if (any) {
+            uint4* dd = reinterpret_cast<uint4*>(delta + gi * NE);
+            uint4* pd = reinterpret_cast<uint4*>(prev + gi * NE);
+#pragma unroll
+            for (int i = 0; i < 3; ++i) { dd[i] = reinterpret_cast<const uint4*>(da)[i]; pd[i] = reinterpret_cast<const uint4*>(pa)[i]; }
+        }
+#pragma unroll
+        for (int i = 0; i < PPT / 4; ++i) reinterpret_cast<int4*>(mask + gi * PPT)[i] = reinterpret_cast<const int4*>(m)[i];
+    }
+}
+
 // Noise-robust input mask, DCSparsify(dilation = k) (reference: src/deltacnn/sparse_layers.py:1233-1248, torch ops
 // there): delta = x - prev at EVERY pixel, mask = max-pool_{k x k, stride 1}(max_c |delta|) > threshold, and the cache
 // takes the new frame where the mask is set. max-pool(v) > t holds exactly when some element of the window has
@@ -643,12 +699,33 @@ int dc_sparsify_u8(const uint8_t* x_u8, const float* scale, const float* offset,
     if (npix == 0) return DC_OK;
     DC_REQUIRE(x_u8); DC_REQUIRE(scale); DC_REQUIRE(offset); DC_REQUIRE(prev_in); DC_REQUIRE(delta); DC_REQUIRE(mask);
     cudaStream_t st = (cudaStream_t)stream;
+    if (dtype != DC_F32 && dtype != DC_F16) return DC_ERR_DTYPE;
     const int g = lanes_per_pixel(channels);
+    const float thr16 = host_round_threshold<__half>(threshold);
+    int64_t done = 0;
+    if (channels == 3 && (reinterpret_cast<uintptr_t>(x_u8) & 3u) == 0 && aligned16(prev_in) && aligned16(delta) && aligned16(mask)) {
+        // RGB frames: runs of 8 (fp16) or 4 (fp32) pixels per thread with vector accesses; the generic kernel takes the ragged tail
+        const int ppt = dtype == DC_F16 ? 8 : 4;
+        const int64_t ngroups = npix / ppt;
+        if (ngroups > 0) {
+            int64_t blocks = divup64(ngroups, 256);
+            const int64_t cap = (int64_t)sm_count() * 16;
+            if (blocks > cap) blocks = cap;
+            if (dtype == DC_F32)
+                launch_pdl(k_sparsify_u8_c3<float>, (unsigned)blocks, dim3(256), 0, st, x_u8, scale, offset, (float*)prev_in, (float*)delta, mask, npix, threshold);
+            else
+                launch_pdl(k_sparsify_u8_c3<__half>, (unsigned)blocks, dim3(256), 0, st, x_u8, scale, offset, (__half*)prev_in, (__half*)delta, mask, npix, thr16);
+        }
+        done = ngroups * ppt;
+        if (done == npix) return check_launch();
+    }
+    const int64_t rest = npix - done;
     if (dtype == DC_F32)
-        launch_pdl(k_sparsify_u8<float>, pixel_grid(npix, g), dim3(256), 0, st, x_u8, scale, offset, (float*)prev_in, (float*)delta, mask, npix, channels, g, threshold);
-    else if (dtype == DC_F16)
-        launch_pdl(k_sparsify_u8<__half>, pixel_grid(npix, g), dim3(256), 0, st, x_u8, scale, offset, (__half*)prev_in, (__half*)delta, mask, npix, channels, g, host_round_threshold<__half>(threshold));
-    else return DC_ERR_DTYPE;
+        launch_pdl(k_sparsify_u8<float>, pixel_grid(rest, g), dim3(256), 0, st, x_u8 + done * channels, scale, offset, (float*)prev_in + done * channels,
+                   (float*)delta + done * channels, mask + done, rest, channels, g, threshold);
+    else
+        launch_pdl(k_sparsify_u8<__half>, pixel_grid(rest, g), dim3(256), 0, st, x_u8 + done * channels, scale, offset, (__half*)prev_in + done * channels,
+                   (__half*)delta + done * channels, mask + done, rest, channels, g, thr16);
     return check_launch();
 }
 
