@@ -195,3 +195,19 @@ def test_depth_stages_in_order_are_the_forward_pass(name, size, cuts):
     assert len(want) == len(got) and all(torch.equal(a, b) for a, b in zip(want, got))
     with pytest.raises(AssertionError):
         net.depth_stages([4, 4])
+
+
+def test_pipeline_buffers_follow_the_structure_between_stages():
+    """The tensors a stage hands to the next one may be nested lists / tuples (parallel branches): the pipeline flattens
+    them into its buffers and rebuilds the same structure from them."""
+    import torch
+    from deltacnn_b200.stepping import _leaves, _like
+    a, b, c, d = (torch.full((2,), float(i)) for i in range(4))
+    nested = [(a, b), [(c, d)]]
+    flat = _leaves(nested)
+    assert [t.data_ptr() for t in flat] == [a.data_ptr(), b.data_ptr(), c.data_ptr(), d.data_ptr()]
+    other = [t + 10 for t in flat]
+    rebuilt = _like(nested, iter(other))
+    assert isinstance(rebuilt, list) and isinstance(rebuilt[0], tuple) and isinstance(rebuilt[1], list) and isinstance(rebuilt[1][0], tuple)
+    assert [float(t[0]) for t in _leaves(rebuilt)] == [10.0, 11.0, 12.0, 13.0]
+    assert _leaves(a) == [a] and _like(a, iter([b])) is b
