@@ -25,10 +25,13 @@ and the fp32 CUDA-core peak for depthwise / thin / RGB layers, BW the HBM copy b
 depend on each other, so the step's roofline time is the sum.
 """
 import collections
+import os
+import sys
 
 import torch
 
-import deltacnn_b200.cuda_kernels as K
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import deltacnn_b200.cuda_kernels as K  # noqa: E402
 
 L2_FLUSH_BYTES = 256 << 20
 
@@ -243,3 +246,49 @@ def roofline_report(delta, frames_dev, stream, peak, tensor_peak_tflops, ms_per_
             "timing": "per-launch CUDA events with L2 flushed before every launch, launches serialised (not the in-graph time)",
             "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms, "launches_timed": top["launches"],
             "share_of_step": top["ms"] / total_ms, "kernels": table, "frame": frame}, density
+
+
+def main():
+    """``python examples/profile.py [config] [streams]``: every layer call of one steady-state frame step (eager, cold
+    L2, CUDA events; the best of three frames per layer) with its algorithmic bytes and the time those bytes take at
+    the measured copy bandwidth of the GPU."""
+    from examples.nets import build_pair
+    from examples.synthetic_video import make_video
+    from deltacnn_b200.stepping import set_depth_thresholds
+    # the copy bandwidth measured on this kind of GPU, if the file with it is there (else an earlier measurement)
+    peaks_file = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    hbm_gbs, kind = 6650.0, "fallback"
+    if os.path.exists(peaks_file):
+        import json
+        with open(peaks_file) as f:
+            hbm_gbs, kind = float(json.load(f)["hbm_gbs"]), "measured"
+    name = sys.argv[1] if len(sys.argv) > 1 else "mobilenet"
+    streams = int(sys.argv[2]) if len(sys.argv) > 2 else 32
+    vids = torch.stack([make_video(name, s).frames(6) for s in range(streams)], dim=1)
+    dev = torch.device("cuda")
+    _, delta = build_pair(name, vids[:4, 0], device=dev, dtype=torch.float16)
+    fd = [vids[i].to(dev, torch.float16).contiguous(memory_format=torch.channels_last) for i in range(6)]
+    stream = torch.cuda.current_stream()
+    runs = []
+    with torch.no_grad():
+        delta(fd[0])
+        set_depth_thresholds(0.03 if name != "mobilenet" else 0.05, 0.01, 0.05)
+        delta(fd[1])
+        delta(fd[2])
+        for f in (3, 4, 5):
+            with OpProfiler(stream) as prof:
+                delta(fd[f])
+            runs.append(prof.records)
+    total = roof = 0.0
+    print(f"{name}, {streams} streams: layer call, best of three frames (cold L2) | algorithmic MB | time of the bytes at {hbm_gbs:.0f} GB/s ({kind})")
+    for i in range(min(len(r) for r in runs)):
+        key, site, _, nbytes, _ = runs[-1][i]
+        ms = min(r[i][2] for r in runs)
+        total += ms
+        roof += nbytes / (hbm_gbs * 1e6)
+        print(f"{i:3d} {key:16s} {site:30s} {ms * 1000:7.1f} us {nbytes / 1e6:8.2f} MB {nbytes / (hbm_gbs * 1e3):6.1f} us")
+    print(f"sum {total:.3f} ms, bytes at bandwidth {roof:.3f} ms")
+
+
+if __name__ == "__main__":
+    main()
