@@ -96,3 +96,48 @@ def test_mask_dilation_property():
                             if 0 <= iy < 11 and 0 <= ix < 13 and m[b, 0, iy, ix]:
                                 want[b, 0, oy, ox] = 1
         assert torch.equal(om, want)
+
+
+def test_frame_pipeline_over_the_depth_is_exact_on_the_oracle():
+    """The frame pipeline of deltacnn_b200/stepping.py rests on two properties of the delta algorithm, checked here on
+    the CPU restatement: a layer that receives an all-zero mask changes nothing and emits an all-zero mask, and a stage
+    that sees the deltas of its predecessor one step late produces the same sequence of states. Stage s of a step
+    works on what stage s-1 produced in the step before; the logits of frame t leave the last stage len(cuts) steps
+    later, bit for bit."""
+    import copy
+    cuts = [5, 9, 13]
+    frames = torch.nn.functional.avg_pool2d(make_video("mobilenet", 3).frames(9), 2)       # 112 x 112, the moving objects included
+    dense, _ = build_pair("mobilenet", frames[:4], device="cpu")
+    net = build_oracle_net("mobilenet", dense.state_dict())
+    with torch.no_grad():
+        net(frames[0:1])
+        Thresholds.set_depth_table(0.05, 0.01, 0.05)
+        net(frames[1:2])
+        twin = copy.deepcopy(net)                               # same weights, caches and thresholds
+        for a, b in zip(net.modules(), twin.modules()):
+            if a in Thresholds.table:
+                Thresholds.table[b] = Thresholds.table[a]
+        want = [net(frames[t:t + 1]).clone() for t in range(1, 9)]       # frame 1 again (zero delta), then frames 2..8
+        assert not torch.equal(want[0], want[-1]), "the frames must change the output for this test to mean anything"
+        stages = twin.depth_stages(cuts)
+        # what lies between the stages: learnt from a pass over the frame seen last (zero delta), then all-zero masks
+        x, between = frames[1:2], []
+        for stage in stages[:-1]:
+            x = stage(x)
+            assert int(x[1].sum()) == 0, "a zero delta must leave every mask empty"
+            between.append((torch.zeros_like(x[0]), torch.zeros_like(x[1])))
+        assert torch.equal(stages[-1](x), want[0])
+        got = []
+        for x in [frames[t:t + 1] for t in range(2, 9)] + [frames[8:9]] * len(cuts):
+            new = list(between)
+            for s, stage in enumerate(stages):
+                y = stage(x if s == 0 else between[s - 1])
+                if s < len(stages) - 1:
+                    new[s] = (y[0].clone(), y[1].clone())
+                else:
+                    got.append(y.clone())
+            between = new
+    for k in range(len(cuts)):                                   # the pipeline fills: the logits of frame 1 stay
+        assert torch.equal(got[k], want[0])
+    for t in range(2, 9):                                        # frame t leaves len(cuts) steps after it entered
+        assert torch.equal(got[t - 2 + len(cuts)], want[t - 1]), t
