@@ -98,46 +98,63 @@ def test_mask_dilation_property():
         assert torch.equal(om, want)
 
 
+def _tmap(f, x):
+    """``f`` applied to every tensor of a nested list / tuple structure."""
+    return f(x) if torch.is_tensor(x) else type(x)(_tmap(f, v) for v in x)
+
+
+def _tlist(x):
+    return [x] if torch.is_tensor(x) else [t for v in x for t in _tlist(v)]
+
+
+def _pipeline_cases():
+    pool2 = lambda f: torch.nn.functional.avg_pool2d(f, 2)
+    return [("mobilenet", pool2(make_video("mobilenet", 3).frames(9)), {}, [5, 9, 13]),
+            ("hrnet", make_video("hrnet", 3).frames(7)[:, :, 96:160, 96:160].contiguous(), dict(blocks_per_branch=1, modules=(1, 1, 2)), [2, 4, 6]),
+            ("centernet", pool2(pool2(make_video("mobilenet", 4).frames(7)))[:, :, :32, :32].contiguous() * 1.0, {}, [3, 7, 9])]
+
+
 def test_frame_pipeline_over_the_depth_is_exact_on_the_oracle():
     """The frame pipeline of deltacnn_b200/stepping.py rests on two properties of the delta algorithm, checked here on
     the CPU restatement: a layer that receives an all-zero mask changes nothing and emits an all-zero mask, and a stage
     that sees the deltas of its predecessor one step late produces the same sequence of states. Stage s of a step
-    works on what stage s-1 produced in the step before; the logits of frame t leave the last stage len(cuts) steps
-    later, bit for bit."""
+    works on what stage s-1 produced in the step before; the outputs of frame t leave the last stage len(cuts) steps
+    later, bit for bit (MobileNetV2; HRNet, whose stages hand lists of branch tensors on; CenterNet with its three heads)."""
     import copy
-    cuts = [5, 9, 13]
-    frames = torch.nn.functional.avg_pool2d(make_video("mobilenet", 3).frames(9), 2)       # 112 x 112, the moving objects included
-    dense, _ = build_pair("mobilenet", frames[:4], device="cpu")
-    net = build_oracle_net("mobilenet", dense.state_dict())
-    with torch.no_grad():
-        net(frames[0:1])
-        Thresholds.set_depth_table(0.05, 0.01, 0.05)
-        net(frames[1:2])
-        twin = copy.deepcopy(net)                               # same weights, caches and thresholds
-        for a, b in zip(net.modules(), twin.modules()):
-            if a in Thresholds.table:
-                Thresholds.table[b] = Thresholds.table[a]
-        want = [net(frames[t:t + 1]).clone() for t in range(1, 9)]       # frame 1 again (zero delta), then frames 2..8
-        assert not torch.equal(want[0], want[-1]), "the frames must change the output for this test to mean anything"
-        stages = twin.depth_stages(cuts)
-        # what lies between the stages: learnt from a pass over the frame seen last (zero delta), then all-zero masks
-        x, between = frames[1:2], []
-        for stage in stages[:-1]:
-            x = stage(x)
-            assert int(x[1].sum()) == 0, "a zero delta must leave every mask empty"
-            between.append((torch.zeros_like(x[0]), torch.zeros_like(x[1])))
-        assert torch.equal(stages[-1](x), want[0])
-        got = []
-        for x in [frames[t:t + 1] for t in range(2, 9)] + [frames[8:9]] * len(cuts):
-            new = list(between)
-            for s, stage in enumerate(stages):
-                y = stage(x if s == 0 else between[s - 1])
-                if s < len(stages) - 1:
-                    new[s] = (y[0].clone(), y[1].clone())
-                else:
-                    got.append(y.clone())
-            between = new
-    for k in range(len(cuts)):                                   # the pipeline fills: the logits of frame 1 stay
-        assert torch.equal(got[k], want[0])
-    for t in range(2, 9):                                        # frame t leaves len(cuts) steps after it entered
-        assert torch.equal(got[t - 2 + len(cuts)], want[t - 1]), t
+    for name, frames, kw, cuts in _pipeline_cases():
+        n = frames.shape[0]
+        dense, _ = build_pair(name, frames[:4], device="cpu", **kw)
+        net = build_oracle_net(name, dense.state_dict(), **kw)
+        with torch.no_grad():
+            net(frames[0:1])
+            Thresholds.set_depth_table(0.05, 0.01, 0.05)
+            net(frames[1:2])
+            twin = copy.deepcopy(net)                               # same weights, caches and thresholds
+            for a, b in zip(net.modules(), twin.modules()):
+                if a in Thresholds.table:
+                    Thresholds.table[b] = Thresholds.table[a]
+            clone = lambda y: _tmap(torch.clone, y)
+            same = lambda p, q: all(torch.equal(u, v) for u, v in zip(_tlist(p), _tlist(q)))
+            want = [clone(net(frames[t:t + 1])) for t in range(1, n)]        # frame 1 again (zero delta), then frames 2..
+            assert not same(want[0], want[-1]), f"{name}: the frames must change the output for this test to mean anything"
+            stages = twin.depth_stages(cuts)
+            # what lies between the stages: learnt from a pass over the frame seen last (zero delta), then all zeros
+            x, between = frames[1:2], []
+            for stage in stages[:-1]:
+                x = stage(x)
+                between.append(_tmap(torch.zeros_like, x))
+            assert same(stages[-1](x), want[0]), f"{name}: a zero delta must change nothing"
+            got = []
+            for x in [frames[t:t + 1] for t in range(2, n)] + [frames[n - 1:n]] * len(cuts):
+                new = list(between)
+                for s, stage in enumerate(stages):
+                    y = stage(x if s == 0 else between[s - 1])
+                    if s < len(stages) - 1:
+                        new[s] = clone(y)
+                    else:
+                        got.append(clone(y))
+                between = new
+        for k in range(len(cuts)):                                   # the pipeline fills: the outputs of frame 1 stay
+            assert same(got[k], want[0]), name
+        for t in range(2, n):                                        # frame t leaves len(cuts) steps after it entered
+            assert same(got[t - 2 + len(cuts)], want[t - 1]), (name, t)
